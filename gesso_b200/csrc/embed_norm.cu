@@ -1,0 +1,121 @@
+// Embedding gather and the fused residual-add + RMSNorm.
+//
+// The residual stream `h` is float32 in both run types; the sum `h + delta (+ bias)` and the
+// norm statistics are computed in float32.  RMSNorm divides first and scales second,
+// y = (x / sqrt(mean(x^2) + eps)) * w, as the reference's row kernel does
+// (src/Operators/cpu.jl:293-311).  The reference fuses the residual add with the norm that
+// follows it on its decode path (src/Inference/Inference.jl:3239-3247); here that fusion is
+// the only form.
+#include "common.cuh"
+
+// ---- embedding ------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                    float* __restrict__ h, int H, int V, float scale) {
+    const int t = blockIdx.x;
+    int id = tokens[t];
+    if (id < 0 || id >= V) id = 0;   // ids are validated on the host; never read outside the table
+    const T* row = table + (size_t)id * H;
+    float* out = h + (size_t)t * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) out[c] = to_f32(row[c]) * scale;
+}
+
+GESSO_API int gesso_embed_gather(const int* tokens, const void* table, int table_dtype, float* h,
+                                 int n_tokens, int H, int V, float scale, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == GESSO_F32)
+        embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, h, H, V, scale);
+    else if (table_dtype == GESSO_BF16)
+        embed_gather_kernel<bf16><<<n_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, h, H, V, scale);
+    else
+        return GESSO_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+// ---- h += delta (+ bias); out = rmsnorm(h) * w ------------------------------------------------
+// One block per output row.  `rows` (optional) selects which rows of h are normed: then h is
+// not written back (the selected rows are the last use of the stream).  The row is staged in
+// dynamic shared memory (H floats) so it is read from global memory once.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                   const float* __restrict__ delta_bias, const float* __restrict__ w,
+                                   float eps, TO* __restrict__ out, const int* __restrict__ rows, int H) {
+    extern __shared__ float srow[];
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* hrow = h + (size_t)src * H;
+    const TD* drow = delta ? delta + (size_t)src * H : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float x = hrow[c];
+        if (drow) {
+            float d = to_f32(drow[c]);
+            if (delta_bias) d += delta_bias[c];
+            x += d;
+            if (!rows) hrow[c] = x;
+        }
+        srow[c] = x;
+        ss += x * x;
+    }
+    ss = block_sum(ss, red);
+    const float denom = sqrtf(ss / (float)H + eps);
+    TO* orow = out + (size_t)r * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) orow[c] = from_f32<TO>((srow[c] / denom) * w[c]);
+}
+
+GESSO_API int gesso_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* delta_bias,
+                                const float* w, float eps, void* out, int out_dtype, const int* rows,
+                                int n_rows, int H, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return GESSO_ERR_BAD_SIZE;
+    int threads = 128;
+    while (threads < 1024 && threads * 4 < H) threads <<= 1;
+    const size_t smem = (size_t)H * sizeof(float);
+#define LAUNCH(TD, TO)                                                                              \
+    do {                                                                                            \
+        if (smem > 48 * 1024)                                                                       \
+            cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)smem);                                                        \
+        add_rmsnorm_kernel<TD, TO><<<n_rows, threads, smem, stream>>>(                              \
+            h, (const TD*)delta, delta_bias, w, eps, (TO*)out, rows, H);                            \
+    } while (0)
+    if (delta_dtype == GESSO_F32 && out_dtype == GESSO_F32) LAUNCH(float, float);
+    else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_BF16) LAUNCH(bf16, bf16);
+    else if (delta_dtype == GESSO_F32 && out_dtype == GESSO_BF16) LAUNCH(float, bf16);
+    else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_F32) LAUNCH(bf16, float);
+    else return GESSO_ERR_BAD_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}
+
+// ---- plain RMSNorm over the last axis of a [rows, D] tensor (per-head norms, tests) ----------------
+template <typename T>
+__global__ void rmsnorm_rows_kernel(const T* __restrict__ x, const float* __restrict__ w, float eps,
+                                    T* __restrict__ out, int n_rows, int D) {
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * warps + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const T* xr = x + (size_t)r * D;
+    float ss = 0.f;
+    for (int c = lane; c < D; c += 32) { float v = to_f32(xr[c]); ss += v * v; }
+    ss = warp_sum(ss);
+    const float denom = sqrtf(ss / (float)D + eps);
+    T* o = out + (size_t)r * D;
+    for (int c = lane; c < D; c += 32) o[c] = from_f32<T>((to_f32(xr[c]) / denom) * w[c]);
+}
+
+GESSO_API int gesso_rmsnorm_rows(const void* x, const float* w, float eps, void* out, int dtype,
+                                 int n_rows, int D, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int warps = 4;
+    const int blocks = (n_rows + warps - 1) / warps;
+    if (dtype == GESSO_F32)
+        rmsnorm_rows_kernel<float><<<blocks, warps * 32, 0, stream>>>((const float*)x, w, eps, (float*)out, n_rows, D);
+    else if (dtype == GESSO_BF16)
+        rmsnorm_rows_kernel<bf16><<<blocks, warps * 32, 0, stream>>>((const bf16*)x, w, eps, (bf16*)out, n_rows, D);
+    else
+        return GESSO_ERR_BAD_DTYPE;
+    return launch_status();
+}

@@ -1,0 +1,169 @@
+// The double-gated short convolution between in_proj and out_proj, on the flat token axis.
+//
+// bcx holds B, C and X side by side ([N, 3H]: columns [0,H)=B, [H,2H)=C, [2H,3H)=X).  For token
+// t and channel c: bx = B*X;  y = sum_{p<L-1} hist[p]*w[c,p] + bx*w[c,L-1];  out = C*y; the
+// history then shifts by one and takes bx (src/Inference/lfm2.jl:253-271).  Taps run oldest to
+// newest, the newest multiplies the current token (:256).  A FIR has no recurrence, so all
+// tokens of a portion run in parallel: the L-1 earlier values of a token come from earlier
+// tokens of the same portion (recomputed from bcx) or, before the portion's start, from the
+// request's state slot, which holds the last L-1 values of bx in float32.
+//
+// Two launches keep the slot free of read/write races: `mix` only reads the slot, `state_update`
+// (one thread per (portion, channel), which owns that slot column) rewrites it afterwards.
+// When every portion is short (decoding), `mix_update_small` does both in one launch with the
+// same ownership.
+#include "common.cuh"
+
+template <typename T>
+__device__ __forceinline__ float bx_at(const T* __restrict__ bcx, const float* __restrict__ in_bias,
+                                       int tok, int c, int H) {
+    const T* row = bcx + (size_t)tok * 3 * H;
+    float b = to_f32(row[c]), x = to_f32(row[2 * H + c]);
+    if (in_bias) { b += in_bias[c]; x += in_bias[2 * H + c]; }
+    return b * x;
+}
+
+// state layout for one layer: state[slot * slot_stride + q * H + c], q = 0 (oldest) .. L-2 (newest)
+template <typename T>
+__global__ void conv_mix_kernel(const T* __restrict__ bcx, const float* __restrict__ in_bias,
+                                const float* __restrict__ taps, const float* __restrict__ conv_bias,
+                                const float* __restrict__ state, long long slot_stride,
+                                const int* __restrict__ seg_of_token, const int* __restrict__ seg_start,
+                                const int* __restrict__ seg_pos0, const int* __restrict__ slots,
+                                T* __restrict__ out, int n_tokens, int H, int L) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x;
+    if (c >= H || t >= n_tokens) return;
+    const int s = seg_of_token[t];
+    const int off = t - seg_start[s];          // index of this token inside its portion
+    const int pos = seg_pos0[s] + off;         // absolute position
+    const float* st = state + (size_t)slots[s] * slot_stride;
+    const float* w = taps + (size_t)c * L;
+    float y = 0.f;
+    for (int p = 0; p < L - 1; ++p) {
+        const int back = (L - 1) - p;          // how many tokens before t
+        float v;
+        if (back > pos) v = 0.f;               // before the start of the sequence
+        else if (back <= off) v = bx_at(bcx, in_bias, t - back, c, H);
+        else v = st[(size_t)((L - 1) - (back - off)) * H + c];
+        y += v * w[p];
+    }
+    y += bx_at(bcx, in_bias, t, c, H) * w[L - 1];
+    if (conv_bias) y += conv_bias[c];
+    const T* row = bcx + (size_t)t * 3 * H;
+    float cg = to_f32(row[H + c]);
+    if (in_bias) cg += in_bias[H + c];
+    out[(size_t)t * H + c] = from_f32<T>(cg * y);
+}
+
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ bcx, const float* __restrict__ in_bias,
+                                         float* __restrict__ state, long long slot_stride,
+                                         const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
+                                         const int* __restrict__ slots, int n_segs, int H, int L) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int s = blockIdx.x;
+    if (c >= H || s >= n_segs) return;
+    const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
+    const int pos_end = seg_pos0[s] + n;       // sequence length after this step
+    float* st = state + (size_t)slots[s] * slot_stride;
+    // new entry q holds bx of the token (L-1-q) places before the end; ascending q never
+    // overwrites an old entry that is still to be read (it reads index q+n > q).
+    for (int q = 0; q < L - 1; ++q) {
+        const int back = (L - 1) - q;          // 1 = last token of the portion
+        float v;
+        if (back > pos_end) v = 0.f;
+        else if (back <= n) v = bx_at(bcx, in_bias, t0 + n - back, c, H);
+        else v = st[(size_t)(q + n) * H + c];
+        st[(size_t)q * H + c] = v;
+    }
+}
+
+// Both steps for short portions (n <= 8): one thread per (portion, channel) walks its tokens in
+// order with the history in registers, as the reference's per-channel loop does.
+template <typename T, int LMAX>
+__global__ void conv_mix_update_small_kernel(const T* __restrict__ bcx, const float* __restrict__ in_bias,
+                                             const float* __restrict__ taps, const float* __restrict__ conv_bias,
+                                             float* __restrict__ state, long long slot_stride,
+                                             const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
+                                             const int* __restrict__ slots, T* __restrict__ out, int n_segs,
+                                             int H, int L) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int s = blockIdx.x;
+    if (c >= H || s >= n_segs) return;
+    const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
+    float* st = state + (size_t)slots[s] * slot_stride;
+    float hist[LMAX], w[LMAX];
+    const bool fresh = seg_pos0[s] == 0;
+#pragma unroll
+    for (int q = 0; q < LMAX; ++q) {
+        hist[q] = (q < L - 1 && !fresh) ? st[(size_t)q * H + c] : 0.f;
+        w[q] = q < L ? taps[(size_t)c * L + q] : 0.f;
+    }
+    for (int i = 0; i < n; ++i) {
+        const int t = t0 + i;
+        const float bx = bx_at(bcx, in_bias, t, c, H);
+        float y = 0.f;
+#pragma unroll
+        for (int p = 0; p < LMAX; ++p)
+            if (p < L - 1) y += hist[p] * w[p];
+        float wl = 0.f;
+#pragma unroll
+        for (int p = 0; p < LMAX; ++p)
+            if (p == L - 1) wl = w[p];
+        y += bx * wl;
+        if (conv_bias) y += conv_bias[c];
+        const T* row = bcx + (size_t)t * 3 * H;
+        float cg = to_f32(row[H + c]);
+        if (in_bias) cg += in_bias[H + c];
+        out[(size_t)t * H + c] = from_f32<T>(cg * y);
+#pragma unroll
+        for (int p = 0; p < LMAX - 1; ++p)
+            if (p < L - 2) hist[p] = hist[p + 1];
+#pragma unroll
+        for (int p = 0; p < LMAX; ++p)
+            if (p == L - 2) hist[p] = bx;
+    }
+#pragma unroll
+    for (int q = 0; q < LMAX; ++q)
+        if (q < L - 1) st[(size_t)q * H + c] = hist[q];
+}
+
+GESSO_API int gesso_short_conv(const void* bcx, int dtype, const float* in_bias, const float* taps,
+                               const float* conv_bias, float* state, long long slot_stride,
+                               const int* seg_of_token, const int* seg_start, const int* seg_pos0,
+                               const int* slots, void* out, int n_tokens, int n_segs, int max_seg_len,
+                               int H, int L, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_segs <= 0) return 0;
+    if (L < 2 || H <= 0) return GESSO_ERR_BAD_SIZE;
+    if (dtype != GESSO_F32 && dtype != GESSO_BF16) return GESSO_ERR_BAD_DTYPE;
+    const int threads = 128;
+    const int cblocks = (H + threads - 1) / threads;
+    if (max_seg_len <= 8 && L <= 8) {
+        dim3 grid(n_segs, cblocks);
+        if (dtype == GESSO_F32)
+            conv_mix_update_small_kernel<float, 8><<<grid, threads, 0, stream>>>(
+                (const float*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_start, seg_pos0, slots,
+                (float*)out, n_segs, H, L);
+        else
+            conv_mix_update_small_kernel<bf16, 8><<<grid, threads, 0, stream>>>(
+                (const bf16*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_start, seg_pos0, slots,
+                (bf16*)out, n_segs, H, L);
+        return launch_status();
+    }
+    dim3 grid(n_tokens, cblocks), sgrid(n_segs, cblocks);
+    if (dtype == GESSO_F32) {
+        conv_mix_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, in_bias, taps, conv_bias, state,
+                                                             slot_stride, seg_of_token, seg_start, seg_pos0, slots,
+                                                             (float*)out, n_tokens, H, L);
+        conv_state_update_kernel<float><<<sgrid, threads, 0, stream>>>((const float*)bcx, in_bias, state, slot_stride,
+                                                                       seg_start, seg_pos0, slots, n_segs, H, L);
+    } else {
+        conv_mix_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, in_bias, taps, conv_bias, state,
+                                                            slot_stride, seg_of_token, seg_start, seg_pos0, slots,
+                                                            (bf16*)out, n_tokens, H, L);
+        conv_state_update_kernel<bf16><<<sgrid, threads, 0, stream>>>((const bf16*)bcx, in_bias, state, slot_stride,
+                                                                      seg_start, seg_pos0, slots, n_segs, H, L);
+    }
+    return launch_status();
+}

@@ -1,0 +1,197 @@
+"""The step function and the device side of the cache.
+
+:class:`Engine` ties a bound :class:`~gesso_b200.engine.model.Model` to a
+:class:`~gesso_b200.cache.manager.CacheManager` and the device memory the manager's indices
+point into.  Its one operation is :meth:`Engine.step`: a batch of (request, next tokens,
+wanted places) runs as one flat batch from the cache that earlier steps left, and the logits
+at the wanted places come back as float32 ``[wanted, vocab]``.  Admission, portioning and
+sampling live above it (scheduler); nothing below it knows about requests.
+
+Reference counterparts: the per-sequence prefill pass and decode step
+(src/Inference/Inference.jl:2272-2530, 3270-3383) and the Session's page manager
+(src/Inference/session.jl:687-828); the reference never batches sequences
+(src/Inference/session.jl:18), so the mixed batch is this engine's own.
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..errors import ErrorCode, GessoError, invalid, resource
+from .batch import StepContext, StepEntry, StepLayout, pack_step
+from .model import Model, PagedView, StateView
+
+
+class DeviceCache:
+    """Device memory for the manager's pages and slots."""
+
+    def __init__(self, model: Model, page_size: int, num_pages: Sequence[int], num_slots: int):
+        plan = model.cache_plan
+        dev, dt = model.rt.device, model.dtype
+        self.kv: List[torch.Tensor] = []
+        for (need, owners), pages in zip(plan.paged_groups, num_pages):
+            # zero-filled: a masked key multiplies its value row by an exact zero, which must
+            # not meet a NaN left in fresh memory
+            self.kv.append(torch.zeros((len(owners), 2, max(pages, 1), need.n_kv_heads, page_size,
+                                        need.head_dim), dtype=dt, device=dev))
+        self.state: List[torch.Tensor] = [
+            torch.zeros((max(num_slots, 1),) + tuple(need.shape), dtype=torch.float32, device=dev)
+            for need, _ in plan.state_entries]
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.kv + self.state)
+
+    def zero_slot(self, slot: int) -> None:
+        for s in self.state:
+            s[slot].zero_()
+
+
+class Engine:
+    def __init__(self, model: Model, *, max_positions: Optional[int] = None, page_size: int = 16,
+                 num_pages: Optional[int] = None, max_requests: int = 8):
+        self.model = model
+        self.max_positions = int(max_positions or model.rt.max_positions)
+        if self.max_positions > model.rt.max_positions:
+            raise invalid(f"context {self.max_positions} exceeds the model's position limit "
+                          f"{model.rt.max_positions}")
+        self.page_size = int(page_size)
+        plan = model.cache_plan
+        per_req = (self.max_positions + self.page_size - 1) // self.page_size
+        if num_pages is None:
+            num_pages = per_req * max_requests
+        self.num_pages = int(num_pages)
+        groups = plan.group_specs()
+        self.cache = CacheManager(groups, self.page_size, [self.num_pages] * len(groups),
+                                  max_requests, self.max_positions)
+        self.device_cache = DeviceCache(model, self.page_size, [self.num_pages] * len(groups), max_requests)
+        self.status = torch.zeros((1,), dtype=torch.int32, device=model.rt.device)
+        self.steps_run = 0
+        self.tokens_run = 0
+        # ring of pinned staging buffers; an event per buffer says when its copy has left it
+        self._pinned: List[Optional[torch.Tensor]] = [None] * 4
+        self._pinned_events: List[Optional[torch.cuda.Event]] = [None] * 4
+        self._pinned_next = 0
+
+    # ---- requests --------------------------------------------------------------------------
+    def admit(self, req_id: Hashable) -> None:
+        self.cache.admit(req_id)
+
+    def release(self, req_id: Hashable) -> None:
+        self.cache.release(req_id)
+
+    def is_live(self, req_id: Hashable) -> bool:
+        return self.cache.is_live(req_id)
+
+    def length(self, req_id: Hashable) -> int:
+        return self.cache.length(req_id)
+
+    # ---- the step ----------------------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise invalid("step: no entries")
+        seen = set()
+        V = self.model.vocab_size
+        for e in entries:
+            if e.req_id in seen:
+                raise invalid(f"step: request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if not self.cache.is_live(e.req_id):
+                raise invalid(f"step: request {e.req_id!r} is not live (admit it first)")
+            n = len(e.tokens)
+            if n < 1:
+                raise invalid(f"step: request {e.req_id!r} brings no tokens")
+            for t in e.tokens:
+                if not (0 <= int(t) < V):
+                    raise invalid(f"step: token id {t} of request {e.req_id!r} is outside the vocabulary (0..{V - 1})")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise invalid(f"step: wanted place {w} of request {e.req_id!r} is outside its {n} tokens")
+
+    def _pinned_buffer(self, n: int):
+        i = self._pinned_next
+        self._pinned_next = (i + 1) % len(self._pinned)
+        if self._pinned_events[i] is not None:
+            self._pinned_events[i].synchronize()
+        if self._pinned[i] is None or self._pinned[i].numel() < n:
+            self._pinned[i] = torch.empty((max(n, 4096),), dtype=torch.int32, pin_memory=True)
+        return i, self._pinned[i]
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Reserve pages, zero fresh slots and upload the step's metadata."""
+        self._validate(entries)
+        for e in entries:
+            n = len(e.tokens)
+            if self.cache.length(e.req_id) + n > self.max_positions:
+                raise resource(f"request {e.req_id!r}: {self.cache.length(e.req_id)}+{n} positions exceed "
+                               f"the context length {self.max_positions}")
+        # all-or-nothing across the batch: check the total need before handing out any page
+        need = [0] * len(self.cache.groups)
+        for e in entries:
+            for g, k in enumerate(self.cache.pages_needed(e.req_id, len(e.tokens))):
+                need[g] += k
+        for g, (k, free) in enumerate(zip(need, self.cache.free_pages())):
+            if k > free:
+                raise resource(f"step needs {k} pages of group {self.cache.groups[g].name}, {free} free")
+        starts, slots = [], []
+        for e in entries:
+            self.cache.reserve(e.req_id, len(e.tokens))
+            starts.append(self.cache.length(e.req_id))
+            slots.append(self.cache.slot(e.req_id))
+            if self.cache.take_fresh(e.req_id):
+                self.device_cache.zero_slot(slots[-1])
+        n_groups = len(self.cache.groups)
+        tables = [[self.cache.block_table(e.req_id, g) for e in entries] for g in range(n_groups)]
+        layout = StepLayout(n_tokens=sum(len(e.tokens) for e in entries), n_segs=len(entries),
+                            n_rows=sum(len(e.want) for e in entries), n_groups=n_groups,
+                            max_pages=self.cache.max_pages_per_request)
+        size = layout.offsets()["_end"]
+        slot_i, host = self._pinned_buffer(size)
+        pack_step(list(entries), starts, slots, tables, layout, host.numpy()[:size])
+        buf = torch.empty((size,), dtype=torch.int32, device=self.model.rt.device)
+        buf.copy_(host[:size], non_blocking=True)
+        if self._pinned_events[slot_i] is None:
+            self._pinned_events[slot_i] = torch.cuda.Event()
+        self._pinned_events[slot_i].record()
+        max_seg = max(len(e.tokens) for e in entries)
+        max_kv = max(s + len(e.tokens) for s, e in zip(starts, entries))
+        return StepContext(layout, buf, self.status, max_seg, max_kv)
+
+    def views(self, ctx: StepContext):
+        plan, dc = self.model.cache_plan, self.device_cache
+        out = []
+        for e, p in enumerate(plan.entries):
+            if p.kind == "paged":
+                kv = dc.kv[p.group][p.index]
+                out.append(PagedView(kv[0], kv[1], ctx.block_tables[p.group], writes=(p.owner == e)))
+            elif p.kind == "state":
+                out.append(StateView(dc.state[p.index], ctx.slots, writes=(p.owner == e)))
+            else:
+                out.append(None)
+        return out
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch; returns float32 logits ``[wanted, vocab]`` (``None`` if nothing is wanted)."""
+        ctx = self.build_context(entries)
+        logits = self.model.forward(ctx, self.views(ctx))
+        for e in entries:
+            self.cache.commit(e.req_id, len(e.tokens))
+        self.steps_run += 1
+        self.tokens_run += ctx.n_tokens
+        return logits
+
+    def check_status(self) -> None:
+        """Raise if a kernel recorded a position without a page (synchronises)."""
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            raise GessoError(ErrorCode.INTERNAL, "a kernel met a position without a cache page")
+
+    def stats(self) -> Dict[str, object]:
+        return {
+            "steps": self.steps_run, "tokens": self.tokens_run,
+            "pages_in_use": self.cache.pages_in_use(), "pages_free": self.cache.free_pages(),
+            "slots_in_use": self.cache.slots_in_use(), "cache_bytes": self.device_cache.bytes(),
+            "live_requests": len(self.cache.live_requests()),
+        }

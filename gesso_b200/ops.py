@@ -1,0 +1,235 @@
+"""Tensor-level wrappers of the kernel library.
+
+Each function checks device, dtype, layout and sizes of its ``torch`` tensors,
+launches one kernel (or a short fixed sequence) on the current CUDA stream and
+returns the output tensor.  Nothing here computes on the CPU and nothing falls
+back to a library implementation of the same operation; the only library call
+is the dense bfloat16 matrix product (cuBLAS through ``torch.mm``), where the
+reference also calls a BLAS (src/Operators/cpu.jl:629-630).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import lib as _lib
+from .errors import ErrorCode, GessoError
+
+F32, BF16 = 0, 1
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise GessoError(ErrorCode.LAUNCH, f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise GessoError(ErrorCode.LAUNCH, msg)
+
+
+def _cuda_contig(t: torch.Tensor, name: str, dtype=None) -> None:
+    _need(t.is_cuda, f"{name} must be a CUDA tensor")
+    _need(t.is_contiguous(), f"{name} must be contiguous")
+    if dtype is not None:
+        _need(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
+
+
+# ---- embedding / norms ---------------------------------------------------------------------
+def embed_gather(tokens: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    _cuda_contig(tokens, "tokens", torch.int32)
+    _cuda_contig(table, "table")
+    n, (V, H) = tokens.numel(), table.shape
+    h = torch.empty((n, H), dtype=torch.float32, device=table.device)
+    _lib.check(_lib.library().gesso_embed_gather(_p(tokens), _p(table), _dt(table), _p(h), n, H, V,
+                                                 float(scale), _stream()), "embed_gather")
+    return h
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor],
+                weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``h += delta (+ bias)`` in place (float32), returns ``rmsnorm(h) * weight`` in ``out_dtype``.
+
+    With ``rows`` only those rows are summed and normed, and ``h`` is left as it was.
+    """
+    _cuda_contig(h, "h", torch.float32)
+    _cuda_contig(weight, "weight", torch.float32)
+    N, H = h.shape
+    _need(weight.numel() == H, "norm weight size differs from the row width")
+    if delta is not None:
+        _cuda_contig(delta, "delta")
+        _need(tuple(delta.shape) == (N, H), "delta shape differs from h")
+    if delta_bias is not None:
+        _cuda_contig(delta_bias, "delta_bias", torch.float32)
+        _need(delta is not None and delta_bias.numel() == H, "delta_bias needs a delta of the same width")
+    if rows is not None:
+        _cuda_contig(rows, "rows", torch.int32)
+    n_out = N if rows is None else rows.numel()
+    out = torch.empty((n_out, H), dtype=out_dtype, device=h.device)
+    _lib.check(_lib.library().gesso_add_rmsnorm(
+        _p(h), _p(delta), _dt(delta) if delta is not None else F32, _p(delta_bias), _p(weight),
+        float(eps), _p(out), _dt(out), _p(rows), n_out, H, _stream()), "add_rmsnorm")
+    return out
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    _cuda_contig(x, "x")
+    _cuda_contig(weight, "weight", torch.float32)
+    D = x.shape[-1]
+    _need(weight.numel() == D, "norm weight size differs from the last axis")
+    out = torch.empty_like(x)
+    _lib.check(_lib.library().gesso_rmsnorm_rows(_p(x), _p(weight), float(eps), _p(out), _dt(x),
+                                                 x.numel() // D, D, _stream()), "rmsnorm_rows")
+    return out
+
+
+# ---- short convolution -----------------------------------------------------------------------
+def short_conv(bcx: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Tensor,
+               conv_bias: Optional[torch.Tensor], state: torch.Tensor, seg_of_token: torch.Tensor,
+               seg_start: torch.Tensor, seg_pos0: torch.Tensor, slots: torch.Tensor,
+               n_segs: int, max_seg_len: int) -> torch.Tensor:
+    """Gated FIR over ``bcx`` [N, 3H]; ``state`` is this layer's view [slots, L-1, H] (float32)."""
+    _cuda_contig(bcx, "bcx")
+    _cuda_contig(taps, "taps", torch.float32)
+    N, H3 = bcx.shape
+    H, L = taps.shape
+    _need(H3 == 3 * H, "bcx width must be three times the tap count")
+    _need(state.dtype == torch.float32 and state.is_cuda, "conv state must be float32 on the device")
+    _need(state.dim() == 3 and state.shape[1] == L - 1 and state.shape[2] == H
+          and state.stride(2) == 1 and state.stride(1) == H, "conv state must be [slots, L-1, H] with dense rows")
+    for name, t in (("seg_of_token", seg_of_token), ("seg_start", seg_start), ("seg_pos0", seg_pos0),
+                    ("slots", slots)):
+        _cuda_contig(t, name, torch.int32)
+    out = torch.empty((N, H), dtype=bcx.dtype, device=bcx.device)
+    _lib.check(_lib.library().gesso_short_conv(
+        _p(bcx), _dt(bcx), _p(in_bias), _p(taps), _p(conv_bias), _p(state), state.stride(0),
+        _p(seg_of_token), _p(seg_start), _p(seg_pos0), _p(slots), _p(out), N, n_segs, max_seg_len,
+        H, L, _stream()), "short_conv")
+    return out
+
+
+# ---- attention ---------------------------------------------------------------------------------
+def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                       eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                       positions: torch.Tensor, seg_of_token: torch.Tensor, block_table: torch.Tensor,
+                       k_pages: torch.Tensor, v_pages: torch.Tensor, nh: int, nkv: int, hd: int,
+                       write_kv: bool, status: torch.Tensor) -> torch.Tensor:
+    """Norm + rotate q and k, write k and v into their pages; returns q as [N, nh, hd]."""
+    _cuda_contig(qkv, "qkv")
+    N = qkv.shape[0]
+    heads = nh + 2 * nkv if write_kv else nh
+    _need(qkv.shape[1] == heads * hd, "fused projection width differs from the head layout")
+    _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype, "cache pages must have the run dtype")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous(), "cache pages must be contiguous")
+    _need(k_pages.dim() == 4 and k_pages.shape[1] == nkv and k_pages.shape[3] == hd,
+          "cache pages must be [pages, kv heads, page size, head size]")
+    page_size = k_pages.shape[2]
+    _cuda_contig(block_table, "block_table", torch.int32)
+    _cuda_contig(positions, "positions", torch.int32)
+    if cos is not None:
+        _cuda_contig(cos, "cos", torch.float32)
+        _cuda_contig(sin, "sin", torch.float32)
+        _need(cos.shape[1] == hd // 2, "rotary table width must be half the head size")
+    q_out = torch.empty((N, nh, hd), dtype=qkv.dtype, device=qkv.device)
+    _lib.check(_lib.library().gesso_qk_norm_rope_store(
+        _p(qkv), _dt(qkv), _p(q_w), _p(k_w), float(eps), _p(cos), _p(sin), _p(positions),
+        _p(seg_of_token), _p(block_table), block_table.shape[1], page_size, _p(q_out), _p(k_pages),
+        _p(v_pages), N, nh, nkv, hd, 1 if write_kv else 0, _p(status), _stream()), "qk_norm_rope_store")
+    return q_out
+
+
+def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                            block_table: torch.Tensor, positions: torch.Tensor,
+                            seg_of_token: torch.Tensor, window: Optional[int], scale: float) -> torch.Tensor:
+    _cuda_contig(q, "q")
+    N, nh, hd = q.shape
+    nkv, page_size = k_pages.shape[1], k_pages.shape[2]
+    _need(k_pages.dtype == q.dtype, "cache pages must have the dtype of q")
+    out = torch.empty((N, nh * hd), dtype=q.dtype, device=q.device)
+    _lib.check(_lib.library().gesso_paged_attention_generic(
+        _p(q), _p(k_pages), _p(v_pages), _dt(q), _p(block_table), block_table.shape[1], page_size,
+        _p(positions), _p(seg_of_token), _p(out), N, nh, nkv, hd, int(window or 0), float(scale),
+        _stream()), "paged_attention_generic")
+    return out
+
+
+# ---- feed-forward ------------------------------------------------------------------------------
+def swiglu(gu: torch.Tensor) -> torch.Tensor:
+    _cuda_contig(gu, "gate_up")
+    N, F2 = gu.shape
+    _need(F2 % 2 == 0, "fused gate/up width must be even")
+    out = torch.empty((N, F2 // 2), dtype=gu.dtype, device=gu.device)
+    _lib.check(_lib.library().gesso_swiglu(_p(gu), _p(out), _dt(gu), N, F2 // 2, _stream()), "swiglu")
+    return out
+
+
+# ---- matrix products ---------------------------------------------------------------------------
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a [M,K] @ w[N,K]^T`` with FP32 FMAs; returns float32."""
+    _cuda_contig(a, "a")
+    _cuda_contig(w, "w")
+    M, K = a.shape
+    N, K2 = w.shape
+    _need(K == K2, f"inner sizes differ: {K} vs {K2}")
+    if bias is not None:
+        _cuda_contig(bias, "bias", torch.float32)
+    c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    _lib.check(_lib.library().gesso_gemm_f32(_p(a), _dt(a), _p(w), _dt(w), _p(bias), _p(c), M, N, K,
+                                             _stream()), "gemm_f32")
+    return c
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x @ w^T`` for a weight stored (out, in).
+
+    bfloat16 activations with a bfloat16 weight use the tensor cores with float32
+    accumulation; any float32 operand (the 32-bit path, or a matrix that was stored
+    in 32 bit) uses the FP32 FMA kernel, so no reduced-precision mode is ever
+    applied to 32-bit data.
+    """
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        _cuda_contig(x, "x")
+        if out_dtype == torch.bfloat16:
+            return torch.mm(x, w.t())
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+    c = gemm_f32(x, w)
+    return c if out_dtype == torch.float32 else c.to(out_dtype)
+
+
+# ---- sampling ----------------------------------------------------------------------------------
+def argmax_rows(logits: torch.Tensor):
+    _cuda_contig(logits, "logits", torch.float32)
+    R, V = logits.shape
+    ids = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    bad = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.library().gesso_argmax_rows(_p(logits), R, V, _p(ids), _p(bad), _stream()), "argmax_rows")
+    return ids, bad
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, u: torch.Tensor):
+    _cuda_contig(logits, "logits", torch.float32)
+    _cuda_contig(temperature, "temperature", torch.float64)
+    _cuda_contig(top_p, "top_p", torch.float64)
+    _cuda_contig(u, "u", torch.float64)
+    R, V = logits.shape
+    _need(temperature.numel() == R and top_p.numel() == R and u.numel() == R, "one parameter per row")
+    ids = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    bad = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.library().gesso_sample_rows(_p(logits), R, V, _p(temperature), _p(top_p), _p(u),
+                                                _p(ids), _p(bad), _stream()), "sample_rows")
+    return ids, bad

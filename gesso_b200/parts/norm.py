@@ -1,0 +1,35 @@
+"""RMSNorm with the residual add folded in.
+
+``y = (x / sqrt(mean(x^2) + eps)) * w`` over the last axis, divide first, scale
+second (src/Operators/cpu.jl:293-311).  The residual stream is float32; the sum
+and the statistics are float32, the output is rounded to the run dtype.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+from .. import ops
+from .base import Norm, ParamDecl
+from .registry import register_norm
+
+
+class RMSNorm(Norm):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.weight = None
+        self.out_dtype = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {"weight": ParamDecl((self.size,), role="vector", init="ones")}
+
+    def bind(self, tensors, rt) -> None:
+        self.weight = tensors["weight"]
+        self.out_dtype = rt.dtype
+
+    def add_norm(self, h, delta, delta_bias, rows=None):
+        return ops.add_rmsnorm(h, delta, delta_bias, self.weight, self.eps, self.out_dtype, rows)
+
+
+register_norm("rmsnorm", RMSNorm, replace=True)
