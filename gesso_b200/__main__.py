@@ -1,0 +1,104 @@
+"""Command line: ``python -m gesso_b200 <command> ...``.
+
+The reference's launcher takes ``--gguf PATH --n-ctx N --check`` and refuses unknown flags
+(scripts/gesso-serve.jl:61-84); its request fields are ``temperature``, ``top_p``, ``seed``,
+``max_tokens``, ``stop`` (docs/serving.md:95-106).  The same names are used here where this engine
+has the same thing; the model comes from a folder (``--model``) instead of a GGUF file.
+
+    generate     --model DIR --prompt-ids 1,2,3 [--max-new-tokens N] [--temperature T] [--top-p P]
+                 [--seed S] [--stop-ids ..] [--eos-ids ..] [--dtype bfloat16|float32] [--n-ctx N]
+                 [--page-size 16] [--num-pages N] [--max-batch B] [--prefill-chunk C]
+    init-random  --config FILE --seed S --out DIR      write a model folder with random weights
+    describe     --model DIR                           print the typed configuration and the layers
+    check                                              build the kernels and run a tiny generation
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+
+def _ids(text: str):
+    return [int(x) for x in text.replace(",", " ").split()]
+
+
+def _parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="gesso_b200", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="command", required=True)
+    g = sub.add_parser("generate", help="generate tokens for one or more prompts")
+    g.add_argument("--model", required=True)
+    g.add_argument("--prompt-ids", action="append", default=[], help="token ids, comma or space separated; repeatable")
+    g.add_argument("--prompt-file", help="one prompt of token ids per line")
+    g.add_argument("--max-new-tokens", type=int, default=8)
+    g.add_argument("--temperature", type=float, default=0.0)
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--seed", type=int, default=0)
+    g.add_argument("--stop-ids", default="")
+    g.add_argument("--eos-ids", default=None)
+    g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    g.add_argument("--n-ctx", type=int, default=4096)
+    g.add_argument("--page-size", type=int, default=16)
+    g.add_argument("--num-pages", type=int, default=None)
+    g.add_argument("--max-batch", type=int, default=8)
+    g.add_argument("--prefill-chunk", type=int, default=512)
+    r = sub.add_parser("init-random", help="write a model folder with random weights")
+    r.add_argument("--config", required=True)
+    r.add_argument("--seed", type=int, required=True)
+    r.add_argument("--out", required=True)
+    r.add_argument("--weights-dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.add_argument("--std", type=float, default=0.02)
+    d = sub.add_parser("describe", help="print the typed configuration")
+    d.add_argument("--model", required=True)
+    sub.add_parser("check", help="build the kernels and run a tiny generation on cuda:0")
+    return ap
+
+
+def main(argv=None) -> int:
+    args = _parser().parse_args(argv)      # an unknown flag prints the usage and exits with 2
+    if args.command == "init-random":
+        from .config.registry import parse_strict_json
+        from .weights.random_init import write_random_model
+        with open(args.config) as f:
+            cfg = parse_strict_json(f.read(), args.config)
+        write_random_model(args.out, cfg, args.seed, dtype=args.weights_dtype, std=args.std)
+        print(args.out)
+        return 0
+    if args.command == "describe":
+        from .config.registry import spec_from_dir
+        spec = spec_from_dir(args.model)
+        print(json.dumps({"architecture": spec.architecture, "config": getattr(spec.source, "__dict__", None),
+                          "layers": [b.mixer.kind for b in spec.blocks]}, indent=1, default=str))
+        return 0
+    if args.command == "check":
+        import os
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        import __graft_entry__ as entry
+        entry.build()
+        entry.smoke()
+        print("ok")
+        return 0
+    # generate
+    import gesso_b200
+    from .engine.session import BatchRequest, Session
+    prompts = [_ids(p) for p in args.prompt_ids]
+    if args.prompt_file:
+        with open(args.prompt_file) as f:
+            prompts += [_ids(line) for line in f if line.strip()]
+    if not prompts:
+        print("generate: no prompt given (--prompt-ids or --prompt-file)", file=sys.stderr)
+        return 2
+    model = gesso_b200.load(args.model, dtype=args.dtype, max_positions=args.n_ctx)
+    s = Session(model, context_length=args.n_ctx, page_size=args.page_size, num_pages=args.num_pages,
+                max_batch=args.max_batch, prefill_chunk=args.prefill_chunk)
+    eos = None if args.eos_ids is None else _ids(args.eos_ids)
+    res = s.run_batch([BatchRequest(p, args.max_new_tokens, args.temperature, args.top_p, args.seed + i,
+                                    _ids(args.stop_ids), eos) for i, p in enumerate(prompts)])
+    for r in res:
+        print(json.dumps({"ids": r.ids, "status": r.status, "error": None if r.error is None else str(r.error)}))
+    return 0 if all(r.status != "failed" for r in res) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,313 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees.
+
+The reference runs one sequence at a time: fixed-size prefill passes
+(src/Inference/Inference.jl:1765-1773) and a round-robin over independent sessions, one token per
+active request per round (src/Runtime/Runtime.jl:130-182), with a typed error as its only answer
+to an exhausted cache (src/Inference/kv_manager.jl:246-257).  This scheduler batches, so those
+decisions are its own:
+
+* **Admission**: first come, first served, while fewer than ``max_batch`` requests are live, a
+  state slot is free and the pages of the request's first portion are free.
+* **Budget**: every step first gives each decoding request its one token, then fills what is left
+  of ``max_tokens_per_step`` with prompt portions of at most ``prefill_chunk`` tokens, oldest
+  request first.  A portion may be cut anywhere.
+* **Decoding**: the token sampled from a request's last logits is emitted; if it stops the request
+  (``max_new_tokens`` reached, an eos/stop id, the callback returned ``False``) it is NOT run
+  through the model (src/Inference/Inference.jl:2585-2592, 2046-2048), else it is the request's
+  one token of the next step.
+* **Pages run out**: new admissions stop first; then prompt portions are shrunk or dropped, newest
+  request first; if the decoding requests alone do not fit, the most recently admitted running
+  request is *preempted*: its pages and slot are freed and it goes back to the head of the queue
+  with everything it has produced so far kept, to be re-prefilled later (recompute; the conv state
+  is rebuilt by the re-prefill; its sampler stream is untouched, so its tokens do not change).
+  The oldest request is never preempted, and a request that could not fit an empty pool is refused
+  when it is added, so the queue always makes progress.
+* **Finish**: pages and slot go back to the pools in the same step.
+
+The scheduler needs of its engine only ``cache`` (a CacheManager), ``admit``, ``release``,
+``step(entries) -> logits`` and a ``select(logits, requests) -> tokens`` function, so its decisions
+are tested on the CPU with a stand-in engine.
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+from ..errors import ErrorCode, GessoError, invalid, resource
+from ..sampling.sampler import SamplingParams, SplitMix64
+from .batch import StepEntry
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+# finish statuses (the reference's BatchResult statuses, src/Runtime/Runtime.jl:46-51, plus "stop")
+COMPLETE, EOS, STOP, CANCELLED, FAILED = "complete", "eos", "stop", "cancelled", "failed"
+
+
+@dataclass
+class Request:
+    prompt: List[int]
+    max_new_tokens: int = 8
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    eos_ids: Tuple[int, ...] = ()
+    stop_ids: Tuple[int, ...] = ()
+    on_token: Optional[Callable[[int], Optional[bool]]] = None
+    req_id: Optional[object] = None
+    # ---- scheduler state ----
+    state: str = WAITING
+    status: Optional[str] = None
+    error: Optional[Exception] = None
+    generated: List[int] = field(default_factory=list)
+    fed: int = 0                      # tokens of prompt+generated that are in the cache
+    preemptions: int = 0
+    cancelled: bool = False
+    rng: Optional[SplitMix64] = None
+    admitted_at: int = -1
+
+    def __post_init__(self):
+        self.prompt = [int(t) for t in self.prompt]
+        if self.max_new_tokens < 0:
+            raise invalid("request: max_new_tokens must be >= 0")
+        self.rng = SplitMix64(self.sampling.seed)
+
+    @property
+    def sequence(self) -> List[int]:
+        return self.prompt + self.generated
+
+    @property
+    def ids(self) -> List[int]:
+        """Prompt plus new ids, the stopping id included (src/Inference/session.jl:1025-1034)."""
+        return self.prompt + self.generated
+
+    def cancel(self) -> None:
+        self.cancelled = True
+
+
+@dataclass
+class StepPlan:
+    entries: List[Tuple[Request, int, int]]      # (request, first index into its sequence, n tokens)
+    preempted: List[Request] = field(default_factory=list)
+    admitted: List[Request] = field(default_factory=list)
+
+    @property
+    def n_tokens(self) -> int:
+        return sum(n for _, _, n in self.entries)
+
+
+class Scheduler:
+    def __init__(self, engine, select: Callable, *, max_batch: int = 8, max_tokens_per_step: int = 2048,
+                 prefill_chunk: int = 512, vocab_size: Optional[int] = None):
+        if max_batch < 1 or max_tokens_per_step < 1 or prefill_chunk < 1:
+            raise invalid("scheduler: max_batch, max_tokens_per_step and prefill_chunk must be >= 1")
+        self.engine = engine
+        self.cache = engine.cache
+        self.select = select
+        self.max_batch = max_batch
+        self.max_tokens_per_step = max_tokens_per_step
+        self.prefill_chunk = prefill_chunk
+        self.vocab_size = vocab_size
+        self.waiting: List[Request] = []
+        self.running: List[Request] = []          # in admission order
+        self._ids = itertools.count()
+        self._clock = itertools.count()
+        self.steps = 0
+        self.preemptions = 0
+
+    # ---- adding --------------------------------------------------------------------------------
+    def add(self, req: Request) -> Request:
+        if req.req_id is None:
+            req.req_id = f"req{next(self._ids)}"
+        if not req.prompt:
+            raise invalid("request: empty prompt")          # src/Inference/session.jl:688-689
+        if self.vocab_size is not None:
+            for t in req.prompt:
+                if not (0 <= t < self.vocab_size):
+                    raise invalid(f"request: token id {t} is outside the vocabulary")   # session.jl:164-177
+        total = len(req.prompt) + req.max_new_tokens
+        if len(req.prompt) > self.cache.max_positions:
+            raise resource(f"request: prompt of {len(req.prompt)} tokens exceeds the context length "
+                           f"{self.cache.max_positions}")     # session.jl:699-706
+        # what the request holds at its longest: every token but the last sampled one is in the cache
+        longest = min(max(len(req.prompt), total - 1), self.cache.max_positions)
+        pages = (longest + self.cache.page_size - 1) // self.cache.page_size
+        for pool, g in zip(self.cache.pools, self.cache.groups):
+            if g.window is None and pages > pool.count:
+                raise resource(f"request: needs {pages} pages of group {g.name}, the pool has {pool.count}")
+        req.state = WAITING
+        if req.max_new_tokens == 0:
+            self._finish(req, COMPLETE)       # returns the prompt (test/test_reference_generate.jl:24-28)
+            return req
+        self.waiting.append(req)
+        return req
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ---- planning (pure bookkeeping: no device work) ------------------------------------------------
+    def _left(self, r: Request) -> int:
+        return len(r.prompt) + len(r.generated) - r.fed
+
+    def _pages_short(self, wants: Dict[object, Tuple[Request, int]], spare: int = 0) -> bool:
+        need = [spare] * len(self.cache.groups)
+        for r, n in wants.values():
+            for g, k in enumerate(self.cache.pages_needed(r.req_id, n)):
+                need[g] += k
+        return any(k > f for k, f in zip(need, self.cache.free_pages()))
+
+    def plan(self) -> StepPlan:
+        plan = StepPlan(entries=[])
+        # cancelled requests leave before anything is planned
+        for r in [r for r in self.running if r.cancelled]:
+            self._finish(r, CANCELLED)
+        for r in [r for r in self.waiting if r.cancelled]:
+            self.waiting.remove(r)
+            self._finish(r, CANCELLED)
+
+        budget = self.max_tokens_per_step
+        wants: Dict[object, Tuple[Request, int]] = {}
+        decoders = [r for r in self.running if self._left(r) == 1 and r.generated]
+        prefillers = [r for r in self.running if r not in decoders]
+        # 1. every decoding request gets its one token; preempt from the newest while they do not fit
+        for r in decoders:
+            wants[r.req_id] = (r, 1)
+        while self._pages_short(wants) and len(self.running) > 1:
+            victim = self.running[-1]
+            self._preempt(victim)
+            plan.preempted.append(victim)
+            wants.pop(victim.req_id, None)
+            if victim in prefillers:
+                prefillers.remove(victim)
+        if self._pages_short(wants):
+            # a single request is left and its next token has no page: it has outgrown the pool
+            for r, _ in list(wants.values()):
+                self._finish(r, FAILED, resource(f"request {r.req_id!r} does not fit the cache pool"))
+            wants.clear()
+        budget -= len(wants)
+        # 2. prompt portions of running requests, oldest first, shrunk to what the pool can hold
+        for r in prefillers:
+            if budget <= 0:
+                break
+            n = min(self._left(r), self.prefill_chunk, budget)
+            n = self._fit(r, n, wants)
+            if n > 0:
+                wants[r.req_id] = (r, n)
+                budget -= n
+        # 3. admissions, first come first served, only while nothing was preempted in this step
+        while (self.waiting and not plan.preempted and budget > 0
+               and len(self.running) < self.max_batch and self.cache.slots.free_count > 0):
+            r = self.waiting[0]
+            self.engine.admit(r.req_id)
+            n = min(self._left(r), self.prefill_chunk, budget)
+            # a newcomer leaves one spare page per running request, so that their next tokens fit
+            n = self._fit(r, n, wants, spare=len(self.running))
+            if n <= 0:
+                self.engine.release(r.req_id)      # no room for even one token now: stays queued
+                break
+            self.waiting.pop(0)
+            r.state, r.admitted_at = RUNNING, next(self._clock)
+            self.running.append(r)
+            plan.admitted.append(r)
+            wants[r.req_id] = (r, n)
+            budget -= n
+        if not wants and self.running:
+            # nothing fits although requests are live: the oldest alone must be able to move
+            r = self.running[0]
+            while len(self.running) > 1:
+                victim = self.running[-1]
+                self._preempt(victim)
+                plan.preempted.append(victim)
+            n = self._fit(r, min(self._left(r), self.prefill_chunk, self.max_tokens_per_step), wants)
+            if n <= 0:
+                self._finish(r, FAILED, resource(f"request {r.req_id!r} does not fit the cache pool"))
+            else:
+                wants[r.req_id] = (r, n)
+        for r in self.running:                      # admission order
+            if r.req_id in wants:
+                plan.entries.append((r, r.fed, wants[r.req_id][1]))
+        return plan
+
+    def _fit(self, r: Request, n: int, wants: Dict[object, Tuple[Request, int]], spare: int = 0) -> int:
+        """Largest portion <= n of request r that the free pages hold beside what is planned."""
+        n = min(n, self.cache.max_positions - self.cache.length(r.req_id))
+        while n > 0:
+            trial = dict(wants)
+            trial[r.req_id] = (r, n)
+            if not self._pages_short(trial, spare):
+                return n
+            # shrink to the last page border below n (or give up)
+            filled = self.cache.length(r.req_id) + n
+            border = ((filled - 1) // self.cache.page_size) * self.cache.page_size
+            n = border - self.cache.length(r.req_id)
+        return 0
+
+    def _preempt(self, r: Request) -> None:
+        self.engine.release(r.req_id)
+        self.running.remove(r)
+        r.state, r.fed = WAITING, 0
+        r.preemptions += 1
+        self.preemptions += 1
+        self.waiting.insert(0, r)
+
+    def _finish(self, r: Request, status: str, error: Optional[Exception] = None) -> None:
+        if r.state == RUNNING:
+            self.engine.release(r.req_id)
+            self.running.remove(r)
+        r.state, r.status, r.error = FINISHED, status, error
+
+    # ---- running a step ---------------------------------------------------------------------------
+    def step(self) -> List[Tuple[Request, int]]:
+        """Plan, run and digest one step; returns the (request, token) pairs emitted by it."""
+        plan = self.plan()
+        if not plan.entries:
+            return []
+        entries, samplers = [], []
+        for r, start, n in plan.entries:
+            seq = r.sequence
+            last = start + n == len(seq)
+            entries.append(StepEntry(r.req_id, seq[start:start + n], [n - 1] if last else []))
+            if last:
+                samplers.append(r)
+        logits = self.engine.step(entries)
+        self.steps += 1
+        for r, _, n in plan.entries:
+            r.fed += n
+        emitted: List[Tuple[Request, int]] = []
+        if samplers:
+            tokens = self.select(logits, samplers)
+            for r, tok in zip(samplers, tokens):
+                if isinstance(tok, Exception):
+                    self._finish(r, FAILED, tok)
+                    continue
+                r.generated.append(int(tok))
+                emitted.append((r, int(tok)))
+                stop_by_hook = False
+                if r.on_token is not None:
+                    try:
+                        stop_by_hook = r.on_token(int(tok)) is False
+                    except Exception as e:      # a failing callback fails only its request
+                        self._finish(r, FAILED, GessoError(ErrorCode.RUNTIME, f"on_token raised: {e!r}"))
+                        continue
+                if int(tok) in r.eos_ids:
+                    self._finish(r, EOS)
+                elif int(tok) in r.stop_ids or stop_by_hook:
+                    self._finish(r, STOP)
+                elif len(r.generated) >= r.max_new_tokens:
+                    self._finish(r, COMPLETE)
+                elif len(r.prompt) + len(r.generated) > self.cache.max_positions:
+                    # the sampled token would not fit the context (src/Inference/session.jl:903-909)
+                    self._finish(r, COMPLETE)
+        return emitted
+
+    def run(self, max_steps: Optional[int] = None) -> None:
+        n = 0
+        while self.has_work:
+            before = (len(self.waiting), len(self.running), self.steps)
+            self.step()
+            n += 1
+            if max_steps is not None and n >= max_steps:
+                break
+            if (len(self.waiting), len(self.running), self.steps) == before and not self.running:
+                # nothing ran and nothing is live: the head of the queue cannot be admitted
+                r = self.waiting.pop(0)
+                self._finish(r, FAILED, resource(f"request {r.req_id!r} cannot be admitted"))

@@ -1,0 +1,130 @@
+"""Token selection: greedy, temperature and nucleus (top-p), one token per logits row.
+
+Semantics are the reference's (src/Inference/sampling.jl:13-74, src/Inference/session.jl:447-458):
+
+* greedy: argmax, ties go to the lowest id; a non-finite logit is a numerical failure and no token
+  is emitted;
+* ``Sampler(temperature > 0, top_p in (0, 1], seed >= 0)``: weights ``exp((logit - max) / T)`` in
+  float64; with ``top_p = 1`` an inverse-CDF walk in id order, else the smallest set of most likely
+  ids (ties by lower id) whose mass reaches ``top_p * total``, renormalised, walked in descending
+  order; exactly one draw of the request's splitmix64 stream per call.
+* ``temperature = 0`` (or no sampler) means greedy, as the reference's server maps it
+  (docs/serving.md:103).
+
+Selection runs on the device (``gesso_b200/csrc/sampling.cu``); the host only draws the uniform
+numbers, so that a request's tokens depend on its own seed and not on the batch it is in.
+:func:`sample_host` is the same rule on the host, for rows that are already there.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..errors import ErrorCode, GessoError, invalid
+
+_M64 = (1 << 64) - 1
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    temperature: float = 0.0
+    top_p: float = 1.0
+    seed: int = 0
+
+    def __post_init__(self):
+        if not (self.temperature >= 0) or math.isinf(self.temperature):
+            raise invalid(f"sampler temperature must be >= 0 and finite, got {self.temperature}")
+        if not (0 < self.top_p <= 1):
+            raise invalid(f"sampler top_p must be in (0, 1], got {self.top_p}")
+        if self.seed < 0:
+            raise invalid(f"sampler seed must be >= 0, got {self.seed}")
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature == 0
+
+
+class SplitMix64:
+    """The reference's generator (src/Inference/sampling.jl:32-39): 53-bit unit floats."""
+
+    def __init__(self, seed: int):
+        self.state = int(seed) & _M64
+
+    def unit(self) -> float:
+        self.state = (self.state + 0x9E3779B97F4A7C15) & _M64
+        z = self.state
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+        z ^= z >> 31
+        return float(z >> 11) * 2.0 ** -53
+
+
+def greedy_host(row: np.ndarray) -> int:
+    if not np.isfinite(row).all():
+        raise GessoError(ErrorCode.NUMERICAL_INSTABILITY, "nonfinite logits; no token may be emitted")
+    return int(np.argmax(row))     # first index on ties
+
+
+def sample_host(row: np.ndarray, params: SamplingParams, rng: SplitMix64) -> int:
+    """The reference's rule on a host row (float64 weights, stable descending order for top-p)."""
+    if params.greedy:
+        return greedy_host(row)
+    if not np.isfinite(row).all():
+        raise GessoError(ErrorCode.NUMERICAL_INSTABILITY, "nonfinite logits; no token may be emitted")
+    x = row.astype(np.float64)
+    w = np.exp((x - x.max()) / params.temperature)
+    total = float(np.add.accumulate(w)[-1])
+    if params.top_p >= 1:
+        r = rng.unit() * total
+        acc = np.add.accumulate(w)
+        i = int(np.searchsorted(acc, r, side="right"))
+        return min(i, len(w) - 1)
+    order = np.argsort(-w, kind="stable")
+    acc = np.add.accumulate(w[order])
+    keep = int(np.searchsorted(acc, params.top_p * total, side="left")) + 1
+    keep = min(keep, len(w))
+    cut = float(acc[keep - 1])
+    r = rng.unit() * cut
+    k = int(np.searchsorted(acc[:keep], r, side="right"))
+    return int(order[min(k, keep - 1)])
+
+
+def select_tokens(logits: torch.Tensor, params: Sequence[SamplingParams],
+                  rngs: Sequence[Optional[SplitMix64]]) -> List[object]:
+    """One token per row of ``logits`` [R, V] (device, float32).
+
+    Returns a list with an ``int`` per row, or a :class:`GessoError` for a row whose logits are not
+    finite (the caller fails that request only).  Sampled rows draw exactly one uniform number from
+    their request's generator.
+    """
+    R = logits.shape[0]
+    if R == 0:
+        return []
+    ids, bad = ops.argmax_rows(logits)
+    sampled = [i for i, p in enumerate(params) if not p.greedy]
+    if sampled:
+        temp = torch.tensor([params[i].temperature if not params[i].greedy else 1.0 for i in range(R)],
+                            dtype=torch.float64)
+        top_p = torch.tensor([params[i].top_p for i in range(R)], dtype=torch.float64)
+        u = torch.tensor([rngs[i].unit() if not params[i].greedy else 0.0 for i in range(R)],
+                         dtype=torch.float64)
+        dev = logits.device
+        sids, sbad = ops.sample_rows(logits, temp.to(dev), top_p.to(dev), u.to(dev))
+        pick = torch.zeros((R,), dtype=torch.bool)
+        pick[sampled] = True
+        pick = pick.to(dev)
+        ids = torch.where(pick, sids, ids)
+        bad = torch.where(pick, sbad, bad)
+    host = torch.stack([ids, bad]).to("cpu").numpy()
+    out: List[object] = []
+    for i in range(R):
+        if host[1, i]:
+            out.append(GessoError(ErrorCode.NUMERICAL_INSTABILITY, "nonfinite logits; no token may be emitted"))
+        else:
+            out.append(int(host[0, i]))
+    return out

@@ -15,9 +15,12 @@ pytestmark = pytest.mark.gpu
 
 # float32: the reference's device tolerance, 1e-4 * max(1, max|ref|) (test/test_lava_lfm25.jl:31-32).
 TOL = {"float32": 1e-4,
-       # bfloat16: every stored activation is rounded to 8 bits (unit roundoff 2^-9 = 2e-3); over the
-       # ~6 roundings per layer of these 4-6 layer models the logits carry about 16 roundoffs.
-       "bfloat16": 16 * 2.0 ** -9}
+       # bfloat16: every stored activation is rounded to 8 bits (unit roundoff u = 2^-9).  The plain
+       # implementation with a bfloat16 rounding at each place where the engine stores an activation
+       # (norm outputs, projection outputs, rotated q/k, attention, conv and SwiGLU outputs) differs
+       # from the exact one by 0.036-0.040 of max|ref| on these models (rms 1.3-2.8 %), so the bound
+       # is 32 u = 0.0625 of max(1, max|ref|).
+       "bfloat16": 32 * 2.0 ** -9}
 
 LENGTHS = {"a": [7, 13, 1, 70, 33, 97, 16, 65],
            "b": [40, 1, 23, 64, 81, 5, 17, 50],
