@@ -1,0 +1,307 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the LFM2-1.2B-shaped model with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers 16]
+    python bench.py --impl reference        # the reference arm (unavailable: a Julia project)
+
+A "step" is one decode step of the whole batch.  The default run: the layer sizes of LFM2-1.2B
+(16 layers, attention at 2,5,8,10,12,14, hidden 2048, 32 heads, 8 kv heads, head 64, ff 8192, vocab
+65536, 3 conv taps, tied head), random weights (seed 0), batch 8, context 4096 with 16-token pages:
+every request holds ``context - steps - warmup - 1`` tokens when the timed steps begin, so the last
+timed step runs at the full context.
+
+One JSON line is printed:
+
+* ``value``: decoded tokens per second, K steps timed on the device with CUDA events (W warm-up steps
+  before); inputs of a step are larger than L2 (all weights are read once per step);
+* ``e2e``: the same through the Python entry point (``Session.open_batch`` + ``step()``): host token
+  ids in, sampled ids out, every step's metadata copied from pinned host memory and its ids read back;
+* ``prefill``: one request of 2,048 tokens, logits at its last position; ``frac`` = flops / time / the
+  bf16 peak;
+* ``roofline``: bytes a decode step has to read (every weight once + the cache of the live requests)
+  / its time, against the measured copy bandwidth;
+* ``points``: decode tokens per second at batch 1 and 64.
+
+Peaks come from ``MEASURED_PEAKS.json`` beside this file when the driver wrote it, else the
+fallback of an earlier measurement on this pool (6.65 TB/s, 1.59 PFLOP/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+LFM2_1_2B = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 16,
+    "num_attention_heads": 32, "num_key_value_heads": 8,
+    "full_attn_idxs": [2, 5, 8, 10, 12, 14],
+    "conv_L_cache": 3, "conv_bias": False, "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True,
+    "block_multiple_of": 256, "norm_eps": 1e-5, "rope_theta": 1000000.0, "tie_embedding": True,
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            out = {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in p:
+                out["bf16_tflops_sustained"] = float(p["bf16_tflops_sustained"])
+            return out
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        super().__init__(daemon=True)
+        self.samples, self.stop_flag = [], threading.Event()
+
+    def run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
+                if out:
+                    self.samples.append([x.strip() for x in out[0].split(",")])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def summary(self):
+        self.stop_flag.set()
+        self.join(timeout=6)
+        mhz, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx = float(s[1])
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def model_flops_per_token(cfg_obj, n_layers_attn, n_layers_conv):
+    H, F, V = cfg_obj.hidden_size, cfg_obj.ff_dim, cfg_obj.vocab_size
+    kv = cfg_obj.num_key_value_heads * cfg_obj.head_dim
+    conv = 3 * H * H + H * H + 3 * F * H
+    attn = H * H + 2 * kv * H + H * H + 3 * F * H
+    return 2 * (n_layers_conv * conv + n_layers_attn * attn), 2 * V * H
+
+
+def decode_setup(gb, model, batch, context, steps, warmup, page_size, seed=1):
+    """A session with ``batch`` requests prefilled so that the timed steps end at the full context."""
+    import torch
+    start_len = max(1, context - steps - warmup - 1)
+    pages = batch * ((context + page_size - 1) // page_size)
+    s = gb.Session(model, context_length=context, page_size=page_size, num_pages=pages, max_batch=batch,
+                   max_tokens_per_step=4096, prefill_chunk=2048)
+    g = torch.Generator().manual_seed(seed)
+    prompts = [torch.randint(0, model.vocab_size, (start_len,), generator=g).tolist() for _ in range(batch)]
+    return s, prompts, start_len
+
+
+def time_decode(gb, model, batch, context, steps, warmup, page_size):
+    """Device-timed decode: K steps of the engine's step function with greedy selection on the device."""
+    import torch
+    from gesso_b200.engine.batch import StepEntry
+    from gesso_b200 import ops
+    s, prompts, start_len = decode_setup(gb, model, batch, context, steps, warmup, page_size)
+    eng = s.engine
+    ids = [f"q{i}" for i in range(batch)]
+    for rid, p in zip(ids, prompts):
+        eng.admit(rid)
+        for c in range(0, len(p), 2048):
+            eng.step([StepEntry(rid, p[c:c + 2048], [])])
+    g = torch.Generator().manual_seed(7)
+    toks = torch.randint(0, model.vocab_size, (warmup + steps, batch), generator=g).tolist()
+
+    def one(k):
+        logits = eng.step([StepEntry(rid, [toks[k][i]], [0]) for i, rid in enumerate(ids)])
+        ops.argmax_rows(logits)
+
+    for k in range(warmup):
+        one(k)
+    torch.cuda.synchronize()
+    launches0 = eng.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(warmup, warmup + steps):
+        one(k)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = eng.launches - launches0 + steps          # + the argmax launch of every step
+    eng.check_status()
+    kv_len_mid = start_len + warmup + steps // 2
+    for rid in ids:
+        eng.release(rid)
+    return ms / steps, launches, kv_len_mid
+
+
+def time_e2e(gb, model, batch, context, steps, warmup, page_size):
+    """The same through the Python entry point: host ids in, sampled ids out, every step."""
+    import torch
+    s, prompts, start_len = decode_setup(gb, model, batch, context, steps, warmup, page_size)
+    sched = s.open_batch([gb.BatchRequest(p, max_new_tokens=warmup + steps + 1) for p in prompts])
+    while any(r.fed < len(r.prompt) for r in sched.running + sched.waiting):
+        sched.step()                                       # prefill
+    for _ in range(warmup):
+        sched.step()
+    torch.cuda.synchronize()
+    h2d0 = s.engine.h2d_bytes
+    t0 = time.perf_counter()
+    emitted = 0
+    for _ in range(steps):
+        emitted += len(sched.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = (s.engine.h2d_bytes - h2d0) / steps
+    d2h = 2 * 4 * batch                                     # ids + flags read back, int32 each
+    return emitted / dt, h2d, d2h
+
+
+def time_prefill(gb, model, tokens, page_size, reps=5):
+    import torch
+    from gesso_b200.engine.batch import StepEntry
+    from gesso_b200.engine.engine import Engine
+    eng = Engine(model, max_positions=max(tokens, 64), page_size=page_size,
+                 num_pages=(tokens + page_size - 1) // page_size + 1, max_requests=1)
+    g = torch.Generator().manual_seed(3)
+    p = torch.randint(0, model.vocab_size, (tokens,), generator=g).tolist()
+    best = None
+    for r in range(reps + 2):
+        eng.admit("p")
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([StepEntry("p", p, [tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        eng.release("p")
+        if r >= 2:
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def reference_arm():
+    """The reference is a Julia 1.12 project (Project.toml, no setup.py / pyproject.toml): pip cannot
+    install it, no Julia toolchain exists here, and its CUDA extension has no short-convolution
+    lowering for LFM2 (ext/GessoCUDAExt.jl:138-157)."""
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "the reference is a Julia project: pip cannot install it offline, no Julia toolchain "
+                      "is on this box, and its CUDA extension does not run LFM2"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    import gesso_b200 as gb
+    from gesso_b200.config import Lfm2Config
+
+    cfg = dict(LFM2_1_2B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers is not None and args.layers < full_layers:
+        cfg["num_hidden_layers"] = args.layers
+        cfg["full_attn_idxs"] = [i for i in cfg["full_attn_idxs"] if i < args.layers]
+    c = Lfm2Config.from_json(cfg)
+    n_attn = sum(c.layer_is_attention)
+    n_conv = c.num_hidden_layers - n_attn
+    model = gb.random_model(cfg, seed=0, dtype="bfloat16", max_positions=args.context)
+    pk = peaks()
+
+    sampler = ClockSampler()
+    sampler.start()
+    ms_step, launches, kv_mid = time_decode(gb, model, args.batch, args.context, args.steps, warmup, args.page_size)
+    clocks = sampler.summary()
+    value = args.batch * 1000.0 / ms_step
+
+    # bytes a decode step has to read: every weight it uses once + the cache of the live requests
+    layer_flops, head_flops = model_flops_per_token(c, n_attn, n_conv)
+    weight_bytes = (layer_flops // 2 + head_flops // 2) * 2                 # bf16
+    kv_bytes = args.batch * kv_mid * n_attn * 2 * c.num_key_value_heads * c.head_dim * 2
+    state_bytes = args.batch * n_conv * (c.conv_L_cache - 1) * c.hidden_size * 4
+    step_bytes = weight_bytes + kv_bytes + state_bytes
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]}
+
+    e2e_value, h2d, d2h = time_e2e(gb, model, args.batch, args.context, args.steps, warmup, args.page_size)
+    e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+           "d2h_bytes_per_step": int(d2h)}
+
+    out = {
+        "metric": "decode tokens/s (LFM2-1.2B layer sizes, random weights)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (uniform-random token ids, random weights seed 0)",
+        "config": {"model": "LFM2-1.2B-shaped", "layers": c.num_hidden_layers, "layers_of_config": full_layers,
+                   "hidden": c.hidden_size, "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
+                   "head_dim": c.head_dim, "ff": c.ff_dim, "vocab": c.vocab_size, "conv_taps": c.conv_L_cache,
+                   "attention_layers": n_attn, "global_batch": args.batch, "seq_len": args.context,
+                   "page_size": args.page_size, "prefill_tokens": args.prefill_tokens,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (all weights read every step)"},
+        "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks,
+    }
+    if not args.no_points:
+        ms_pf = time_prefill(gb, model, args.prefill_tokens, args.page_size)
+        T = args.prefill_tokens
+        attn_flops = n_attn * 4 * c.num_attention_heads * c.head_dim * (T * (T + 1) // 2)
+        pf_flops = T * layer_flops + head_flops + attn_flops
+        out["prefill"] = {"value": round(T * 1000.0 / ms_pf, 1), "tokens": T, "ms": round(ms_pf, 3),
+                          "frac": round(pf_flops / (ms_pf * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        pts = {}
+        for b in (1, 64):
+            ms_b, _, _ = time_decode(gb, model, b, args.context, min(args.steps, 64), warmup, args.page_size)
+            pts[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+        out["points"] = pts
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -72,7 +72,17 @@ def declare(name: str, argtypes) -> None:
         fn.restype = c_int
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launchers of this library have been called so far (by this process)."""
+    return _launches
+
+
 def check(status: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if status == 0:
         return
     if status < 0:
@@ -80,4 +90,4 @@ def check(status: int, what: str) -> None:
     raise GessoError(ErrorCode.LAUNCH, f"{what}: CUDA error {status} at launch")
 
 
-__all__ = ["library", "check", "declare", "c_double", "P", "I", "F", "LL"]
+__all__ = ["library", "check", "declare", "launch_count", "c_double", "P", "I", "F", "LL"]

@@ -20,6 +20,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
+from ..csrc.lib import launch_count
 from ..errors import ErrorCode, GessoError, invalid, resource
 from .batch import StepContext, StepEntry, StepLayout, pack_step
 from .model import Model, PagedView, StateView
@@ -51,7 +52,7 @@ class DeviceCache:
 
 class Engine:
     def __init__(self, model: Model, *, max_positions: Optional[int] = None, page_size: int = 16,
-                 num_pages: Optional[int] = None, max_requests: int = 8):
+                 num_pages: Optional[int] = None, max_requests: int = 8, use_graphs: bool = True):
         self.model = model
         self.max_positions = int(max_positions or model.rt.max_positions)
         if self.max_positions > model.rt.max_positions:
@@ -70,6 +71,12 @@ class Engine:
         self.status = torch.zeros((1,), dtype=torch.int32, device=model.rt.device)
         self.steps_run = 0
         self.tokens_run = 0
+        self.launches = 0            # kernels of this library launched by steps (graph nodes included)
+        self.h2d_bytes = 0           # metadata bytes copied to the device by steps
+        self.use_graphs = use_graphs
+        self.max_graph_batch = 256
+        self._graphs: Dict = {}
+        self._graph_pool = None
         # ring of pinned staging buffers; an event per buffer says when its copy has left it
         self._pinned: List[Optional[torch.Tensor]] = [None] * 4
         self._pinned_events: List[Optional[torch.cuda.Event]] = [None] * 4
@@ -119,8 +126,8 @@ class Engine:
             self._pinned[i] = torch.empty((max(n, 4096),), dtype=torch.int32, pin_memory=True)
         return i, self._pinned[i]
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Reserve pages, zero fresh slots and upload the step's metadata."""
+    def _prepare(self, entries: Sequence[StepEntry]):
+        """Validate, reserve pages, zero fresh slots and pack the step's metadata on the host."""
         self._validate(entries)
         for e in entries:
             n = len(e.tokens)
@@ -150,13 +157,22 @@ class Engine:
         size = layout.offsets()["_end"]
         slot_i, host = self._pinned_buffer(size)
         pack_step(list(entries), starts, slots, tables, layout, host.numpy()[:size])
-        buf = torch.empty((size,), dtype=torch.int32, device=self.model.rt.device)
-        buf.copy_(host[:size], non_blocking=True)
+        max_seg = max(len(e.tokens) for e in entries)
+        max_kv = max(s + len(e.tokens) for s, e in zip(starts, entries))
+        return layout, slot_i, host[:size], max_seg, max_kv
+
+    def _upload(self, buf: torch.Tensor, slot_i: int, host: torch.Tensor) -> None:
+        buf.copy_(host, non_blocking=True)
         if self._pinned_events[slot_i] is None:
             self._pinned_events[slot_i] = torch.cuda.Event()
         self._pinned_events[slot_i].record()
-        max_seg = max(len(e.tokens) for e in entries)
-        max_kv = max(s + len(e.tokens) for s, e in zip(starts, entries))
+        self.h2d_bytes += host.numel() * 4
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Reserve pages, zero fresh slots and upload the step's metadata (one transfer)."""
+        layout, slot_i, host, max_seg, max_kv = self._prepare(entries)
+        buf = torch.empty((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
+        self._upload(buf, slot_i, host)
         return StepContext(layout, buf, self.status, max_seg, max_kv)
 
     def views(self, ctx: StepContext):
@@ -173,14 +189,56 @@ class Engine:
         return out
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Run one batch; returns float32 logits ``[wanted, vocab]`` (``None`` if nothing is wanted)."""
-        ctx = self.build_context(entries)
-        logits = self.model.forward(ctx, self.views(ctx))
+        """Run one batch; returns float32 logits ``[wanted, vocab]`` (``None`` if nothing is wanted).
+
+        A step of single tokens only (decoding) replays a CUDA graph captured for its batch size:
+        the metadata goes into the graph's fixed buffer and the whole layer loop is one launch.
+        The logits of such a step live in the graph's output buffer and are valid until the next
+        step of the same shape.
+        """
+        layout, slot_i, host, max_seg, max_kv = self._prepare(entries)
+        if self.use_graphs and max_seg == 1 and layout.n_segs <= self.max_graph_batch:
+            logits = self._step_graph(layout, slot_i, host, max_kv)
+        else:
+            buf = torch.empty((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
+            self._upload(buf, slot_i, host)
+            ctx = StepContext(layout, buf, self.status, max_seg, max_kv)
+            before = launch_count()
+            logits = self.model.forward(ctx, self.views(ctx))
+            self.launches += launch_count() - before
         for e in entries:
             self.cache.commit(e.req_id, len(e.tokens))
         self.steps_run += 1
-        self.tokens_run += ctx.n_tokens
+        self.tokens_run += layout.n_tokens
         return logits
+
+    def _step_graph(self, layout: StepLayout, slot_i: int, host: torch.Tensor, max_kv: int):
+        key = (layout.n_segs, layout.n_rows)
+        g = self._graphs.get(key)
+        if g is None:
+            buf = torch.zeros((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
+            self._upload(buf, slot_i, host)
+            ctx = StepContext(layout, buf, self.status, 1, self.max_positions)
+            views = self.views(ctx)
+            # One eager run first: libraries initialise lazily, and capture records rather than runs,
+            # so this run is also the one that produces the step's result.
+            before = launch_count()
+            logits = self.model.forward(ctx, views)
+            n_launch = launch_count() - before
+            self.launches += n_launch
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                out = self.model.forward(ctx, views)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            self._graphs[key] = (graph, buf, out, n_launch)
+            return logits
+        graph, buf, out, n_launch = g
+        self._upload(buf, slot_i, host)
+        graph.replay()
+        self.launches += n_launch
+        return out
 
     def check_status(self) -> None:
         """Raise if a kernel recorded a position without a page (synchronises)."""

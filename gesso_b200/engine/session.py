@@ -195,6 +195,23 @@ class Session:
         finally:
             self._leave()
 
+    def open_batch(self, requests: Sequence[BatchRequest]) -> Scheduler:
+        """The same stream as :meth:`run_batch`, stepped by the caller: returns the scheduler with the
+        requests added; every ``step()`` of it runs one engine step and returns the (request, token)
+        pairs it emitted, until ``has_work`` is false."""
+        self.reset()
+        sched = Scheduler(self.engine, _select, max_batch=self.max_batch,
+                          max_tokens_per_step=self.max_tokens_per_step, prefill_chunk=self.prefill_chunk,
+                          vocab_size=self.model.vocab_size)
+        self.last_scheduler = sched
+        for i, br in enumerate(requests):
+            req = Request(list(br.prompt), br.max_new_tokens,
+                          SamplingParams(float(br.temperature), float(br.top_p), int(br.seed)),
+                          self._eos(br.eos_ids), tuple(int(x) for x in br.stop_ids), br.on_token, req_id=f"b{i}")
+            br._request = req
+            sched.add(req)
+        return sched
+
     def stats(self):
         s = self.engine.stats()
         if self.last_scheduler is not None:

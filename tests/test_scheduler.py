@@ -1,0 +1,200 @@
+"""The scheduler's decisions on the CPU, with a stand-in engine around a real cache manager."""
+import pytest
+
+from gesso_b200.cache import CacheManager, PagedGroupSpec
+from gesso_b200.engine.scheduler import (CANCELLED, COMPLETE, EOS, FAILED, STOP, Request, Scheduler)
+from gesso_b200.errors import ErrorCode, GessoError
+from gesso_b200.sampling import SamplingParams
+
+
+class FakeEngine:
+    """Keeps the cache manager honest and records every step; 'logits' are the entries themselves."""
+
+    def __init__(self, num_pages=16, page_size=4, slots=4, ctx=64):
+        self.cache = CacheManager([PagedGroupSpec("kv")], page_size, num_pages, slots, ctx)
+        self.log = []
+
+    def admit(self, rid):
+        self.cache.admit(rid)
+
+    def release(self, rid):
+        self.cache.release(rid)
+
+    def step(self, entries):
+        for e in entries:
+            self.cache.reserve(e.req_id, len(e.tokens))
+        for e in entries:
+            self.cache.commit(e.req_id, len(e.tokens))
+        self.cache.check_invariants()
+        self.log.append([(e.req_id, list(e.tokens), list(e.want)) for e in entries])
+        return [e for e in entries if e.want]
+
+
+def next_token(logits, requests):
+    """Deterministic 'model': the next token is a function of the request's sequence so far."""
+    return [(sum(r.sequence) * 31 + len(r.sequence)) % 97 for r in requests]
+
+
+def make(engine=None, **kw):
+    engine = engine or FakeEngine()
+    return engine, Scheduler(engine, next_token, vocab_size=100, **kw)
+
+
+def solo(prompt, n):
+    eng, s = make()
+    r = s.add(Request(prompt, n))
+    s.run()
+    return r.ids
+
+
+def test_single_request_runs_to_completion_and_frees():
+    eng, s = make(prefill_chunk=3)
+    r = s.add(Request([1, 2, 3, 4, 5, 6, 7], 4))
+    s.run()
+    assert r.status == COMPLETE and len(r.generated) == 4
+    # prompt in portions of 3, 3, 1; then one token per step; the last sampled token is never run
+    assert [len(st[0][1]) for st in eng.log] == [3, 3, 1, 1, 1, 1]
+    assert eng.log[0][0][2] == [] and eng.log[2][0][2] == [0]
+    assert eng.cache.pages_in_use() == [0] and eng.cache.slots_in_use() == 0
+
+
+def test_max_new_tokens_zero_returns_the_prompt():
+    eng, s = make()
+    r = s.add(Request([5, 6], 0))
+    assert r.status == COMPLETE and r.ids == [5, 6] and not s.has_work and eng.log == []
+
+
+def test_batched_equals_solo():
+    prompts = [[1, 2, 3], [9] * 11, [4], [7, 8, 9, 10, 11, 12]]
+    eng, s = make(max_batch=3, max_tokens_per_step=8, prefill_chunk=4)
+    reqs = [s.add(Request(p, 5)) for p in prompts]
+    s.run()
+    for p, r in zip(prompts, reqs):
+        assert r.status == COMPLETE and r.ids == solo(p, 5)
+    assert max(len(st) for st in eng.log) <= 3
+    assert all(sum(len(e[1]) for e in st) <= 8 for st in eng.log)          # the token budget
+    # decoding requests come first in the budget: once a request decodes it is in every later step
+    assert eng.cache.pages_in_use() == [0]
+
+
+def test_decodes_before_portions_and_fifo():
+    eng, s = make(max_batch=4, max_tokens_per_step=6, prefill_chunk=6)
+    a = s.add(Request([1] * 4, 3))
+    b = s.add(Request([2] * 9, 2))
+    s.step()                                        # a: 4 tokens, b: 2 tokens (budget 6)
+    assert eng.log[-1] == [("req0", [1] * 4, [3]), ("req1", [2] * 2, [])]
+    s.step()                                        # a decodes (1), b gets the other 5
+    assert [len(e[1]) for e in eng.log[-1]] == [1, 5]
+    s.run()
+    assert a.status == b.status == COMPLETE
+
+
+def test_stops():
+    # eos and stop ids end the request with the id returned but not run; the hook can stop too
+    first = solo([3, 4], 1)[-1]
+    eng, s = make()
+    r = s.add(Request([3, 4], 5, eos_ids=(first,)))
+    s.run()
+    assert r.status == EOS and r.ids == [3, 4, first] and len(eng.log) == 1
+    eng, s = make()
+    r = s.add(Request([3, 4], 5, stop_ids=(first,)))
+    s.run()
+    assert r.status == STOP and r.ids == [3, 4, first]
+    seen = []
+    eng, s = make()
+    r = s.add(Request([3, 4], 5, on_token=lambda t: (seen.append(t), len(seen) < 2)[1]))
+    s.run()
+    assert r.status == STOP and seen == r.generated and len(seen) == 2
+
+
+def test_callback_failure_is_contained():
+    def boom(t):
+        raise ValueError("no")
+    eng, s = make()
+    bad = s.add(Request([1, 2], 4, on_token=boom))
+    good = s.add(Request([5, 6, 7], 4))
+    s.run()
+    assert bad.status == FAILED and bad.error.code == ErrorCode.RUNTIME
+    assert good.status == COMPLETE and good.ids == solo([5, 6, 7], 4)
+    assert eng.cache.pages_in_use() == [0] and eng.cache.slots_in_use() == 0
+
+
+def test_cancel():
+    eng, s = make()
+    a = s.add(Request([1, 2, 3], 50))
+    b = s.add(Request([4, 5], 3))
+    c = s.add(Request([6], 3))
+    c.cancel()                                      # before it is admitted
+    s.step()
+    s.step()
+    a.cancel()                                      # between tokens
+    s.run()
+    assert a.status == CANCELLED and 1 <= len(a.generated) < 50
+    assert c.status == CANCELLED and c.generated == []
+    assert b.status == COMPLETE and b.ids == solo([4, 5], 3)
+    assert eng.cache.pages_in_use() == [0]
+
+
+def test_refusals_at_add():
+    eng, s = make(FakeEngine(num_pages=4, ctx=32))
+    with pytest.raises(GessoError):
+        s.add(Request([], 3))                       # empty prompt
+    with pytest.raises(GessoError):
+        s.add(Request([1, 200], 3))                 # outside the vocabulary
+    with pytest.raises(GessoError) as e:
+        s.add(Request([1] * 33, 1))                 # longer than the context
+    assert e.value.code == ErrorCode.RESOURCE_LIMIT
+    with pytest.raises(GessoError) as e:
+        s.add(Request([1] * 10, 20))                # 29 cached tokens need 8 pages, the pool has 4
+    assert e.value.code == ErrorCode.RESOURCE_LIMIT
+    with pytest.raises(GessoError):
+        Request([1], -1)
+
+
+def test_context_limit_ends_generation():
+    eng, s = make(FakeEngine(num_pages=16, ctx=8))
+    r = s.add(Request([1] * 6, 50))
+    s.run()
+    assert r.status == COMPLETE and len(r.prompt) + len(r.generated) == 9     # 8 cached + the last sampled id
+    assert eng.cache.pages_in_use() == [0]
+
+
+def test_pages_run_out_preempts_newest_and_results_do_not_change():
+    # 6 pages of 4 positions; three requests that together outgrow them
+    prompts = [[1] * 6, [2] * 6, [3] * 5]
+    eng = FakeEngine(num_pages=6, page_size=4, slots=4, ctx=24)
+    _, s = make(eng, max_batch=3, prefill_chunk=8)
+    reqs = [s.add(Request(p, 12)) for p in prompts]
+    s.run()
+    assert s.preemptions >= 1
+    assert reqs[0].preemptions == 0                 # the oldest request is never preempted
+    for p, r in zip(prompts, reqs):
+        assert r.status == COMPLETE and r.ids == solo(p, 12)
+    assert eng.cache.pages_in_use() == [0] and eng.cache.slots_in_use() == 0
+    # a preempted request was prefilled again from its first token
+    rid = next(r.req_id for r in reqs if r.preemptions)
+    starts = [e for st in eng.log for e in st if e[0] == rid and len(e[1]) > 1]
+    assert len(starts) >= 2
+
+
+def test_admission_waits_for_slots_and_pages():
+    eng = FakeEngine(num_pages=16, slots=2)
+    _, s = make(eng, max_batch=8)
+    reqs = [s.add(Request([i + 1] * 3, 2)) for i in range(5)]
+    s.step()
+    assert len(s.running) == 2 and len(s.waiting) == 3     # two slots
+    s.run()
+    assert all(r.status == COMPLETE for r in reqs)
+    order = []
+    for st in eng.log:
+        for e in st:
+            if e[0] not in order:
+                order.append(e[0])
+    assert order == [r.req_id for r in reqs]                # first come, first served
+
+
+def test_sampling_params_validation():
+    for bad in (dict(temperature=-1), dict(top_p=0), dict(top_p=1.5), dict(seed=-1)):
+        with pytest.raises(GessoError):
+            SamplingParams(**bad)
+    assert SamplingParams().greedy and not SamplingParams(temperature=0.7).greedy
