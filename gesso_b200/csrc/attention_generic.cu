@@ -40,9 +40,9 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     for (int u = lo + lane; u <= pos; u += 32) {
         const int page = bt[u / page_size];
         if (page < 0) continue;
-        const size_t row = (((size_t)page * nkv + kvh) * page_size + (u % page_size)) * hd;
-        const T* kr = k_pages + row;
-        const T* vr = v_pages + row;
+        const T* kr = k_pages + (((size_t)page * nkv + kvh) * page_size + (u % page_size)) * hd;
+        // V is stored [feature][slot] inside a page
+        const T* vr = v_pages + ((size_t)page * nkv + kvh) * hd * page_size + (u % page_size);
         float dot = 0.f;
 #pragma unroll
         for (int j = 0; j < HD_PAD; ++j)
@@ -59,7 +59,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
         l += p;
 #pragma unroll
         for (int j = 0; j < HD_PAD; ++j)
-            if (j < hd) acc[j] += p * to_f32(vr[j]);
+            if (j < hd) acc[j] += p * to_f32(vr[(size_t)j * page_size]);
     }
     const float M = warp_max(m);
     const float f = (m == -INFINITY) ? 0.f : expf(m - M);

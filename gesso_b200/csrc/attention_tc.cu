@@ -1,0 +1,411 @@
+// Tensor-core paged attention for bfloat16: a split-KV kernel for steps of single tokens and a
+// flash kernel for steps with prompt portions.  Head sizes 32, 64, 96, 128; page sizes that are
+// multiples of 16.  Other sizes are refused (the caller then takes the FP32-arithmetic kernel).
+//
+// Both kernels read K and V fragments straight from the cache pages into registers, with no
+// shared-memory staging and no transposition:
+//   * scores S = Q K^T use mma.m16n8k16 with K as the B operand: b(k = feature, n = key) is two
+//     consecutive features of one K row, so a thread reads 16 contiguous bytes of a K row and
+//     uses them for two k16 steps.  The sum over features is order-free, so features are assigned
+//     to fragment slots as the loads deliver them (thread t of a quad holds features 8t..8t+7 of
+//     each 32-feature chunk), and Q's A fragment uses the same assignment.
+//   * outputs O = P V use V as the B operand: b(k = key, n = feature) is two consecutive keys of
+//     one feature, contiguous because V pages are stored [feature][slot].  The 16 keys of a block
+//     are assigned to the two 8-key score tiles so that a thread's four probabilities are keys
+//     4t..4t+3, which is one 8-byte read of a V^T row.
+// Softmax statistics and the output accumulate in float32 with a running maximum (base-2
+// exponentials with the 1/sqrt(d) scale folded in).  Reference design inputs: the split-K decode
+// kernels of ext/cuda_attention.jl:421-550 (block = kv head x key chunk, all query heads of the
+// group from one read, LSE combine); formulas as src/Inference/Inference.jl:1201-1207, 1398,
+// 1414-1457.
+#include <math.h>
+
+#include "common.cuh"
+
+#define LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// K and V fragments of one 16-key block for one kv head.
+template <int HD>
+struct KVFrag {
+    uint4 k[2][HD / 32];     // [score tile][32-feature chunk]
+    uint2 v[HD / 8];         // [8-feature tile]
+};
+
+template <int HD>
+__device__ __forceinline__ void load_block(KVFrag<HD>& f, const bf16* __restrict__ k_pages,
+                                           const bf16* __restrict__ v_pages, const int* __restrict__ bt,
+                                           int block, int page_size, int nkv, int kvh, int g, int t) {
+    const int key0 = block * 16;
+    const int page = bt[key0 / page_size];
+    const int sub = key0 % page_size;
+    if (page < 0) {   // a page that was given back (behind a window): masked anyway, read nothing
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) f.k[0][c] = f.k[1][c] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) f.v[j] = make_uint2(0, 0);
+        return;
+    }
+    const size_t pk = ((size_t)page * nkv + kvh);
+    // score tile 0 column g is key 4(g/2) + g%2, tile 1 column g is key 4(g/2) + 2 + g%2
+    const int key_a = 4 * (g >> 1) + (g & 1);
+    const bf16* ka = k_pages + (pk * page_size + sub + key_a) * HD + 8 * t;
+    const bf16* kb = ka + 2 * HD;
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+        f.k[0][c] = *reinterpret_cast<const uint4*>(ka + 32 * c);
+        f.k[1][c] = *reinterpret_cast<const uint4*>(kb + 32 * c);
+    }
+    const bf16* vt = v_pages + (pk * HD + g) * page_size + sub + 4 * t;
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) f.v[j] = *reinterpret_cast<const uint2*>(vt + (size_t)(8 * j) * page_size);
+}
+
+// One 16-key block against one m16 tile of queries: scores, running softmax, outputs.
+// qf[c] / qg[c]: Q rows g and g+8, features 32c+8t..+8.  pos_a / pos_b: last visible key of rows g
+// and g+8; lo_a / lo_b: first visible key.  key0: first key of the block.
+template <int HD>
+__device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&qf)[HD / 32],
+                                             const uint4 (&qg)[HD / 32], float (&o)[HD / 8][4], float (&m)[2],
+                                             float (&l)[2], int key0, int t, int pos_a, int pos_b, int lo_a,
+                                             int lo_b, float scale_log2, bool need_mask) {
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+        mma_bf16(s0, qf[c].x, qg[c].x, qf[c].y, qg[c].y, f.k[0][c].x, f.k[0][c].y);
+        mma_bf16(s0, qf[c].z, qg[c].z, qf[c].w, qg[c].w, f.k[0][c].z, f.k[0][c].w);
+        mma_bf16(s1, qf[c].x, qg[c].x, qf[c].y, qg[c].y, f.k[1][c].x, f.k[1][c].y);
+        mma_bf16(s1, qf[c].z, qg[c].z, qf[c].w, qg[c].w, f.k[1][c].z, f.k[1][c].w);
+    }
+    // this thread's keys: key0 + 4t + {0,1} (tile 0) and + {2,3} (tile 1); rows g (idx 0,1) and g+8 (2,3)
+    float sa[4] = {s0[0], s0[1], s1[0], s1[1]};
+    float sb[4] = {s0[2], s0[3], s1[2], s1[3]};
+    const int kbase = key0 + 4 * t;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        sa[i] *= scale_log2;
+        sb[i] *= scale_log2;
+        if (need_mask) {
+            const int key = kbase + i;
+            if (key > pos_a || key < lo_a) sa[i] = -INFINITY;
+            if (key > pos_b || key < lo_b) sb[i] = -INFINITY;
+        }
+    }
+    const float ma = quad_max(fmaxf(fmaxf(sa[0], sa[1]), fmaxf(sa[2], sa[3])));
+    const float mb = quad_max(fmaxf(fmaxf(sb[0], sb[1]), fmaxf(sb[2], sb[3])));
+    const float na = fmaxf(m[0], ma), nb = fmaxf(m[1], mb);
+    const float ua = na == -INFINITY ? 0.f : na, ub = nb == -INFINITY ? 0.f : nb;   // all masked so far
+    const float alpha_a = exp2f(m[0] - ua), alpha_b = exp2f(m[1] - ub);
+    m[0] = na;
+    m[1] = nb;
+    float pa[4], pb[4];
+    float la = 0.f, lb = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        pa[i] = exp2f(sa[i] - ua);
+        pb[i] = exp2f(sb[i] - ub);
+        la += pa[i];
+        lb += pb[i];
+    }
+    l[0] = l[0] * alpha_a + la;
+    l[1] = l[1] * alpha_b + lb;
+    const unsigned a0 = pack_bf16(pa[0], pa[1]), a1 = pack_bf16(pb[0], pb[1]);
+    const unsigned a2 = pack_bf16(pa[2], pa[3]), a3 = pack_bf16(pb[2], pb[3]);
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) {
+        o[j][0] *= alpha_a;
+        o[j][1] *= alpha_a;
+        o[j][2] *= alpha_b;
+        o[j][3] *= alpha_b;
+        mma_bf16(o[j], a0, a1, a2, a3, f.v[j].x, f.v[j].y);
+    }
+}
+
+// ================================ decode: split-KV ==============================================
+// grid (splits, nkv, segments), 128 threads.  The m16 rows are the query heads of the kv group
+// (up to 16).  Every warp walks its share of the split's 16-key blocks; the warps are merged in
+// shared memory; with more than one split the partial (m, l, O) goes to the workspace and the last
+// split to arrive merges them (a ticket per (segment, kv head), reset for the next launch).
+template <int HD>
+__global__ void __launch_bounds__(128)
+decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
+                        const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
+                        int page_size, const int* __restrict__ positions, const int* __restrict__ seg_start,
+                        bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int n_splits,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets) {
+    extern __shared__ float smem[];          // [4 warps][16 rows][HD + 2]
+    __shared__ int s_last;
+    const int split = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
+    const int G = nh / nkv;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int tok = seg_start[seg];          // the segment's single token
+    const int pos = positions[tok];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int* bt = block_table + (size_t)seg * max_pages;
+
+    // Q fragments: row g is head kvh*G + g (zero rows beyond the group)
+    uint4 qf[HD / 32], qg[HD / 32];
+    {
+        const bf16* qa = q + ((size_t)tok * nh + (size_t)kvh * G + g) * HD + 8 * t;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            qf[c] = g < G ? *reinterpret_cast<const uint4*>(qa + 32 * c) : make_uint4(0, 0, 0, 0);
+            qg[c] = g + 8 < G ? *reinterpret_cast<const uint4*>(qa + 8 * HD + 32 * c) : make_uint4(0, 0, 0, 0);
+        }
+    }
+    const int first_block = lo / 16, last_block = pos / 16;
+    const int n_blocks = last_block - first_block + 1;
+    const int per = (n_blocks + n_splits - 1) / n_splits;
+    const int b0 = first_block + split * per;
+    const int b1 = min(last_block + 1, b0 + per);
+
+    float o[HD / 8][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+    KVFrag<HD> cur, nxt;
+    int b = b0 + w;
+    if (b < b1) load_block<HD>(cur, k_pages, v_pages, bt, b, page_size, nkv, kvh, g, t);
+    for (; b < b1; b += 4) {
+        const bool more = b + 4 < b1;
+        if (more) load_block<HD>(nxt, k_pages, v_pages, bt, b + 4, page_size, nkv, kvh, g, t);
+        const bool need_mask = (b * 16 + 15 > pos) || (b * 16 < lo);
+        attend_block<HD>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask);
+        if (more) cur = nxt;
+    }
+    l[0] = quad_sum(l[0]);
+    l[1] = quad_sum(l[1]);
+
+    // ---- merge the four warps ----
+    float* mine = smem + (size_t)w * 16 * (HD + 2);
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) {
+        mine[g * (HD + 2) + 8 * j + 2 * t] = o[j][0];
+        mine[g * (HD + 2) + 8 * j + 2 * t + 1] = o[j][1];
+        mine[(g + 8) * (HD + 2) + 8 * j + 2 * t] = o[j][2];
+        mine[(g + 8) * (HD + 2) + 8 * j + 2 * t + 1] = o[j][3];
+    }
+    if (t == 0) {
+        mine[g * (HD + 2) + HD] = m[0];
+        mine[g * (HD + 2) + HD + 1] = l[0];
+        mine[(g + 8) * (HD + 2) + HD] = m[1];
+        mine[(g + 8) * (HD + 2) + HD + 1] = l[1];
+    }
+    __syncthreads();
+    // thread -> (head row r, feature d): G*HD outputs
+    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+        const int r = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int ww = 0; ww < 4; ++ww) M = fmaxf(M, smem[((size_t)ww * 16 + r) * (HD + 2) + HD]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < 4; ++ww) {
+            const float* row = smem + ((size_t)ww * 16 + r) * (HD + 2);
+            const float f = row[HD] == -INFINITY ? 0.f : exp2f(row[HD] - M);
+            L += row[HD + 1] * f;
+            acc += row[d] * f;
+        }
+        const int head = kvh * G + r;
+        if (n_splits == 1) {
+            out[((size_t)tok * nh + head) * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            const size_t pi = ((size_t)seg * nh + head) * n_splits + split;
+            part_o[pi * HD + d] = acc;
+            if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+        }
+    }
+    if (n_splits == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(&tickets[seg * nkv + kvh], 1);
+        s_last = ticket == n_splits - 1;
+        if (s_last) tickets[seg * nkv + kvh] = 0;     // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+        const int r = idx / HD, d = idx % HD;
+        const int head = kvh * G + r;
+        const size_t p0 = ((size_t)seg * nh + head) * n_splits;
+        float M = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(part_ml + (p0 + s) * 2));
+        float L = 0.f, acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = __ldcg(part_ml + (p0 + s) * 2);
+            const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            L += __ldcg(part_ml + (p0 + s) * 2 + 1) * f;
+            acc += __ldcg(part_o + (p0 + s) * HD + d) * f;
+        }
+        out[((size_t)tok * nh + head) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+// ================================ prefill: flash ================================================
+// grid (64-token tiles, nkv, G / HPW), 128 threads.  A warp owns 16 consecutive tokens of one
+// request and HPW query heads of one kv group; it walks the 16-key blocks up to its last row's
+// position.  tile_seg / tile_q0 list the tiles (a tile never crosses a request).
+template <int HD, int HPW>
+__global__ void __launch_bounds__(128)
+prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
+                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
+                         int page_size, const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
+                         const int* __restrict__ tile_seg, const int* __restrict__ tile_q0,
+                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2) {
+    const int tile = blockIdx.x, kvh = blockIdx.y;
+    const int G = nh / nkv;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int seg = tile_seg[tile];
+    const int t0 = seg_start[seg], n = seg_start[seg + 1] - t0;
+    const int q0 = tile_q0[tile] + 16 * w;          // first row of this warp inside the request's portion
+    if (q0 >= n) return;
+    const int rows = min(16, n - q0);
+    const int p0 = seg_pos0[seg];
+    // rows beyond the portion repeat its last row (computed, never stored)
+    const int ra = min(g, rows - 1), rb = min(g + 8, rows - 1);
+    const int pos_a = p0 + q0 + ra, pos_b = p0 + q0 + rb;
+    const int lo_a = window > 0 ? max(0, pos_a - window + 1) : 0;
+    const int lo_b = window > 0 ? max(0, pos_b - window + 1) : 0;
+    const int pos_first = p0 + q0, pos_last = p0 + q0 + rows - 1;
+    const int first_block = (window > 0 ? max(0, pos_first - window + 1) : 0) / 16;
+    const int last_block = pos_last / 16;
+    const int* bt = block_table + (size_t)seg * max_pages;
+    const int head0 = kvh * G + blockIdx.z * HPW;
+
+    uint4 qf[HPW][HD / 32], qg[HPW][HD / 32];
+    float o[HPW][HD / 8][4], m[HPW][2], l[HPW][2];
+#pragma unroll
+    for (int h = 0; h < HPW; ++h) {
+        const bf16* qa = q + ((size_t)(t0 + q0 + ra) * nh + head0 + h) * HD + 8 * t;
+        const bf16* qb = q + ((size_t)(t0 + q0 + rb) * nh + head0 + h) * HD + 8 * t;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            qf[h][c] = *reinterpret_cast<const uint4*>(qa + 32 * c);
+            qg[h][c] = *reinterpret_cast<const uint4*>(qb + 32 * c);
+        }
+        m[h][0] = m[h][1] = -INFINITY;
+        l[h][0] = l[h][1] = 0.f;
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) o[h][j][0] = o[h][j][1] = o[h][j][2] = o[h][j][3] = 0.f;
+    }
+    KVFrag<HD> cur, nxt;
+    load_block<HD>(cur, k_pages, v_pages, bt, first_block, page_size, nkv, kvh, g, t);
+    for (int b = first_block; b <= last_block; ++b) {
+        const bool more = b < last_block;
+        if (more) load_block<HD>(nxt, k_pages, v_pages, bt, b + 1, page_size, nkv, kvh, g, t);
+        // a block needs masking if some row cannot see its last key, or a window cuts into it
+        const bool need_mask = (b * 16 + 15 > pos_first) || (window > 0 && b * 16 < max(lo_a, lo_b));
+#pragma unroll
+        for (int h = 0; h < HPW; ++h)
+            attend_block<HD>(cur, qf[h], qg[h], o[h], m[h], l[h], b * 16, t, pos_a, pos_b, lo_a, lo_b, scale_log2,
+                             need_mask);
+        if (more) cur = nxt;
+    }
+#pragma unroll
+    for (int h = 0; h < HPW; ++h) {
+        const float la = quad_sum(l[h][0]), lb = quad_sum(l[h][1]);
+        const float ia = 1.f / la, ib = 1.f / lb;
+        bf16* oa = out + ((size_t)(t0 + q0 + g) * nh + head0 + h) * HD + 2 * t;
+        bf16* ob = out + ((size_t)(t0 + q0 + g + 8) * nh + head0 + h) * HD + 2 * t;
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) {
+            if (g < rows)
+                *reinterpret_cast<__nv_bfloat162*>(oa + 8 * j) = __floats2bfloat162_rn(o[h][j][0] * ia, o[h][j][1] * ia);
+            if (g + 8 < rows)
+                *reinterpret_cast<__nv_bfloat162*>(ob + 8 * j) = __floats2bfloat162_rn(o[h][j][2] * ib, o[h][j][3] * ib);
+        }
+    }
+}
+
+// ---- launchers -------------------------------------------------------------------------------------
+GESSO_API int gesso_attention_tc_takes(int hd, int page_size, int nh, int nkv) {
+    if (!(hd == 32 || hd == 64 || hd == 96 || hd == 128)) return 0;
+    if (page_size <= 0 || page_size % 16 != 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0) return 0;
+    return 1;
+}
+
+// Workspace sizes (in elements) of the split-KV kernel for `segs` single-token requests.
+GESSO_API long long gesso_decode_attention_workspace(int segs, int nh, int nkv, int hd, int n_splits,
+                                                     long long* part_ml_floats, long long* ticket_ints) {
+    *part_ml_floats = (long long)segs * nh * n_splits * 2;
+    *ticket_ints = (long long)segs * nkv;
+    return (long long)segs * nh * n_splits * hd;
+}
+
+GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const void* v_pages,
+                                     const int* block_table, int max_pages, int page_size, const int* positions,
+                                     const int* seg_start, void* out, int n_segs, int nh, int nkv, int hd,
+                                     int window, float scale, int n_splits, float* part_o, float* part_ml,
+                                     int* tickets, cudaStream_t stream) {
+    if (n_segs <= 0) return 0;
+    if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
+    const int G = nh / nkv;
+    if (G > 16 || n_splits < 1 || n_splits > 65535 || n_segs > 65535 || nkv > 65535) return GESSO_ERR_BAD_SIZE;
+    if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return GESSO_ERR_BAD_SIZE;
+    dim3 grid(n_splits, nkv, n_segs);
+    const size_t smem = (size_t)4 * 16 * (hd + 2) * sizeof(float);
+    const float scale_log2 = scale * LOG2E;
+#define GO(HD)                                                                                              \
+    do {                                                                                                    \
+        if (smem > 48 * 1024)                                                                               \
+            cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                 (int)smem);                                                                \
+        decode_attention_kernel<HD><<<grid, 128, smem, stream>>>(                                           \
+            (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,  \
+            positions, seg_start, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml,       \
+            tickets);                                                                                       \
+    } while (0)
+    if (hd == 32) GO(32);
+    else if (hd == 64) GO(64);
+    else if (hd == 96) GO(96);
+    else GO(128);
+#undef GO
+    return launch_status();
+}
+
+GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const void* v_pages,
+                                      const int* block_table, int max_pages, int page_size, const int* seg_start,
+                                      const int* seg_pos0, const int* tile_seg, const int* tile_q0, int n_tiles,
+                                      void* out, int nh, int nkv, int hd, int window, float scale,
+                                      cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
+    const int G = nh / nkv;
+    if (nkv > 65535) return GESSO_ERR_BAD_SIZE;
+    const float scale_log2 = scale * LOG2E;
+#define GO(HD, HPW)                                                                                          \
+    prefill_attention_kernel<HD, HPW><<<dim3(n_tiles, nkv, G / HPW), 128, 0, stream>>>(                      \
+        (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,       \
+        seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, window, scale_log2)
+    if (hd <= 64 && G % 2 == 0) {
+        if (hd == 32) GO(32, 2); else GO(64, 2);
+    } else {
+        if (hd == 32) GO(32, 1); else if (hd == 64) GO(64, 1); else if (hd == 96) GO(96, 1); else GO(128, 1);
+    }
+#undef GO
+    return launch_status();
+}

@@ -8,7 +8,8 @@
 //   x_i' = x_i cos - x_{i+hd/2} sin,   x_{i+hd/2}' = x_i sin + x_{i+hd/2} cos.
 // cos/sin come from a float32 table [max_positions, hd/2] that the host fills from float64
 // angles, so the angle itself never loses precision at large positions.  The cache holds the
-// normed, rotated K and the raw V (src/Inference/Inference.jl:2417-2421).
+// normed, rotated K and the raw V (src/Inference/Inference.jl:2417-2421).  Page layouts:
+// K [page][kv head][slot][feature], V [page][kv head][feature][slot].
 //
 // One warp per (token, head).  Everything is float32 inside; stores round to the run type.
 #include "common.cuh"
@@ -41,12 +42,14 @@ __global__ void qk_norm_rope_store_kernel(
             if (lane == 0) atomicExch(status, 1);
             return;
         }
-        T* base = is_k ? k_pages : v_pages;
-        dst = base + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd;
-    }
-    if (!is_q && !is_k) {   // v: copy
-        for (int j = lane; j < hd; j += 32) dst[j] = src[j];
-        return;
+        if (!is_k) {
+            // v is stored transposed inside its page, [head size][page size], so that the attention
+            // kernels read the values of consecutive keys of one feature as one contiguous piece
+            T* vt = v_pages + ((size_t)page * nkv + kvh) * hd * page_size + (pos % page_size);
+            for (int j = lane; j < hd; j += 32) vt[(size_t)j * page_size] = src[j];
+            return;
+        }
+        dst = k_pages + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd;
     }
     const float* w = is_q ? q_w : k_w;
     float ss = 0.f;

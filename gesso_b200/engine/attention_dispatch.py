@@ -1,9 +1,9 @@
 """Which attention kernel a step's queries run on.
 
-float32 runs always take the FP32 kernel.  bfloat16 runs take the tensor-core kernels
-when the head size fits them (a multiple of 16 up to 128): the flash prefill kernel for steps
-with portions, the split-KV kernel for steps of single tokens; other head sizes take the FP32
-arithmetic kernel on bfloat16 data.  Every branch is one of this library's own kernels.
+float32 runs always take the FP32-arithmetic kernel.  bfloat16 runs take the tensor-core kernels
+when the sizes fit them (head 32/64/96/128, pages in multiples of 16 slots): the split-KV kernel
+for steps of single tokens, the flash kernel for steps with portions; other sizes take the
+FP32-arithmetic kernel on bfloat16 data.  Every branch is one of this library's own kernels.
 """
 from __future__ import annotations
 
@@ -13,8 +13,24 @@ from .. import ops
 
 
 def paged_attention(rt, q, cache, ctx, window, scale):
-    fast = getattr(ops, "paged_attention_fast", None)
-    if fast is not None and q.dtype == torch.bfloat16 and ops.fast_attention_takes(q.shape[2]):
-        return fast(q, cache.k_pages, cache.v_pages, cache.block_table, ctx, window, scale)
+    N, nh, hd = q.shape
+    nkv, page_size = cache.k_pages.shape[1], cache.k_pages.shape[2]
+    if q.dtype == torch.bfloat16 and ops.fast_attention_takes(hd, page_size, nh, nkv):
+        if ctx.decode_only:
+            splits = ops.decode_splits(ctx.n_segs, nkv, ctx.max_kv_len)
+            ws = None
+            if splits > 1:
+                key = ("decode_attention_workspace", ctx.n_segs, nh, nkv, hd, splits)
+                ws = rt.shared.get(key)
+                if ws is None:
+                    dev = q.device
+                    ws = (torch.empty((ctx.n_segs * nh * splits * hd,), dtype=torch.float32, device=dev),
+                          torch.empty((ctx.n_segs * nh * splits * 2,), dtype=torch.float32, device=dev),
+                          torch.zeros((ctx.n_segs * nkv,), dtype=torch.int32, device=dev))
+                    rt.shared[key] = ws
+            return ops.decode_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
+                                        ctx.seg_start, window, scale, splits, ws)
+        return ops.prefill_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
+                                     ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale)
     return ops.paged_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table,
                                        ctx.positions, ctx.seg_of_token, window, scale)

@@ -7,7 +7,10 @@ description (:class:`StepContext`) is built on the host into one pinned int32 bu
 copied with a single transfer:
 
 ``token_ids[N]  positions[N]  seg_of_token[N]  seg_start[S+1]  seg_pos0[S]  slots[S]
-logit_rows[R]  block_table[g][S][max_pages] for each paged group g``
+logit_rows[R]  tile_seg[NT]  tile_q0[NT]  block_table[g][S][max_pages] for each paged group g``
+
+(``tile_*`` list the 64-token query tiles of the step for the prefill attention kernel; a tile never
+crosses a request)
 
 (the reference's only per-pass metadata is the position vector,
 src/Inference/Inference.jl:2322-2323, because it runs one sequence at a time).
@@ -21,6 +24,13 @@ import numpy as np
 import torch
 
 from ..cache.manager import FREED
+
+
+QUERY_TILE = 64   # tokens per query tile of the prefill attention kernel
+
+
+def count_tiles(lengths) -> int:
+    return sum((n + QUERY_TILE - 1) // QUERY_TILE for n in lengths)
 
 
 @dataclass
@@ -39,12 +49,14 @@ class StepLayout:
     n_rows: int
     n_groups: int
     max_pages: int
+    n_tiles: int = 0
 
     def offsets(self) -> Dict[str, int]:
         N, S, R = self.n_tokens, self.n_segs, self.n_rows
         o, cur = {}, 0
         for name, size in (("token_ids", N), ("positions", N), ("seg_of_token", N),
-                           ("seg_start", S + 1), ("seg_pos0", S), ("slots", S), ("logit_rows", R)):
+                           ("seg_start", S + 1), ("seg_pos0", S), ("slots", S), ("logit_rows", R),
+                           ("tile_seg", self.n_tiles), ("tile_q0", self.n_tiles)):
             o[name] = cur
             cur += size
         for g in range(self.n_groups):
@@ -74,6 +86,9 @@ class StepContext:
         self.seg_pos0 = buf[o["seg_pos0"]:o["seg_pos0"] + S]
         self.slots = buf[o["slots"]:o["slots"] + S]
         self.logit_rows = buf[o["logit_rows"]:o["logit_rows"] + R]
+        self.n_tiles = layout.n_tiles
+        self.tile_seg = buf[o["tile_seg"]:o["tile_seg"] + layout.n_tiles]
+        self.tile_q0 = buf[o["tile_q0"]:o["tile_q0"] + layout.n_tiles]
         self.block_tables = [
             buf[o[f"block_table{g}"]:o[f"block_table{g}"] + S * layout.max_pages].view(S, layout.max_pages)
             for g in range(layout.n_groups)]
@@ -94,9 +109,15 @@ def pack_step(entries: List[StepEntry], starts: List[int], slots: List[int],
     seg = out[o["seg_of_token"]:o["seg_of_token"] + N]
     seg_start = out[o["seg_start"]:o["seg_start"] + layout.n_segs + 1]
     rows = out[o["logit_rows"]:o["logit_rows"] + layout.n_rows]
-    cur, r = 0, 0
+    tile_seg = out[o["tile_seg"]:o["tile_seg"] + layout.n_tiles]
+    tile_q0 = out[o["tile_q0"]:o["tile_q0"] + layout.n_tiles]
+    cur, r, nt = 0, 0, 0
     for i, e in enumerate(entries):
         n = len(e.tokens)
+        for q0 in range(0, n, QUERY_TILE):
+            tile_seg[nt] = i
+            tile_q0[nt] = q0
+            nt += 1
         tok[cur:cur + n] = np.asarray(e.tokens, dtype=np.int32)
         pos[cur:cur + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
         seg[cur:cur + n] = i

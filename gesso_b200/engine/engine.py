@@ -22,7 +22,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..csrc.lib import launch_count
 from ..errors import ErrorCode, GessoError, invalid, resource
-from .batch import StepContext, StepEntry, StepLayout, pack_step
+from .batch import StepContext, StepEntry, StepLayout, count_tiles, pack_step
 from .model import Model, PagedView, StateView
 
 
@@ -73,7 +73,7 @@ class Engine:
         self.tokens_run = 0
         self.launches = 0            # kernels of this library launched by steps (graph nodes included)
         self.h2d_bytes = 0           # metadata bytes copied to the device by steps
-        self.use_graphs = use_graphs
+        self.use_graphs = use_graphs and getattr(model, "graph_safe", True)
         self.max_graph_batch = 256
         self._graphs: Dict = {}
         self._graph_pool = None
@@ -153,7 +153,8 @@ class Engine:
         tables = [[self.cache.block_table(e.req_id, g) for e in entries] for g in range(n_groups)]
         layout = StepLayout(n_tokens=sum(len(e.tokens) for e in entries), n_segs=len(entries),
                             n_rows=sum(len(e.want) for e in entries), n_groups=n_groups,
-                            max_pages=self.cache.max_pages_per_request)
+                            max_pages=self.cache.max_pages_per_request,
+                            n_tiles=count_tiles(len(e.tokens) for e in entries))
         size = layout.offsets()["_end"]
         slot_i, host = self._pinned_buffer(size)
         pack_step(list(entries), starts, slots, tables, layout, host.numpy()[:size])
@@ -181,7 +182,10 @@ class Engine:
         for e, p in enumerate(plan.entries):
             if p.kind == "paged":
                 kv = dc.kv[p.group][p.index]
-                out.append(PagedView(kv[0], kv[1], ctx.block_tables[p.group], writes=(p.owner == e)))
+                # K pages are [page, kv head, slot, feature]; V pages hold the same bytes as
+                # [page, kv head, feature, slot]
+                v = kv[1].view(kv.shape[1], kv.shape[2], kv.shape[4], kv.shape[3])
+                out.append(PagedView(kv[0], v, ctx.block_tables[p.group], writes=(p.owner == e)))
             elif p.kind == "state":
                 out.append(StateView(dc.state[p.index], ctx.slots, writes=(p.owner == e)))
             else:

@@ -132,6 +132,8 @@ class Model:
         self.embedding = dev["embedding.weight"]
         self.lm_head = self.embedding if spec.tie_embedding else dev["lm_head.weight"]
         self.cache_plan = CachePlan(spec, self.blocks)
+        self.graph_safe = all(getattr(part, "graph_safe", True) for blk in self.blocks
+                              for _, part in getattr(blk, "parts", lambda: [])())
         self.param_bytes = sum(t.numel() * t.element_size() for t in dev.values())
 
     @property

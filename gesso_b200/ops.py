@@ -19,6 +19,10 @@ from .errors import ErrorCode, GessoError
 
 F32, BF16 = 0, 1
 
+# The library matrix product accumulates in float32 from start to end: no bfloat16 intermediate sums
+# (split-K partials rounded to 16 bits cost about a digit of accuracy).
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 
 def _dt(t: torch.Tensor) -> int:
     if t.dtype == torch.float32:
@@ -136,7 +140,9 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
     _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype, "cache pages must have the run dtype")
     _need(k_pages.is_contiguous() and v_pages.is_contiguous(), "cache pages must be contiguous")
     _need(k_pages.dim() == 4 and k_pages.shape[1] == nkv and k_pages.shape[3] == hd,
-          "cache pages must be [pages, kv heads, page size, head size]")
+          "K pages must be [pages, kv heads, page size, head size]")
+    _need(tuple(v_pages.shape) == (k_pages.shape[0], nkv, hd, k_pages.shape[2]),
+          "V pages must be [pages, kv heads, head size, page size]")
     page_size = k_pages.shape[2]
     _cuda_contig(block_table, "block_table", torch.int32)
     _cuda_contig(positions, "positions", torch.int32)
@@ -233,3 +239,70 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
     _lib.check(_lib.library().gesso_sample_rows(_p(logits), R, V, _p(temperature), _p(top_p), _p(u),
                                                 _p(ids), _p(bad), _stream()), "sample_rows")
     return ids, bad
+
+
+# ---- tensor-core attention (bfloat16) ------------------------------------------------------------
+_lib.declare("gesso_attention_tc_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
+_lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
+                                        _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P, _lib.P,
+                                        _lib.P, _lib.P])
+_lib.declare("gesso_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
+                                         _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.P])
+
+SM_COUNT = 148   # B200
+
+
+def fast_attention_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
+    """Sizes the tensor-core attention kernels take: head 32/64/96/128, pages in multiples of 16
+    slots, at most 16 query heads per kv head for single-token steps."""
+    return bool(_lib.library().gesso_attention_tc_takes(hd, page_size, nh, nkv)) and nh // nkv <= 16
+
+
+def decode_splits(n_segs: int, nkv: int, max_kv_len: int) -> int:
+    """How many ways the keys of a request are split so that about two blocks per SM are busy."""
+    blocks = (max_kv_len + 15) // 16
+    want = (2 * SM_COUNT + n_segs * nkv - 1) // (n_segs * nkv)
+    return max(1, min(want, (blocks + 3) // 4))
+
+
+def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     block_table: torch.Tensor, positions: torch.Tensor, seg_start: torch.Tensor,
+                     window: Optional[int], scale: float, n_splits: int,
+                     workspace=None) -> torch.Tensor:
+    """Split-KV attention for a step of single tokens.  ``workspace`` = (part_o, part_ml, tickets) of
+    sizes [segs*nh*splits*hd], [segs*nh*splits*2] float32 and [segs*nkv] int32 (zeroed once)."""
+    _cuda_contig(q, "q", torch.bfloat16)
+    S, nh, hd = q.shape
+    nkv, page_size = k_pages.shape[1], k_pages.shape[2]
+    _need(k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16, "cache pages must be bfloat16")
+    out = torch.empty((S, nh * hd), dtype=q.dtype, device=q.device)
+    if n_splits > 1:
+        if workspace is None:
+            workspace = (torch.empty((S * nh * n_splits * hd,), dtype=torch.float32, device=q.device),
+                         torch.empty((S * nh * n_splits * 2,), dtype=torch.float32, device=q.device),
+                         torch.zeros((S * nkv,), dtype=torch.int32, device=q.device))
+        part_o, part_ml, tickets = workspace
+        _need(part_o.numel() >= S * nh * n_splits * hd and part_ml.numel() >= S * nh * n_splits * 2
+              and tickets.numel() >= S * nkv, "split-KV workspace is too small")
+    else:
+        part_o = part_ml = tickets = None
+    _lib.check(_lib.library().gesso_decode_attention(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(positions),
+        _p(seg_start), _p(out), S, nh, nkv, hd, int(window or 0), float(scale), int(n_splits), _p(part_o),
+        _p(part_ml), _p(tickets), _stream()), "decode_attention")
+    return out
+
+
+def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      block_table: torch.Tensor, seg_start: torch.Tensor, seg_pos0: torch.Tensor,
+                      tile_seg: torch.Tensor, tile_q0: torch.Tensor, window: Optional[int],
+                      scale: float) -> torch.Tensor:
+    _cuda_contig(q, "q", torch.bfloat16)
+    N, nh, hd = q.shape
+    nkv, page_size = k_pages.shape[1], k_pages.shape[2]
+    out = torch.empty((N, nh * hd), dtype=q.dtype, device=q.device)
+    _lib.check(_lib.library().gesso_prefill_attention(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(seg_start),
+        _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), _p(out), nh, nkv, hd, int(window or 0),
+        float(scale), _stream()), "prefill_attention")
+    return out

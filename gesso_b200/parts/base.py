@@ -68,6 +68,10 @@ class StateNeed:
 class Part:
     """Base of all parts: declares tensors, is bound once."""
 
+    # False if the part's forward synchronises with the host or launches work whose shape depends
+    # on the step's contents; the engine then runs decoding steps eagerly instead of as a CUDA graph.
+    graph_safe = True
+
     def __init__(self, spec):
         self.spec = spec
 

@@ -1,0 +1,277 @@
+"""Generation through the Python entry point and the command line, long decoding, the first tokens of
+a sequence, and weights made so that cache faults would show."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import configs
+
+pytestmark = pytest.mark.gpu
+
+TOL32 = 1e-4
+TOL16 = 32 * 2.0 ** -9
+
+
+@pytest.fixture(scope="module")
+def models(model_dirs):
+    import gesso_b200
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            cache[(name, dtype)] = gesso_b200.load(model_dirs[name], dtype=dtype, max_positions=512)
+        return cache[(name, dtype)]
+    return get
+
+
+def prompts_for(name, lengths, seed=0):
+    vocab = configs.TINY[name][0]["vocab_size"]
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+
+
+# ---- greedy generation ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_greedy_generate_equals_plain_float32(name, models, plain_models):
+    import gesso_b200
+    model = models(name, "float32")
+    s = gesso_b200.Session(model, context_length=128, page_size=16, max_batch=4)
+    for p in prompts_for(name, [7, 13, 1, 30]):
+        got = s.generate(p, max_new_tokens=8)
+        assert got == plain_models[name].greedy(p, 8)
+        assert got[:len(p)] == p and len(got) == len(p) + 8
+    assert s.generate([3, 4], max_new_tokens=0) == [3, 4]          # test/test_reference_generate.jl:24-28
+    assert s.engine.cache.pages_in_use() == [0] and s.engine.cache.slots_in_use() == 0
+
+
+def near_max(plain, ids, n_prompt, tol):
+    """Every generated id is a maximum of the plain logits up to the tolerance of the run type."""
+    lg = plain.logits(ids[:-1])
+    for k in range(n_prompt, len(ids)):
+        row = lg[k - 1]
+        assert float(row.max() - row[ids[k]]) <= tol * max(1.0, float(row.abs().max())), (k, ids[k])
+
+
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_greedy_generate_bfloat16(name, models, plain_models):
+    import gesso_b200
+    s = gesso_b200.Session(models(name, "bfloat16"), context_length=128, max_batch=4)
+    for p in prompts_for(name, [7, 40, 1]):
+        ids = s.generate(p, max_new_tokens=12)
+        near_max(plain_models[name], ids, len(p), TOL16)
+
+
+def test_batch_equals_solo_and_is_deterministic(models, plain_models):
+    """Continuous batching with chunked prefill does not change anybody's tokens (greedy and sampled)."""
+    import gesso_b200
+    model = models("b", "float32")
+    prompts = prompts_for("b", [40, 1, 23, 5, 17], seed=3)
+    s = gesso_b200.Session(model, context_length=128, max_batch=3, max_tokens_per_step=24, prefill_chunk=8)
+    reqs = [gesso_b200.BatchRequest(p, max_new_tokens=9, temperature=0.7 if i % 2 else 0.0, top_p=0.9, seed=1 + i)
+            for i, p in enumerate(prompts)]
+    res = s.run_batch(reqs)
+    assert [r.status for r in res] == ["complete"] * 5
+    solo = gesso_b200.Session(model, context_length=128, max_batch=1)
+    for i, (p, r) in enumerate(zip(prompts, res)):
+        assert r.ids == solo.generate(p, 9, temperature=0.7 if i % 2 else 0.0, top_p=0.9, seed=1 + i)
+        if i % 2 == 0:
+            assert r.ids == plain_models["b"].greedy(p, 9)
+    assert [r.ids for r in s.run_batch(reqs)] == [r.ids for r in res]        # same seeds, same ids
+    assert s.stats()["pages_in_use"] == [0]
+
+
+def test_sampled_ids_follow_the_plain_sampler(models, plain_models):
+    import gesso_b200
+    from plain_lfm2 import PlainSampler
+    model = models("a", "float32")
+    s = gesso_b200.Session(model, context_length=64, max_batch=1)
+    p = prompts_for("a", [9], seed=5)[0]
+    got = s.generate(p, 6, temperature=0.8, top_p=0.95, seed=42)
+    sampler, ids = PlainSampler(0.8, 0.95, 42), list(p)
+    for _ in range(6):
+        ids.append(sampler.sample(plain_models["a"].logits(ids)[-1].tolist()))
+    assert got == ids
+
+
+def test_stops_hooks_and_failures(models):
+    import gesso_b200
+    model = models("a", "float32")
+    s = gesso_b200.Session(model, context_length=64, max_batch=4)
+    p = [5, 6, 7]
+    full = s.generate(p, 6)
+    assert s.generate(p, 6, stop_ids=[full[4]]) == full[:5]                 # the stopping id is returned
+    assert s.generate(p, 6, eos_ids=[full[3]]) == full[:4]
+    seen = []
+    assert s.generate(p, 6, on_token=lambda t: (seen.append(t), len(seen) < 3)[1]) == full[:6]
+    assert seen == full[3:6]                                                # test/test_generate_hooks.jl:41-81
+
+    def boom(t):
+        raise RuntimeError("hook")
+    res = s.run_batch([gesso_b200.BatchRequest(p, 4, on_token=boom), gesso_b200.BatchRequest(p, 4),
+                       gesso_b200.BatchRequest([], 4), gesso_b200.BatchRequest([9999], 4)])
+    assert [r.status for r in res] == ["failed", "complete", "failed", "failed"]
+    assert res[1].ids == full[:7] and res[0].error.code == gesso_b200.ErrorCode.RUNTIME
+    with pytest.raises(gesso_b200.GessoError):
+        s.generate([1] * 65, 1)                                             # longer than the context
+    assert s.engine.cache.pages_in_use() == [0]
+
+
+def test_pages_run_out_preemption_keeps_the_tokens(models, plain_models):
+    """A pool too small for everybody: requests are preempted and recomputed, ids do not change."""
+    import gesso_b200
+    model = models("a", "float32")
+    prompts = prompts_for("a", [30, 28, 25, 20], seed=8)
+    s = gesso_b200.Session(model, context_length=64, page_size=16, num_pages=7, max_batch=4, prefill_chunk=16)
+    res = s.run_batch([gesso_b200.BatchRequest(p, max_new_tokens=30) for p in prompts])
+    assert s.stats()["preemptions"] >= 1
+    for p, r in zip(prompts, res):
+        assert r.status == "complete" and r.ids == plain_models["a"].greedy(p, 30)
+
+
+# ---- prefill / decode of a Session ----------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL32), ("bfloat16", TOL16)])
+def test_session_prefill_decode(dtype, tol, models, plain_models):
+    import gesso_b200
+    s = gesso_b200.Session(models("b", dtype), context_length=128, page_size=16)
+    p = prompts_for("b", [21], seed=9)[0]
+    logits = s.prefill(p)
+    ref = plain_models["b"].logits(p).numpy()
+    assert logits.shape == ref.shape and np.abs(logits - ref).max() <= tol * max(1, np.abs(ref).max())
+    assert s.kv_len == len(p)
+    ids = list(p)
+    for step in range(5):
+        tok = s.decode()
+        ids.append(tok)
+        assert s.kv_len == len(p) + step + 1                                # test/test_reference_generate.jl:39-46
+    if dtype == "float32":
+        assert ids == plain_models["b"].greedy(p, 5)
+    with pytest.raises(gesso_b200.GessoError):
+        gesso_b200.Session(models("b", dtype), context_length=128).decode()  # nothing prefilled
+
+
+# ---- long decoding, first tokens ----------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL32), ("bfloat16", TOL16)])
+def test_long_decoding_token_by_token(dtype, tol, models, plain_models):
+    """300 tokens, all but the first fed one by one (CUDA-graph steps), across many pages."""
+    from gesso_b200.engine import Engine, StepEntry
+    model = models("c", dtype)
+    ids = prompts_for("c", [300], seed=4)[0]
+    ref = plain_models["c"].logits(ids).numpy()
+    eng = Engine(model, max_positions=320, page_size=16, num_pages=20, max_requests=1)
+    eng.admit("r")
+    scale = max(1.0, float(np.abs(ref).max()))
+    for t, tok in enumerate(ids):
+        row = eng.step([StepEntry("r", [tok], [0])])[0].cpu().numpy()
+        err = float(np.abs(row - ref[t]).max())
+        assert err <= tol * scale, f"position {t}: {err:.3e}"
+    eng.check_status()
+
+
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_first_tokens_of_a_sequence(name, models, plain_models):
+    """Prompts of 1, 2, 3 tokens, whole and token by token: the conv history is shorter than its
+    kernel and the cache holds a single partly filled page."""
+    from gesso_b200.engine import Engine, StepEntry
+    model = models(name, "float32")
+    for n in (1, 2, 3, 4):
+        ids = prompts_for(name, [n], seed=20 + n)[0]
+        ref = plain_models[name].logits(ids).numpy()
+        for cuts in ([n], [1] * n):
+            eng = Engine(model, max_positions=16, page_size=16, num_pages=1, max_requests=1)
+            eng.admit("r")
+            rows, p = [], 0
+            for c in cuts:
+                rows.append(eng.step([StepEntry("r", ids[p:p + c], list(range(c)))]).cpu().numpy().copy())
+                p += c
+            assert np.abs(np.concatenate(rows) - ref).max() <= TOL32 * max(1, np.abs(ref).max())
+
+
+# ---- weights made so that faults show ----------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def sharp_model_dir(model_dirs, tmp_path_factory):
+    """Model 'a' with its q/k norm weights scaled by 4: attention scores spread over +-16, so single
+    keys dominate and a wrong key, page or position changes the logits by far more than rounding."""
+    from gesso_b200.weights import read_safetensors_file, write_safetensors_file
+    d = str(tmp_path_factory.mktemp("model_a_sharp"))
+    t = read_safetensors_file(os.path.join(model_dirs["a"], "model.safetensors"))
+    for k in t:
+        if k.endswith("q_layernorm.weight"):
+            t[k] = t[k] * 4.0
+    write_safetensors_file(os.path.join(d, "model.safetensors"), t)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(configs.TINY_A, f)
+    return d
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL32), ("bfloat16", 2 * TOL16)])
+def test_sharp_attention_far_keys_and_page_edges(dtype, tol, sharp_model_dir):
+    """A 400-token request decoded across page edges beside another request whose pages were used before."""
+    import gesso_b200
+    from gesso_b200.engine import Engine, StepEntry
+    from plain_lfm2 import PlainModel
+    plain = PlainModel(sharp_model_dir)
+    model = gesso_b200.load(sharp_model_dir, dtype=dtype, max_positions=512)
+    g = torch.Generator().manual_seed(77)
+    a = torch.randint(0, 256, (400,), generator=g).tolist()
+    b = torch.randint(0, 256, (90,), generator=g).tolist()
+    ref_a, ref_b = plain.logits(a).numpy(), plain.logits(b).numpy()
+    # the plain attention is sharp: the largest probability of the last rows is well above uniform
+    eng = Engine(model, max_positions=512, page_size=16, num_pages=32, max_requests=2)
+    eng.admit("old")
+    eng.step([StepEntry("old", b[:70], [])])          # fills pages that "b" will get again
+    eng.release("old")
+    eng.admit("a")
+    eng.admit("b")
+    got_a = [eng.step([StepEntry("a", a[:250], list(range(250)))]).cpu().numpy().copy()]
+    pa, pb = 250, 0
+    got_b = []
+    while pa < len(a) or pb < len(b):
+        entries = []
+        if pa < len(a):
+            n = 1 if pa >= 300 else min(31, len(a) - pa)
+            entries.append(StepEntry("a", a[pa:pa + n], list(range(n))))
+        if pb < len(b):
+            m = min(7, len(b) - pb) if pb < 60 else 1
+            entries.append(StepEntry("b", b[pb:pb + m], list(range(m))))
+        out = eng.step(entries).cpu().numpy().copy()
+        if pa < len(a):
+            got_a.append(out[:n])
+            out = out[n:]
+            pa += n
+        if pb < len(b):
+            got_b.append(out)
+            pb += m
+    for got, ref, what in ((np.concatenate(got_a), ref_a, "a"), (np.concatenate(got_b), ref_b, "b")):
+        err = np.abs(got - ref).max(axis=1)
+        bad = np.nonzero(err > tol * max(1, np.abs(ref).max()))[0]
+        assert bad.size == 0, f"request {what}: first wrong position {bad[0]} (error {err[bad[0]]:.3e})"
+    eng.check_status()
+
+
+# ---- the command line ---------------------------------------------------------------------------------
+def test_command_line(model_dirs, plain_models, tmp_path):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root)
+    p = subprocess.run([sys.executable, "-m", "gesso_b200", "generate", "--model", model_dirs["a"], "--dtype", "float32",
+                        "--prompt-ids", "5,6,7", "--prompt-ids", "9 8", "--max-new-tokens", "4", "--n-ctx", "64"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-1500:]
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
+    assert [l["ids"] for l in lines] == [plain_models["a"].greedy([5, 6, 7], 4), plain_models["a"].greedy([9, 8], 4)]
+    bad = subprocess.run([sys.executable, "-m", "gesso_b200", "generate", "--model", model_dirs["a"], "--no-such-flag"],
+                         capture_output=True, text=True, env=env, timeout=120)
+    assert bad.returncode == 2 and "usage" in bad.stderr.lower()
+    # random-weights mode writes a model folder that loads
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(configs.TINY_C))
+    out = tmp_path / "m"
+    r = subprocess.run([sys.executable, "-m", "gesso_b200", "init-random", "--config", str(cfg), "--seed", "3", "--out", str(out)],
+                       capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and sorted(os.listdir(out)) == ["config.json", "model.safetensors"]
+    d = subprocess.run([sys.executable, "-m", "gesso_b200", "describe", "--model", str(out)], capture_output=True, text=True, env=env)
+    assert d.returncode == 0 and "short_conv" in d.stdout

@@ -1,0 +1,396 @@
+"""Each kernel alone against a plain PyTorch float32/float64 reference of the same operation, at
+sizes other than the engine's (ragged widths, odd vocabularies, several head sizes)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+BF16_EPS = 2.0 ** -8          # spacing of bfloat16 relative to the value (one rounding is half of it)
+
+
+def rel_err(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).abs().max() / max(1e-30, float(b.abs().max())))
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+# ---- embedding, norms ------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H", [48, 1000, 2048])
+def test_embed_and_add_rmsnorm(dtype, H):
+    from gesso_b200 import ops
+    g = torch.Generator().manual_seed(H)
+    V, N = 301, 37
+    table = torch.randn(V, H, generator=g).to(dtype).to(DEV)
+    toks = torch.randint(0, V, (N,), generator=g)
+    h = ops.embed_gather(i32(toks.tolist()), table, 1.0)
+    assert torch.equal(h.cpu(), table.float().cpu()[toks])
+    delta = torch.randn(N, H, generator=g).to(dtype).to(DEV)
+    bias = torch.randn(H, generator=g).to(DEV)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(DEV)
+    h0 = h.clone()
+    out = ops.add_rmsnorm(h, delta, bias, w, 1e-5, dtype)
+    want_h = h0.double() + delta.double() + bias.double()
+    assert rel_err(h, want_h) < 1e-6
+    want = P.rmsnorm(want_h.cpu(), w.double().cpu(), 1e-5)
+    assert rel_err(out, want) < (2e-6 if dtype == torch.float32 else BF16_EPS)
+    # row selection: only the chosen rows, h untouched
+    rows = i32([5, 0, 36])
+    h1 = h.clone()
+    sel = ops.add_rmsnorm(h, delta, None, w, 1e-6, torch.float32, rows=rows)
+    assert torch.equal(h, h1)
+    want = P.rmsnorm((h1.double() + delta.double()).cpu()[[5, 0, 36]], w.double().cpu(), 1e-6)
+    assert rel_err(sel, want) < 2e-6
+    # no delta: plain norm
+    out = ops.add_rmsnorm(h, None, None, w, 1e-5, torch.float32)
+    assert rel_err(out, P.rmsnorm(h1.double().cpu(), w.double().cpu(), 1e-5)) < 2e-6
+
+
+def test_rmsnorm_rows_per_head():
+    from gesso_b200 import ops
+    x = torch.randn(11, 5, 24, device=DEV)
+    w = torch.rand(24, device=DEV) + 0.5
+    assert rel_err(ops.rmsnorm_rows(x, w, 1e-6), P.rmsnorm(x.double().cpu(), w.double().cpu(), 1e-6)) < 2e-6
+
+
+# ---- matrix product, SwiGLU ---------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (7, 130, 33), (65, 64, 16), (200, 503, 96), (3, 2048, 700)])
+def test_gemm_f32_is_true_fp32(M, N, K):
+    from gesso_b200 import ops
+    a = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV)
+    got = ops.gemm_f32(a, w)
+    want = a.double() @ w.double().T
+    assert rel_err(got, want) < 1e-6        # TF32 would be ~1e-3
+    # rows do not depend on the batch they are in
+    if M > 2:
+        assert torch.equal(ops.gemm_f32(a[1:2].contiguous(), w), got[1:2])
+    # mixed operands: bfloat16 activations with a matrix that stays float32
+    ab = a.to(torch.bfloat16)
+    assert rel_err(ops.gemm_f32(ab, w), ab.double() @ w.double().T) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    from gesso_b200 import ops
+    gu = (3 * torch.randn(19, 2 * 77, device=DEV)).to(dtype)
+    g, u = gu[:, :77].double(), gu[:, 77:].double()
+    want = (g / (1 + torch.exp(-g))) * u
+    assert rel_err(ops.swiglu(gu), want) < (2e-6 if dtype == torch.float32 else BF16_EPS)
+
+
+def test_linear_bf16_and_fp32_logits():
+    from gesso_b200 import ops
+    x = torch.randn(9, 160, device=DEV).to(torch.bfloat16)
+    w = torch.randn(333, 160, device=DEV).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    assert rel_err(ops.linear(x, w, out_dtype=torch.float32), want) < 1e-5
+    assert rel_err(ops.linear(x, w), want) < BF16_EPS
+
+
+# ---- short convolution -----------------------------------------------------------------------------
+def conv_reference(bcx, in_bias, taps, conv_bias):
+    b = bcx.double().cpu()
+    if in_bias is not None:
+        b = b + in_bias.double().cpu()
+    return P.short_conv_fir(b, taps.double().cpu(), None if conv_bias is None else conv_bias.double().cpu())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,L,bias", [(1, 2, False), (13, 4, True), (200, 3, False), (333, 4, True)])
+def test_short_conv_carried_state(dtype, H, L, bias):
+    """A sequence fed in calls of 5, 1, 1, 4, 2, 30 tokens equals one call (the reference's device
+    parity test feeds (5, 1, 1, 4), test/test_lava_lfm25.jl:44-53); two requests share the batch and
+    a reused slot starts from zero."""
+    from gesso_b200 import ops
+    g = torch.Generator().manual_seed(H * 10 + L)
+    cuts = [5, 1, 1, 4, 2, 30]
+    T = sum(cuts)
+    taps = torch.randn(H, L, generator=g).to(DEV)
+    in_b = torch.randn(3 * H, generator=g).to(DEV) if bias else None
+    cv_b = torch.randn(H, generator=g).to(DEV) if bias else None
+    seqs = [torch.randn(T, 3 * H, generator=g).to(dtype).to(DEV) for _ in range(2)]
+    want = [conv_reference(s, in_b, taps, cv_b) for s in seqs]
+    state = torch.full((3, L - 1, H), 7.0, device=DEV)         # garbage: position 0 must ignore it
+    state[1].zero_()
+    state[2].zero_()
+    pos = 0
+    outs = [[], []]
+    for n in cuts:
+        # batch: request 0 (slot 2) and request 1 (slot 1), the second one token behind at first
+        bcx = torch.cat([seqs[0][pos:pos + n], seqs[1][pos:pos + n]])
+        out = ops.short_conv(bcx, in_b, taps, cv_b, state, i32([0] * n + [1] * n), i32([0, n, 2 * n]),
+                             i32([pos, pos]), i32([2, 1]), 2, n)
+        outs[0].append(out[:n])
+        outs[1].append(out[n:])
+        pos += n
+    tol = 2e-6 if dtype == torch.float32 else BF16_EPS
+    for k in range(2):
+        assert rel_err(torch.cat(outs[k]), want[k]) < tol
+    # slot 0 still holds garbage; a request starting there at position 0 must not read it
+    fresh = ops.short_conv(seqs[0][:9].contiguous(), in_b, taps, cv_b, state, i32([0] * 9), i32([0, 9]),
+                           i32([0]), i32([0]), 1, 9)
+    assert rel_err(fresh, want[0][:9]) < tol
+    # the two code paths (portion kernel + state update, and the short-portion kernel) leave the same state
+    st_a = torch.zeros((1, L - 1, H), device=DEV)
+    st_b = torch.zeros((1, L - 1, H), device=DEV)
+    ops.short_conv(seqs[0][:12].contiguous(), in_b, taps, cv_b, st_a, i32([0] * 12), i32([0, 12]), i32([0]), i32([0]), 1, 12)
+    for p in range(0, 12, 3):
+        ops.short_conv(seqs[0][p:p + 3].contiguous(), in_b, taps, cv_b, st_b, i32([0] * 3), i32([0, 3]), i32([p]),
+                       i32([0]), 1, 3)
+    assert torch.equal(st_a, st_b)
+
+
+def test_short_conv_tap_order_identity():
+    """All-ones B, C, X with taps [2, -1, 3] gives [3, 2, 4, 4] (the newest tap is on the current
+    token; test/test_lfm25.jl:79-90 without its norm factor); reversed taps give something else."""
+    from gesso_b200 import ops
+    bcx = torch.ones(4, 3, device=DEV)
+    state = torch.zeros(1, 2, 1, device=DEV)
+    out = ops.short_conv(bcx, None, torch.tensor([[2.0, -1.0, 3.0]], device=DEV), None, state, i32([0] * 4),
+                         i32([0, 4]), i32([0]), i32([0]), 1, 4)
+    assert out.flatten().tolist() == [3.0, 2.0, 4.0, 4.0]
+    state.zero_()
+    out = ops.short_conv(bcx, None, torch.tensor([[3.0, -1.0, 2.0]], device=DEV), None, state, i32([0] * 4),
+                         i32([0, 4]), i32([0]), i32([0]), 1, 4)
+    assert out.flatten().tolist() == [2.0, 1.0, 4.0, 4.0]
+
+
+def test_short_conv_nan_stays_in_its_channel():
+    from gesso_b200 import ops
+    bcx = torch.randn(6, 3 * 5, device=DEV)
+    bcx[2, 3] = float("nan")                     # B of channel 3
+    state = torch.zeros(1, 2, 5, device=DEV)
+    out = ops.short_conv(bcx, None, torch.randn(5, 3, device=DEV), None, state, i32([0] * 6), i32([0, 6]),
+                         i32([0]), i32([0]), 1, 6)
+    bad = torch.isnan(out).any(dim=0).cpu()
+    assert bad.tolist() == [False, False, False, True, False]
+
+
+# ---- q/k norm, rotation, cache write -------------------------------------------------------------------
+def build_cache(seqs_k, seqs_v, nkv, hd, page_size, dtype, shuffle_seed=0):
+    """Paged K [pages, nkv, slot, hd] and V [pages, nkv, hd, slot] holding the given sequences on
+    shuffled pages; returns (k_pages, v_pages, block_table)."""
+    n_pages = sum((len(k) + page_size - 1) // page_size for k in seqs_k) + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(shuffle_seed)).tolist()
+    kp = torch.randn(n_pages, nkv, page_size, hd).to(dtype)      # stale finite values on unused slots
+    vp = torch.randn(n_pages, nkv, hd, page_size).to(dtype)
+    max_pages = max((len(k) + page_size - 1) // page_size for k in seqs_k) + 1
+    bt = torch.full((len(seqs_k), max_pages), -1, dtype=torch.int32)
+    nxt = 0
+    for s, (k, v) in enumerate(zip(seqs_k, seqs_v)):
+        for p in range((len(k) + page_size - 1) // page_size):
+            page = perm[nxt]
+            nxt += 1
+            bt[s, p] = page
+            rows = slice(p * page_size, min(len(k), (p + 1) * page_size))
+            n = rows.stop - rows.start
+            kp[page, :, :n] = k[rows].to(dtype).transpose(0, 1)
+            vp[page, :, :, :n] = v[rows].to(dtype).permute(1, 2, 0)
+    return kp.to(DEV), vp.to(DEV), bt.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 16), (3, 1, 24, 8), (6, 3, 64, 16), (2, 2, 128, 32)])
+def test_qk_norm_rope_store(dtype, nh, nkv, hd, page):
+    from gesso_b200 import ops
+    from gesso_b200.parts.rope import rope_tables
+    g = torch.Generator().manual_seed(nh * 100 + hd)
+    lens, starts = [5, 1, 19], [0, 40, 7]              # three portions at different positions
+    N = sum(lens)
+    qkv = torch.randn(N, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    qw = torch.rand(hd, generator=g) + 0.5
+    kw = torch.rand(hd, generator=g) + 0.5
+    theta, eps = 12345.0, 1e-5
+    cos, sin = rope_tables(theta, hd, 64)
+    positions = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)])
+    seg = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)])
+    n_pages, max_pages = 16, (64 + page - 1) // page
+    bt = torch.full((3, max_pages), -1, dtype=torch.int32)
+    free = list(range(n_pages))[::-1]
+    for i, (s, n) in enumerate(zip(starts, lens)):
+        for p in range((s + n + page - 1) // page):
+            bt[i, p] = free.pop()
+    kp = torch.zeros(n_pages, nkv, page, hd, dtype=dtype, device=DEV)
+    vp = torch.zeros(n_pages, nkv, hd, page, dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q = ops.qk_norm_rope_store(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, cos.to(DEV), sin.to(DEV), i32(positions.tolist()),
+                               i32(seg.tolist()), bt.to(DEV), kp, vp, nh, nkv, hd, True, status)
+    x = qkv.double()
+    qr = P.rope(P.rmsnorm(x[:, :nh * hd].reshape(N, nh, hd), qw.double(), eps), positions.tolist(), theta)
+    kr = P.rope(P.rmsnorm(x[:, nh * hd:(nh + nkv) * hd].reshape(N, nkv, hd), kw.double(), eps), positions.tolist(), theta)
+    vr = x[:, (nh + nkv) * hd:].reshape(N, nkv, hd)
+    tol = 3e-6 if dtype == torch.float32 else BF16_EPS
+    assert rel_err(q, qr) < tol
+    for tkn in range(N):
+        s, pos = int(seg[tkn]), int(positions[tkn])
+        page_id, slot = int(bt[s, pos // page]), pos % page
+        assert rel_err(kp[page_id, :, slot], kr[tkn]) < tol
+        assert torch.equal(vp[page_id, :, :, slot].cpu().double(), vr[tkn].to(dtype).double())
+    assert int(status.item()) == 0
+    # a position without a page is recorded, nothing is written
+    bt2 = bt.clone()
+    bt2[1, 40 // page] = -1
+    before = kp.clone()
+    ops.qk_norm_rope_store(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, cos.to(DEV), sin.to(DEV), i32(positions.tolist()),
+                           i32(seg.tolist()), bt2.to(DEV), kp, vp, nh, nkv, hd, True, status)
+    assert int(status.item()) == 1 and torch.equal(kp, before)
+
+
+# ---- attention -----------------------------------------------------------------------------------
+def attention_reference(q, ks, vs, seg_lens_new, window):
+    """q [N, nh, hd]; per request: all keys/values so far (the new tokens are the last ones)."""
+    outs = []
+    cur = 0
+    for k, v, n in zip(ks, vs, seg_lens_new):
+        Lk = k.shape[0]
+        qq = torch.zeros(Lk, q.shape[1], q.shape[2], dtype=torch.float64)
+        qq[Lk - n:] = q[cur:cur + n].double()
+        outs.append(P.causal_attention(qq, k.double(), v.double(), window)[Lk - n:])
+        cur += n
+    return torch.cat(outs).reshape(q.shape[0], -1)
+
+
+CASES = [  # nh, nkv, hd, page
+    (4, 2, 16, 16), (4, 1, 24, 8), (6, 3, 32, 16), (8, 2, 64, 16), (16, 1, 64, 32), (3, 3, 96, 16), (4, 2, 128, 16),
+]
+
+
+def make_attention_case(nh, nkv, hd, page, dtype, kv_lens, new_lens, seed):
+    g = torch.Generator().manual_seed(seed)
+    ks = [torch.randn(L, nkv, hd, generator=g).to(dtype) for L in kv_lens]
+    vs = [torch.randn(L, nkv, hd, generator=g).to(dtype) for L in kv_lens]
+    N = sum(new_lens)
+    q = (2.0 * torch.randn(N, nh, hd, generator=g)).to(dtype)
+    # one far key stands out: scale one (query, key) pair so that a single score dominates
+    ks[0][3 % kv_lens[0]] *= 6.0
+    kp, vp, bt = build_cache(ks, vs, nkv, hd, page, dtype, seed)
+    positions = torch.cat([torch.arange(L - n, L) for L, n in zip(kv_lens, new_lens)])
+    seg = torch.cat([torch.full((n,), i) for i, n in enumerate(new_lens)])
+    starts = [0]
+    for n in new_lens:
+        starts.append(starts[-1] + n)
+    return q, ks, vs, kp, vp, bt, positions, seg, starts
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 37])
+@pytest.mark.parametrize("nh,nkv,hd,page", CASES)
+def test_generic_attention(dtype, window, nh, nkv, hd, page):
+    from gesso_b200 import ops
+    kv_lens, new_lens = [150, 33, 1, 64], [20, 1, 1, 64]
+    q, ks, vs, kp, vp, bt, positions, seg, _ = make_attention_case(nh, nkv, hd, page, dtype, kv_lens, new_lens, hd + page)
+    out = ops.paged_attention_generic(q.to(DEV), kp, vp, bt, i32(positions.tolist()), i32(seg.tolist()), window,
+                                      1.0 / math.sqrt(hd))
+    want = attention_reference(q, ks, vs, new_lens, window)
+    assert rel_err(out, want) < (5e-6 if dtype == torch.float32 else 2 * BF16_EPS)
+
+
+@pytest.mark.parametrize("window", [None, 50])
+@pytest.mark.parametrize("nh,nkv,hd,page", [c for c in CASES if c[2] in (32, 64, 96, 128)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_decode_attention_split_kv(window, nh, nkv, hd, page, splits):
+    from gesso_b200 import ops
+    assert ops.fast_attention_takes(hd, page, nh, nkv)
+    kv_lens = [500, 17, 1, 16, 129]
+    new_lens = [1] * len(kv_lens)
+    q, ks, vs, kp, vp, bt, positions, seg, starts = make_attention_case(nh, nkv, hd, page, torch.bfloat16, kv_lens,
+                                                                         new_lens, hd + splits)
+    want = attention_reference(q, ks, vs, new_lens, window)
+    S = len(kv_lens)
+    ws = (torch.empty(S * nh * splits * hd, device=DEV), torch.empty(S * nh * splits * 2, device=DEV),
+          torch.zeros(S * nkv, dtype=torch.int32, device=DEV))
+    for _ in range(2):      # twice with one workspace: the tickets of the first launch must have been reset
+        out = ops.decode_attention(q.to(DEV), kp, vp, bt, i32(positions.tolist()), i32(starts), window,
+                                   1.0 / math.sqrt(hd), splits, ws)
+        assert rel_err(out, want) < 2 * BF16_EPS
+
+
+@pytest.mark.parametrize("window", [None, 50])
+@pytest.mark.parametrize("nh,nkv,hd,page", [c for c in CASES if c[2] in (32, 64, 96, 128)])
+def test_prefill_attention_flash(window, nh, nkv, hd, page):
+    from gesso_b200 import ops
+    from gesso_b200.engine.batch import QUERY_TILE
+    kv_lens, new_lens = [200, 70, 1, 130, 16], [200, 3, 1, 65, 2]     # whole prompt, portions, single tokens
+    q, ks, vs, kp, vp, bt, positions, seg, starts = make_attention_case(nh, nkv, hd, page, torch.bfloat16, kv_lens,
+                                                                         new_lens, hd + page + 1)
+    tile_seg, tile_q0 = [], []
+    for s, n in enumerate(new_lens):
+        for q0 in range(0, n, QUERY_TILE):
+            tile_seg.append(s)
+            tile_q0.append(q0)
+    pos0 = [L - n for L, n in zip(kv_lens, new_lens)]
+    out = ops.prefill_attention(q.to(DEV), kp, vp, bt, i32(starts), i32(pos0), i32(tile_seg), i32(tile_q0), window,
+                                1.0 / math.sqrt(hd))
+    want = attention_reference(q, ks, vs, new_lens, window)
+    assert rel_err(out, want) < 2 * BF16_EPS
+
+
+def test_fast_attention_refuses_other_sizes():
+    from gesso_b200 import ops
+    assert not ops.fast_attention_takes(24, 16, 4, 1)
+    assert not ops.fast_attention_takes(64, 8, 4, 1)
+    assert not ops.fast_attention_takes(64, 16, 32, 1)      # 32 query heads per kv head
+
+
+# ---- sampling ----------------------------------------------------------------------------------------
+def test_argmax_ties_and_nonfinite():
+    from gesso_b200 import ops
+    V = 5003
+    x = torch.randn(6, V)
+    x[0, 4000] = x[0, 17] = 9.0                      # tie: the lowest id wins
+    x[1, V - 1] = 11.0
+    x[2, 3] = float("nan")
+    x[3, 100] = float("inf")
+    x[4] = -3.0                                      # all equal
+    ids, bad = ops.argmax_rows(x.to(DEV))
+    assert ids.tolist()[:2] == [17, V - 1] and ids.tolist()[4] == 0
+    assert ids.tolist()[5] == int(torch.argmax(x[5]))
+    assert bad.tolist() == [0, 0, 1, 1, 0, 0]
+
+
+@pytest.mark.parametrize("V", [503, 65536])
+def test_sampler_matches_the_plain_rule(V):
+    """Same seed, same ids as the plain full-sort sampler (temperature and nucleus)."""
+    from gesso_b200.sampling import SamplingParams, SplitMix64, sample_host, select_tokens
+    g = torch.Generator().manual_seed(V)
+    rows = 12
+    logits = 3.0 * torch.randn(rows, V, generator=g)
+    logits[3] = 0.25                                  # flat row: every weight ties
+    logits[4, 7] = 40.0                               # peaked row
+    logits[5, :] = torch.round(logits[5, :])          # many ties
+    params = [SamplingParams(temperature=[0.7, 1.3, 0.05][i % 3], top_p=[1.0, 0.9, 0.5, 0.999][i % 4], seed=i)
+              for i in range(rows)]
+    dev_rngs = [SplitMix64(p.seed) for p in params]
+    host_rngs = [SplitMix64(p.seed) for p in params]
+    plain = [P.PlainSampler(p.temperature, p.top_p, p.seed) for p in params]
+    for _ in range(4):                                # several draws: the streams stay aligned
+        got = select_tokens(logits.to(DEV), params, dev_rngs)
+        want_host = [sample_host(logits[i].numpy(), params[i], host_rngs[i]) for i in range(rows)]
+        want_plain = [plain[i].sample(logits[i].tolist()) for i in range(rows)] if V < 1000 else want_host
+        assert got == want_host == want_plain
+
+
+def test_sampler_low_temperature_is_argmax_and_nucleus_keeps_the_top_set():
+    from gesso_b200.sampling import SamplingParams, SplitMix64, select_tokens
+    V = 1000
+    logits = torch.randn(4, V)
+    got = select_tokens(logits.to(DEV), [SamplingParams(1e-4, 1.0, s) for s in range(4)],
+                        [SplitMix64(s) for s in range(4)])
+    assert got == torch.argmax(logits, dim=1).tolist()
+    # nucleus of mass 0.5 over three dominant ids: only they are ever drawn
+    row = torch.full((1, V), -30.0)
+    row[0, [5, 50, 500]] = torch.tensor([2.0, 1.5, 1.0])
+    seen = set()
+    for s in range(40):
+        seen.add(select_tokens(row.to(DEV), [SamplingParams(1.0, 0.5, s)], [SplitMix64(s)])[0])
+    assert seen <= {5, 50} and 5 in seen

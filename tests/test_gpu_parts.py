@@ -1,0 +1,345 @@
+"""Each part of a layer alone against the plain implementation, the layer order as data (a layer
+named twice, a layer that reads another layer's cache), and a toy mixer with a state of its own
+that is registered, built and stepped from this file alone."""
+import math
+
+import pytest
+import torch
+
+import plain_lfm2 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF16_EPS = 2.0 ** -8
+
+
+def rel_err(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).abs().max() / max(1e-30, float(b.abs().max())))
+
+
+def make_ctx(engine, entries):
+    ctx = engine.build_context(entries)
+    return ctx, engine.views(ctx)
+
+
+# ---- helpers: a one-layer "model" around the part under test --------------------------------------------
+def tiny_spec(mixer, ff=None, H=48, V=64, n_layers=1, schedule=None, arch="PartTest"):
+    from gesso_b200.config import BlockSpec, ModelSpec, PartSpec, default_schedule
+    norm = PartSpec("rmsnorm", {"size": H, "eps": 1e-5})
+    ff = ff or PartSpec("swiglu", {"hidden_size": H, "ff_dim": 40})
+    mixers = mixer if isinstance(mixer, (list, tuple)) else [mixer] * n_layers
+    blocks = tuple(BlockSpec("prenorm", m, ff, norm, norm, f"layers.{i}.") for i, m in enumerate(mixers))
+    return ModelSpec(architecture=arch, vocab_size=V, hidden_size=H, blocks=blocks,
+                     schedule=schedule or default_schedule(len(blocks)), final_norm=norm, tie_embedding=True)
+
+
+def build_model(spec, dtype, seed=0, max_positions=256):
+    from gesso_b200.engine import Model
+    from gesso_b200.weights import random_tensors
+    tensors = random_tensors(spec, seed, style="fan_in")
+    return Model(spec, tensors, dtype, DEV, max_positions), {k: v.double() for k, v in tensors.items()}
+
+
+ATTN = dict(hidden_size=48, n_heads=6, n_kv_heads=2, head_dim=8, qk_norm_eps=1e-5, window=None)
+
+
+def attn_spec(**kw):
+    from gesso_b200.config import PartSpec
+    p = dict(ATTN, **kw)
+    p["position"] = PartSpec("rope", {"theta": 777.0, "rotary_dim": p["head_dim"]})
+    return PartSpec("gqa_attention", p)
+
+
+def conv_spec(**kw):
+    from gesso_b200.config import PartSpec
+    return PartSpec("short_conv", dict(dict(hidden_size=48, kernel=3, bias=True), **kw))
+
+
+# ---- parts alone ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from gesso_b200.config import PartSpec
+    from gesso_b200.engine.model import Runtime
+    from gesso_b200.parts import build_norm
+    part = build_norm(PartSpec("rmsnorm", {"size": 100, "eps": 1e-6}))
+    assert part.param_decls()["weight"].shape == (100,)
+    w = torch.rand(100, device=DEV) + 0.5
+    part.bind({"weight": w}, Runtime(DEV, dtype, 16))
+    h = torch.randn(7, 100, device=DEV)
+    d = torch.randn(7, 100, device=DEV).to(dtype)
+    want_h = h.double() + d.double()
+    out = part.add_norm(h, d, None)
+    assert out.dtype == dtype and rel_err(h, want_h) < 1e-6
+    assert rel_err(out, P.rmsnorm(want_h.cpu(), w.double().cpu(), 1e-6)) < (2e-6 if dtype == torch.float32 else BF16_EPS)
+
+
+def test_rope_part_tables_and_refusal():
+    from gesso_b200.config import PartSpec
+    from gesso_b200.engine.model import Runtime
+    from gesso_b200.errors import GessoError
+    from gesso_b200.parts import build_position
+    part = build_position(PartSpec("rope", {"theta": 1e6, "rotary_dim": 24}))
+    rt = Runtime(DEV, torch.float32, 4096)
+    part.bind({}, rt)
+    cos, sin = part.tables()
+    assert cos.shape == (4096, 12) and cos.dtype == torch.float32
+    # float64 angles: the far end of the table is still exact to float32 rounding
+    pos, i = 4095, 0
+    assert abs(float(cos[pos, i]) - math.cos(pos * 1e6 ** (-2 * i / 24))) < 1e-7
+    assert abs(float(sin[pos, 5]) - math.sin(pos * 1e6 ** (-10 / 24))) < 1e-7
+    part.check_head_dim(24)
+    with pytest.raises(GessoError):
+        part.check_head_dim(32)                   # partial rotary is refused
+    # one table per (theta, size) is shared
+    other = build_position(PartSpec("rope", {"theta": 1e6, "rotary_dim": 24}))
+    other.bind({}, rt)
+    assert other.tables()[0] is cos
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 5])
+def test_attention_part_alone(dtype, window):
+    """The mixer alone: two portions and a decoded token of one request, against plain attention."""
+    from gesso_b200.engine import Engine, StepEntry
+    spec = tiny_spec(attn_spec(window=window))
+    model, w = build_model(spec, dtype)
+    eng = Engine(model, max_positions=64, page_size=4, num_pages=16, max_requests=2)
+    part = model.blocks[0].mixer
+    T = 23
+    x = torch.randn(T, 48, generator=torch.Generator().manual_seed(5)).to(dtype)
+    eng.admit("r")
+    outs = []
+    for a, b in ((0, 9), (9, 22), (22, 23)):
+        entries = [StepEntry("r", [0] * (b - a), [])]
+        ctx, views = make_ctx(eng, entries)
+        delta, bias = part.forward(x[a:b].to(DEV).contiguous(), ctx, views[0])
+        assert bias is None
+        outs.append(delta)
+        eng.cache.commit("r", b - a)
+    p = "layers.0.mixer."
+    want = P.attention_mixer(x.double(), w[p + "q_proj.weight"], w[p + "k_proj.weight"], w[p + "v_proj.weight"],
+                             w[p + "o_proj.weight"], w[p + "q_norm.weight"], w[p + "k_norm.weight"], 6, 2, 8, 1e-5,
+                             777.0, window)
+    assert rel_err(torch.cat(outs), want) < (1e-5 if dtype == torch.float32 else 4 * BF16_EPS)
+    if window:   # pages behind the window went back to the pool
+        assert eng.cache.pages_in_use()[0] < (T + 3) // 4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kernel,bias", [(2, False), (3, True), (4, True)])
+def test_short_conv_part_alone(dtype, kernel, bias):
+    from gesso_b200.engine import Engine, StepEntry
+    spec = tiny_spec(conv_spec(kernel=kernel, bias=bias))
+    model, w = build_model(spec, dtype)
+    eng = Engine(model, max_positions=64, page_size=4, num_pages=4, max_requests=2)
+    part = model.blocks[0].mixer
+    assert part.cache_need().shape == (kernel - 1, 48)
+    T = 20
+    x = torch.randn(T, 48, generator=torch.Generator().manual_seed(6)).to(dtype)
+    eng.admit("r")
+    outs = []
+    for a, b in ((0, 1), (1, 3), (3, 14), (14, 15), (15, 20)):
+        ctx, views = make_ctx(eng, [StepEntry("r", [0] * (b - a), [])])
+        delta, dbias = part.forward(x[a:b].to(DEV).contiguous(), ctx, views[0])
+        outs.append(delta.double() + (dbias.double() if dbias is not None else 0))
+        eng.cache.commit("r", b - a)
+    p = "layers.0.mixer."
+    want = P.short_conv_mixer(x.double(), w[p + "in_proj.weight"], w[p + "conv.weight"], w[p + "out_proj.weight"],
+                              w.get(p + "in_proj.bias"), w.get(p + "conv.bias"), w.get(p + "out_proj.bias"))
+    assert rel_err(torch.cat(outs), want) < (1e-5 if dtype == torch.float32 else 4 * BF16_EPS)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part_alone(dtype):
+    spec = tiny_spec(conv_spec())
+    model, w = build_model(spec, dtype)
+    part = model.blocks[0].feed_forward
+    x = torch.randn(11, 48).to(dtype)
+    delta, bias = part.forward(x.to(DEV), None)
+    p = "layers.0.feed_forward."
+    want = P.swiglu_ffn(x.double(), w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
+    assert bias is None and rel_err(delta, want) < (1e-5 if dtype == torch.float32 else 4 * BF16_EPS)
+
+
+# ---- the layer order is data ----------------------------------------------------------------------------
+def plain_forward(spec, w, ids, schedule):
+    """The plain model for the toy specs of this file (attention and conv mixers of the sizes above)."""
+    h = P.embedding(w["embedding.weight"], ids)
+    kv_of = {}
+    for e, entry in enumerate(schedule):
+        b = spec.blocks[entry.layer]
+        p = b.prefix
+        xn = P.rmsnorm(h, w[p + "mixer_norm.weight"], 1e-5)
+        if b.mixer.kind == "gqa_attention":
+            m = b.mixer
+            nh, nkv, hd = m["n_heads"], m["n_kv_heads"], m["head_dim"]
+            T = xn.shape[0]
+            q = P.rope(P.rmsnorm((xn @ w[p + "mixer.q_proj.weight"].T).reshape(T, nh, hd), w[p + "mixer.q_norm.weight"], 1e-5),
+                       list(range(T)), 777.0)
+            if entry.cache_of is None:
+                k = P.rope(P.rmsnorm((xn @ w[p + "mixer.k_proj.weight"].T).reshape(T, nkv, hd),
+                                     w[p + "mixer.k_norm.weight"], 1e-5), list(range(T)), 777.0)
+                v = (xn @ w[p + "mixer.v_proj.weight"].T).reshape(T, nkv, hd)
+                kv_of[e] = (k, v)
+            else:
+                k, v = kv_of[entry.cache_of]          # reads the keys and values another entry wrote
+            mix = P.causal_attention(q, k, v, m.get("window")).reshape(T, nh * hd) @ w[p + "mixer.o_proj.weight"].T
+        else:
+            mix = P.short_conv_mixer(xn, w[p + "mixer.in_proj.weight"], w[p + "mixer.conv.weight"],
+                                     w[p + "mixer.out_proj.weight"], w.get(p + "mixer.in_proj.bias"),
+                                     w.get(p + "mixer.conv.bias"), w.get(p + "mixer.out_proj.bias"))
+        h = h + mix
+        h = h + P.swiglu_ffn(P.rmsnorm(h, w[p + "ff_norm.weight"], 1e-5), w[p + "feed_forward.gate_proj.weight"],
+                             w[p + "feed_forward.up_proj.weight"], w[p + "feed_forward.down_proj.weight"])
+    return P.rmsnorm(h, w["final_norm.weight"], 1e-5) @ w["embedding.weight"].T
+
+
+def run_cut(model, ids, cuts, page_size=4, num_pages=32):
+    from gesso_b200.engine import Engine, StepEntry
+    eng = Engine(model, max_positions=128, page_size=page_size, num_pages=num_pages, max_requests=2)
+    eng.admit("r")
+    rows, p = [], 0
+    for n in cuts:
+        rows.append(eng.step([StepEntry("r", ids[p:p + n], list(range(n)))]).clone())
+        p += n
+    assert p == len(ids)
+    eng.release("r")
+    eng.cache.check_invariants()
+    return torch.cat(rows)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_schedule_names_a_layer_twice_and_shares_a_cache(dtype):
+    """Layers [attention A, conv, attention B (window 6)]; order A, conv, A again, B reading the cache
+    of the first A.  The second run of A has a cache of its own; B has none."""
+    from gesso_b200.config import ScheduleEntry
+    sched = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2, cache_of=0), ScheduleEntry(1))
+    spec = tiny_spec([attn_spec(), conv_spec(), attn_spec(window=6)], schedule=sched)
+    model, w = build_model(spec, dtype, seed=3)
+    plan = model.cache_plan
+    assert [p.kind for p in plan.entries] == ["paged", "state", "paged", "paged", "state"]
+    assert plan.entries[3].owner == 0 and plan.entries[2].owner == 2 and len(plan.state_entries) == 2
+    ids = torch.randint(0, 64, (37,), generator=torch.Generator().manual_seed(1)).tolist()
+    want = plain_forward(spec, w, ids, sched)
+    tol = 1e-4 if dtype == torch.float32 else 32 * 2.0 ** -9
+    for cuts in ([37], [30, 1, 1, 1, 1, 1, 1, 1], [7, 2, 5, 3, 2, 11, 2, 5]):
+        got = run_cut(model, ids, cuts)
+        scale = max(1.0, float(want.abs().max()))
+        assert float((got.double().cpu() - want).abs().max()) <= tol * scale, cuts
+
+
+def test_layers_with_different_needs_get_pages_of_their_own():
+    spec = tiny_spec([attn_spec(), attn_spec(window=6), attn_spec(n_kv_heads=1, n_heads=6), conv_spec()])
+    model, _ = build_model(spec, torch.float32)
+    groups = model.cache_plan.paged_groups
+    assert len(groups) == 3 and [g[0].window for g in groups] == [None, 6, None]
+    from gesso_b200.engine import Engine, StepEntry
+    eng = Engine(model, max_positions=64, page_size=4, num_pages=16, max_requests=2)
+    eng.admit("r")
+    eng.step([StepEntry("r", list(range(30)), [])])
+    used = eng.cache.pages_in_use()
+    assert used[0] == 8 and used[2] == 8 and used[1] <= 3      # the windowed group gave its old pages back
+    eng.release("r")
+    assert eng.cache.pages_in_use() == [0, 0, 0]
+
+
+# ---- a toy mixer with a state of its own, defined here -------------------------------------------------
+def register_toy():
+    from gesso_b200.parts import Mixer, ParamDecl, StateNeed, register_mixer
+
+    class DecayMixer(Mixer):
+        """state_t = decay * state_{t-1} + x_t W^T (per request); output = state_t.  Written with torch
+        operations and host loops: it is a toy, so it opts out of graph capture."""
+
+        graph_safe = False
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.hidden, self.decay = int(spec["hidden_size"]), float(spec["decay"])
+
+        def param_decls(self):
+            return {"proj.weight": ParamDecl((self.hidden, self.hidden), fan_in=self.hidden)}
+
+        def cache_need(self):
+            return StateNeed((self.hidden,))
+
+        def bind(self, tensors, rt):
+            self.w = tensors["proj.weight"]
+
+        def forward(self, x, ctx, cache):
+            u = (x.float() @ self.w.float().T)
+            out = torch.empty_like(u)
+            starts, slots = ctx.seg_start.tolist(), cache.slots.tolist()
+            for s in range(ctx.n_segs):
+                st = cache.state[slots[s]].clone()
+                for t in range(starts[s], starts[s + 1]):
+                    st = self.decay * st + u[t]
+                    out[t] = st
+                cache.state[slots[s]] = st
+            return out.to(x.dtype), None
+
+    register_mixer("toy_decay", DecayMixer, replace=True)
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps():
+    from gesso_b200.config import PartSpec, register_architecture, spec_from_config, unregister_architecture
+    from gesso_b200.engine import Engine, Model, StepEntry
+    from gesso_b200.parts import unregister
+    from gesso_b200.weights import random_tensors
+    register_toy()
+
+    def adapter(cfg):
+        toy = PartSpec("toy_decay", {"hidden_size": cfg["width"], "decay": cfg["decay"]})
+        return tiny_spec([toy, conv_spec(hidden_size=cfg["width"]), toy], H=cfg["width"], V=cfg["vocab"], arch="ToyDecayLM")
+
+    register_architecture("ToyDecayLM", adapter, replace=True)
+    try:
+        spec = spec_from_config({"architectures": ["ToyDecayLM"], "width": 48, "vocab": 64, "decay": 0.5})
+        tensors = random_tensors(spec, 4, style="fan_in")
+        model = Model(spec, tensors, torch.float32, DEV, 128)
+        assert not model.graph_safe and len(model.cache_plan.state_entries) == 3
+        w = {k: v.double() for k, v in tensors.items()}
+        ids = torch.randint(0, 64, (19,), generator=torch.Generator().manual_seed(2)).tolist()
+        ids2 = [5, 9, 1]
+
+        def plain(ids):
+            h = P.embedding(w["embedding.weight"], ids)
+            for i, b in enumerate(spec.blocks):
+                p = b.prefix
+                xn = P.rmsnorm(h, w[p + "mixer_norm.weight"], 1e-5)
+                if b.mixer.kind == "toy_decay":
+                    u, st, rows = xn @ w[p + "mixer.proj.weight"].T, torch.zeros(48, dtype=torch.float64), []
+                    for t in range(len(ids)):
+                        st = 0.5 * st + u[t]
+                        rows.append(st)
+                    mix = torch.stack(rows)
+                else:
+                    mix = P.short_conv_mixer(xn, w[p + "mixer.in_proj.weight"], w[p + "mixer.conv.weight"],
+                                             w[p + "mixer.out_proj.weight"], w.get(p + "mixer.in_proj.bias"),
+                                             w.get(p + "mixer.conv.bias"), w.get(p + "mixer.out_proj.bias"))
+                h = h + mix
+                h = h + P.swiglu_ffn(P.rmsnorm(h, w[p + "ff_norm.weight"], 1e-5), w[p + "feed_forward.gate_proj.weight"],
+                                     w[p + "feed_forward.up_proj.weight"], w[p + "feed_forward.down_proj.weight"])
+            return P.rmsnorm(h, w["final_norm.weight"], 1e-5) @ w["embedding.weight"].T
+
+        eng = Engine(model, max_positions=64, page_size=4, num_pages=8, max_requests=2)
+        assert eng.cache.groups == []                       # no paged group at all: only state slots
+        eng.admit("a")
+        eng.admit("b")
+        got_a, got_b = [], []
+        got_a.append(eng.step([StepEntry("a", ids[:7], list(range(7)))]))
+        out = eng.step([StepEntry("a", ids[7:9], [0, 1]), StepEntry("b", ids2, [0, 1, 2])])    # mixed batch
+        got_a.append(out[:2])
+        got_b.append(out[2:])
+        for t in range(9, 19):
+            got_a.append(eng.step([StepEntry("a", [ids[t]], [0])]))
+        assert rel_err(torch.cat(got_a), plain(ids)) < 1e-5
+        assert rel_err(torch.cat(got_b), plain(ids2)) < 1e-5
+        # a slot that is used again starts from zero
+        eng.release("a")
+        eng.admit("c")
+        assert rel_err(eng.step([StepEntry("c", ids2, [0, 1, 2])]), plain(ids2)) < 1e-5
+    finally:
+        unregister_architecture("ToyDecayLM")
+        unregister("mixer", "toy_decay")
