@@ -1,0 +1,297 @@
+// Skinny matrix products for steps of few tokens (decoding): Y[M,N] = X[M,K] * W[N,K]^T, M <= 16.
+//
+// With so few rows the product is bound by the one pass over W, so the kernel is built around that
+// stream: a block owns 16 rows of W and its 8 warps walk K in interleaved 32-element chunks (the
+// block reads 512 contiguous bytes of each row per round).  Every thread streams 16 bytes of two W
+// rows per chunk through a private ring in shared memory (asynchronous copies, ten chunks in
+// flight) into the A fragment of mma.m16n8k16 (the sum over k is order-free, so the k index of a
+// fragment slot is whatever the load delivers; the X fragment uses the same assignment), and
+// accumulates in float32.  The weights sit on
+// the M side of the MMA and the tokens on its N side (8 per tile), so no tensor work is wasted on
+// padding.  The 8 partial sums of a block are added in shared memory in a fixed order: a row's
+// result does not depend on the grid or on how many other tokens share the step.
+//
+// Fused into the kernel, to save launches and passes over activations:
+//   prologue NORM:   X = rmsnorm(h) * w computed from the float32 residual stream (each block
+//                    recomputes the row statistics: M*K floats from L2);
+//   epilogue BF16:   Y stored as bfloat16;       F32: Y stored as float32 (logits);
+//            RESID:  h[M,N] += Y (+ bias), the residual add of the sublayer, in float32;
+//            SWIGLU: rows g and g+8 of a block are gate_i and up_i (the caller packs the fused
+//                    gate/up matrix in groups of 8), out[M, N/2] = silu(gate) * up.
+// Formulas: src/Operators/cpu.jl:293-311 (norm), 482-488 (SwiGLU), 629-630 (x W^T).
+#include <math.h>
+
+#include "common.cuh"
+
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESID = 2, EPI_SWIGLU = 3 };
+
+__device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;   // weights are read once: do not keep them in L1
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ unsigned pack2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+#define SK_WARPS 8
+#define SK_STAGES 10      // chunks in flight per thread (2 x 16 bytes each)
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// W is streamed through a ring of SK_STAGES private slots per thread (asynchronous copies global ->
+// shared, read back by the same thread), so the bytes in flight do not cost registers and no
+// block-wide barrier sits in the inner loop.  Blocks are persistent: a block walks the tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ... and its stream runs on across tile borders, so the fixed
+// costs (norm statistics, pipeline fill) are paid once per block.  ROWS = 16 or 8 rows of W per tile
+// (8 when there are too few 16-row tiles to fill the device; rows 8..15 of the MMA are then zero).
+// XC: chunks per warp and tile whose token-side fragments are kept in registers across tiles (0: reload).
+template <int NT, int EPI, bool NORM, int ROWS, int XC>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, const float* __restrict__ norm_w,
+                   float eps, const bf16* __restrict__ W, void* __restrict__ out, const float* __restrict__ bias,
+                   int M, int N, int K) {
+    constexpr int RSLOTS = ROWS / 8;                      // 16-byte pieces per thread and chunk
+    extern __shared__ uint4 ring[];                       // [stage][RSLOTS][256 threads]
+    __shared__ float part[2][SK_WARPS][ROWS][NT * 8 + 1];
+    __shared__ float rinv[NT * 8];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int n_chunks = K / 32;
+    const int CH = (n_chunks + SK_WARPS - 1) / SK_WARPS;  // loop steps per tile (chunk w + 8 i, if it exists)
+    const int n_tiles = N / ROWS;
+    const int my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int total = my_tiles * CH;
+
+    uint4* slot = ring + threadIdx.x;
+    constexpr int stage_stride = RSLOTS * SK_WARPS * 32;
+    const bf16* wbase = W + (size_t)g * K + 8 * t;        // + tile row offset + chunk offset
+
+    // producer cursor: item (tile, step) -> asynchronous copies into the ring
+    int p_tile = blockIdx.x, p_i = 0, p_stage = 0, p_item = 0;
+    auto issue = [&]() {
+        if (p_item < total) {
+            const int c = w + p_i * SK_WARPS;
+            if (c < n_chunks) {
+                const bf16* src = wbase + (size_t)p_tile * ROWS * K + (size_t)c * 32;
+                cp_async16(slot + p_stage * stage_stride, src);
+                if (RSLOTS == 2) cp_async16(slot + p_stage * stage_stride + SK_WARPS * 32, src + (size_t)8 * K);
+            }
+            ++p_item;
+            if (++p_i == CH) { p_i = 0; p_tile += gridDim.x; }
+            if (++p_stage == SK_STAGES) p_stage = 0;
+        }
+        cp_async_commit();                                // an empty group keeps the count in step
+    };
+#pragma unroll
+    for (int sidx = 0; sidx < SK_STAGES; ++sidx) issue();   // start the stream before anything else
+
+    if (NORM) {
+        // 1 / sqrt(mean(h^2) + eps) of every token row; warp w takes rows w, w+8, ...
+        for (int m = w; m < M; m += SK_WARPS) {
+            const float4* row = reinterpret_cast<const float4*>(h_in + (size_t)m * K);
+            float ss = 0.f;
+            for (int i = lane; i < K / 4; i += 32) {
+                const float4 v = row[i];
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) rinv[m] = 1.f / sqrtf(ss / (float)K + eps);
+        }
+        __syncthreads();
+    }
+
+    // the token side of the product for chunk c and token tile j
+    auto load_x = [&](int c, int j) -> uint4 {
+        const int m = j * 8 + g;
+        const int k = c * 32 + 8 * t;
+        uint4 xb = make_uint4(0, 0, 0, 0);
+        if (m < M && c < n_chunks) {
+            if (NORM) {
+                const float4 h0 = *reinterpret_cast<const float4*>(h_in + (size_t)m * K + k);
+                const float4 h1 = *reinterpret_cast<const float4*>(h_in + (size_t)m * K + k + 4);
+                const float4 w0 = *reinterpret_cast<const float4*>(norm_w + k);
+                const float4 w1 = *reinterpret_cast<const float4*>(norm_w + k + 4);
+                const float r = rinv[m];
+                xb.x = pack2((h0.x * r) * w0.x, (h0.y * r) * w0.y);
+                xb.y = pack2((h0.z * r) * w0.z, (h0.w * r) * w0.w);
+                xb.z = pack2((h1.x * r) * w1.x, (h1.y * r) * w1.y);
+                xb.w = pack2((h1.z * r) * w1.z, (h1.w * r) * w1.w);
+            } else {
+                xb = *reinterpret_cast<const uint4*>(x + (size_t)m * K + k);
+            }
+        }
+        return xb;
+    };
+    uint4 xc[XC > 0 ? XC : 1][NT];
+    if (XC > 0) {
+#pragma unroll
+        for (int i = 0; i < XC; ++i)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) xc[i][j] = load_x(w + i * SK_WARPS, j);
+    }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+    int c_stage = 0, buf = 0;
+    for (int tk = 0; tk < my_tiles; ++tk) {
+        const int tile = blockIdx.x + tk * gridDim.x;
+#pragma unroll 1
+        for (int i0 = 0; i0 < CH; i0 += (XC > 0 ? XC : 1)) {
+#pragma unroll
+            for (int ii = 0; ii < (XC > 0 ? XC : 1); ++ii) {
+                const int i = i0 + ii;
+                if (i >= CH) break;
+                const int c = w + i * SK_WARPS;
+                uint4 xb[NT];
+#pragma unroll
+                for (int j = 0; j < NT; ++j) xb[j] = XC > 0 ? xc[ii][j] : load_x(c, j);
+                cp_async_wait<SK_STAGES - 1>();           // the oldest group (this item) has landed
+                const uint4 fa = slot[c_stage * stage_stride];
+                const uint4 fb = RSLOTS == 2 ? slot[c_stage * stage_stride + SK_WARPS * 32] : make_uint4(0, 0, 0, 0);
+                if (++c_stage == SK_STAGES) c_stage = 0;
+                issue();                                  // refill the slot with the item SK_STAGES ahead
+                if (c < n_chunks) {
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        mma16816(acc[j], fa.x, fb.x, fa.y, fb.y, xb[j].x, xb[j].y);
+                        mma16816(acc[j], fa.z, fb.z, fa.w, fb.w, xb[j].z, xb[j].w);
+                    }
+                }
+            }
+        }
+        // ---- add the 8 partial sums of the block in a fixed order ----
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            part[buf][w][g][j * 8 + 2 * t] = acc[j][0];
+            part[buf][w][g][j * 8 + 2 * t + 1] = acc[j][1];
+            if (ROWS == 16) {
+                part[buf][w][(g + 8) % ROWS][j * 8 + 2 * t] = acc[j][2];
+                part[buf][w][(g + 8) % ROWS][j * 8 + 2 * t + 1] = acc[j][3];
+            }
+            acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        }
+        __syncthreads();      // one barrier per tile: `part` is double buffered
+        const int n0 = tile * ROWS;
+        if (EPI == EPI_SWIGLU) {
+            // 8 outputs per token: row r is gate, row r + 8 is up (ROWS == 16)
+            for (int idx = threadIdx.x; idx < 8 * NT * 8; idx += blockDim.x) {
+                const int r = idx & 7, m = idx >> 3;
+                if (m >= M) continue;
+                float gt = 0.f, up = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < SK_WARPS; ++ww) { gt += part[buf][ww][r][m]; up += part[buf][ww][(r + 8) % ROWS][m]; }
+                reinterpret_cast<bf16*>(out)[(size_t)m * (N / 2) + tile * 8 + r] =
+                    __float2bfloat16_rn((gt / (1.f + expf(-gt))) * up);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < ROWS * NT * 8; idx += blockDim.x) {
+                const int r = idx % ROWS, m = idx / ROWS;
+                if (m >= M) continue;
+                float v = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < SK_WARPS; ++ww) v += part[buf][ww][r][m];
+                const size_t o = (size_t)m * N + n0 + r;
+                if (EPI == EPI_BF16) reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v);
+                else if (EPI == EPI_F32) reinterpret_cast<float*>(out)[o] = v;
+                else reinterpret_cast<float*>(out)[o] += v + (bias ? bias[n0 + r] : 0.f);
+            }
+        }
+        buf ^= 1;
+    }
+    cp_async_wait<0>();
+}
+
+#define SK_RING_BYTES(ROWS) (SK_STAGES * ((ROWS) / 8) * SK_WARPS * 32 * 16)
+#define SK_MAX_BLOCKS (2 * 148)
+
+GESSO_API int gesso_skinny_gemm_takes(int M, int N, int K) {
+    return M >= 1 && M <= 16 && N >= 16 && N % 16 == 0 && K >= 32 && K % 32 == 0;
+}
+
+template <int NT, int EPI, bool NORM, int ROWS, int XC>
+static int launch_one(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
+                      const float* bias, int M, int N, int K, cudaStream_t stream) {
+    static bool configured = false;   // once per instantiation, outside any stream capture
+    if (!configured) {
+        cudaFuncSetAttribute(skinny_gemm_kernel<NT, EPI, NORM, ROWS, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SK_RING_BYTES(ROWS));
+        configured = true;
+    }
+    const int n_tiles = N / ROWS;
+    const int blocks = n_tiles < SK_MAX_BLOCKS ? n_tiles : SK_MAX_BLOCKS;
+    skinny_gemm_kernel<NT, EPI, NORM, ROWS, XC><<<blocks, SK_WARPS * 32, SK_RING_BYTES(ROWS), stream>>>(
+        (const bf16*)x, h_in, norm_w, eps, (const bf16*)W, out, bias, M, N, K);
+    return launch_status();
+}
+
+template <int NT, int EPI, bool NORM>
+static int launch_shape(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
+                        const float* bias, int M, int N, int K, cudaStream_t stream) {
+    // token-side fragments stay in registers when a warp has at most 8 chunks per tile (K <= 2048)
+    const bool cache_x = K / 32 <= 8 * SK_WARPS && K % (32 * SK_WARPS) == 0 && NT == 1;
+    const bool small_rows = EPI != EPI_SWIGLU && N / 16 < SK_MAX_BLOCKS && N % 8 == 0;
+    const int xc = cache_x ? K / (32 * SK_WARPS) : 0;
+#define GO(ROWS, XC) return launch_one<NT, EPI, NORM, ROWS, XC>(x, h_in, norm_w, eps, W, out, bias, M, N, K, stream)
+    if (EPI != EPI_SWIGLU && small_rows) {
+        if (xc == 8) GO(8, 8);
+        if (xc == 4) GO(8, 4);
+        if (xc == 2) GO(8, 2);
+        GO(8, 0);
+    }
+    if (xc == 8) GO(16, 8);
+    if (xc == 4) GO(16, 4);
+    if (xc == 2) GO(16, 2);
+    GO(16, 0);
+#undef GO
+}
+
+template <int NT>
+static int launch_skinny(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
+                         const float* bias, int M, int N, int K, int epi, cudaStream_t stream) {
+    const bool norm = h_in != nullptr;
+#define GO(E, NM) return launch_shape<NT, E, NM>(x, h_in, norm_w, eps, W, out, bias, M, N, K, stream)
+    if (norm) {
+        if (epi == EPI_BF16) GO(EPI_BF16, true);
+        else if (epi == EPI_F32) GO(EPI_F32, true);
+        else if (epi == EPI_SWIGLU) GO(EPI_SWIGLU, true);
+        else return GESSO_ERR_UNSUPPORTED;
+    } else {
+        if (epi == EPI_BF16) GO(EPI_BF16, false);
+        else if (epi == EPI_F32) GO(EPI_F32, false);
+        else if (epi == EPI_RESID) GO(EPI_RESID, false);
+        else if (epi == EPI_SWIGLU) GO(EPI_SWIGLU, false);
+        else return GESSO_ERR_UNSUPPORTED;
+    }
+#undef GO
+}
+
+// x: bf16 [M,K] (or null with h_in/norm_w: the norm is fused); W: bf16 [N,K]; out by `epi`.
+GESSO_API int gesso_skinny_gemm(const void* x, const float* h_in, const float* norm_w, float eps, const void* W,
+                                void* out, const float* bias, int M, int N, int K, int epi, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (!gesso_skinny_gemm_takes(M, N, K)) return GESSO_ERR_BAD_SIZE;
+    if ((x == nullptr) == (h_in == nullptr)) return GESSO_ERR_UNSUPPORTED;
+    if (h_in && M > 16) return GESSO_ERR_BAD_SIZE;      // the fused norm is for a handful of rows
+    if (M <= 8) return launch_skinny<1>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, stream);
+    return launch_skinny<2>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, stream);
+}

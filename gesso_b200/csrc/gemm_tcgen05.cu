@@ -1,0 +1,354 @@
+// Dense bfloat16 matrix product on the 5th-generation tensor cores:
+//   C[M,N] = A[M,K] * W[N,K]^T, float32 accumulation in tensor memory.
+//
+// One block computes a 128 x BN tile of C (BN = 256 or 128).  Three roles:
+//   warp 0  one elected thread issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of a
+//           128 x 64 tile of A and a BN x 64 tile of W per stage into a ring of shared-memory
+//           stages, each guarded by a "full" mbarrier (transaction bytes) and an "empty" mbarrier;
+//   warp 1  allocates BN tensor-memory columns; one elected thread issues tcgen05.mma
+//           (cta_group::1, kind::f16, M = 128, N = BN, K = 16; four per stage) on shared-memory
+//           descriptors, frees a stage with tcgen05.commit -> its "empty" barrier and signals the
+//           finished accumulator through a last commit;
+//   warps 2..5  the epilogue: tcgen05.ld (32 lanes x 32 columns per warp and step) brings the
+//           accumulator rows to registers; each thread owns one row of C and stores 32 consecutive
+//           columns per step as bfloat16 / float32, or adds them into the float32 residual stream, or
+//           applies SwiGLU to packed gate/up columns.
+// Both operands are K-major (A row-major, W stored (out, in) as the reference stores projection
+// weights, src/Operators/cpu.jl:629-630), which is the canonical layout of the shared-memory
+// descriptor: 8-row groups 1024 bytes apart, 128-byte rows, 16-byte chunks XOR-swizzled by the row.
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT failed polls the thread records a code in
+// the status word, and every role then leaves its loop, so the kernel always ends, frees its
+// tensor memory and the host reads the status.  Rows beyond M and columns beyond N / K are zero
+// filled by TMA on the way in and predicated on the way out.
+#include <cuda.h>
+#include <math.h>
+
+#include "common.cuh"
+
+enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_RESID = 2, TC_EPI_SWIGLU = 3 };
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define WAIT_LIMIT (1u << 22)
+
+// ---- small PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false after WAIT_LIMIT polls (the caller records the failure and leaves).
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, void* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
+            "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    unsigned pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void tmem_alloc(void* smem_dst, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_dst)), "r"(cols));
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(void* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void umma_f16(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
+                                         unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: start address, leading
+// byte offset 1 (unused with a swizzle), stride byte offset 1024 (one 8-row group), version 1,
+// layout type 2 (SWIZZLE_128B).  All offsets in units of 16 bytes.
+__device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr >> 4) & 0x3fff);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+// Instruction descriptor of kind::f16: D float32, A and B bfloat16, both K-major, N and M.
+__host__ __device__ constexpr unsigned make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct __align__(1024) TcSmem {
+    bf16 a[STAGES][TC_BM * TC_BK];     // 16 KB per stage
+    bf16 b[STAGES][BN * TC_BK];        // 32 or 16 KB per stage
+    unsigned long long full[STAGES], empty[STAGES], acc_full;
+    unsigned tmem_base;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    void* __restrict__ out, const float* __restrict__ bias, int M, int N, int K,
+                    int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    // the swizzled stages must start on a 1024-byte boundary
+    TcSmem<BN, STAGES>& s =
+        *reinterpret_cast<TcSmem<BN, STAGES>*>(((size_t)smem_raw + 1023) & ~(size_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    constexpr unsigned STAGE_BYTES = (TC_BM + BN) * TC_BK * sizeof(bf16);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.empty[i], 1);
+        }
+        mbar_init(&s.acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {               // this warp owns the tensor memory: allocate BN columns
+        tmem_alloc(&s.tmem_base, BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = s.tmem_base;
+
+    if (warp == 0) {
+        // ---- producer ----
+        if (elect_one()) {
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int st = kb % STAGES;
+                const unsigned phase = (kb / STAGES) & 1;
+                if (!mbar_wait(&s.empty[st], phase ^ 1)) { atomicExch(status, 2); break; }
+                mbar_expect_tx(&s.full[st], STAGE_BYTES);
+                tma_load_2d(s.a[st], &map_a, kb * TC_BK, m0, &s.full[st]);
+                tma_load_2d(s.b[st], &map_w, kb * TC_BK, n0, &s.full[st]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- tensor-core issue ----
+        if (elect_one()) {
+            constexpr unsigned idesc = make_idesc(TC_BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int st = kb % STAGES;
+                const unsigned phase = (kb / STAGES) & 1;
+                if (!mbar_wait(&s.full[st], phase)) { atomicExch(status, 3); ok = false; break; }
+                tc_fence_after();
+                const unsigned long long da = make_desc(smem_u32(s.a[st]));
+                const unsigned long long db = make_desc(smem_u32(s.b[st]));
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)     // 16 elements = 32 bytes = 2 descriptor units
+                    umma_f16(tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&s.empty[st]);               // the stage is free once these MMAs have read it
+            }
+            umma_commit(&s.acc_full);                     // arrives even after a failure, so the epilogue ends
+        }
+    } else {
+        // ---- epilogue: warp q may touch tensor-memory lanes 32q .. 32q+31 ----
+        const int q = warp & 3;
+        const bool ready = mbar_wait(&s.acc_full, 0);
+        if (!ready && lane == 0) atomicExch(status, 4);
+        tc_fence_after();
+        const int row = m0 + q * 32 + lane;
+        if (ready) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                unsigned r[32];
+                tmem_ld32(tmem + ((unsigned)(q * 32) << 16) + (unsigned)c, r);
+                tmem_ld_wait();
+                const int col = n0 + c;
+                if (row >= M || col >= N) continue;
+                if (EPI == TC_EPI_SWIGLU) {
+                    // packed columns: 8 gate then their 8 up; 32 columns give 16 outputs
+                    bf16* o = reinterpret_cast<bf16*>(out) + (size_t)row * (N / 2) + col / 2;
+#pragma unroll
+                    for (int grp = 0; grp < 2; ++grp) {
+                        if (col + grp * 16 >= N) break;
+                        unsigned pk[4];
+#pragma unroll
+                        for (int i = 0; i < 8; i += 2) {
+                            const float g0 = __uint_as_float(r[grp * 16 + i]), g1 = __uint_as_float(r[grp * 16 + i + 1]);
+                            const float u0 = __uint_as_float(r[grp * 16 + 8 + i]), u1 = __uint_as_float(r[grp * 16 + 9 + i]);
+                            __nv_bfloat162 v = __floats2bfloat162_rn((g0 / (1.f + expf(-g0))) * u0,
+                                                                     (g1 / (1.f + expf(-g1))) * u1);
+                            pk[i / 2] = *reinterpret_cast<unsigned*>(&v);
+                        }
+                        *reinterpret_cast<uint4*>(o + grp * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                } else if (EPI == TC_EPI_BF16) {
+                    bf16* o = reinterpret_cast<bf16*>(out) + (size_t)row * N + col;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        if (col + i >= N) break;
+                        unsigned pk[4];
+#pragma unroll
+                        for (int j = 0; j < 8; j += 2) {
+                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[i + j]), __uint_as_float(r[i + j + 1]));
+                            pk[j / 2] = *reinterpret_cast<unsigned*>(&v);
+                        }
+                        *reinterpret_cast<uint4*>(o + i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                } else {
+                    float* o = reinterpret_cast<float*>(out) + (size_t)row * N + col;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        if (col + i >= N) break;
+                        float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                                               __uint_as_float(r[i + 3]));
+                        if (EPI == TC_EPI_RESID) {
+                            const float4 old = *reinterpret_cast<const float4*>(o + i);
+                            v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                            if (bias) {
+                                v.x += bias[col + i]; v.y += bias[col + i + 1]; v.z += bias[col + i + 2]; v.w += bias[col + i + 3];
+                            }
+                        }
+                        *reinterpret_cast<float4*>(o + i) = v;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, BN);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A row-major [rows, K] bfloat16 matrix, tiles of box_rows x 64 elements, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return GESSO_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(bf16)};
+    const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : GESSO_ERR_UNSUPPORTED;
+}
+
+GESSO_API int gesso_gemm_tcgen05_takes(int M, int N, int K) {
+    // TMA: 16-byte aligned rows (K % 8); vector stores: N % 8 (bfloat16) / N % 4 (float32)
+    return M >= 1 && N >= 8 && N % 8 == 0 && K >= 8 && K % 8 == 0;
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, const float* bias, int M, int N, int K,
+                     int* status, cudaStream_t stream) {
+    const size_t smem = sizeof(TcSmem<BN, STAGES>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    const dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+    gemm_tcgen05_kernel<BN, STAGES, EPI><<<grid, TC_THREADS, smem, stream>>>(ma, mw, out, bias, M, N, K, status);
+    return launch_status();
+}
+
+// A: bfloat16 [M,K]; W: bfloat16 [N,K]; out by `epi` (bf16 [M,N], f32 [M,N], f32 residual [M,N] +=,
+// bf16 [M,N/2] SwiGLU of packed gate/up columns); status: one int, 0 unless a wait ran out.
+GESSO_API int gesso_gemm_tcgen05(const void* A, const void* W, void* out, const float* bias, int M, int N, int K,
+                                 int epi, int* status, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (!gesso_gemm_tcgen05_takes(M, N, K)) return GESSO_ERR_BAD_SIZE;
+    if (epi == TC_EPI_SWIGLU && N % 16 != 0) return GESSO_ERR_BAD_SIZE;
+    if (((size_t)A & 15) || ((size_t)W & 15) || ((size_t)out & 15)) return GESSO_ERR_BAD_SIZE;
+    const bool wide = N % 256 == 0 || N >= 1024;
+    CUtensorMap ma, mw;
+    int r = make_map(&ma, A, M, K, TC_BM);
+    if (r) return r;
+    r = make_map(&mw, W, N, K, wide ? 256 : 128);
+    if (r) return r;
+#define GO(BN, ST)                                                                                              \
+    switch (epi) {                                                                                              \
+        case TC_EPI_BF16: return launch_tc<BN, ST, TC_EPI_BF16>(ma, mw, out, bias, M, N, K, status, stream);    \
+        case TC_EPI_F32: return launch_tc<BN, ST, TC_EPI_F32>(ma, mw, out, bias, M, N, K, status, stream);      \
+        case TC_EPI_RESID: return launch_tc<BN, ST, TC_EPI_RESID>(ma, mw, out, bias, M, N, K, status, stream);  \
+        case TC_EPI_SWIGLU: return launch_tc<BN, ST, TC_EPI_SWIGLU>(ma, mw, out, bias, M, N, K, status, stream); \
+        default: return GESSO_ERR_UNSUPPORTED;                                                                  \
+    }
+    if (wide) { GO(256, 4) } else { GO(128, 4) }
+#undef GO
+}

@@ -70,13 +70,14 @@ class StepContext:
     """Device views of one step's metadata plus the host-side sizes kernels are launched with."""
 
     def __init__(self, layout: StepLayout, buf: torch.Tensor, status: torch.Tensor,
-                 max_seg_len: int, max_kv_len: int):
+                 max_seg_len: int, max_kv_len: int, rows_are_all_tokens: bool = False):
         self.layout = layout
         self.buf = buf
         self.status = status
         self.n_tokens, self.n_segs, self.n_rows = layout.n_tokens, layout.n_segs, layout.n_rows
         self.max_seg_len = max_seg_len      # longest portion of the step
         self.max_kv_len = max_kv_len        # longest sequence after the step
+        self.rows_are_all_tokens = rows_are_all_tokens   # logit_rows == 0..N-1
         o = layout.offsets()
         N, S, R = self.n_tokens, self.n_segs, self.n_rows
         self.token_ids = buf[o["token_ids"]:o["token_ids"] + N]

@@ -14,6 +14,7 @@ Reference counterparts: the per-sequence prefill pass and decode step
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -160,6 +161,7 @@ class Engine:
         pack_step(list(entries), starts, slots, tables, layout, host.numpy()[:size])
         max_seg = max(len(e.tokens) for e in entries)
         max_kv = max(s + len(e.tokens) for s, e in zip(starts, entries))
+        self._all_rows = all(list(e.want) == list(range(len(e.tokens))) for e in entries)
         return layout, slot_i, host[:size], max_seg, max_kv
 
     def _upload(self, buf: torch.Tensor, slot_i: int, host: torch.Tensor) -> None:
@@ -174,7 +176,7 @@ class Engine:
         layout, slot_i, host, max_seg, max_kv = self._prepare(entries)
         buf = torch.empty((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
         self._upload(buf, slot_i, host)
-        return StepContext(layout, buf, self.status, max_seg, max_kv)
+        return StepContext(layout, buf, self.status, max_seg, max_kv, self._all_rows)
 
     def views(self, ctx: StepContext):
         plan, dc = self.model.cache_plan, self.device_cache
@@ -206,7 +208,7 @@ class Engine:
         else:
             buf = torch.empty((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
             self._upload(buf, slot_i, host)
-            ctx = StepContext(layout, buf, self.status, max_seg, max_kv)
+            ctx = StepContext(layout, buf, self.status, max_seg, max_kv, self._all_rows)
             before = launch_count()
             logits = self.model.forward(ctx, self.views(ctx))
             self.launches += launch_count() - before
@@ -217,12 +219,12 @@ class Engine:
         return logits
 
     def _step_graph(self, layout: StepLayout, slot_i: int, host: torch.Tensor, max_kv: int):
-        key = (layout.n_segs, layout.n_rows)
+        key = (layout.n_segs, layout.n_rows, self._all_rows)
         g = self._graphs.get(key)
         if g is None:
             buf = torch.zeros((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
             self._upload(buf, slot_i, host)
-            ctx = StepContext(layout, buf, self.status, 1, self.max_positions)
+            ctx = StepContext(layout, buf, self.status, 1, self.max_positions, self._all_rows)
             views = self.views(ctx)
             # One eager run first: libraries initialise lazily, and capture records rather than runs,
             # so this run is also the one that produces the step's result.
@@ -232,8 +234,17 @@ class Engine:
             self.launches += n_launch
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                out = self.model.forward(ctx, views)
+            # No garbage collection while the stream records: a collected object that owns device
+            # resources (an older engine's graphs, for one) would free them in the middle of the
+            # capture, which CUDA forbids and which invalidates the capture.
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    out = self.model.forward(ctx, views)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
             self._graphs[key] = (graph, buf, out, n_launch)

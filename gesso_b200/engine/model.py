@@ -149,5 +149,13 @@ class Model:
         if ctx.n_rows == 0:
             # the last sublayer's output is only needed by the head; nothing to return
             return None
-        x = self.final_norm.add_norm(h, pending[0], pending[1], rows=ctx.logit_rows)
+        if ctx.rows_are_all_tokens and pending[0] is None:
+            # every token's logits are wanted, in order: no gather, and the norm can ride in the
+            # prologue of the head's matrix product
+            try:
+                x = self.final_norm.add_norm(h, None, None, lazy=True)
+            except TypeError:
+                x = self.final_norm.add_norm(h, None, None)
+        else:
+            x = self.final_norm.add_norm(h, pending[0], pending[1], rows=ctx.logit_rows)
         return ops.linear(x, self.lm_head, out_dtype=torch.float32)

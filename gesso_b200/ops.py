@@ -174,13 +174,24 @@ def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
 
 
 # ---- feed-forward ------------------------------------------------------------------------------
-def swiglu(gu: torch.Tensor) -> torch.Tensor:
+def swiglu(gu: torch.Tensor, packed: bool = False) -> torch.Tensor:
+    """``silu(gate) * up`` on the fused projection [N, 2F].  Plain layout: gate columns first, then
+    up columns.  ``packed``: groups of 16 columns hold 8 gate and then the matching 8 up columns."""
     _cuda_contig(gu, "gate_up")
     N, F2 = gu.shape
     _need(F2 % 2 == 0, "fused gate/up width must be even")
+    _need(not packed or F2 % 16 == 0, "the packed gate/up layout needs a width that is a multiple of 16")
     out = torch.empty((N, F2 // 2), dtype=gu.dtype, device=gu.device)
-    _lib.check(_lib.library().gesso_swiglu(_p(gu), _p(out), _dt(gu), N, F2 // 2, _stream()), "swiglu")
+    _lib.check(_lib.library().gesso_swiglu(_p(gu), _p(out), _dt(gu), N, F2 // 2, 1 if packed else 0, _stream()),
+               "swiglu")
     return out
+
+
+def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Fused gate/up matrix [2F, H] in groups of 16 rows: 8 gate rows, then the matching 8 up rows
+    (the layout whose SwiGLU the skinny matrix product can apply in its epilogue).  F % 8 == 0."""
+    F, H = gate.shape
+    return torch.stack([gate.reshape(F // 8, 8, H), up.reshape(F // 8, 8, H)], dim=1).reshape(2 * F, H).contiguous()
 
 
 # ---- matrix products ---------------------------------------------------------------------------
@@ -199,15 +210,73 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = No
     return c
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``x @ w^T`` for a weight stored (out, in).
+class LazyNorm:
+    """A norm that has not run yet: ``rmsnorm(h) * weight`` of the float32 residual stream.
 
-    bfloat16 activations with a bfloat16 weight use the tensor cores with float32
-    accumulation; any float32 operand (the 32-bit path, or a matrix that was stored
-    in 32 bit) uses the FP32 FMA kernel, so no reduced-precision mode is ever
-    applied to 32-bit data.
+    The skinny matrix product can apply it in its prologue; every other consumer calls
+    :meth:`materialize`, which runs the norm kernel."""
+
+    def __init__(self, h: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype):
+        self.h, self.weight, self.eps, self.dtype = h, weight, float(eps), out_dtype
+        self.shape = h.shape
+
+    def materialize(self) -> torch.Tensor:
+        return add_rmsnorm(self.h, None, None, self.weight, self.eps, self.dtype)
+
+
+EPI_BF16, EPI_F32, EPI_RESID, EPI_SWIGLU = 0, 1, 2, 3
+SKINNY_MAX_ROWS = 16
+SKINNY_NORM_MAX_ROWS = 16
+
+
+def skinny_takes(M: int, w: torch.Tensor, x_dtype) -> bool:
+    """Whether the skinny (few-token) matrix product takes this product: bfloat16 operands, at most
+    16 rows, an output width that is a multiple of 16 and an inner size that is a multiple of 32."""
+    N, K = w.shape
+    return (w.dtype == torch.bfloat16 and x_dtype == torch.bfloat16 and w.is_contiguous() and 1 <= M <= SKINNY_MAX_ROWS
+            and N >= 16 and N % 16 == 0 and K >= 32 and K % 32 == 0)
+
+
+def _skinny(x, w, out, bias, epi):
+    """x: bfloat16 tensor or LazyNorm with at most SKINNY_NORM_MAX_ROWS rows."""
+    N, K = w.shape
+    if isinstance(x, LazyNorm):
+        M = x.shape[0]
+        _cuda_contig(x.h, "h", torch.float32)
+        args = (None, _p(x.h), _p(x.weight), x.eps)
+    else:
+        M = x.shape[0]
+        _cuda_contig(x, "x", torch.bfloat16)
+        args = (_p(x), None, None, 0.0)
+    _lib.check(_lib.library().gesso_skinny_gemm(*args, _p(w), _p(out), _p(bias), M, N, K, epi, _stream()),
+               "skinny_gemm")
+
+
+def _as_tensor(x):
+    return x.materialize() if isinstance(x, LazyNorm) else x
+
+
+def _skinny_input(x):
+    if isinstance(x, LazyNorm) and x.shape[0] > SKINNY_NORM_MAX_ROWS:
+        return x.materialize()
+    return x
+
+
+def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x @ w^T`` for a weight stored (out, in); ``x`` is a tensor or a :class:`LazyNorm`.
+
+    bfloat16 activations with a bfloat16 weight use the tensor cores with float32 accumulation
+    (this library's skinny kernel for steps of few tokens, the library matrix product otherwise);
+    any float32 operand (the 32-bit path, or a matrix that was stored in 32 bit) uses the FP32 FMA
+    kernel, so no reduced-precision mode is ever applied to 32-bit data.
     """
     out_dtype = out_dtype or x.dtype
+    M = x.shape[0]
+    if skinny_takes(M, w, x.dtype) and out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty((M, w.shape[0]), dtype=out_dtype, device=w.device)
+        _skinny(_skinny_input(x), w, out, None, EPI_BF16 if out_dtype == torch.bfloat16 else EPI_F32)
+        return out
+    x = _as_tensor(x)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         _cuda_contig(x, "x")
         if out_dtype == torch.bfloat16:
@@ -215,6 +284,27 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     c = gemm_f32(x, w)
     return c if out_dtype == torch.float32 else c.to(out_dtype)
+
+
+def linear_residual(x, w: torch.Tensor, h: torch.Tensor, bias: Optional[torch.Tensor]):
+    """``h += x @ w^T (+ bias)`` when the skinny kernel can add in its epilogue (returns ``None``);
+    otherwise returns the product for the caller to pass on as a pending residual."""
+    M = x.shape[0]
+    if skinny_takes(M, w, x.dtype) and tuple(h.shape) == (M, w.shape[0]):
+        _cuda_contig(h, "h", torch.float32)
+        _skinny(_as_tensor(x), w, h, bias, EPI_RESID)
+        return None
+    return linear(x, w, out_dtype=x.dtype)
+
+
+def linear_swiglu(x, w_gate_up: torch.Tensor, packed: bool) -> torch.Tensor:
+    """``silu(gate(x)) * up(x)`` for the fused gate/up matrix (see :func:`pack_gate_up`)."""
+    M = x.shape[0]
+    if packed and skinny_takes(M, w_gate_up, x.dtype):
+        out = torch.empty((M, w_gate_up.shape[0] // 2), dtype=torch.bfloat16, device=w_gate_up.device)
+        _skinny(_skinny_input(x), w_gate_up, out, None, EPI_SWIGLU)
+        return out
+    return swiglu(linear(x, w_gate_up, out_dtype=x.dtype), packed)
 
 
 # ---- sampling ----------------------------------------------------------------------------------
@@ -305,4 +395,51 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(seg_start),
         _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), _p(out), nh, nkv, hd, int(window or 0),
         float(scale), _stream()), "prefill_attention")
+    return out
+
+
+# ---- tcgen05 matrix product (steps of many tokens) ---------------------------------------------------
+_lib.declare("gesso_gemm_tcgen05_takes", [_lib.I, _lib.I, _lib.I])
+_lib.declare("gesso_gemm_tcgen05", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P])
+
+_tc_status = {}
+
+
+def tc_status_tensor(device) -> torch.Tensor:
+    """One int32 per device that the tcgen05 kernel writes when one of its bounded waits runs out."""
+    key = str(device)
+    if key not in _tc_status:
+        _tc_status[key] = torch.zeros((1,), dtype=torch.int32, device=device)
+    return _tc_status[key]
+
+
+def check_tc_status(device="cuda") -> None:
+    """Raise if a tcgen05 matrix product gave up on a wait since the last check (synchronises)."""
+    st = tc_status_tensor(device)
+    code = int(st.item())
+    if code != 0:
+        st.zero_()
+        raise GessoError(ErrorCode.RUNTIME, f"tcgen05 matrix product: a pipeline wait ran out (role code {code})")
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epi: int = EPI_BF16, out: Optional[torch.Tensor] = None,
+                 bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [M,K] @ w [N,K]^T`` on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory).
+
+    ``epi``: EPI_BF16 / EPI_F32 give a new tensor; EPI_RESID adds into ``out`` (float32 [M,N], with
+    ``bias``); EPI_SWIGLU gives ``silu(gate) * up`` [M, N/2] for packed gate/up rows of ``w``."""
+    _cuda_contig(x, "x", torch.bfloat16)
+    _cuda_contig(w, "w", torch.bfloat16)
+    M, K = x.shape
+    N, K2 = w.shape
+    _need(K == K2, f"inner sizes differ: {K} vs {K2}")
+    if epi == EPI_RESID:
+        _need(out is not None and out.dtype == torch.float32 and tuple(out.shape) == (M, N), "residual must be float32 [M,N]")
+        _cuda_contig(out, "out")
+    elif epi == EPI_SWIGLU:
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    else:
+        out = torch.empty((M, N), dtype=torch.bfloat16 if epi == EPI_BF16 else torch.float32, device=x.device)
+    _lib.check(_lib.library().gesso_gemm_tcgen05(_p(x), _p(w), _p(out), _p(bias), M, N, K, epi,
+                                                 _p(tc_status_tensor(x.device)), _stream()), "gemm_tcgen05")
     return out

@@ -25,6 +25,9 @@ from .registry import build_position, register_mixer
 
 
 class GQAttention(Mixer):
+    accepts_lazy_norm = True
+    fuses_residual = True
+
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden = int(spec["hidden_size"])
@@ -72,7 +75,7 @@ class GQAttention(Mixer):
         self.position.bind({}, rt)
         self.rt = rt
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, residual=None):
         writes = cache.writes
         qkv = ops.linear(x, self.w_qkv if writes else self.w_q, out_dtype=x.dtype)
         cos, sin = self.position.tables()
@@ -80,6 +83,8 @@ class GQAttention(Mixer):
                                    cos, sin, ctx.positions, ctx.seg_of_token, cache.block_table,
                                    cache.k_pages, cache.v_pages, self.nh, self.nkv, self.hd, writes, ctx.status)
         o = self.rt.attention(q, cache, ctx, self.window, self.scale)
+        if residual is not None:
+            return ops.linear_residual(o, self.w_o, residual, None), None
         return ops.linear(o, self.w_o, out_dtype=x.dtype), None
 
 

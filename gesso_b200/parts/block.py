@@ -45,10 +45,29 @@ class PreNormBlock:
             part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, rt)
 
     def forward(self, h, pending, ctx, cache):
-        x = self.mixer_norm.add_norm(h, pending[0], pending[1])
-        m = self.mixer.forward(x, ctx, cache)
-        x = self.ff_norm.add_norm(h, m[0], m[1])
+        """``pending`` is the previous sublayer's (delta, bias) not yet added to ``h`` (or Nones).
+
+        Parts that set ``accepts_lazy_norm`` may be handed a norm that has not run yet; parts that
+        set ``fuses_residual`` are given ``residual=h`` and may add their output into it themselves
+        (they then return ``(None, None)``)."""
+        x = self._norm(self.mixer_norm, self.mixer, h, pending)
+        if getattr(self.mixer, "fuses_residual", False):
+            m = self.mixer.forward(x, ctx, cache, residual=h)
+        else:
+            m = self.mixer.forward(x, ctx, cache)
+        x = self._norm(self.ff_norm, self.feed_forward, h, m)
+        if getattr(self.feed_forward, "fuses_residual", False):
+            return self.feed_forward.forward(x, ctx, residual=h)
         return self.feed_forward.forward(x, ctx)
+
+    @staticmethod
+    def _norm(norm, consumer, h, pending):
+        if getattr(consumer, "accepts_lazy_norm", False):
+            try:
+                return norm.add_norm(h, pending[0], pending[1], lazy=True)
+            except TypeError:          # a norm part without the lazy option
+                pass
+        return norm.add_norm(h, pending[0], pending[1])
 
 
 register_block("prenorm", PreNormBlock, replace=True)

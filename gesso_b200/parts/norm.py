@@ -3,6 +3,10 @@
 ``y = (x / sqrt(mean(x^2) + eps)) * w`` over the last axis, divide first, scale
 second (src/Operators/cpu.jl:293-311).  The residual stream is float32; the sum
 and the statistics are float32, the output is rounded to the run dtype.
+
+With ``lazy=True`` and nothing to add, the norm is not run: a
+:class:`~gesso_b200.ops.LazyNorm` is returned, which the consumer's first matrix
+product applies in its prologue for steps of few tokens (or materialises).
 """
 from __future__ import annotations
 
@@ -28,7 +32,9 @@ class RMSNorm(Norm):
         self.weight = tensors["weight"]
         self.out_dtype = rt.dtype
 
-    def add_norm(self, h, delta, delta_bias, rows=None):
+    def add_norm(self, h, delta, delta_bias, rows=None, lazy=False):
+        if lazy and delta is None and rows is None:
+            return ops.LazyNorm(h, self.weight, self.eps, self.out_dtype)
         return ops.add_rmsnorm(h, delta, delta_bias, self.weight, self.eps, self.out_dtype, rows)
 
 

@@ -21,6 +21,9 @@ from .registry import register_mixer
 
 
 class ShortConv(Mixer):
+    accepts_lazy_norm = True
+    fuses_residual = True
+
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden = int(spec["hidden_size"])
@@ -55,10 +58,13 @@ class ShortConv(Mixer):
         self.b_conv = tensors.get("conv.bias")
         self.b_out = tensors.get("out_proj.bias")
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, residual=None):
         bcx = ops.linear(x, self.w_in, out_dtype=x.dtype)
         y = ops.short_conv(bcx, self.b_in, self.taps, self.b_conv, cache.state, ctx.seg_of_token,
                            ctx.seg_start, ctx.seg_pos0, cache.slots, ctx.n_segs, ctx.max_seg_len)
+        if residual is not None:
+            d = ops.linear_residual(y, self.w_out, residual, self.b_out)
+            return (None, None) if d is None else (d, self.b_out)
         return ops.linear(y, self.w_out, out_dtype=x.dtype), self.b_out
 
 
