@@ -156,6 +156,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets) {
     extern __shared__ float smem[];          // [4 warps][16 rows][HD + 2]
     __shared__ int s_last;
+    pdl_wait();
+    pdl_launch_dependents();
     const int split = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
     const int G = nh / nkv;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -374,7 +376,7 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
         if (smem > 48 * 1024)                                                                               \
             cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                                  (int)smem);                                                                \
-        decode_attention_kernel<HD><<<grid, 128, smem, stream>>>(                                           \
+        launch_pdl(decode_attention_kernel<HD>, grid, dim3(128), smem, stream,                              \
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,  \
             positions, seg_start, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml,       \
             tickets);                                                                                       \

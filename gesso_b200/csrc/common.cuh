@@ -57,3 +57,30 @@ static inline int launch_status() {
     cudaError_t e = cudaGetLastError();
     return (int)e;
 }
+
+// ---- programmatic dependent launch ------------------------------------------------------------------
+// Kernels of a decoding step are launched with the "programmatic stream serialization" attribute: a
+// kernel may be scheduled while its predecessor still runs, does what does not depend on earlier
+// kernels (its weight prefetch), and executes pdl_wait() before it touches anything an earlier
+// kernel produced; pdl_launch_dependents() lets its own successor in.  Without the attribute both
+// calls do nothing, so every kernel also runs correctly when launched the plain way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+extern int gesso_pdl_enabled;   // runtime.cu; set through gesso_set_pdl()
+
+template <typename... KArgs, typename... Args>
+static inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = gesso_pdl_enabled ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -12,6 +12,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                     float* __restrict__ h, int H, int V, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     int id = tokens[t];
     if (id < 0 || id >= V) id = 0;   // ids are validated on the host; never read outside the table
@@ -25,9 +27,9 @@ GESSO_API int gesso_embed_gather(const int* tokens, const void* table, int table
     if (n_tokens <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == GESSO_F32)
-        embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, h, H, V, scale);
+        launch_pdl(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, h, H, V, scale);
     else if (table_dtype == GESSO_BF16)
-        embed_gather_kernel<bf16><<<n_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, h, H, V, scale);
+        launch_pdl(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const bf16*)table, h, H, V, scale);
     else
         return GESSO_ERR_BAD_DTYPE;
     return launch_status();

@@ -102,13 +102,18 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     };
 #pragma unroll
     for (int sidx = 0; sidx < SK_STAGES; ++sidx) issue();   // start the stream before anything else
+    // The weights do not depend on earlier kernels; everything below does.  Let the next kernel in
+    // (it starts its own weight stream) and wait for the producers of the activations.
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (NORM) {
         // 1 / sqrt(mean(h^2) + eps) of every token row; warp w takes rows w, w+8, ...
         for (int m = w; m < M; m += SK_WARPS) {
             const float4* row = reinterpret_cast<const float4*>(h_in + (size_t)m * K);
             float ss = 0.f;
-            for (int i = lane; i < K / 4; i += 32) {
+#pragma unroll 8
+            for (int i = lane; i < K / 4; i += 32) {      // independent loads: keep several in flight
                 const float4 v = row[i];
                 ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             }
@@ -239,8 +244,8 @@ static int launch_one(const void* x, const float* h_in, const float* norm_w, flo
     }
     const int n_tiles = N / ROWS;
     const int blocks = n_tiles < SK_MAX_BLOCKS ? n_tiles : SK_MAX_BLOCKS;
-    skinny_gemm_kernel<NT, EPI, NORM, ROWS, XC><<<blocks, SK_WARPS * 32, SK_RING_BYTES(ROWS), stream>>>(
-        (const bf16*)x, h_in, norm_w, eps, (const bf16*)W, out, bias, M, N, K);
+    launch_pdl(skinny_gemm_kernel<NT, EPI, NORM, ROWS, XC>, dim3(blocks), dim3(SK_WARPS * 32), SK_RING_BYTES(ROWS), stream,
+               (const bf16*)x, h_in, norm_w, eps, (const bf16*)W, out, bias, M, N, K);
     return launch_status();
 }
 
@@ -248,7 +253,7 @@ template <int NT, int EPI, bool NORM>
 static int launch_shape(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
                         const float* bias, int M, int N, int K, cudaStream_t stream) {
     // token-side fragments stay in registers when a warp has at most 8 chunks per tile (K <= 2048)
-    const bool cache_x = K / 32 <= 8 * SK_WARPS && K % (32 * SK_WARPS) == 0 && NT == 1;
+    const bool cache_x = K / 32 <= 8 * SK_WARPS && K % (32 * SK_WARPS) == 0 && NT * (K / (32 * SK_WARPS)) <= 16;
     const bool small_rows = EPI != EPI_SWIGLU && N / 16 < SK_MAX_BLOCKS && N % 8 == 0;
     const int xc = cache_x ? K / (32 * SK_WARPS) : 0;
 #define GO(ROWS, XC) return launch_one<NT, EPI, NORM, ROWS, XC>(x, h_in, norm_w, eps, W, out, bias, M, N, K, stream)

@@ -7,6 +7,7 @@ fallback path that could stand in for a missing library.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
 
@@ -33,7 +34,7 @@ _SIGNATURES = {
     "gesso_skinny_gemm_takes": [I, I, I],
     "gesso_skinny_gemm": [P, P, P, F, P, P, P, I, I, I, I, P],
     "gesso_gemm_f32": [P, I, P, I, P, P, I, I, I, P],
-    "gesso_argmax_rows": [P, I, I, P, P, P],
+    "gesso_argmax_rows": [P, I, I, P, P, P, P, P],
     "gesso_sample_rows": [P, I, I, P, P, P, P, P, P],
 }
 
@@ -61,6 +62,11 @@ def library():
                 continue   # optional entry points are declared where they are used
             fn.argtypes = argtypes
             fn.restype = c_int
+        if hasattr(lib, "gesso_set_pdl"):
+            lib.gesso_set_pdl.argtypes = [c_int]
+            lib.gesso_set_pdl.restype = c_int
+            # GESSO_PDL=0 launches the kernels of decoding steps without programmatic dependent launch
+            lib.gesso_set_pdl(0 if os.environ.get("GESSO_PDL", "1") == "0" else 1)
         _lib = lib
         return lib
 

@@ -21,6 +21,8 @@ __global__ void qk_norm_rope_store_kernel(
     const int* __restrict__ seg_of_token, const int* __restrict__ block_table, int max_pages, int page_size,
     T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int nh, int nkv,
     int hd, int write_kv, int* __restrict__ status) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int heads = write_kv ? nh + 2 * nkv : nh;   // without a cache write the input holds q heads only
     const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
     const long long wi = (long long)blockIdx.x * warps + (threadIdx.x >> 5);
@@ -83,11 +85,11 @@ GESSO_API int gesso_qk_norm_rope_store(const void* qkv, int dtype, const float* 
     const long long blocks = (total + warps - 1) / warps;
     if (blocks > 2147483647LL) return GESSO_ERR_BAD_SIZE;
     if (dtype == GESSO_F32)
-        qk_norm_rope_store_kernel<float><<<(unsigned)blocks, warps * 32, 0, stream>>>(
+        launch_pdl(qk_norm_rope_store_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
             (const float*)qkv, q_w, k_w, eps, cos_t, sin_t, positions, seg_of_token, block_table, max_pages,
             page_size, (float*)q_out, (float*)k_pages, (float*)v_pages, n_tokens, nh, nkv, hd, write_kv, status);
     else if (dtype == GESSO_BF16)
-        qk_norm_rope_store_kernel<bf16><<<(unsigned)blocks, warps * 32, 0, stream>>>(
+        launch_pdl(qk_norm_rope_store_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
             (const bf16*)qkv, q_w, k_w, eps, cos_t, sin_t, positions, seg_of_token, block_table, max_pages,
             page_size, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, n_tokens, nh, nkv, hd, write_kv, status);
     else

@@ -63,11 +63,72 @@ argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ id
     }
 }
 
+// Wide rows: ARGMAX_SPLIT blocks per row scan a slice each and leave (value, id, nonfinite) in the
+// caller's scratch; a second small kernel picks the winner (ties still go to the lowest id).
+#define ARGMAX_SPLIT 32
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict__ pval, int* __restrict__ pidx) {
+    __shared__ float s_val[8];
+    __shared__ int s_idx[8], s_bad[8];
+    const int row = blockIdx.y, part = blockIdx.x;
+    const int per = (V + ARGMAX_SPLIT - 1) / ARGMAX_SPLIT;
+    const int lo = part * per, hi = min(V, lo + per);
+    const float* r = logits + (size_t)row * V;
+    float best = -INFINITY;
+    int bi = 0x7fffffff, bad = 0;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = r[i];
+        if (!isfinite(v)) bad = 1;
+        if (v > best) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) { s_val[wid] = best; s_idx[wid] = bi; s_bad[wid] = bad; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+            if (s_val[w] > best || (s_val[w] == best && s_idx[w] < bi)) { best = s_val[w]; bi = s_idx[w]; }
+            bad |= s_bad[w];
+        }
+        pval[row * ARGMAX_SPLIT + part] = best;
+        pidx[(row * ARGMAX_SPLIT + part) * 2] = bi;
+        pidx[(row * ARGMAX_SPLIT + part) * 2 + 1] = bad;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx,
+                                    int* __restrict__ ids, int* __restrict__ nonfinite) {
+    const int row = blockIdx.x, lane = threadIdx.x;     // 32 threads, one per slice
+    float best = pval[row * ARGMAX_SPLIT + lane];
+    int bi = pidx[(row * ARGMAX_SPLIT + lane) * 2], bad = pidx[(row * ARGMAX_SPLIT + lane) * 2 + 1];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { ids[row] = bi == 0x7fffffff ? 0 : bi; nonfinite[row] = bad; }
+}
+
+// scratch: n_rows * ARGMAX_SPLIT floats and 2 * n_rows * ARGMAX_SPLIT ints (may be null for narrow rows)
 GESSO_API int gesso_argmax_rows(const float* logits, int n_rows, int V, int* ids, int* nonfinite,
-                                cudaStream_t stream) {
+                                float* scratch_val, int* scratch_idx, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0) return GESSO_ERR_BAD_SIZE;
-    argmax_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, ids, nonfinite);
+    if (V < 8192 || !scratch_val || !scratch_idx || n_rows > 65535) {
+        argmax_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, ids, nonfinite);
+        return launch_status();
+    }
+    argmax_partial_kernel<<<dim3(ARGMAX_SPLIT, n_rows), 256, 0, stream>>>(logits, V, scratch_val, scratch_idx);
+    argmax_final_kernel<<<n_rows, 32, 0, stream>>>(scratch_val, scratch_idx, ids, nonfinite);
     return launch_status();
 }
 

@@ -88,6 +88,8 @@ __global__ void conv_mix_update_small_kernel(const T* __restrict__ bcx, const fl
                                              const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
                                              const int* __restrict__ slots, T* __restrict__ out, int n_segs,
                                              int H, int L) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int s = blockIdx.x;
     if (c >= H || s >= n_segs) return;
@@ -142,11 +144,11 @@ GESSO_API int gesso_short_conv(const void* bcx, int dtype, const float* in_bias,
     if (max_seg_len <= 8 && L <= 8) {
         dim3 grid(n_segs, cblocks);
         if (dtype == GESSO_F32)
-            conv_mix_update_small_kernel<float, 8><<<grid, threads, 0, stream>>>(
+            launch_pdl(conv_mix_update_small_kernel<float, 8>, grid, dim3(threads), 0, stream,
                 (const float*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_start, seg_pos0, slots,
                 (float*)out, n_segs, H, L);
         else
-            conv_mix_update_small_kernel<bf16, 8><<<grid, threads, 0, stream>>>(
+            launch_pdl(conv_mix_update_small_kernel<bf16, 8>, grid, dim3(threads), 0, stream,
                 (const bf16*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_start, seg_pos0, slots,
                 (bf16*)out, n_segs, H, L);
         return launch_status();

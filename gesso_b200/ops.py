@@ -4,12 +4,15 @@ Each function checks device, dtype, layout and sizes of its ``torch`` tensors,
 launches one kernel (or a short fixed sequence) on the current CUDA stream and
 returns the output tensor.  Nothing here computes on the CPU and nothing falls
 back to a library implementation of the same operation; the only library call
-is the dense bfloat16 matrix product (cuBLAS through ``torch.mm``), where the
-reference also calls a BLAS (src/Operators/cpu.jl:629-630).
+is the dense bfloat16 matrix product (cuBLAS through ``torch.mm``) for steps of
+17 to 1023 tokens, where the reference also calls a BLAS
+(src/Operators/cpu.jl:629-630); fewer tokens take the skinny kernel, more take
+the tcgen05 kernel.
 """
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -237,6 +240,20 @@ def skinny_takes(M: int, w: torch.Tensor, x_dtype) -> bool:
             and N >= 16 and N % 16 == 0 and K >= 32 and K % 32 == 0)
 
 
+# Steps of at least this many tokens take this library's tcgen05 matrix product (TMA-fed, accumulators
+# in tensor memory, residual add / SwiGLU in its epilogue); between the skinny kernel's rows and this
+# the library product is used, whose small-tile and split-K variants are faster there.
+TC_MIN_ROWS = int(os.environ.get("GESSO_TC_MIN_ROWS", "1024"))
+
+
+def tc_takes(M: int, w: torch.Tensor, x_dtype) -> bool:
+    """Whether the tcgen05 matrix product takes this product: bfloat16 operands, at least TC_MIN_ROWS
+    rows, inner and output sizes that are multiples of 8 (16-byte rows for TMA and vector stores)."""
+    N, K = w.shape
+    return (w.dtype == torch.bfloat16 and x_dtype == torch.bfloat16 and w.is_contiguous() and M >= TC_MIN_ROWS
+            and N >= 8 and N % 8 == 0 and K >= 8 and K % 8 == 0 and w.data_ptr() % 16 == 0)
+
+
 def _skinny(x, w, out, bias, epi):
     """x: bfloat16 tensor or LazyNorm with at most SKINNY_NORM_MAX_ROWS rows."""
     N, K = w.shape
@@ -277,6 +294,8 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch
         _skinny(_skinny_input(x), w, out, None, EPI_BF16 if out_dtype == torch.bfloat16 else EPI_F32)
         return out
     x = _as_tensor(x)
+    if tc_takes(M, w, x.dtype) and out_dtype in (torch.bfloat16, torch.float32):
+        return gemm_tcgen05(x, w, EPI_BF16 if out_dtype == torch.bfloat16 else EPI_F32)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         _cuda_contig(x, "x")
         if out_dtype == torch.bfloat16:
@@ -294,6 +313,9 @@ def linear_residual(x, w: torch.Tensor, h: torch.Tensor, bias: Optional[torch.Te
         _cuda_contig(h, "h", torch.float32)
         _skinny(_as_tensor(x), w, h, bias, EPI_RESID)
         return None
+    if tc_takes(M, w, x.dtype) and tuple(h.shape) == (M, w.shape[0]):
+        gemm_tcgen05(_as_tensor(x), w, EPI_RESID, out=h, bias=bias)
+        return None
     return linear(x, w, out_dtype=x.dtype)
 
 
@@ -304,6 +326,8 @@ def linear_swiglu(x, w_gate_up: torch.Tensor, packed: bool) -> torch.Tensor:
         out = torch.empty((M, w_gate_up.shape[0] // 2), dtype=torch.bfloat16, device=w_gate_up.device)
         _skinny(_skinny_input(x), w_gate_up, out, None, EPI_SWIGLU)
         return out
+    if packed and tc_takes(M, w_gate_up, x.dtype) and w_gate_up.shape[0] % 16 == 0:
+        return gemm_tcgen05(_as_tensor(x), w_gate_up, EPI_SWIGLU)
     return swiglu(linear(x, w_gate_up, out_dtype=x.dtype), packed)
 
 
@@ -313,7 +337,12 @@ def argmax_rows(logits: torch.Tensor):
     R, V = logits.shape
     ids = torch.empty((R,), dtype=torch.int32, device=logits.device)
     bad = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    _lib.check(_lib.library().gesso_argmax_rows(_p(logits), R, V, _p(ids), _p(bad), _stream()), "argmax_rows")
+    sv = si = None
+    if V >= 8192:      # wide rows are scanned by 32 blocks each; their partial results need scratch
+        sv = torch.empty((R * 32,), dtype=torch.float32, device=logits.device)
+        si = torch.empty((R * 64,), dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.library().gesso_argmax_rows(_p(logits), R, V, _p(ids), _p(bad), _p(sv), _p(si), _stream()),
+               "argmax_rows")
     return ids, bad
 
 

@@ -107,3 +107,20 @@ def test_trace_run_program(model_dirs, plain_logits, tmp_path):
     assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(tb.steps))]
     rows = tt.read_rows(tb, str(out), configs.TINY_A["vocab_size"])
     tt.compare_with_plain(rows, ref, TOL["float32"], "trace_run a/mixed/float32")
+
+
+def test_replay_through_the_tcgen05_product(model_dirs, plain_logits, tmp_path, monkeypatch):
+    """Steps of 17 tokens or more forced onto the tcgen05 matrix product (fused residual add and
+    SwiGLU epilogues included), on the tiny models, against the plain implementation."""
+    import gesso_b200
+    from gesso_b200 import ops
+    monkeypatch.setattr(ops, "TC_MIN_ROWS", 17)
+    for name in ("a", "c"):
+        reqs, ref = plain_logits(name)
+        model = gesso_b200.load(model_dirs[name], dtype="bfloat16", max_positions=1024)
+        for sched in ("whole", "mixed"):
+            tb, max_tokens = SCHEDULES[sched](reqs)
+            d = tmp_path / f"{name}_{sched}"
+            tt.run_in_process(model, tb, max_tokens, str(d))
+            tt.compare_with_plain(tt.read_rows(tb, str(d), model.vocab_size), ref, TOL["bfloat16"], f"tcgen05 {name}/{sched}")
+        ops.check_tc_status()
