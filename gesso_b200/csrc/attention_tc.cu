@@ -186,15 +186,17 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-    KVFrag<HD> cur, nxt;
+    // two blocks are in flight behind the one being computed (the kernel is bound by the KV stream)
+    KVFrag<HD> cur, nx1, nx2;
     int b = b0 + w;
     if (b < b1) load_block<HD>(cur, k_pages, v_pages, bt, b, page_size, nkv, kvh, g, t);
+    if (b + 4 < b1) load_block<HD>(nx1, k_pages, v_pages, bt, b + 4, page_size, nkv, kvh, g, t);
     for (; b < b1; b += 4) {
-        const bool more = b + 4 < b1;
-        if (more) load_block<HD>(nxt, k_pages, v_pages, bt, b + 4, page_size, nkv, kvh, g, t);
+        if (b + 8 < b1) load_block<HD>(nx2, k_pages, v_pages, bt, b + 8, page_size, nkv, kvh, g, t);
         const bool need_mask = (b * 16 + 15 > pos) || (b * 16 < lo);
         attend_block<HD>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask);
-        if (more) cur = nxt;
+        cur = nx1;
+        nx1 = nx2;
     }
     l[0] = quad_sum(l[0]);
     l[1] = quad_sum(l[1]);
@@ -254,8 +256,10 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         const int head = kvh * G + r;
         const size_t p0 = ((size_t)seg * nh + head) * n_splits;
         float M = -INFINITY;
+#pragma unroll 8
         for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(part_ml + (p0 + s) * 2));
         float L = 0.f, acc = 0.f;
+#pragma unroll 8
         for (int s = 0; s < n_splits; ++s) {
             const float ms = __ldcg(part_ml + (p0 + s) * 2);
             const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);

@@ -145,13 +145,17 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
         }
         return xb;
     };
-    uint4 xc[XC > 0 ? XC : 1][NT];
-    if (XC > 0) {
+    // Token-side fragments live in a small register queue: slot ii serves the items i = ii, ii + XD,
+    // ... of every tile.  With XC > 0 a tile has exactly XC items per warp and the queue is filled
+    // once; otherwise a slot is refilled right after it is used, XD items ahead, so that the L2
+    // latency of the activations never sits between the arrival of W and the MMA.
+    constexpr int XD = XC > 0 ? XC : 4;
+    const int CH_pad = ((CH + XD - 1) / XD) * XD;
+    uint4 xq[XD][NT];
 #pragma unroll
-        for (int i = 0; i < XC; ++i)
+    for (int i = 0; i < XD; ++i)
 #pragma unroll
-            for (int j = 0; j < NT; ++j) xc[i][j] = load_x(w + i * SK_WARPS, j);
-    }
+        for (int j = 0; j < NT; ++j) xq[i][j] = load_x(w + i * SK_WARPS, j);
 
     float acc[NT][4];
 #pragma unroll
@@ -161,15 +165,21 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     for (int tk = 0; tk < my_tiles; ++tk) {
         const int tile = blockIdx.x + tk * gridDim.x;
 #pragma unroll 1
-        for (int i0 = 0; i0 < CH; i0 += (XC > 0 ? XC : 1)) {
+        for (int i0 = 0; i0 < CH; i0 += XD) {
 #pragma unroll
-            for (int ii = 0; ii < (XC > 0 ? XC : 1); ++ii) {
+            for (int ii = 0; ii < XD; ++ii) {
                 const int i = i0 + ii;
                 if (i >= CH) break;
                 const int c = w + i * SK_WARPS;
                 uint4 xb[NT];
 #pragma unroll
-                for (int j = 0; j < NT; ++j) xb[j] = XC > 0 ? xc[ii][j] : load_x(c, j);
+                for (int j = 0; j < NT; ++j) xb[j] = xq[ii][j];
+                if (XC == 0) {
+                    int ni = i + XD;
+                    if (ni >= CH_pad) ni = ii;            // the same slot of the next tile
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) xq[ii][j] = load_x(w + ni * SK_WARPS, j);
+                }
                 cp_async_wait<SK_STAGES - 1>();           // the oldest group (this item) has landed
                 const uint4 fa = slot[c_stage * stage_stride];
                 const uint4 fb = RSLOTS == 2 ? slot[c_stage * stage_stride + SK_WARPS * 32] : make_uint4(0, 0, 0, 0);
