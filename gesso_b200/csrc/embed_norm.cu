@@ -67,11 +67,88 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     for (int c = threadIdx.x; c < H; c += blockDim.x) orow[c] = from_f32<TO>((srow[c] / denom) * w[c]);
 }
 
+// The same, four elements at a time, the row kept in registers (H a multiple of 4, at most 8192):
+// the form steps with many tokens take, where the kernel is bound by its memory traffic.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x), b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&a);
+    u.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+#define NORM_VEC_THREADS 256
+#define NORM_VEC_MAX 8
+
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(NORM_VEC_THREADS)
+add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ delta_bias,
+                       const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
+                       int H) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* hrow = h + (size_t)src * H;
+    const TD* drow = delta ? delta + (size_t)src * H : nullptr;
+    const int nv = H >> 2;
+    float4 x[NORM_VEC_MAX];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NORM_VEC_MAX; ++v) {
+        const int i = (threadIdx.x + v * NORM_VEC_THREADS) * 4;
+        if (i < nv * 4) {
+            float4 a = load4(hrow + i);
+            if (drow) {
+                float4 d = load4(drow + i);
+                if (delta_bias) {
+                    const float4 b = load4(delta_bias + i);
+                    d.x += b.x; d.y += b.y; d.z += b.z; d.w += b.w;
+                }
+                a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+                if (!rows) store4(hrow + i, a);
+            }
+            x[v] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    ss = block_sum(ss, red);
+    const float denom = sqrtf(ss / (float)H + eps);
+    TO* orow = out + (size_t)r * H;
+#pragma unroll
+    for (int v = 0; v < NORM_VEC_MAX; ++v) {
+        const int i = (threadIdx.x + v * NORM_VEC_THREADS) * 4;
+        if (i < nv * 4) {
+            const float4 ww = load4(w + i);
+            store4(orow + i, make_float4((x[v].x / denom) * ww.x, (x[v].y / denom) * ww.y, (x[v].z / denom) * ww.z,
+                                         (x[v].w / denom) * ww.w));
+        }
+    }
+}
+
 GESSO_API int gesso_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* delta_bias,
                                 const float* w, float eps, void* out, int out_dtype, const int* rows,
                                 int n_rows, int H, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return GESSO_ERR_BAD_SIZE;
+    if (H % 4 == 0 && H <= 4 * NORM_VEC_THREADS * NORM_VEC_MAX) {
+#define VLAUNCH(TD, TO)                                                                             \
+    add_rmsnorm_vec_kernel<TD, TO><<<n_rows, NORM_VEC_THREADS, 0, stream>>>(h, (const TD*)delta, delta_bias, w, eps, \
+                                                                             (TO*)out, rows, H)
+        if (delta_dtype == GESSO_F32 && out_dtype == GESSO_F32) VLAUNCH(float, float);
+        else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_BF16) VLAUNCH(bf16, bf16);
+        else if (delta_dtype == GESSO_F32 && out_dtype == GESSO_BF16) VLAUNCH(float, bf16);
+        else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_F32) VLAUNCH(bf16, float);
+        else return GESSO_ERR_BAD_DTYPE;
+#undef VLAUNCH
+        return launch_status();
+    }
     int threads = 128;
     while (threads < 1024 && threads * 4 < H) threads <<= 1;
     const size_t smem = (size_t)H * sizeof(float);

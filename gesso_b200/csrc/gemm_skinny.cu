@@ -47,7 +47,7 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 }
 
 #define SK_WARPS 8
-#define SK_STAGES 10      // chunks in flight per thread (2 x 16 bytes each)
+#define SK_STAGES_FOR(ROWS) (160 / (ROWS))   // chunks in flight per thread: 10 of 32 bytes or 20 of 16 bytes
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -70,6 +70,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                    float eps, const bf16* __restrict__ W, void* __restrict__ out, const float* __restrict__ bias,
                    int M, int N, int K) {
     constexpr int RSLOTS = ROWS / 8;                      // 16-byte pieces per thread and chunk
+    constexpr int STAGES = SK_STAGES_FOR(ROWS);           // ring depth: 80 KB of W in flight per block
     extern __shared__ uint4 ring[];                       // [stage][RSLOTS][256 threads]
     __shared__ float part[2][SK_WARPS][ROWS][NT * 8 + 1];
     __shared__ float rinv[NT * 8];
@@ -96,12 +97,12 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
             }
             ++p_item;
             if (++p_i == CH) { p_i = 0; p_tile += gridDim.x; }
-            if (++p_stage == SK_STAGES) p_stage = 0;
+            if (++p_stage == STAGES) p_stage = 0;
         }
         cp_async_commit();                                // an empty group keeps the count in step
     };
 #pragma unroll
-    for (int sidx = 0; sidx < SK_STAGES; ++sidx) issue();   // start the stream before anything else
+    for (int sidx = 0; sidx < STAGES; ++sidx) issue();   // start the stream before anything else
     // The weights do not depend on earlier kernels; everything below does.  Let the next kernel in
     // (it starts its own weight stream) and wait for the producers of the activations.
     pdl_launch_dependents();
@@ -180,10 +181,10 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
 #pragma unroll
                     for (int j = 0; j < NT; ++j) xq[ii][j] = load_x(w + ni * SK_WARPS, j);
                 }
-                cp_async_wait<SK_STAGES - 1>();           // the oldest group (this item) has landed
+                cp_async_wait<STAGES - 1>();              // the oldest group (this item) has landed
                 const uint4 fa = slot[c_stage * stage_stride];
                 const uint4 fb = RSLOTS == 2 ? slot[c_stage * stage_stride + SK_WARPS * 32] : make_uint4(0, 0, 0, 0);
-                if (++c_stage == SK_STAGES) c_stage = 0;
+                if (++c_stage == STAGES) c_stage = 0;
                 issue();                                  // refill the slot with the item SK_STAGES ahead
                 if (c < n_chunks) {
 #pragma unroll
@@ -236,7 +237,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     cp_async_wait<0>();
 }
 
-#define SK_RING_BYTES(ROWS) (SK_STAGES * ((ROWS) / 8) * SK_WARPS * 32 * 16)
+#define SK_RING_BYTES(ROWS) (SK_STAGES_FOR(ROWS) * ((ROWS) / 8) * SK_WARPS * 32 * 16)
 #define SK_MAX_BLOCKS (2 * 148)
 
 GESSO_API int gesso_skinny_gemm_takes(int M, int N, int K) {

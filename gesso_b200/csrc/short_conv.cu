@@ -56,6 +56,95 @@ __global__ void conv_mix_kernel(const T* __restrict__ bcx, const float* __restri
     out[(size_t)t * H + c] = from_f32<T>(cg * y);
 }
 
+// The same for VEC consecutive channels per thread (16-byte loads): the form long portions take.
+template <typename T> struct ConvVec;
+template <> struct ConvVec<float> { static constexpr int N = 4; };
+template <> struct ConvVec<bf16> { static constexpr int N = 8; };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float (&v)[ConvVec<T>::N]);
+template <>
+__device__ __forceinline__ void load_vec<float>(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+template <>
+__device__ __forceinline__ void load_vec<bf16>(const bf16* p, float (&v)[8]) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const unsigned u[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&u[i]);
+        v[2 * i] = __low2float(h2);
+        v[2 * i + 1] = __high2float(h2);
+    }
+}
+__device__ __forceinline__ void store_vec(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store_vec(bf16* p, const float (&v)[8]) {
+    unsigned u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        u[i] = *reinterpret_cast<unsigned*>(&h2);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(u[0], u[1], u[2], u[3]);
+}
+
+template <typename T>
+__global__ void conv_mix_vec_kernel(const T* __restrict__ bcx, const float* __restrict__ in_bias,
+                                    const float* __restrict__ taps, const float* __restrict__ conv_bias,
+                                    const float* __restrict__ state, long long slot_stride,
+                                    const int* __restrict__ seg_of_token, const int* __restrict__ seg_start,
+                                    const int* __restrict__ seg_pos0, const int* __restrict__ slots,
+                                    T* __restrict__ out, int n_tokens, int H, int L) {
+    constexpr int V = ConvVec<T>::N;
+    const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    const int t = blockIdx.x;
+    if (c0 >= H || t >= n_tokens) return;
+    const int s = seg_of_token[t];
+    const int off = t - seg_start[s];
+    const int pos = seg_pos0[s] + off;
+    const float* st = state + (size_t)slots[s] * slot_stride;
+    float y[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) y[v] = 0.f;
+    for (int p = 0; p < L; ++p) {
+        const int back = (L - 1) - p;          // how many tokens before t (0: the token itself)
+        float val[V];
+        if (back > pos) {
+#pragma unroll
+            for (int v = 0; v < V; ++v) val[v] = 0.f;
+        } else if (back <= off) {
+            const T* row = bcx + (size_t)(t - back) * 3 * H;
+            float b[V], x[V];
+            load_vec<T>(row + c0, b);
+            load_vec<T>(row + 2 * H + c0, x);
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                if (in_bias) { b[v] += in_bias[c0 + v]; x[v] += in_bias[2 * H + c0 + v]; }
+                val[v] = b[v] * x[v];
+            }
+        } else {
+            const float* sp = st + (size_t)((L - 1) - (back - off)) * H + c0;
+#pragma unroll
+            for (int v = 0; v < V; ++v) val[v] = sp[v];
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) y[v] += val[v] * taps[(size_t)(c0 + v) * L + p];
+    }
+    float cg[V];
+    load_vec<T>(bcx + (size_t)t * 3 * H + H + c0, cg);
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        if (conv_bias) y[v] += conv_bias[c0 + v];
+        if (in_bias) cg[v] += in_bias[H + c0 + v];
+        y[v] *= cg[v];
+    }
+    store_vec(out + (size_t)t * H + c0, y);
+}
+
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ bcx, const float* __restrict__ in_bias,
                                          float* __restrict__ state, long long slot_stride,
@@ -154,6 +243,26 @@ GESSO_API int gesso_short_conv(const void* bcx, int dtype, const float* in_bias,
         return launch_status();
     }
     dim3 grid(n_tokens, cblocks), sgrid(n_segs, cblocks);
+    const int vec = dtype == GESSO_F32 ? 4 : 8;
+    if (H % vec == 0) {
+        // 16 bytes of channels per thread
+        const int vthreads = 128;
+        dim3 vgrid(n_tokens, (H / vec + vthreads - 1) / vthreads);
+        if (dtype == GESSO_F32) {
+            conv_mix_vec_kernel<float><<<vgrid, vthreads, 0, stream>>>(
+                (const float*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_of_token, seg_start, seg_pos0, slots,
+                (float*)out, n_tokens, H, L);
+            conv_state_update_kernel<float><<<sgrid, threads, 0, stream>>>((const float*)bcx, in_bias, state, slot_stride,
+                                                                           seg_start, seg_pos0, slots, n_segs, H, L);
+        } else {
+            conv_mix_vec_kernel<bf16><<<vgrid, vthreads, 0, stream>>>(
+                (const bf16*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_of_token, seg_start, seg_pos0, slots,
+                (bf16*)out, n_tokens, H, L);
+            conv_state_update_kernel<bf16><<<sgrid, threads, 0, stream>>>((const bf16*)bcx, in_bias, state, slot_stride,
+                                                                          seg_start, seg_pos0, slots, n_segs, H, L);
+        }
+        return launch_status();
+    }
     if (dtype == GESSO_F32) {
         conv_mix_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, in_bias, taps, conv_bias, state,
                                                              slot_stride, seg_of_token, seg_start, seg_pos0, slots,

@@ -262,6 +262,7 @@ def attention_reference(q, ks, vs, seg_lens_new, window):
 
 CASES = [  # nh, nkv, hd, page
     (4, 2, 16, 16), (4, 1, 24, 8), (6, 3, 32, 16), (8, 2, 64, 16), (16, 1, 64, 32), (3, 3, 96, 16), (4, 2, 128, 16),
+    (8, 2, 64, 32), (4, 2, 64, 16), (8, 1, 64, 16), (4, 1, 128, 48),
 ]
 
 
