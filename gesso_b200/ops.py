@@ -366,7 +366,7 @@ _lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, 
                                         _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P, _lib.P,
                                         _lib.P, _lib.P])
 _lib.declare("gesso_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
-                                         _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.P])
+                                         _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P])
 
 SM_COUNT = 148   # B200
 
@@ -415,7 +415,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
 def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_table: torch.Tensor, seg_start: torch.Tensor, seg_pos0: torch.Tensor,
                       tile_seg: torch.Tensor, tile_q0: torch.Tensor, window: Optional[int],
-                      scale: float) -> torch.Tensor:
+                      scale: float, variant: int = 0) -> torch.Tensor:
     _cuda_contig(q, "q", torch.bfloat16)
     N, nh, hd = q.shape
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
@@ -423,7 +423,7 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     _lib.check(_lib.library().gesso_prefill_attention(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(seg_start),
         _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), _p(out), nh, nkv, hd, int(window or 0),
-        float(scale), _stream()), "prefill_attention")
+        float(scale), int(variant), _stream()), "prefill_attention")
     return out
 
 
