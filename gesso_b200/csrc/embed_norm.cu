@@ -64,7 +64,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     ss = block_sum(ss, red);
     const float denom = sqrtf(ss / (float)H + eps);
     TO* orow = out + (size_t)r * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) orow[c] = from_f32<TO>((srow[c] / denom) * w[c]);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) orow[c] = from_f32<TO>((srow[c] / denom) * (w ? w[c] : 1.f));
 }
 
 // The same, four elements at a time, the row kept in registers (H a multiple of 4, at most 8192):
@@ -125,7 +125,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, cons
     for (int v = 0; v < NORM_VEC_MAX; ++v) {
         const int i = (threadIdx.x + v * NORM_VEC_THREADS) * 4;
         if (i < nv * 4) {
-            const float4 ww = load4(w + i);
+            const float4 ww = w ? load4(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
             store4(orow + i, make_float4((x[v].x / denom) * ww.x, (x[v].y / denom) * ww.y, (x[v].z / denom) * ww.z,
                                          (x[v].w / denom) * ww.w));
         }

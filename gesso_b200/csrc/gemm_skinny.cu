@@ -74,6 +74,11 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     extern __shared__ uint4 ring[];                       // [stage][RSLOTS][256 threads]
     __shared__ float part[2][SK_WARPS][ROWS][NT * 8 + 1];
     __shared__ float rinv[NT * 8];
+    __shared__ float ssw[SK_WARPS][NT * 8];
+    // NORM with norm_w == nullptr: the norm's weight was folded into W's columns by the caller.  Then
+    // X = bf16(h) goes into the MMA as it is, sum(h^2) is gathered from the very fragments the warps
+    // load anyway, and 1/sqrt(mean(h^2) + eps) scales the result in the epilogue: no extra pass over h.
+    const bool folded = NORM && norm_w == nullptr;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int n_chunks = K / 32;
     const int CH = (n_chunks + SK_WARPS - 1) / SK_WARPS;  // loop steps per tile (chunk w + 8 i, if it exists)
@@ -108,7 +113,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     pdl_launch_dependents();
     pdl_wait();
 
-    if (NORM) {
+    if (NORM && !folded) {
         // 1 / sqrt(mean(h^2) + eps) of every token row; warp w takes rows w, w+8, ...
         for (int m = w; m < M; m += SK_WARPS) {
             const float4* row = reinterpret_cast<const float4*>(h_in + (size_t)m * K);
@@ -125,12 +130,25 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     }
 
     // the token side of the product for chunk c and token tile j
-    auto load_x = [&](int c, int j) -> uint4 {
+    float ssq[NT];                                        // folded norm: this thread's share of sum(h^2)
+#pragma unroll
+    for (int j = 0; j < NT; ++j) ssq[j] = 0.f;
+    auto load_x = [&](int c, int j, bool count) -> uint4 {
         const int m = j * 8 + g;
         const int k = c * 32 + 8 * t;
         uint4 xb = make_uint4(0, 0, 0, 0);
         if (m < M && c < n_chunks) {
-            if (NORM) {
+            if (NORM && folded) {
+                const float4 h0 = *reinterpret_cast<const float4*>(h_in + (size_t)m * K + k);
+                const float4 h1 = *reinterpret_cast<const float4*>(h_in + (size_t)m * K + k + 4);
+                if (count)
+                    ssq[j] += h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w + h1.x * h1.x + h1.y * h1.y +
+                              h1.z * h1.z + h1.w * h1.w;
+                xb.x = pack2(h0.x, h0.y);
+                xb.y = pack2(h0.z, h0.w);
+                xb.z = pack2(h1.x, h1.y);
+                xb.w = pack2(h1.z, h1.w);
+            } else if (NORM) {
                 const float4 h0 = *reinterpret_cast<const float4*>(h_in + (size_t)m * K + k);
                 const float4 h1 = *reinterpret_cast<const float4*>(h_in + (size_t)m * K + k + 4);
                 const float4 w0 = *reinterpret_cast<const float4*>(norm_w + k);
@@ -156,7 +174,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
 #pragma unroll
     for (int i = 0; i < XD; ++i)
 #pragma unroll
-        for (int j = 0; j < NT; ++j) xq[i][j] = load_x(w + i * SK_WARPS, j);
+        for (int j = 0; j < NT; ++j) xq[i][j] = load_x(w + i * SK_WARPS, j, true);
 
     float acc[NT][4];
 #pragma unroll
@@ -177,9 +195,10 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                 for (int j = 0; j < NT; ++j) xb[j] = xq[ii][j];
                 if (XC == 0) {
                     int ni = i + XD;
-                    if (ni >= CH_pad) ni = ii;            // the same slot of the next tile
+                    const bool wrapped = ni >= CH_pad;
+                    if (wrapped) ni = ii;                 // the same slot of the next tile
 #pragma unroll
-                    for (int j = 0; j < NT; ++j) xq[ii][j] = load_x(w + ni * SK_WARPS, j);
+                    for (int j = 0; j < NT; ++j) xq[ii][j] = load_x(w + ni * SK_WARPS, j, tk == 0 && !wrapped);
                 }
                 cp_async_wait<STAGES - 1>();              // the oldest group (this item) has landed
                 const uint4 fa = slot[c_stage * stage_stride];
@@ -206,7 +225,26 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
             }
             acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
         }
+        if (NORM && folded && tk == 0) {
+            // every chunk of h has passed through some warp during the first tile: finish sum(h^2)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                float v = ssq[j];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                if (t == 0) ssw[w][j * 8 + g] = v;
+            }
+        }
         __syncthreads();      // one barrier per tile: `part` is double buffered
+        if (NORM && folded && tk == 0) {
+            if (threadIdx.x < NT * 8) {
+                float v = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < SK_WARPS; ++ww) v += ssw[ww][threadIdx.x];
+                rinv[threadIdx.x] = 1.f / sqrtf(v / (float)K + eps);
+            }
+            __syncthreads();
+        }
         const int n0 = tile * ROWS;
         if (EPI == EPI_SWIGLU) {
             // 8 outputs per token: row r is gate, row r + 8 is up (ROWS == 16)
@@ -216,6 +254,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                 float gt = 0.f, up = 0.f;
 #pragma unroll
                 for (int ww = 0; ww < SK_WARPS; ++ww) { gt += part[buf][ww][r][m]; up += part[buf][ww][(r + 8) % ROWS][m]; }
+                if (NORM && folded) { gt *= rinv[m]; up *= rinv[m]; }
                 reinterpret_cast<bf16*>(out)[(size_t)m * (N / 2) + tile * 8 + r] =
                     __float2bfloat16_rn((gt / (1.f + expf(-gt))) * up);
             }
@@ -226,6 +265,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                 float v = 0.f;
 #pragma unroll
                 for (int ww = 0; ww < SK_WARPS; ++ww) v += part[buf][ww][r][m];
+                if (NORM && folded) v *= rinv[m];
                 const size_t o = (size_t)m * N + n0 + r;
                 if (EPI == EPI_BF16) reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v);
                 else if (EPI == EPI_F32) reinterpret_cast<float*>(out)[o] = v;

@@ -67,16 +67,18 @@ def embed_gather(tokens: torch.Tensor, table: torch.Tensor, scale: float = 1.0) 
 
 
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor],
-                weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``h += delta (+ bias)`` in place (float32), returns ``rmsnorm(h) * weight`` in ``out_dtype``.
 
-    With ``rows`` only those rows are summed and normed, and ``h`` is left as it was.
+    With ``rows`` only those rows are summed and normed, and ``h`` is left as it was.  ``weight`` may
+    be ``None`` (no scaling: the weight was folded into the matrix that consumes the result).
     """
     _cuda_contig(h, "h", torch.float32)
-    _cuda_contig(weight, "weight", torch.float32)
     N, H = h.shape
-    _need(weight.numel() == H, "norm weight size differs from the row width")
+    if weight is not None:
+        _cuda_contig(weight, "weight", torch.float32)
+        _need(weight.numel() == H, "norm weight size differs from the row width")
     if delta is not None:
         _cuda_contig(delta, "delta")
         _need(tuple(delta.shape) == (N, H), "delta shape differs from h")
@@ -190,6 +192,12 @@ def swiglu(gu: torch.Tensor, packed: bool = False) -> torch.Tensor:
     return out
 
 
+def fold_norm_weight(w: torch.Tensor, norm_weight: torch.Tensor) -> torch.Tensor:
+    """``w[n, k] * norm_weight[k]``: a matrix that takes ``x / rms(x)`` instead of ``rmsnorm(x) * weight``.
+    The product is formed in float32 and rounded once to the matrix's own type."""
+    return (w.float() * norm_weight.float()[None, :]).to(w.dtype).contiguous()
+
+
 def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """Fused gate/up matrix [2F, H] in groups of 16 rows: 8 gate rows, then the matching 8 up rows
     (the layout whose SwiGLU the skinny matrix product can apply in its epilogue).  F % 8 == 0."""
@@ -217,9 +225,10 @@ class LazyNorm:
     """A norm that has not run yet: ``rmsnorm(h) * weight`` of the float32 residual stream.
 
     The skinny matrix product can apply it in its prologue; every other consumer calls
-    :meth:`materialize`, which runs the norm kernel."""
+    :meth:`materialize`, which runs the norm kernel.  ``weight`` is ``None`` when the consumer's
+    matrix already carries the norm's weight (see :func:`fold_norm_weight`)."""
 
-    def __init__(self, h: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype):
+    def __init__(self, h: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype):
         self.h, self.weight, self.eps, self.dtype = h, weight, float(eps), out_dtype
         self.shape = h.shape
 

@@ -75,6 +75,11 @@ class GQAttention(Mixer):
         self.position.bind({}, rt)
         self.rt = rt
 
+    def fold_input_scale(self, scale) -> bool:
+        self.w_q = ops.fold_norm_weight(self.w_q, scale)
+        self.w_qkv = ops.fold_norm_weight(self.w_qkv, scale)
+        return True
+
     def forward(self, x, ctx, cache, residual=None):
         writes = cache.writes
         qkv = ops.linear(x, self.w_qkv if writes else self.w_q, out_dtype=x.dtype)

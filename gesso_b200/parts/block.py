@@ -43,6 +43,13 @@ class PreNormBlock:
     def bind(self, tensors, rt) -> None:
         for prefix, part in self.parts():
             part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, rt)
+        # a norm's weight may move into the first matrix of the part it feeds (bfloat16 runs): the
+        # norm then only divides by the root mean square, which the consumer's skinny matrix product
+        # gathers on the fly
+        for norm, consumer in ((self.mixer_norm, self.mixer), (self.ff_norm, self.feed_forward)):
+            fold = getattr(norm, "fold_into", None)
+            if fold is not None:
+                fold(consumer)
 
     def forward(self, h, pending, ctx, cache):
         """``pending`` is the previous sublayer's (delta, bias) not yet added to ``h`` (or Nones).

@@ -43,6 +43,10 @@ class SwiGLU(FeedForward):
             self.w_gate_up = torch.cat([g.to(common), u.to(common)], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
+    def fold_input_scale(self, scale) -> bool:
+        self.w_gate_up = ops.fold_norm_weight(self.w_gate_up, scale)
+        return True
+
     def forward(self, x, ctx, residual=None):
         a = ops.linear_swiglu(x, self.w_gate_up, self.packed)
         if residual is not None:

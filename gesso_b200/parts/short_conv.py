@@ -58,6 +58,10 @@ class ShortConv(Mixer):
         self.b_conv = tensors.get("conv.bias")
         self.b_out = tensors.get("out_proj.bias")
 
+    def fold_input_scale(self, scale) -> bool:
+        self.w_in = ops.fold_norm_weight(self.w_in, scale)
+        return True
+
     def forward(self, x, ctx, cache, residual=None):
         bcx = ops.linear(x, self.w_in, out_dtype=x.dtype)
         y = ops.short_conv(bcx, self.b_in, self.taps, self.b_conv, cache.state, ctx.seg_of_token,

@@ -464,3 +464,27 @@ def test_skinny_gemm_refuses_other_sizes():
     x = torch.randn(4, 200, device=DEV).to(torch.bfloat16)
     w2 = torch.randn(64, 200, device=DEV).to(torch.bfloat16)
     assert rel_err(ops.linear(x, w2), x.double() @ w2.double().T) < BF16_EPS
+
+
+@pytest.mark.parametrize("M", [1, 7, 8, 13, 16])
+@pytest.mark.parametrize("N,K", [(64, 64), (6144, 2048), (48, 8192), (32, 352)])
+def test_skinny_gemm_folded_norm(M, N, K):
+    """The norm's weight folded into the matrix: the kernel takes bf16(h), gathers sum(h^2) from the
+    fragments it loads and scales in the epilogue.  Compared with the exact rmsnorm(h)*w @ W^T."""
+    from gesso_b200 import ops
+    g = torch.Generator().manual_seed(M * 7 + N + K)
+    h = (3 * torch.randn(M, K, generator=g)).to(DEV)
+    nw = (1 + 0.2 * torch.randn(K, generator=g)).to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    wf = ops.fold_norm_weight(w, nw)
+    exact = P.rmsnorm(h.double().cpu(), nw.double().cpu(), 1e-5) @ w.double().cpu().T
+    lazy = ops.LazyNorm(h, None, 1e-5, torch.bfloat16)
+    assert rel_err(ops.linear(lazy, wf, out_dtype=torch.float32), exact) < BF16_EPS
+    assert rel_err(ops.linear(lazy, wf), exact) < 2 * BF16_EPS
+    # the materialised form (norm kernel without a weight, then any product) agrees
+    assert rel_err(lazy.materialize().double() @ wf.double().T, exact) < BF16_EPS
+    if N % 16 == 0:
+        F = N // 2
+        a = ops.linear_swiglu(lazy, ops.pack_gate_up(wf[:F].contiguous(), wf[F:].contiguous()), True)
+        gg, uu = exact[:, :F], exact[:, F:]
+        assert rel_err(a, (gg / (1 + torch.exp(-gg))) * uu) < 2 * BF16_EPS

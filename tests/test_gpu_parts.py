@@ -34,6 +34,12 @@ def tiny_spec(mixer, ff=None, H=48, V=64, n_layers=1, schedule=None, arch="PartT
                      schedule=schedule or default_schedule(len(blocks)), final_norm=norm, tie_embedding=True)
 
 
+def folded_input(x, w, name, dtype):
+    """In bfloat16 runs a block folds its norm's weight into the first matrix of the part the norm
+    feeds, so that part, called alone with input x, computes what the plain part computes on x * weight."""
+    return x.double() * w[name] if dtype == torch.bfloat16 else x.double()
+
+
 def build_model(spec, dtype, seed=0, max_positions=256):
     from gesso_b200.engine import Model
     from gesso_b200.weights import random_tensors
@@ -118,7 +124,7 @@ def test_attention_part_alone(dtype, window):
         outs.append(delta)
         eng.cache.commit("r", b - a)
     p = "layers.0.mixer."
-    want = P.attention_mixer(x.double(), w[p + "q_proj.weight"], w[p + "k_proj.weight"], w[p + "v_proj.weight"],
+    want = P.attention_mixer(folded_input(x, w, "layers.0.mixer_norm.weight", dtype), w[p + "q_proj.weight"], w[p + "k_proj.weight"], w[p + "v_proj.weight"],
                              w[p + "o_proj.weight"], w[p + "q_norm.weight"], w[p + "k_norm.weight"], 6, 2, 8, 1e-5,
                              777.0, window)
     assert rel_err(torch.cat(outs), want) < (1e-5 if dtype == torch.float32 else 4 * BF16_EPS)
@@ -145,7 +151,8 @@ def test_short_conv_part_alone(dtype, kernel, bias):
         outs.append(delta.double() + (dbias.double() if dbias is not None else 0))
         eng.cache.commit("r", b - a)
     p = "layers.0.mixer."
-    want = P.short_conv_mixer(x.double(), w[p + "in_proj.weight"], w[p + "conv.weight"], w[p + "out_proj.weight"],
+    want = P.short_conv_mixer(folded_input(x, w, "layers.0.mixer_norm.weight", dtype), w[p + "in_proj.weight"],
+                              w[p + "conv.weight"], w[p + "out_proj.weight"],
                               w.get(p + "in_proj.bias"), w.get(p + "conv.bias"), w.get(p + "out_proj.bias"))
     assert rel_err(torch.cat(outs), want) < (1e-5 if dtype == torch.float32 else 4 * BF16_EPS)
 
@@ -158,7 +165,8 @@ def test_feed_forward_part_alone(dtype):
     x = torch.randn(11, 48).to(dtype)
     delta, bias = part.forward(x.to(DEV), None)
     p = "layers.0.feed_forward."
-    want = P.swiglu_ffn(x.double(), w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
+    want = P.swiglu_ffn(folded_input(x, w, "layers.0.ff_norm.weight", dtype), w[p + "gate_proj.weight"],
+                        w[p + "up_proj.weight"], w[p + "down_proj.weight"])
     assert bias is None and rel_err(delta, want) < (1e-5 if dtype == torch.float32 else 4 * BF16_EPS)
 
 
