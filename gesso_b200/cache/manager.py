@@ -27,6 +27,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
+
 from ..errors import ErrorCode, GessoError, invalid, resource
 
 FREED = -1   # block-table entry of a page that was given back (window) or never held
@@ -84,6 +86,7 @@ class _Request:
     length: int = 0                               # positions committed so far
     reserved: int = 0                             # positions covered by pages (>= length)
     tables: List[List[int]] = field(default_factory=list)   # per group: page id per page index
+    rows: List[np.ndarray] = field(default_factory=list)    # the same as fixed-width int32 rows (FREED padded)
     fresh: bool = True                            # state slot not zeroed yet
 
 
@@ -114,7 +117,9 @@ class CacheManager:
         if req_id in self._req:
             raise invalid(f"request {req_id!r} is already live")
         slot = self.slots.alloc()
-        self._req[req_id] = _Request(slot=slot, tables=[[] for _ in self.groups])
+        self._req[req_id] = _Request(slot=slot, tables=[[] for _ in self.groups],
+                                     rows=[np.full((self.max_pages_per_request,), FREED, dtype=np.int32)
+                                           for _ in self.groups])
         return slot
 
     def is_live(self, req_id: Hashable) -> bool:
@@ -170,9 +175,10 @@ class CacheManager:
         for n, p, g in zip(need, self.pools, self.groups):
             if n > p.free_count:
                 raise resource(f"group {g.name}: {n} pages needed, {p.free_count} free")
-        for n, p, t in zip(need, self.pools, r.tables):
+        for n, p, t, row in zip(need, self.pools, r.tables, r.rows):
             for _ in range(n):
                 t.append(p.alloc())
+                row[len(t) - 1] = t[-1]
         r.reserved = max(r.reserved, r.length + n_new)
 
     def commit(self, req_id: Hashable, n_new: int) -> None:
@@ -182,7 +188,7 @@ class CacheManager:
             raise GessoError(ErrorCode.INTERNAL,
                              f"request {req_id!r}: commit of {n_new} beyond the reserved {r.reserved}")
         r.length += n_new
-        for g, p, t in zip(self.groups, self.pools, r.tables):
+        for g, p, t, row in zip(self.groups, self.pools, r.tables, r.rows):
             if g.window is None:
                 continue
             # the next query sits at position >= length and reads keys >= length - window + 1
@@ -192,6 +198,7 @@ class CacheManager:
                 if t[i] != FREED:
                     p.free(t[i])
                     t[i] = FREED
+                    row[i] = FREED
 
     def release(self, req_id: Hashable) -> None:
         """The request ended: its pages and its slot go back to the pools."""
@@ -205,6 +212,11 @@ class CacheManager:
 
     def block_table(self, req_id: Hashable, group: int) -> List[int]:
         return self._get(req_id).tables[group]
+
+    def block_table_row(self, req_id: Hashable, group: int) -> np.ndarray:
+        """The block table as a fixed-width int32 row (``FREED`` where no page is held); a view that the
+        manager keeps up to date, for packing a step's metadata without a conversion."""
+        return self._get(req_id).rows[group]
 
     # ---- accounting (derived, as the reference derives kv_bytes from its page table,
     #      src/Inference/kv_manager.jl:446-469) ---------------------------------------------------

@@ -112,6 +112,22 @@ def pack_step(entries: List[StepEntry], starts: List[int], slots: List[int],
     rows = out[o["logit_rows"]:o["logit_rows"] + layout.n_rows]
     tile_seg = out[o["tile_seg"]:o["tile_seg"] + layout.n_tiles]
     tile_q0 = out[o["tile_q0"]:o["tile_q0"] + layout.n_tiles]
+    if layout.n_tokens == layout.n_segs:
+        # single tokens only (decoding): no per-entry loops
+        S = layout.n_segs
+        tok[:] = [e.tokens[0] for e in entries]
+        pos[:] = starts
+        seg[:] = np.arange(S, dtype=np.int32)
+        seg_start[:] = np.arange(S + 1, dtype=np.int32)
+        tile_seg[:] = seg
+        tile_q0[:] = 0
+        r = 0
+        for i, e in enumerate(entries):
+            for w in e.want:
+                rows[r] = i + w
+                r += 1
+        _pack_tail(entries, starts, slots, tables, layout, out, o)
+        return
     cur, r, nt = 0, 0, 0
     for i, e in enumerate(entries):
         n = len(e.tokens)
@@ -128,6 +144,10 @@ def pack_step(entries: List[StepEntry], starts: List[int], slots: List[int],
             r += 1
         cur += n
     seg_start[layout.n_segs] = cur
+    _pack_tail(entries, starts, slots, tables, layout, out, o)
+
+
+def _pack_tail(entries, starts, slots, tables, layout, out, o) -> None:
     out[o["seg_pos0"]:o["seg_pos0"] + layout.n_segs] = np.asarray(starts, dtype=np.int32)
     out[o["slots"]:o["slots"] + layout.n_segs] = np.asarray(slots, dtype=np.int32)
     for g in range(layout.n_groups):
@@ -135,5 +155,7 @@ def pack_step(entries: List[StepEntry], starts: List[int], slots: List[int],
         bt = bt.reshape(layout.n_segs, layout.max_pages)
         bt[:] = FREED
         for i, t in enumerate(tables[g]):
-            if t:
+            if isinstance(t, np.ndarray):
+                bt[i, :] = t                      # the manager's fixed-width row
+            elif t:
                 bt[i, :len(t)] = np.asarray(t, dtype=np.int32)

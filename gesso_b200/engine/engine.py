@@ -151,7 +151,7 @@ class Engine:
             if self.cache.take_fresh(e.req_id):
                 self.device_cache.zero_slot(slots[-1])
         n_groups = len(self.cache.groups)
-        tables = [[self.cache.block_table(e.req_id, g) for e in entries] for g in range(n_groups)]
+        tables = [[self.cache.block_table_row(e.req_id, g) for e in entries] for g in range(n_groups)]
         layout = StepLayout(n_tokens=sum(len(e.tokens) for e in entries), n_segs=len(entries),
                             n_rows=sum(len(e.want) for e in entries), n_groups=n_groups,
                             max_pages=self.cache.max_pages_per_request,

@@ -75,6 +75,19 @@ class Request:
         return self.prompt + self.generated
 
     @property
+    def length(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+    def tokens(self, start: int, n: int) -> List[int]:
+        """``sequence[start:start+n]`` without building the sequence (it is asked for every step)."""
+        p = len(self.prompt)
+        if start >= p:
+            return self.generated[start - p:start - p + n]
+        if start + n <= p:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.generated[:start + n - p]
+
+    @property
     def ids(self) -> List[int]:
         """Prompt plus new ids, the stopping id included (src/Inference/session.jl:1025-1034)."""
         return self.prompt + self.generated
@@ -163,6 +176,18 @@ class Scheduler:
         for r in [r for r in self.waiting if r.cancelled]:
             self.waiting.remove(r)
             self._finish(r, CANCELLED)
+
+        # steady decoding (nobody waits, everybody has exactly its last sampled token to run, and the
+        # pools hold a page for everyone who crosses a page border): nothing to decide
+        if not self.waiting and self.running and len(self.running) <= self.max_tokens_per_step \
+                and all(r.generated and self._left(r) == 1 for r in self.running):
+            ps = self.cache.page_size
+            at_border = sum(1 for r in self.running if self.cache.length(r.req_id) % ps == 0)
+            free = self.cache.free_pages()
+            if (not free or at_border <= min(free)) and \
+                    all(self.cache.length(r.req_id) < self.cache.max_positions for r in self.running):
+                plan.entries = [(r, r.fed, 1) for r in self.running]
+                return plan
 
         budget = self.max_tokens_per_step
         wants: Dict[object, Tuple[Request, int]] = {}
@@ -263,9 +288,8 @@ class Scheduler:
             return []
         entries, samplers = [], []
         for r, start, n in plan.entries:
-            seq = r.sequence
-            last = start + n == len(seq)
-            entries.append(StepEntry(r.req_id, seq[start:start + n], [n - 1] if last else []))
+            last = start + n == r.length
+            entries.append(StepEntry(r.req_id, r.tokens(start, n), [n - 1] if last else []))
             if last:
                 samplers.append(r)
         logits = self.engine.step(entries)

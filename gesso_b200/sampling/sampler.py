@@ -107,6 +107,11 @@ def select_tokens(logits: torch.Tensor, params: Sequence[SamplingParams],
         return []
     ids, bad = ops.argmax_rows(logits)
     sampled = [i for i, p in enumerate(params) if not p.greedy]
+    if not sampled and ids.data_ptr() + 4 * R == bad.data_ptr():
+        # all greedy: ids and flags sit in one buffer, one copy brings both
+        host = ids.new_empty(0).set_(ids.untyped_storage(), ids.storage_offset(), (2, R)).to("cpu").numpy()
+        return [GessoError(ErrorCode.NUMERICAL_INSTABILITY, "nonfinite logits; no token may be emitted")
+                if host[1, i] else int(host[0, i]) for i in range(R)]
     if sampled:
         temp = torch.tensor([params[i].temperature if not params[i].greedy else 1.0 for i in range(R)],
                             dtype=torch.float64)
