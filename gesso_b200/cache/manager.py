@@ -181,6 +181,45 @@ class CacheManager:
                 row[len(t) - 1] = t[-1]
         r.reserved = max(r.reserved, r.length + n_new)
 
+    def reserve_single_tokens(self, req_ids: Sequence[Hashable]):
+        """One more position for each request (a decoding step), all or none: returns
+        ``(starts, slots, fresh_slots, rows)`` where ``rows[g][i]`` is request i's block-table row in
+        group g.  The same checks as :meth:`reserve`, with one lookup per request."""
+        reqs = []
+        need = [0] * len(self.groups)
+        ps = self.page_size
+        for rid in req_ids:
+            r = self._req.get(rid)
+            if r is None:
+                raise invalid(f"request {rid!r} is not live")
+            if r.length + 1 > self.max_positions:
+                raise resource(f"request {rid!r}: {r.length}+1 positions exceed the context length "
+                               f"{self.max_positions}")
+            want = (r.length + ps) // ps                     # pages that cover length + 1 positions
+            for g, t in enumerate(r.tables):
+                if want > len(t):
+                    need[g] += want - len(t)
+            reqs.append((r, want))
+        for g, (k, p) in enumerate(zip(need, self.pools)):
+            if k > p.free_count:
+                raise resource(f"step needs {k} pages of group {self.groups[g].name}, {p.free_count} free")
+        starts, slots, fresh = [], [], []
+        rows: List[List[np.ndarray]] = [[] for _ in self.groups]
+        for r, want in reqs:
+            for g, (t, row, p) in enumerate(zip(r.tables, r.rows, self.pools)):
+                while len(t) < want:
+                    t.append(p.alloc())
+                    row[len(t) - 1] = t[-1]
+                rows[g].append(row)
+            if r.length + 1 > r.reserved:
+                r.reserved = r.length + 1
+            starts.append(r.length)
+            slots.append(r.slot)
+            if r.fresh:
+                r.fresh = False
+                fresh.append(r.slot)
+        return starts, slots, fresh, rows
+
     def commit(self, req_id: Hashable, n_new: int) -> None:
         """``n_new`` positions were written; windowed groups give back what no query will read."""
         r = self._get(req_id)

@@ -127,8 +127,36 @@ class Engine:
             self._pinned[i] = torch.empty((max(n, 4096),), dtype=torch.int32, pin_memory=True)
         return i, self._pinned[i]
 
+    def _prepare_single_tokens(self, entries: Sequence[StepEntry]):
+        """:meth:`_prepare` for a step of single tokens (decoding): one pass over the entries."""
+        V = self.model.vocab_size
+        seen = set()
+        for e in entries:
+            tok = e.tokens[0]
+            if not (0 <= tok < V):
+                raise invalid(f"step: token id {tok} of request {e.req_id!r} is outside the vocabulary (0..{V - 1})")
+            for w in e.want:
+                if w != 0:
+                    raise invalid(f"step: wanted place {w} of request {e.req_id!r} is outside its 1 tokens")
+            seen.add(e.req_id)
+        if len(seen) != len(entries):
+            raise invalid("step: a request appears twice in one step")
+        starts, slots, fresh, tables = self.cache.reserve_single_tokens([e.req_id for e in entries])
+        for slot in fresh:
+            self.device_cache.zero_slot(slot)
+        n = len(entries)
+        layout = StepLayout(n_tokens=n, n_segs=n, n_rows=sum(len(e.want) for e in entries),
+                            n_groups=len(self.cache.groups), max_pages=self.cache.max_pages_per_request, n_tiles=n)
+        size = layout.offsets()["_end"]
+        slot_i, host = self._pinned_buffer(size)
+        pack_step(list(entries), starts, slots, tables, layout, host.numpy()[:size])
+        self._all_rows = layout.n_rows == n
+        return layout, slot_i, host[:size], 1, max(starts) + 1
+
     def _prepare(self, entries: Sequence[StepEntry]):
         """Validate, reserve pages, zero fresh slots and pack the step's metadata on the host."""
+        if entries and all(len(e.tokens) == 1 for e in entries):
+            return self._prepare_single_tokens(entries)
         self._validate(entries)
         for e in entries:
             n = len(e.tokens)

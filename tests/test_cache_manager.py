@@ -150,3 +150,37 @@ def test_random_orders_lose_no_page(seed):
         m.release(r)
     assert m.pages_in_use() == [0] * len(m.groups) and m.slots_in_use() == 0
     assert reused, "pages were never used again: the pool is too large for this test"
+
+
+def test_single_token_reservation_equals_the_general_one():
+    """The decoding fast path hands out the same pages as ``reserve`` one request at a time, is all or
+    nothing, and reports a fresh slot exactly once."""
+    a, b = make(num_pages=14, page_size=4, slots=3, ctx=40, window=6), make(num_pages=14, page_size=4, slots=3, ctx=40, window=6)
+    for m in (a, b):
+        for r in ("x", "y", "z"):
+            m.admit(r)
+    fresh_seen = []
+    for step in range(13):
+        starts, slots, fresh, rows = a.reserve_single_tokens(["x", "y", "z"])
+        fresh_seen += fresh
+        for r in ("x", "y", "z"):
+            b.reserve(r, 1)
+        assert starts == [b.length(r) for r in ("x", "y", "z")] and slots == [b.slot(r) for r in ("x", "y", "z")]
+        for g in range(2):
+            for i, r in enumerate(("x", "y", "z")):
+                assert rows[g][i].tolist()[:len(b.block_table(r, g))] == b.block_table(r, g)
+                assert a.block_table(r, g) == b.block_table(r, g)
+        for r in ("x", "y", "z"):
+            a.commit(r, 1)
+            b.commit(r, 1)
+        a.check_invariants()
+    assert sorted(fresh_seen) == [0, 1, 2]
+    # all or nothing: 2 pages, three requests at a page border need 3 pages
+    c = make(num_pages=2, page_size=4, slots=3, ctx=40)
+    for r in ("x", "y", "z"):
+        c.admit(r)
+    with pytest.raises(GessoError):
+        c.reserve_single_tokens(["x", "y", "z"])
+    assert c.pages_in_use() == [0]
+    with pytest.raises(GessoError):
+        c.reserve_single_tokens(["nobody"])
