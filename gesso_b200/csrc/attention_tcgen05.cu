@@ -1,0 +1,321 @@
+// Flash prefill attention on the 5th-generation tensor cores (bfloat16, head size 64, paged cache).
+//
+// A block owns 128 query rows: 128/G consecutive tokens of one request times the G query heads of
+// one kv group, so a single copy of K and V serves every head of the group (the GQA map
+// h -> h / (nh/nkv) of src/Inference/Inference.jl:1398).  It walks the keys in blocks of 128:
+//
+//   TMA warp      Q once (3-D tensor map [token][head][feature], 128-byte swizzle); per key block 8
+//                 K pages ([slot][feature] rows of 128 bytes, 128-byte swizzle) and 8 V pages
+//                 ([feature][slot] rows of 32 bytes, 32-byte swizzle) into a two-stage ring;
+//   MMA thread    S[128 x 128] = Q K^T   (tcgen05.mma, M 128, N 128, K 4 x 16) into tensor memory;
+//                 O_blk[128 x 64] = P V  (A operand P read from tensor memory, B = one V page per
+//                 K = 16 step);
+//   4 softmax warps  one thread per query row: tcgen05.ld of its S row, scale by log2(e)/sqrt(d),
+//                 causal / window mask, running maximum and sum (no shuffles: a row is one thread),
+//                 P as packed bfloat16 back to tensor memory (tcgen05.st), then O += O_blk with the
+//                 running rescale, all in float32 registers.
+// Formulas: scores q.k/sqrt(d), query at position p reads keys max(0, p-window+1)..p, softmax, weighted
+// sum of values (src/Inference/Inference.jl:1201-1207, 1414-1457).  All waits are bounded and
+// report through the status word.  Two blocks fit an SM (80 KB of shared memory, 256 tensor-memory
+// columns each), so one block's softmax overlaps the other's tensor work.
+#include <math.h>
+
+#include "tcgen05.cuh"
+
+#define FA_HD 64
+#define FA_BK 128
+#define FA_STAGES 2
+#define FA_THREADS 192
+#define FA_LOG2E 1.4426950408889634f
+
+struct __align__(1024) FaSmem {
+    bf16 q[128 * FA_HD];                       // 16 KB
+    bf16 k[FA_STAGES][FA_BK * FA_HD];          // 16 KB per stage: 8 pages x [16][64]
+    bf16 v[FA_STAGES][FA_BK * FA_HD];          // 16 KB per stage: 8 pages x [64][16]
+    unsigned long long q_full, full[FA_STAGES], empty[FA_STAGES], s_full, p_ready, o_full;
+    unsigned tmem_base;
+};
+
+__global__ void __launch_bounds__(FA_THREADS)
+prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
+                                 int max_pages, int page_size, const int* __restrict__ seg_start,
+                                 const int* __restrict__ seg_pos0, const int* __restrict__ tile_seg,
+                                 const int* __restrict__ tile_q0, bf16* __restrict__ out, int nh, int nkv, int G,
+                                 int window, float scale_log2, int* __restrict__ status) {
+    extern __shared__ unsigned char fa_raw[];
+    FaSmem& s = *reinterpret_cast<FaSmem*>(((size_t)fa_raw + 1023) & ~(size_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int TOK = 128 / G;                      // tokens per block
+    const int sub = 64 / TOK;                     // blocks per 64-token tile of the step's tile list
+    // long tiles first: the queries at the end of a prompt have the most keys to read
+    const int bx = gridDim.x - 1 - blockIdx.x;
+    const int tile = bx / sub, kvh = blockIdx.y;
+    const int seg = tile_seg[tile];
+    const int t0 = seg_start[seg], n = seg_start[seg + 1] - t0;
+    const int q0 = tile_q0[tile] + (bx % sub) * TOK;
+    if (q0 >= n) return;                          // nothing of this block lies inside the portion
+    const int p0 = seg_pos0[seg];
+    const int rows_tok = min(TOK, n - q0);        // valid tokens of this block
+    const int pos_first = p0 + q0, pos_last = p0 + q0 + rows_tok - 1;
+    const int first_key = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int kb0 = first_key / FA_BK, kb1 = pos_last / FA_BK;         // key blocks kb0..kb1
+    const int n_blocks = kb1 - kb0 + 1;
+    const int* bt = block_table + (size_t)seg * max_pages;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&s.q_full, 1);
+        for (int i = 0; i < FA_STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
+        mbar_init(&s.s_full, 1);
+        mbar_init(&s.p_ready, 128);
+        mbar_init(&s.o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {       // S: columns 0..127, P: 128..191 (bfloat16 pairs), O_blk: 192..255
+        tmem_alloc(&s.tmem_base, 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = s.tmem_base;
+    const unsigned tm_s = tmem, tm_p = tmem + 128, tm_o = tmem + 192;
+
+    if (warp == 0) {
+        // ---- TMA producer ----
+        // Lanes 0..7 each own one 16-key page of a block: they look their page up (one coalesced read of
+        // the block table, one block ahead) and issue its two TMA loads themselves, so the eight
+        // lookups and sixteen loads of a block go out side by side instead of one after the other.
+        if (lane == 0) {
+            mbar_expect_tx(&s.q_full, 128 * FA_HD * sizeof(bf16));
+            tma_load_3d(s.q, &map_q, 0, kvh * G, t0 + q0, &s.q_full);
+        }
+        auto lookup = [&](int j) -> int {
+            const int key0 = (kb0 + j) * FA_BK + lane * 16;
+            int page = (lane < FA_BK / 16 && j < n_blocks && key0 <= pos_last) ? bt[key0 / page_size] : 0;
+            return page < 0 ? 0 : page;      // beyond the sequence or behind a window: masked, any valid page will do
+        };
+        int page = lookup(0);
+        bool ok = true;
+        for (int j = 0; j < n_blocks && ok; ++j) {
+            const int st = j % FA_STAGES;
+            const int next_page = lookup(j + 1);
+            if (lane == 0) {
+                if (!mbar_wait(&s.empty[st], ((j / FA_STAGES) & 1) ^ 1)) { atomicExch(status, 12); ok = false; }
+                else mbar_expect_tx(&s.full[st], 2 * FA_BK * FA_HD * sizeof(bf16));
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (ok && lane < FA_BK / 16) {
+                const int sl = ((kb0 + j) * FA_BK + lane * 16) % page_size;
+                tma_load_2d(s.k[st] + lane * 16 * FA_HD, &map_k, 0, (page * nkv + kvh) * page_size + sl, &s.full[st]);
+                tma_load_2d(s.v[st] + lane * 16 * FA_HD, &map_v, sl, (page * nkv + kvh) * FA_HD, &s.full[st]);
+            }
+            page = next_page;
+        }
+    } else if (warp == 1) {
+        // ---- tensor-core issue ----
+        if (elect_one()) {
+            constexpr unsigned idesc_s = make_idesc(128, FA_BK);
+            constexpr unsigned idesc_o = make_idesc(128, FA_HD);
+            bool ok = mbar_wait(&s.q_full, 0);
+            if (!ok) atomicExch(status, 13);
+            const unsigned long long dq = make_desc(smem_u32(s.q));
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int st = j % FA_STAGES;
+                if (!mbar_wait(&s.full[st], (j / FA_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
+                tc_fence_after();
+                const unsigned long long dk = make_desc(smem_u32(s.k[st]));
+#pragma unroll
+                for (int k = 0; k < FA_HD / 16; ++k) umma_f16(tm_s, dq + 2 * k, dk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(&s.s_full);
+                // the softmax warps turn S into P (and have taken the previous O_blk before that)
+                if (!mbar_wait(&s.p_ready, j & 1)) { atomicExch(status, 15); ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < FA_BK / 16; ++kk)
+                    umma_f16_ts(tm_o, tm_p + 8 * kk, make_desc_sw32(smem_u32(s.v[st] + kk * 16 * FA_HD)), idesc_o,
+                                kk > 0 ? 1u : 0u);
+                umma_commit(&s.o_full);
+                umma_commit(&s.empty[st]);
+            }
+            if (!ok) { umma_commit(&s.s_full); umma_commit(&s.o_full); }
+        }
+    } else {
+        // ---- softmax: one thread per query row ----
+        const int qw = warp & 3;
+        const int r = qw * 32 + lane;                     // row = token * G + head
+        const int tok = r / G, hg = r % G;
+        const bool valid = tok < rows_tok;
+        const int pos = p0 + q0 + min(tok, rows_tok - 1);
+        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const unsigned lane_base = (unsigned)(qw * 32) << 16;
+        float o[FA_HD];
+#pragma unroll
+        for (int d = 0; d < FA_HD; ++d) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_blocks && ok; ++j) {
+            const int key0 = (kb0 + j) * FA_BK;
+            if (!mbar_wait(&s.s_full, j & 1)) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
+            tc_fence_after();
+            const bool need_mask = key0 + FA_BK - 1 > pos_first || key0 < lo;
+            // pass 1: the row maximum of this block
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < FA_BK; c += 32) {
+                unsigned v[32];
+                tmem_ld32(tm_s + lane_base + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x = __uint_as_float(v[i]) * scale_log2;
+                    if (need_mask) { const int key = key0 + c + i; if (key > pos || key < lo) x = -INFINITY; }
+                    mx = fmaxf(mx, x);
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m - m_use);
+            m = m_new;
+            // pass 2: probabilities, their sum, P as packed bfloat16 into tensor memory
+            float l_blk = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < FA_BK; c += 32) {
+                unsigned v[32];
+                tmem_ld32(tm_s + lane_base + c, v);
+                tmem_ld_wait();
+                unsigned pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0 = __uint_as_float(v[i]) * scale_log2, x1 = __uint_as_float(v[i + 1]) * scale_log2;
+                    if (need_mask) {
+                        const int key = key0 + c + i;
+                        if (key > pos || key < lo) x0 = -INFINITY;
+                        if (key + 1 > pos || key + 1 < lo) x1 = -INFINITY;
+                    }
+                    const float e0 = exp2f(x0 - m_use), e1 = exp2f(x1 - m_use);
+                    l_blk += e0 + e1;
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                    pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
+                }
+                tmem_st16(tm_p + lane_base + c / 2, pk);
+            }
+            l = l * alpha + l_blk;
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&s.p_ready);
+            // O_blk = P V of this block
+            if (!mbar_wait(&s.o_full, j & 1)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < FA_HD; c += 32) {
+                unsigned v[32];
+                tmem_ld32(tm_o + lane_base + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c + i] = o[c + i] * alpha + __uint_as_float(v[i]);
+            }
+        }
+        if (ok && valid) {
+            const float inv = 1.f / l;
+            bf16* dst = out + ((size_t)(t0 + q0 + tok) * nh + (size_t)kvh * G + hg) * FA_HD;
+#pragma unroll
+            for (int d = 0; d < FA_HD; d += 8) {
+                unsigned pk[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(o[d + i] * inv, o[d + i + 1] * inv);
+                    pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
+                }
+                *reinterpret_cast<uint4*>(dst + d) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 256);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------
+typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static FaEncodeFn fa_encode_fn() {
+    static FaEncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (FaEncodeFn)p;
+    }
+    return fn;
+}
+
+GESSO_API int gesso_attention_tcgen05_takes(int hd, int page_size, int nh, int nkv) {
+    if (hd != FA_HD || page_size < 16 || page_size % 16 != 0 || nkv <= 0 || nh % nkv != 0) return 0;
+    const int G = nh / nkv;
+    return G == 2 || G == 4 || G == 8 || G == 16;
+}
+
+// q: bf16 [n_tokens, nh, 64]; k_pages bf16 [pages, nkv, page_size, 64]; v_pages bf16 [pages, nkv, 64, page_size];
+// tile_seg / tile_q0: the step's 64-token tiles; out bf16 [n_tokens, nh*64].
+GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages, const void* v_pages, int num_pages,
+                                              const int* block_table, int max_pages, int page_size,
+                                              const int* seg_start, const int* seg_pos0, const int* tile_seg,
+                                              const int* tile_q0, int n_tiles, int n_tokens, void* out, int nh, int nkv,
+                                              int window, float scale, int* status, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (!gesso_attention_tcgen05_takes(FA_HD, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
+    FaEncodeFn fn = fa_encode_fn();
+    if (!fn) return GESSO_ERR_UNSUPPORTED;
+    const int G = nh / nkv, TOK = 128 / G;
+    CUtensorMap mq, mk, mv;
+    {
+        const cuuint64_t dims[3] = {FA_HD, (cuuint64_t)nh, (cuuint64_t)n_tokens};
+        const cuuint64_t strides[2] = {FA_HD * sizeof(bf16), (cuuint64_t)nh * FA_HD * sizeof(bf16)};
+        const cuuint32_t box[3] = {FA_HD, (cuuint32_t)G, (cuuint32_t)TOK};
+        const cuuint32_t elem[3] = {1, 1, 1};
+        if (fn(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return GESSO_ERR_UNSUPPORTED;
+    }
+    {
+        const cuuint64_t dims[2] = {FA_HD, (cuuint64_t)num_pages * nkv * page_size};
+        const cuuint64_t strides[1] = {FA_HD * sizeof(bf16)};
+        const cuuint32_t box[2] = {FA_HD, 16};
+        const cuuint32_t elem[2] = {1, 1};
+        if (fn(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(k_pages), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return GESSO_ERR_UNSUPPORTED;
+    }
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)page_size, (cuuint64_t)num_pages * nkv * FA_HD};
+        const cuuint64_t strides[1] = {(cuuint64_t)page_size * sizeof(bf16)};
+        const cuuint32_t box[2] = {16, FA_HD};
+        const cuuint32_t elem[2] = {1, 1};
+        if (fn(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(v_pages), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return GESSO_ERR_UNSUPPORTED;
+    }
+    const size_t smem = sizeof(FaSmem) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(prefill_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    const dim3 grid(n_tiles * (64 / TOK), nkv);
+    prefill_attention_tcgen05_kernel<<<grid, FA_THREADS, smem, stream>>>(
+        mq, mk, mv, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, G,
+        window, scale * FA_LOG2E, status);
+    return launch_status();
+}

@@ -2,8 +2,9 @@
 
 float32 runs always take the FP32-arithmetic kernel.  bfloat16 runs take the tensor-core kernels
 when the sizes fit them (head 32/64/96/128, pages in multiples of 16 slots): the split-KV kernel
-for steps of single tokens, the flash kernel for steps with portions; other sizes take the
-FP32-arithmetic kernel on bfloat16 data.  Every branch is one of this library's own kernels.
+for steps of single tokens; for steps with portions the tcgen05 flash kernel (head 64, 2 to 16 query
+heads per kv head) or else the mma.sync flash kernel; other sizes take the FP32-arithmetic kernel
+on bfloat16 data.  Every branch is one of this library's own kernels.
 """
 from __future__ import annotations
 
@@ -30,6 +31,10 @@ def paged_attention(rt, q, cache, ctx, window, scale):
                     rt.shared[key] = ws
             return ops.decode_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                         ctx.seg_start, window, scale, splits, ws)
+        if ops.attention_tcgen05_takes(hd, page_size, nh, nkv):
+            # head 64 with 2..16 query heads per kv head: S and P in tensor memory, pages by TMA
+            return ops.prefill_attention_tcgen05(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
+                                                 ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale)
         return ops.prefill_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
                                      ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale)
     return ops.paged_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table,

@@ -481,3 +481,32 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epi: int = EPI_BF16, out: Opt
     _lib.check(_lib.library().gesso_gemm_tcgen05(_p(x), _p(w), _p(out), _p(bias), M, N, K, epi,
                                                  _p(tc_status_tensor(x.device)), _stream()), "gemm_tcgen05")
     return out
+
+
+# ---- tcgen05 flash prefill attention -----------------------------------------------------------------
+_lib.declare("gesso_attention_tcgen05_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
+_lib.declare("gesso_prefill_attention_tcgen05", [_lib.P, _lib.P, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P,
+                                                 _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.F,
+                                                 _lib.P, _lib.P])
+
+
+def attention_tcgen05_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
+    """Head size 64, pages in multiples of 16 slots, 2 / 4 / 8 / 16 query heads per kv head."""
+    return bool(_lib.library().gesso_attention_tcgen05_takes(hd, page_size, nh, nkv))
+
+
+def prefill_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                              block_table: torch.Tensor, seg_start: torch.Tensor, seg_pos0: torch.Tensor,
+                              tile_seg: torch.Tensor, tile_q0: torch.Tensor, window: Optional[int],
+                              scale: float) -> torch.Tensor:
+    """Flash prefill attention on tcgen05 (S and P in tensor memory, K/V pages by TMA)."""
+    _cuda_contig(q, "q", torch.bfloat16)
+    N, nh, hd = q.shape
+    nkv, page_size = k_pages.shape[1], k_pages.shape[2]
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous(), "cache pages must be contiguous")
+    out = torch.empty((N, nh * hd), dtype=q.dtype, device=q.device)
+    _lib.check(_lib.library().gesso_prefill_attention_tcgen05(
+        _p(q), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table), block_table.shape[1], page_size,
+        _p(seg_start), _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), N, _p(out), nh, nkv,
+        int(window or 0), float(scale), _p(tc_status_tensor(q.device)), _stream()), "prefill_attention_tcgen05")
+    return out

@@ -41,3 +41,29 @@ def test_tcgen05_gemm(M, N, K):
         gg, uu = want[:, :F], want[:, F:]
         assert rel_err(a, (gg / (1 + torch.exp(-gg))) * uu) < BF16_EPS
     ops.check_tc_status()
+
+
+# ---- flash prefill attention on tcgen05 --------------------------------------------------------------
+@pytest.mark.parametrize("window", [None, 50, 200])
+@pytest.mark.parametrize("nh,nkv,page", [(8, 2, 16), (32, 8, 16), (4, 2, 32), (8, 1, 16), (16, 1, 32)])
+def test_tcgen05_prefill_attention(window, nh, nkv, page):
+    import test_gpu_kernels as K
+    from gesso_b200 import ops
+    from gesso_b200.engine.batch import QUERY_TILE
+    hd = 64
+    assert ops.attention_tcgen05_takes(hd, page, nh, nkv)
+    kv_lens, new_lens = [300, 70, 1, 130, 16, 257], [300, 3, 1, 65, 2, 129]   # whole prompt, portions, single tokens
+    q, ks, vs, kp, vp, bt, positions, seg, starts = K.make_attention_case(nh, nkv, hd, page, torch.bfloat16, kv_lens,
+                                                                           new_lens, nh + page)
+    tile_seg, tile_q0 = [], []
+    for s, n in enumerate(new_lens):
+        for q0 in range(0, n, QUERY_TILE):
+            tile_seg.append(s)
+            tile_q0.append(q0)
+    pos0 = [L - n for L, n in zip(kv_lens, new_lens)]
+    out = ops.prefill_attention_tcgen05(q.to(DEV), kp, vp, bt, K.i32(starts), K.i32(pos0), K.i32(tile_seg), K.i32(tile_q0),
+                                        window, 1.0 / math.sqrt(hd))
+    ops.check_tc_status()
+    want = K.attention_reference(q, ks, vs, new_lens, window)
+    assert torch.isfinite(out).all()
+    assert rel_err(out, want) < 2 * BF16_EPS
