@@ -18,6 +18,11 @@
 //            RESID:  h[M,N] += Y (+ bias), the residual add of the sublayer, in float32;
 //            SWIGLU: rows g and g+8 of a block are gate_i and up_i (the caller packs the fused
 //                    gate/up matrix in groups of 8), out[M, N/2] = silu(gate) * up.
+// A long inner size with a narrow output (the feed-forward's down projection) is split along K over
+// S blocks per tile, so that a block's share of K is short enough for its token-side fragments to
+// stay in registers and there are enough blocks to fill the device.  The S partial tiles go to a
+// workspace; the block that arrives last (a ticket per tile) adds them in the order 0..S-1 and
+// runs the epilogue, so the result is the same whichever block that is.
 // Formulas: src/Operators/cpu.jl:293-311 (norm), 482-488 (SwiGLU), 629-630 (x W^T).
 #include <math.h>
 
@@ -68,13 +73,18 @@ template <int NT, int EPI, bool NORM, int ROWS, int XC>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, const float* __restrict__ norm_w,
                    float eps, const bf16* __restrict__ W, void* __restrict__ out, const float* __restrict__ bias,
-                   int M, int N, int K) {
+                   int M, int N, int K, int ldk, int S, float* __restrict__ ws, int* __restrict__ tickets) {
+    // K: this block's share of the inner size; ldk: the row pitch of W and x (K * S)
     constexpr int RSLOTS = ROWS / 8;                      // 16-byte pieces per thread and chunk
     constexpr int STAGES = SK_STAGES_FOR(ROWS);           // ring depth: 80 KB of W in flight per block
     extern __shared__ uint4 ring[];                       // [stage][RSLOTS][256 threads]
     __shared__ float part[2][SK_WARPS][ROWS][NT * 8 + 1];
     __shared__ float rinv[NT * 8];
     __shared__ float ssw[SK_WARPS][NT * 8];
+    __shared__ int s_last;
+    const int ks = S > 1 ? (int)(blockIdx.x % (unsigned)S) : 0;      // which share of K
+    const int bid = S > 1 ? (int)(blockIdx.x / (unsigned)S) : (int)blockIdx.x;
+    const int gdim = S > 1 ? (int)(gridDim.x / (unsigned)S) : (int)gridDim.x;
     // NORM with norm_w == nullptr: the norm's weight was folded into W's columns by the caller.  Then
     // X = bf16(h) goes into the MMA as it is, sum(h^2) is gathered from the very fragments the warps
     // load anyway, and 1/sqrt(mean(h^2) + eps) scales the result in the epilogue: no extra pass over h.
@@ -83,25 +93,35 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     const int n_chunks = K / 32;
     const int CH = (n_chunks + SK_WARPS - 1) / SK_WARPS;  // loop steps per tile (chunk w + 8 i, if it exists)
     const int n_tiles = N / ROWS;
-    const int my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int my_tiles = bid < n_tiles ? (n_tiles - bid + gdim - 1) / gdim : 0;
     const int total = my_tiles * CH;
+    // Blocks start at different places along K (step i of a tile covers chunk w + 8 ((i + rot) mod CH)):
+    // otherwise every block reads the same offset of its rows at the same time, and with a row pitch
+    // that is a large power of two those addresses crowd onto few memory channels.
+    const int rot = (int)(((unsigned)bid * 7u) % (unsigned)CH);
+    auto chunk_of = [&](int i) -> int {
+        if (i >= CH) return n_chunks;                     // padding step of the register queue
+        int r = i + rot;
+        if (r >= CH) r -= CH;
+        return w + r * SK_WARPS;
+    };
 
     uint4* slot = ring + threadIdx.x;
     constexpr int stage_stride = RSLOTS * SK_WARPS * 32;
-    const bf16* wbase = W + (size_t)g * K + 8 * t;        // + tile row offset + chunk offset
+    const bf16* wbase = W + (size_t)g * ldk + (size_t)ks * K + 8 * t;   // + tile row offset + chunk offset
 
     // producer cursor: item (tile, step) -> asynchronous copies into the ring
-    int p_tile = blockIdx.x, p_i = 0, p_stage = 0, p_item = 0;
+    int p_tile = bid, p_i = 0, p_stage = 0, p_item = 0;
     auto issue = [&]() {
         if (p_item < total) {
-            const int c = w + p_i * SK_WARPS;
+            const int c = chunk_of(p_i);
             if (c < n_chunks) {
-                const bf16* src = wbase + (size_t)p_tile * ROWS * K + (size_t)c * 32;
+                const bf16* src = wbase + (size_t)p_tile * ROWS * ldk + (size_t)c * 32;
                 cp_async16(slot + p_stage * stage_stride, src);
-                if (RSLOTS == 2) cp_async16(slot + p_stage * stage_stride + SK_WARPS * 32, src + (size_t)8 * K);
+                if (RSLOTS == 2) cp_async16(slot + p_stage * stage_stride + SK_WARPS * 32, src + (size_t)8 * ldk);
             }
             ++p_item;
-            if (++p_i == CH) { p_i = 0; p_tile += gridDim.x; }
+            if (++p_i == CH) { p_i = 0; p_tile += gdim; }
             if (++p_stage == STAGES) p_stage = 0;
         }
         cp_async_commit();                                // an empty group keeps the count in step
@@ -159,7 +179,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                 xb.z = pack2((h1.x * r) * w1.x, (h1.y * r) * w1.y);
                 xb.w = pack2((h1.z * r) * w1.z, (h1.w * r) * w1.w);
             } else {
-                xb = *reinterpret_cast<const uint4*>(x + (size_t)m * K + k);
+                xb = *reinterpret_cast<const uint4*>(x + (size_t)m * ldk + (size_t)ks * K + k);
             }
         }
         return xb;
@@ -174,7 +194,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
 #pragma unroll
     for (int i = 0; i < XD; ++i)
 #pragma unroll
-        for (int j = 0; j < NT; ++j) xq[i][j] = load_x(w + i * SK_WARPS, j, true);
+        for (int j = 0; j < NT; ++j) xq[i][j] = load_x(chunk_of(i), j, true);
 
     float acc[NT][4];
 #pragma unroll
@@ -182,14 +202,14 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
 
     int c_stage = 0, buf = 0;
     for (int tk = 0; tk < my_tiles; ++tk) {
-        const int tile = blockIdx.x + tk * gridDim.x;
+        const int tile = bid + tk * gdim;
 #pragma unroll 1
         for (int i0 = 0; i0 < CH; i0 += XD) {
 #pragma unroll
             for (int ii = 0; ii < XD; ++ii) {
                 const int i = i0 + ii;
                 if (i >= CH) break;
-                const int c = w + i * SK_WARPS;
+                const int c = chunk_of(i);
                 uint4 xb[NT];
 #pragma unroll
                 for (int j = 0; j < NT; ++j) xb[j] = xq[ii][j];
@@ -198,7 +218,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                     const bool wrapped = ni >= CH_pad;
                     if (wrapped) ni = ii;                 // the same slot of the next tile
 #pragma unroll
-                    for (int j = 0; j < NT; ++j) xq[ii][j] = load_x(w + ni * SK_WARPS, j, tk == 0 && !wrapped);
+                    for (int j = 0; j < NT; ++j) xq[ii][j] = load_x(chunk_of(ni), j, tk == 0 && !wrapped);
                 }
                 cp_async_wait<STAGES - 1>();              // the oldest group (this item) has landed
                 const uint4 fa = slot[c_stage * stage_stride];
@@ -246,7 +266,39 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
             __syncthreads();
         }
         const int n0 = tile * ROWS;
-        if (EPI == EPI_SWIGLU) {
+        if (EPI != EPI_SWIGLU && !NORM && S > 1) {
+            // this block's partial tile -> workspace; the last of the S blocks adds them up
+            constexpr int TILE = ROWS * NT * 8;
+            float* wsp = ws + (size_t)tile * S * TILE;
+            for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
+                const int r = idx % ROWS, m = idx / ROWS;
+                float v = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < SK_WARPS; ++ww) v += part[buf][ww][r][m];
+                __stcg(wsp + ks * TILE + idx, v);
+            }
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const int old = atomicAdd(tickets + tile, 1);
+                s_last = old == S - 1;
+                if (old == S - 1) tickets[tile] = 0;      // all S have arrived: ready for the next launch
+            }
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
+                    const int r = idx % ROWS, m = idx / ROWS;
+                    if (m >= M) continue;
+                    float v = 0.f;
+                    for (int sp = 0; sp < S; ++sp) v += __ldcg(wsp + sp * TILE + idx);
+                    const size_t o = (size_t)m * N + n0 + r;
+                    if (EPI == EPI_BF16) reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v);
+                    else if (EPI == EPI_F32) reinterpret_cast<float*>(out)[o] = v;
+                    else reinterpret_cast<float*>(out)[o] += v + (bias ? bias[n0 + r] : 0.f);
+                }
+            }
+        } else if (EPI == EPI_SWIGLU) {
             // 8 outputs per token: row r is gate, row r + 8 is up (ROWS == 16)
             for (int idx = threadIdx.x; idx < 8 * NT * 8; idx += blockDim.x) {
                 const int r = idx & 7, m = idx >> 3;
@@ -284,9 +336,11 @@ GESSO_API int gesso_skinny_gemm_takes(int M, int N, int K) {
     return M >= 1 && M <= 16 && N >= 16 && N % 16 == 0 && K >= 32 && K % 32 == 0;
 }
 
+#define SK_TICKETS 4096                                  // tiles a split product may have (ints at the head of the workspace)
+
 template <int NT, int EPI, bool NORM, int ROWS, int XC>
 static int launch_one(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
-                      const float* bias, int M, int N, int K, cudaStream_t stream) {
+                      const float* bias, int M, int N, int K, int S, void* ws, cudaStream_t stream) {
     static bool configured = false;   // once per instantiation, outside any stream capture
     if (!configured) {
         cudaFuncSetAttribute(skinny_gemm_kernel<NT, EPI, NORM, ROWS, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -294,20 +348,33 @@ static int launch_one(const void* x, const float* h_in, const float* norm_w, flo
         configured = true;
     }
     const int n_tiles = N / ROWS;
-    const int blocks = n_tiles < SK_MAX_BLOCKS ? n_tiles : SK_MAX_BLOCKS;
+    const int per_share = n_tiles < SK_MAX_BLOCKS / S ? n_tiles : SK_MAX_BLOCKS / S;
+    const int blocks = per_share * S;
     launch_pdl(skinny_gemm_kernel<NT, EPI, NORM, ROWS, XC>, dim3(blocks), dim3(SK_WARPS * 32), SK_RING_BYTES(ROWS), stream,
-               (const bf16*)x, h_in, norm_w, eps, (const bf16*)W, out, bias, M, N, K);
+               (const bf16*)x, h_in, norm_w, eps, (const bf16*)W, out, bias, M, N, K / S, K, S,
+               (float*)((int*)ws + SK_TICKETS), (int*)ws);
     return launch_status();
 }
 
 template <int NT, int EPI, bool NORM>
 static int launch_shape(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
-                        const float* bias, int M, int N, int K, cudaStream_t stream) {
+                        const float* bias, int M, int N, int K, void* ws, long long ws_bytes, cudaStream_t stream) {
     // token-side fragments stay in registers when a warp has at most 8 chunks per tile (K <= 2048)
-    const bool cache_x = K / 32 <= 8 * SK_WARPS && K % (32 * SK_WARPS) == 0 && NT * (K / (32 * SK_WARPS)) <= 16;
-    const bool small_rows = EPI != EPI_SWIGLU && N / 16 < SK_MAX_BLOCKS && N % 8 == 0;
-    const int xc = cache_x ? K / (32 * SK_WARPS) : 0;
-#define GO(ROWS, XC) return launch_one<NT, EPI, NORM, ROWS, XC>(x, h_in, norm_w, eps, W, out, bias, M, N, K, stream)
+    auto cacheable = [](int k) { return k / 32 <= 8 * SK_WARPS && k % (32 * SK_WARPS) == 0 && NT * (k / (32 * SK_WARPS)) <= 16; };
+    int S = 1;
+    if (!cacheable(K) && !NORM && EPI != EPI_SWIGLU && ws != nullptr && N / 8 <= SK_TICKETS) {
+        // split K over S blocks per tile, the smallest S whose share is cacheable and fits the workspace
+        for (int s = 2; s <= 16; s *= 2) {
+            // sized for 16 token rows whatever M is: the choice of S must not depend on the batch
+            const long long need = (long long)SK_TICKETS * 4 + (long long)N * s * 16 * 4;
+            if (K % s == 0 && cacheable(K / s) && need <= ws_bytes) { S = s; break; }
+        }
+    }
+    const int Ks = K / S;
+    const bool cache_x = cacheable(Ks);
+    const bool small_rows = EPI != EPI_SWIGLU && (N / 16) * S < SK_MAX_BLOCKS && N % 8 == 0;
+    const int xc = cache_x ? Ks / (32 * SK_WARPS) : 0;
+#define GO(ROWS, XC) return launch_one<NT, EPI, NORM, ROWS, XC>(x, h_in, norm_w, eps, W, out, bias, M, N, K, S, ws, stream)
     if (EPI != EPI_SWIGLU && small_rows) {
         if (xc == 8) GO(8, 8);
         if (xc == 4) GO(8, 4);
@@ -323,9 +390,10 @@ static int launch_shape(const void* x, const float* h_in, const float* norm_w, f
 
 template <int NT>
 static int launch_skinny(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
-                         const float* bias, int M, int N, int K, int epi, cudaStream_t stream) {
+                         const float* bias, int M, int N, int K, int epi, void* ws, long long ws_bytes,
+                         cudaStream_t stream) {
     const bool norm = h_in != nullptr;
-#define GO(E, NM) return launch_shape<NT, E, NM>(x, h_in, norm_w, eps, W, out, bias, M, N, K, stream)
+#define GO(E, NM) return launch_shape<NT, E, NM>(x, h_in, norm_w, eps, W, out, bias, M, N, K, ws, ws_bytes, stream)
     if (norm) {
         if (epi == EPI_BF16) GO(EPI_BF16, true);
         else if (epi == EPI_F32) GO(EPI_F32, true);
@@ -342,12 +410,16 @@ static int launch_skinny(const void* x, const float* h_in, const float* norm_w, 
 }
 
 // x: bf16 [M,K] (or null with h_in/norm_w: the norm is fused); W: bf16 [N,K]; out by `epi`.
+// ws: optional workspace for products split along K (zeroed once by the caller, at least 16 KB of
+// tickets plus the partial tiles; products it is too small for are not split); one per stream.
 GESSO_API int gesso_skinny_gemm(const void* x, const float* h_in, const float* norm_w, float eps, const void* W,
-                                void* out, const float* bias, int M, int N, int K, int epi, cudaStream_t stream) {
+                                void* out, const float* bias, int M, int N, int K, int epi, void* ws,
+                                long long ws_bytes, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (!gesso_skinny_gemm_takes(M, N, K)) return GESSO_ERR_BAD_SIZE;
     if ((x == nullptr) == (h_in == nullptr)) return GESSO_ERR_UNSUPPORTED;
     if (h_in && M > 16) return GESSO_ERR_BAD_SIZE;      // the fused norm is for a handful of rows
-    if (M <= 8) return launch_skinny<1>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, stream);
-    return launch_skinny<2>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, stream);
+    if (ws_bytes < (long long)SK_TICKETS * 4) ws = nullptr;
+    if (M <= 8) return launch_skinny<1>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, ws, ws_bytes, stream);
+    return launch_skinny<2>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, ws, ws_bytes, stream);
 }

@@ -32,7 +32,7 @@ _SIGNATURES = {
     "gesso_paged_attention_generic": [P, P, P, I, P, I, I, P, P, P, I, I, I, I, I, F, P],
     "gesso_swiglu": [P, P, I, I, I, I, P],
     "gesso_skinny_gemm_takes": [I, I, I],
-    "gesso_skinny_gemm": [P, P, P, F, P, P, P, I, I, I, I, P],
+    "gesso_skinny_gemm": [P, P, P, F, P, P, P, I, I, I, I, P, LL, P],
     "gesso_gemm_f32": [P, I, P, I, P, P, I, I, I, P],
     "gesso_argmax_rows": [P, I, I, P, P, P, P, P],
     "gesso_sample_rows": [P, I, I, P, P, P, P, P, P],

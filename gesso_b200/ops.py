@@ -263,6 +263,20 @@ def tc_takes(M: int, w: torch.Tensor, x_dtype) -> bool:
             and N >= 8 and N % 8 == 0 and K >= 8 and K % 8 == 0 and w.data_ptr() % 16 == 0)
 
 
+_skinny_ws = {}
+SKINNY_WS_BYTES = 16 * 1024 + 4 * 1024 * 1024
+
+
+def _skinny_workspace(device) -> torch.Tensor:
+    """Tickets and partial tiles for skinny products that are split along K: one zeroed buffer per
+    device and stream (launches on one stream run in order, so they can share it)."""
+    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
+    ws = _skinny_ws.get(key)
+    if ws is None:
+        ws = _skinny_ws[key] = torch.zeros((SKINNY_WS_BYTES,), dtype=torch.uint8, device=device)
+    return ws
+
+
 def _skinny(x, w, out, bias, epi):
     """x: bfloat16 tensor or LazyNorm with at most SKINNY_NORM_MAX_ROWS rows."""
     N, K = w.shape
@@ -274,8 +288,9 @@ def _skinny(x, w, out, bias, epi):
         M = x.shape[0]
         _cuda_contig(x, "x", torch.bfloat16)
         args = (_p(x), None, None, 0.0)
-    _lib.check(_lib.library().gesso_skinny_gemm(*args, _p(w), _p(out), _p(bias), M, N, K, epi, _stream()),
-               "skinny_gemm")
+    ws = _skinny_workspace(w.device)
+    _lib.check(_lib.library().gesso_skinny_gemm(*args, _p(w), _p(out), _p(bias), M, N, K, epi, _p(ws), ws.numel(),
+                                                _stream()), "skinny_gemm")
 
 
 def _as_tensor(x):

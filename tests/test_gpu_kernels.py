@@ -400,7 +400,8 @@ def test_sampler_low_temperature_is_argmax_and_nucleus_keeps_the_top_set():
 
 # ---- skinny matrix product (steps of few tokens) -------------------------------------------------------
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(16, 32), (48, 96), (2048, 2048), (160, 8192), (503 * 16, 64), (32, 352)])
+@pytest.mark.parametrize("N,K", [(16, 32), (48, 96), (2048, 2048), (160, 8192), (503 * 16, 64), (32, 352),
+                                 (64, 4096), (2048, 8192), (48, 6144)])
 def test_skinny_gemm_epilogues(M, N, K):
     from gesso_b200 import ops
     g = torch.Generator().manual_seed(M * 1000 + N + K)
