@@ -113,10 +113,11 @@ def model_flops_per_token(cfg_obj, n_layers_attn, n_layers_conv):
     return 2 * (n_layers_conv * conv + n_layers_attn * attn), 2 * V * H
 
 
-def decode_setup(gb, model, batch, context, steps, warmup, page_size, seed=1):
-    """A session with ``batch`` requests prefilled so that the timed steps end at the full context."""
+def decode_setup(gb, model, batch, context, steps, warmup, page_size, seed=1, margin=0):
+    """A session with ``batch`` requests prefilled so that the timed steps end at the full context
+    (``margin`` tokens short of it)."""
     import torch
-    start_len = max(1, context - steps - warmup - 1)
+    start_len = max(1, context - steps - warmup - 1 - margin)
     pages = batch * ((context + page_size - 1) // page_size)
     s = gb.Session(model, context_length=context, page_size=page_size, num_pages=pages, max_batch=batch,
                    max_tokens_per_step=4096, prefill_chunk=2048)
@@ -166,8 +167,12 @@ def time_decode(gb, model, batch, context, steps, warmup, page_size):
 def time_e2e(gb, model, batch, context, steps, warmup, page_size):
     """The same through the Python entry point: host ids in, sampled ids out, every step."""
     import torch
-    s, prompts, start_len = decode_setup(gb, model, batch, context, steps, warmup, page_size)
-    sched = s.open_batch([gb.BatchRequest(p, max_new_tokens=warmup + steps + 1) for p in prompts])
+    # While the later prompts are still being prefilled the earlier requests already decode; the
+    # margin keeps every request short of the context until the timed steps are over, so that the
+    # batch stays whole (no request ends, and no step of another batch size falls into the timed region).
+    margin = batch * (context // 4096 + 1) + 2
+    s, prompts, start_len = decode_setup(gb, model, batch, context, steps, warmup, page_size, margin=margin)
+    sched = s.open_batch([gb.BatchRequest(p, max_new_tokens=context - start_len) for p in prompts])
     while any(r.fed < len(r.prompt) for r in sched.running + sched.waiting):
         sched.step()                                       # prefill
     for _ in range(warmup):

@@ -15,6 +15,7 @@ Reference counterparts: the per-sequence prefill pass and decode step
 from __future__ import annotations
 
 import gc
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -25,6 +26,19 @@ from ..csrc.lib import launch_count
 from ..errors import ErrorCode, GessoError, invalid, resource
 from .batch import StepContext, StepEntry, StepLayout, count_tiles, pack_step
 from .model import Model, PagedView, StateView
+
+
+@dataclass
+class StagedStep:
+    """A decoding step prepared before its tokens are known: pages reserved, metadata packed in pinned
+    host memory with the token ids left open (:meth:`Engine.stage_single_tokens`)."""
+
+    req_ids: tuple
+    layout: StepLayout
+    slot_i: int
+    host: torch.Tensor
+    max_kv: int
+    all_rows: bool
 
 
 class DeviceCache:
@@ -71,6 +85,7 @@ class Engine:
         self.device_cache = DeviceCache(model, self.page_size, [self.num_pages] * len(groups), max_requests)
         self.status = torch.zeros((1,), dtype=torch.int32, device=model.rt.device)
         self.steps_run = 0
+        self.staged_steps_run = 0
         self.tokens_run = 0
         self.launches = 0            # kernels of this library launched by steps (graph nodes included)
         self.h2d_bytes = 0           # metadata bytes copied to the device by steps
@@ -246,6 +261,37 @@ class Engine:
         self.tokens_run += layout.n_tokens
         return logits
 
+    def stage_single_tokens(self, req_ids: Sequence[Hashable]) -> Optional[StagedStep]:
+        """Prepare the decoding step that gives every request of ``req_ids`` one more token, while the
+        device still runs the step before it: everything but the token ids (pages, positions, block
+        tables) is settled on the host now, so that once the ids are sampled only they have to be
+        filled in before the launch.  Returns ``None`` where steps are not replayed from graphs.  A
+        staged step that is never run costs nothing but its page reservations, which the requests keep."""
+        if not self.use_graphs or not req_ids or len(req_ids) > self.max_graph_batch:
+            return None
+        entries = [StepEntry(rid, [0], [0]) for rid in req_ids]
+        layout, slot_i, host, _, max_kv = self._prepare_single_tokens(entries)
+        return StagedStep(tuple(req_ids), layout, slot_i, host, max_kv, self._all_rows)
+
+    def step_staged(self, staged: StagedStep, tokens: Sequence[int]) -> torch.Tensor:
+        """Run a staged step with its tokens (one per request, in the staged order); logits of every request."""
+        V = self.model.vocab_size
+        if len(tokens) != len(staged.req_ids):
+            raise invalid("step: a staged step takes one token per request")
+        for rid, tok in zip(staged.req_ids, tokens):
+            if not (0 <= tok < V):
+                raise invalid(f"step: token id {tok} of request {rid!r} is outside the vocabulary (0..{V - 1})")
+        at = staged.layout.offsets()["token_ids"]
+        staged.host.numpy()[at:at + len(tokens)] = tokens
+        self._all_rows = staged.all_rows
+        logits = self._step_graph(staged.layout, staged.slot_i, staged.host, staged.max_kv)
+        for rid in staged.req_ids:
+            self.cache.commit(rid, 1)
+        self.steps_run += 1
+        self.staged_steps_run += 1
+        self.tokens_run += staged.layout.n_tokens
+        return logits
+
     def _step_graph(self, layout: StepLayout, slot_i: int, host: torch.Tensor, max_kv: int):
         key = (layout.n_segs, layout.n_rows, self._all_rows)
         g = self._graphs.get(key)
@@ -291,7 +337,7 @@ class Engine:
 
     def stats(self) -> Dict[str, object]:
         return {
-            "steps": self.steps_run, "tokens": self.tokens_run,
+            "steps": self.steps_run, "staged_steps": self.staged_steps_run, "tokens": self.tokens_run,
             "pages_in_use": self.cache.pages_in_use(), "pages_free": self.cache.free_pages(),
             "slots_in_use": self.cache.slots_in_use(), "cache_bytes": self.device_cache.bytes(),
             "live_requests": len(self.cache.live_requests()),

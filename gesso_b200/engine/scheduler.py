@@ -125,6 +125,7 @@ class Scheduler:
         self._clock = itertools.count()
         self.steps = 0
         self.preemptions = 0
+        self._staged = None                       # the next decoding step, prepared while this one runs
 
     # ---- adding --------------------------------------------------------------------------------
     def add(self, req: Request) -> Request:
@@ -292,10 +293,24 @@ class Scheduler:
             entries.append(StepEntry(r.req_id, r.tokens(start, n), [n - 1] if last else []))
             if last:
                 samplers.append(r)
-        logits = self.engine.step(entries)
+        staged, self._staged = self._staged, None
+        decoding = len(samplers) == len(entries) and all(n == 1 for _, _, n in plan.entries)
+        if staged is not None and decoding and staged.req_ids == tuple(e.req_id for e in entries):
+            logits = self.engine.step_staged(staged, [e.tokens[0] for e in entries])
+        else:
+            logits = self.engine.step(entries)
         self.steps += 1
         for r, _, n in plan.entries:
             r.fed += n
+        # While the device runs this step, prepare the next one if it will most likely be the same
+        # requests with one more token each; only their sampled ids are missing then.
+        stage = getattr(self.engine, "stage_single_tokens", None)
+        if (stage is not None and decoding and not self.waiting and len(samplers) == len(self.running)
+                and all(len(r.generated) + 1 < r.max_new_tokens and not r.cancelled for r in samplers)):
+            try:
+                self._staged = stage([r.req_id for r in samplers])
+            except GessoError:
+                self._staged = None               # no page or no room: the ordinary path decides
         emitted: List[Tuple[Request, int]] = []
         if samplers:
             tokens = self.select(logits, samplers)

@@ -94,6 +94,18 @@ def sample_host(row: np.ndarray, params: SamplingParams, rng: SplitMix64) -> int
     return int(order[min(k, keep - 1)])
 
 
+_pinned: dict = {}
+
+
+def _pinned_rows(R: int) -> torch.Tensor:
+    """A pinned [2, R] int32 host buffer (ids and flags), kept per row count: the copy back needs no
+    staging through pageable memory."""
+    buf = _pinned.get(R)
+    if buf is None:
+        buf = _pinned[R] = torch.empty((2, R), dtype=torch.int32, pin_memory=True)
+    return buf
+
+
 def select_tokens(logits: torch.Tensor, params: Sequence[SamplingParams],
                   rngs: Sequence[Optional[SplitMix64]]) -> List[object]:
     """One token per row of ``logits`` [R, V] (device, float32).
@@ -109,7 +121,11 @@ def select_tokens(logits: torch.Tensor, params: Sequence[SamplingParams],
     sampled = [i for i, p in enumerate(params) if not p.greedy]
     if not sampled and ids.data_ptr() + 4 * R == bad.data_ptr():
         # all greedy: ids and flags sit in one buffer, one copy brings both
-        host = ids.new_empty(0).set_(ids.untyped_storage(), ids.storage_offset(), (2, R)).to("cpu").numpy()
+        both = ids.new_empty(0).set_(ids.untyped_storage(), ids.storage_offset(), (2, R))
+        pinned = _pinned_rows(R)
+        pinned.copy_(both, non_blocking=True)
+        torch.cuda.current_stream(ids.device).synchronize()
+        host = pinned.numpy()
         return [GessoError(ErrorCode.NUMERICAL_INSTABILITY, "nonfinite logits; no token may be emitted")
                 if host[1, i] else int(host[0, i]) for i in range(R)]
     if sampled:

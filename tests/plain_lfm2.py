@@ -80,8 +80,9 @@ class PlainModel:
         self.window = None   # LFM2 has no sliding window (src/Inference/lfm2.jl:73-76)
 
     # ---- whole model ---------------------------------------------------------------------------
-    def logits(self, token_ids):
-        """All logits [T, V] of one whole sequence (src/Inference/Inference.jl:179-391)."""
+    def logits(self, token_ids, rows=None):
+        """All logits [T, V] of one whole sequence (src/Inference/Inference.jl:179-391); with ``rows``
+        only those positions go through the head (wide vocabularies)."""
         w = self.w
         h = embedding(w["model.embed_tokens.weight"], token_ids)
         for i, attn in enumerate(self.is_attn):
@@ -101,6 +102,8 @@ class PlainModel:
             h = h + swiglu_ffn(rmsnorm(h, w[p + "ffn_norm.weight"], self.eps),
                                w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"],
                                w[p + "feed_forward.w2.weight"])    # Inference.jl:2514-2517
+        if rows is not None:
+            h = h[list(rows)]
         hn = rmsnorm(h, w["model.embedding_norm.weight"], self.eps)   # the final norm, lfm2.jl:173
         head = w["model.embed_tokens.weight"] if self.tied else w["lm_head.weight"]
         return hn @ head.T                                          # Inference.jl:2747-2800

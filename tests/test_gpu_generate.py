@@ -85,6 +85,28 @@ def test_batch_equals_solo_and_is_deterministic(models, plain_models):
     assert s.stats()["pages_in_use"] == [0]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_steps_staged_ahead_keep_the_tokens(dtype, models, plain_models):
+    """Decoding steps are prepared one ahead while the device runs; requests of different lengths end
+    at different steps (a staged step is dropped then), pages are crossed, and nobody's ids change."""
+    import gesso_b200
+    model = models("c", dtype)
+    prompts = prompts_for("c", [14, 3, 31], seed=11)
+    news = [40, 9, 22]
+    s = gesso_b200.Session(model, context_length=128, page_size=16, max_batch=3)
+    res = s.run_batch([gesso_b200.BatchRequest(p, max_new_tokens=n) for p, n in zip(prompts, news)])
+    assert s.stats()["staged_steps"] >= 20
+    solo = gesso_b200.Session(model, context_length=128, page_size=16, max_batch=1)
+    for p, n, r in zip(prompts, news, res):
+        assert r.status == "complete"
+        if dtype == "float32":
+            assert r.ids == plain_models["c"].greedy(p, n)
+            assert r.ids == solo.generate(p, n)
+        else:
+            near_max(plain_models["c"], r.ids, len(p), TOL16)
+    assert s.stats()["pages_in_use"] == [0]
+
+
 def test_sampled_ids_follow_the_plain_sampler(models, plain_models):
     import gesso_b200
     from plain_lfm2 import PlainSampler

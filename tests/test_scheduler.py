@@ -198,3 +198,73 @@ def test_sampling_params_validation():
         with pytest.raises(GessoError):
             SamplingParams(**bad)
     assert SamplingParams().greedy and not SamplingParams(temperature=0.7).greedy
+
+
+# ---- staged decoding steps: the next step is prepared while the device runs this one -----------------
+class StagingEngine(FakeEngine):
+    """A stand-in with the engine's staging interface: reserves at staging time, commits at run time."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.staged_made = self.staged_run = 0
+
+    def stage_single_tokens(self, req_ids):
+        self.cache.reserve_single_tokens(list(req_ids))
+        self.staged_made += 1
+
+        class Staged:
+            pass
+        st = Staged()
+        st.req_ids = tuple(req_ids)
+        return st
+
+    def step_staged(self, staged, tokens):
+        from gesso_b200.engine.batch import StepEntry
+        self.staged_run += 1
+        for rid in staged.req_ids:
+            self.cache.commit(rid, 1)
+        self.cache.check_invariants()
+        entries = [StepEntry(rid, [int(t)], [0]) for rid, t in zip(staged.req_ids, tokens)]
+        self.log.append([(e.req_id, list(e.tokens), list(e.want)) for e in entries])
+        return entries
+
+
+def test_staged_steps_give_the_same_tokens_and_are_used():
+    prompts = [[1, 2, 3], [9] * 11, [4]]
+    eng = StagingEngine()
+    s = Scheduler(eng, next_token, vocab_size=100, max_batch=3, prefill_chunk=4)
+    reqs = [s.add(Request(p, n)) for p, n in zip(prompts, (9, 5, 7))]
+    s.run()
+    for p, r, n in zip(prompts, reqs, (9, 5, 7)):
+        assert r.status == COMPLETE and r.ids == solo(p, n)
+    assert eng.staged_run > 0
+    assert eng.cache.pages_in_use() == [0] and eng.cache.slots_in_use() == 0
+
+
+def test_staged_step_is_dropped_when_the_batch_changes():
+    eng = StagingEngine()
+    s = Scheduler(eng, next_token, vocab_size=100, max_batch=3, prefill_chunk=8)
+    a = s.add(Request([1, 2, 3], 12))
+    for _ in range(3):
+        s.step()
+    assert s._staged is not None                    # a alone, decoding: its next step is staged
+    made = eng.staged_made
+    b = s.add(Request([5, 6, 7, 8], 6))             # a newcomer: the staged step no longer fits
+    s.step()
+    assert eng.staged_made == made and s._staged is None
+    assert [e[0] for e in eng.log[-1]] == [a.req_id, b.req_id]
+    s.run()
+    assert a.ids == solo([1, 2, 3], 12) and b.ids == solo([5, 6, 7, 8], 6)
+    assert eng.cache.pages_in_use() == [0]
+
+
+def test_staging_yields_to_page_pressure():
+    # a pool so small that staging one step ahead finds no page: the ordinary path decides, as before
+    eng = StagingEngine(num_pages=3, page_size=4, slots=2, ctx=12)
+    s = Scheduler(eng, next_token, vocab_size=100, max_batch=2, prefill_chunk=8)
+    a = s.add(Request([1, 2, 3], 9))
+    b = s.add(Request([4, 5, 6], 3))
+    s.run()
+    assert a.status == COMPLETE and b.status == COMPLETE
+    assert a.ids == solo([1, 2, 3], 9) and b.ids == solo([4, 5, 6], 3)
+    assert eng.cache.pages_in_use() == [0]
