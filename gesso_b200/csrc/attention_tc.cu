@@ -147,28 +147,105 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
 }
 
 // ================================ decode: split-KV ==============================================
-// grid (splits, nkv, segments), 128 threads.  The m16 rows are the query heads of the kv group
-// (up to 16).  Every warp walks its share of the split's 16-key blocks; the warps are merged in
-// shared memory; with more than one split the partial (m, l, O) goes to the workspace and the last
-// split to arrive merges them (a ticket per (segment, kv head), reset for the next launch).
+// grid (splits, nkv, segments), 128 threads; a step of single tokens (token i is segment i).  The
+// m16 rows are the query heads of the kv group (up to 16).  Every warp walks its share of the
+// split's 16-key blocks; the warps are merged in shared memory; with more than one split the
+// partial (m, l, O) goes to the workspace and the last split to arrive merges them (a ticket per
+// (segment, kv head), reset for the next launch).
+//
+// The kernel is bound by the stream of K and V, so that stream is kept deep and started early:
+// every thread copies the fragments it will need (64 bytes of K rows, 64 bytes of V^T rows per block
+// at head size 64) asynchronously into a private ring in shared memory, DA_STAGES blocks ahead; the
+// page ids of a warp's blocks are fetched by its lanes in one go, so no lookup sits in the chain;
+// and everything but the block that holds the step's own token is requested before the wait for
+// the preceding kernels (which write that token's K and V and the queries), so the first keys are
+// on their way while those still run.
+#define DA_STAGES 6
+
+__device__ __forceinline__ void cp_async_zfill16(void* smem_dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(valid ? 16 : 0));
+}
+__device__ __forceinline__ void cp_async_zfill8(void* smem_dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(valid ? 8 : 0));
+}
+
 template <int HD>
 __global__ void __launch_bounds__(128)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
-                        int page_size, const int* __restrict__ positions, const int* __restrict__ seg_start,
+                        int page_size, const int* __restrict__ positions,
                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int n_splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets) {
-    extern __shared__ float smem[];          // [4 warps][16 rows][HD + 2]
+    // ring: [stage][piece][128 threads]: HD/16 pieces of 16 bytes for K, then HD/8 pieces of 8 bytes for V;
+    // afterwards the same memory serves the merge of the warps ([4 warps][16 rows][HD + 2] floats)
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* smem = reinterpret_cast<float*>(smem_raw);
     __shared__ int s_last;
-    pdl_wait();
-    pdl_launch_dependents();
+    constexpr int KP = HD / 16, VP = HD / 8;
+    constexpr int STAGE_BYTES = (KP * 16 + VP * 8) * 128;
     const int split = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
     const int G = nh / nkv;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int tok = seg_start[seg];          // the segment's single token
+    const int tok = seg;                     // a step of single tokens
     const int pos = positions[tok];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int* bt = block_table + (size_t)seg * max_pages;
+
+    const int first_block = lo / 16, last_block = pos / 16;
+    const int n_blocks = last_block - first_block + 1;
+    const int per = (n_blocks + n_splits - 1) / n_splits;
+    const int b0 = first_block + split * per;
+    const int b1 = min(last_block + 1, b0 + per);
+    const int mine_n = b0 + w < b1 ? (b1 - b0 - w + 3) / 4 : 0;      // blocks b0 + w + 4 i of this warp
+
+    // page ids of this warp's blocks, 32 at a time: lane i holds the page of block i of the batch
+    int pages = 0;
+    auto fetch_pages = [&](int first_i) {
+        const int i = first_i + lane;
+        pages = i < mine_n ? bt[((b0 + w + 4 * i) * 16) / page_size] : -1;
+    };
+    fetch_pages(0);
+
+    unsigned char* ring = smem_raw;
+    const int key_a = 4 * (g >> 1) + (g & 1);
+    int issued = 0;
+    auto issue = [&]() {                     // request block `issued` of this warp into its ring stage
+        if (issued < mine_n) {
+            const int b = b0 + w + 4 * issued;
+            const int page = __shfl_sync(0xffffffffu, pages, issued & 31);
+            const bool valid = page >= 0;    // a page given back behind a window: masked, zero-filled
+            const size_t pk = (size_t)(valid ? page : 0) * nkv + kvh;
+            const int sub = (b * 16) % page_size;
+            unsigned char* st = ring + (size_t)(issued % DA_STAGES) * STAGE_BYTES;
+            const bf16* ka = k_pages + (pk * page_size + sub + key_a) * HD + 8 * t;
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                cp_async_zfill16(st + ((size_t)(2 * c) * 128 + threadIdx.x) * 16, ka + 32 * c, valid);
+                cp_async_zfill16(st + ((size_t)(2 * c + 1) * 128 + threadIdx.x) * 16, ka + 2 * HD + 32 * c, valid);
+            }
+            const bf16* vt = v_pages + (pk * HD + g) * page_size + sub + 4 * t;
+            unsigned char* sv = st + (size_t)KP * 16 * 128;
+#pragma unroll
+            for (int j = 0; j < VP; ++j)
+                cp_async_zfill8(sv + ((size_t)j * 128 + threadIdx.x) * 8, vt + (size_t)(8 * j) * page_size, valid);
+            ++issued;
+            if ((issued & 31) == 0) fetch_pages(issued);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);      // an empty group keeps the count in step
+    };
+    // before the wait: everything but the block of the step's own token
+    int early = 0;
+#pragma unroll 1
+    for (; early < DA_STAGES; ++early) {
+        if (issued < mine_n && b0 + w + 4 * issued == last_block) break;
+        issue();
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+#pragma unroll 1
+    for (; early < DA_STAGES; ++early) issue();
 
     // Q fragments: row g is head kvh*G + g (zero rows beyond the group)
     uint4 qf[HD / 32], qg[HD / 32];
@@ -180,28 +257,31 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             qg[c] = g + 8 < G ? *reinterpret_cast<const uint4*>(qa + 8 * HD + 32 * c) : make_uint4(0, 0, 0, 0);
         }
     }
-    const int first_block = lo / 16, last_block = pos / 16;
-    const int n_blocks = last_block - first_block + 1;
-    const int per = (n_blocks + n_splits - 1) / n_splits;
-    const int b0 = first_block + split * per;
-    const int b1 = min(last_block + 1, b0 + per);
 
     float o[HD / 8][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-    // two blocks are in flight behind the one being computed (the kernel is bound by the KV stream)
-    KVFrag<HD> cur, nx1, nx2;
-    int b = b0 + w;
-    if (b < b1) load_block<HD>(cur, k_pages, v_pages, bt, b, page_size, nkv, kvh, g, t);
-    if (b + 4 < b1) load_block<HD>(nx1, k_pages, v_pages, bt, b + 4, page_size, nkv, kvh, g, t);
-    for (; b < b1; b += 4) {
-        if (b + 8 < b1) load_block<HD>(nx2, k_pages, v_pages, bt, b + 8, page_size, nkv, kvh, g, t);
+#pragma unroll 1
+    for (int i = 0; i < mine_n; ++i) {
+        const int b = b0 + w + 4 * i;
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(DA_STAGES - 1));
+        const unsigned char* st = ring + (size_t)(i % DA_STAGES) * STAGE_BYTES;
+        KVFrag<HD> cur;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            cur.k[0][c] = *reinterpret_cast<const uint4*>(st + ((size_t)(2 * c) * 128 + threadIdx.x) * 16);
+            cur.k[1][c] = *reinterpret_cast<const uint4*>(st + ((size_t)(2 * c + 1) * 128 + threadIdx.x) * 16);
+        }
+        const unsigned char* sv = st + (size_t)KP * 16 * 128;
+#pragma unroll
+        for (int j = 0; j < VP; ++j) cur.v[j] = *reinterpret_cast<const uint2*>(sv + ((size_t)j * 128 + threadIdx.x) * 8);
+        issue();                                          // refill the stage just read
         const bool need_mask = (b * 16 + 15 > pos) || (b * 16 < lo);
         attend_block<HD>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask);
-        cur = nx1;
-        nx1 = nx2;
     }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncthreads();                                      // the ring is free: it becomes the merge buffer
     l[0] = quad_sum(l[0]);
     l[1] = quad_sum(l[1]);
 
@@ -539,7 +619,7 @@ GESSO_API long long gesso_decode_attention_workspace(int segs, int nh, int nkv, 
 
 GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const void* v_pages,
                                      const int* block_table, int max_pages, int page_size, const int* positions,
-                                     const int* seg_start, void* out, int n_segs, int nh, int nkv, int hd,
+                                     void* out, int n_segs, int nh, int nkv, int hd,
                                      int window, float scale, int n_splits, float* part_o, float* part_ml,
                                      int* tickets, cudaStream_t stream) {
     if (n_segs <= 0) return 0;
@@ -548,17 +628,21 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
     if (G > 16 || n_splits < 1 || n_splits > 65535 || n_segs > 65535 || nkv > 65535) return GESSO_ERR_BAD_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return GESSO_ERR_BAD_SIZE;
     dim3 grid(n_splits, nkv, n_segs);
-    const size_t smem = (size_t)4 * 16 * (hd + 2) * sizeof(float);
+    const size_t merge = (size_t)4 * 16 * (hd + 2) * sizeof(float);
+    const size_t ring = (size_t)DA_STAGES * (hd / 16 * 16 + hd / 8 * 8) * 128;
+    const size_t smem = ring > merge ? ring : merge;
     const float scale_log2 = scale * LOG2E;
 #define GO(HD)                                                                                              \
     do {                                                                                                    \
-        if (smem > 48 * 1024)                                                                               \
+        static bool configured = false;   /* once per head size, outside any stream capture */              \
+        if (!configured) {                                                                                  \
             cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                                  (int)smem);                                                                \
+            configured = true;                                                                              \
+        }                                                                                                   \
         launch_pdl(decode_attention_kernel<HD>, grid, dim3(128), smem, stream,                              \
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,  \
-            positions, seg_start, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml,       \
-            tickets);                                                                                       \
+            positions, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml, tickets);        \
     } while (0)
     if (hd == 32) GO(32);
     else if (hd == 64) GO(64);

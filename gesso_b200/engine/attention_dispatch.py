@@ -30,7 +30,7 @@ def paged_attention(rt, q, cache, ctx, window, scale):
                           torch.zeros((ctx.n_segs * nkv,), dtype=torch.int32, device=dev))
                     rt.shared[key] = ws
             return ops.decode_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
-                                        ctx.seg_start, window, scale, splits, ws)
+                                        window, scale, splits, ws)
         if ops.attention_tcgen05_takes(hd, page_size, nh, nkv):
             # head 64 with 2..16 query heads per kv head: S and P in tensor memory, pages by TMA
             return ops.prefill_attention_tcgen05(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,

@@ -386,7 +386,7 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
 
 # ---- tensor-core attention (bfloat16) ------------------------------------------------------------
 _lib.declare("gesso_attention_tc_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
-_lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
+_lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P,
                                         _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P, _lib.P,
                                         _lib.P, _lib.P])
 _lib.declare("gesso_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
@@ -401,18 +401,22 @@ def fast_attention_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
     return bool(_lib.library().gesso_attention_tc_takes(hd, page_size, nh, nkv)) and nh // nkv <= 16
 
 
+DECODE_BLOCKS_PER_SM = int(os.environ.get("GESSO_DECODE_BLOCKS_PER_SM", "2"))
+
+
 def decode_splits(n_segs: int, nkv: int, max_kv_len: int) -> int:
-    """How many ways the keys of a request are split so that about two blocks per SM are busy."""
+    """How many ways the keys of a request are split so that about DECODE_BLOCKS_PER_SM blocks per SM
+    are busy."""
     blocks = (max_kv_len + 15) // 16
-    want = (2 * SM_COUNT + n_segs * nkv - 1) // (n_segs * nkv)
+    want = (DECODE_BLOCKS_PER_SM * SM_COUNT) // (n_segs * nkv)      # rounded down: all blocks resident at once
     return max(1, min(want, (blocks + 3) // 4))
 
 
 def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
-                     block_table: torch.Tensor, positions: torch.Tensor, seg_start: torch.Tensor,
+                     block_table: torch.Tensor, positions: torch.Tensor,
                      window: Optional[int], scale: float, n_splits: int,
                      workspace=None) -> torch.Tensor:
-    """Split-KV attention for a step of single tokens.  ``workspace`` = (part_o, part_ml, tickets) of
+    """Split-KV attention for a step of single tokens (token i is request i).  ``workspace`` = (part_o, part_ml, tickets) of
     sizes [segs*nh*splits*hd], [segs*nh*splits*2] float32 and [segs*nkv] int32 (zeroed once)."""
     _cuda_contig(q, "q", torch.bfloat16)
     S, nh, hd = q.shape
@@ -431,7 +435,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         part_o = part_ml = tickets = None
     _lib.check(_lib.library().gesso_decode_attention(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(positions),
-        _p(seg_start), _p(out), S, nh, nkv, hd, int(window or 0), float(scale), int(n_splits), _p(part_o),
+        _p(out), S, nh, nkv, hd, int(window or 0), float(scale), int(n_splits), _p(part_o),
         _p(part_ml), _p(tickets), _stream()), "decode_attention")
     return out
 

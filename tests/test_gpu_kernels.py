@@ -311,7 +311,7 @@ def test_decode_attention_split_kv(window, nh, nkv, hd, page, splits):
     ws = (torch.empty(S * nh * splits * hd, device=DEV), torch.empty(S * nh * splits * 2, device=DEV),
           torch.zeros(S * nkv, dtype=torch.int32, device=DEV))
     for _ in range(2):      # twice with one workspace: the tickets of the first launch must have been reset
-        out = ops.decode_attention(q.to(DEV), kp, vp, bt, i32(positions.tolist()), i32(starts), window,
+        out = ops.decode_attention(q.to(DEV), kp, vp, bt, i32(positions.tolist()), window,
                                    1.0 / math.sqrt(hd), splits, ws)
         assert rel_err(out, want) < 2 * BF16_EPS
 
