@@ -242,8 +242,9 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         if (issued < mine_n && b0 + w + 4 * issued == last_block) break;
         issue();
     }
-    pdl_wait();
+    // let the successor in first (it only prefetches what no running kernel writes until its own wait)
     pdl_launch_dependents();
+    pdl_wait();
 #pragma unroll 1
     for (; early < DA_STAGES; ++early) issue();
 

@@ -12,8 +12,9 @@
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                     float* __restrict__ h, int H, int V, float scale) {
-    pdl_wait();
+    // let the successor in first (it only prefetches what no running kernel writes until its own wait)
     pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = tokens[t];
     if (id < 0 || id >= V) id = 0;   // ids are validated on the host; never read outside the table

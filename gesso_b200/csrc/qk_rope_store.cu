@@ -21,8 +21,9 @@ __global__ void qk_norm_rope_store_kernel(
     const int* __restrict__ seg_of_token, const int* __restrict__ block_table, int max_pages, int page_size,
     T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int nh, int nkv,
     int hd, int write_kv, int* __restrict__ status) {
-    pdl_wait();
+    // let the successor in first (it only prefetches what no running kernel writes until its own wait)
     pdl_launch_dependents();
+    pdl_wait();
     const int heads = write_kv ? nh + 2 * nkv : nh;   // without a cache write the input holds q heads only
     const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
     const long long wi = (long long)blockIdx.x * warps + (threadIdx.x >> 5);

@@ -177,8 +177,9 @@ __global__ void conv_mix_update_small_kernel(const T* __restrict__ bcx, const fl
                                              const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
                                              const int* __restrict__ slots, T* __restrict__ out, int n_segs,
                                              int H, int L) {
-    pdl_wait();
+    // let the successor in first (it only prefetches what no running kernel writes until its own wait)
     pdl_launch_dependents();
+    pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int s = blockIdx.x;
     if (c >= H || s >= n_segs) return;
