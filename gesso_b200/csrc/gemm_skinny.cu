@@ -17,7 +17,11 @@
 //   epilogue BF16:   Y stored as bfloat16;       F32: Y stored as float32 (logits);
 //            RESID:  h[M,N] += Y (+ bias), the residual add of the sublayer, in float32;
 //            SWIGLU: rows g and g+8 of a block are gate_i and up_i (the caller packs the fused
-//                    gate/up matrix in groups of 8), out[M, N/2] = silu(gate) * up.
+//                    gate/up matrix in groups of 8), out[M, N/2] = silu(gate) * up;
+//            CONV:   24 rows of a block are B, C and X of 8 channels (the caller packs the input
+//                    projection of the short convolution so); for a step of single tokens the
+//                    epilogue forms bx = B X, runs the FIR over the request's state and bx, gates
+//                    with C, stores y[M, H] and shifts bx into the state: no kernel of its own.
 // A long inner size with a narrow output (the feed-forward's down projection) is split along K over
 // S blocks per tile, so that a block's share of K is short enough for its token-side fragments to
 // stay in registers and there are enough blocks to fill the device.  The S partial tiles go to a
@@ -28,7 +32,19 @@
 
 #include "common.cuh"
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESID = 2, EPI_SWIGLU = 3 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_CONV = 4 };
+
+// What the short-convolution epilogue needs beside the product (see short_conv.cu for the layer).
+struct ConvEpi {
+    const float* taps;        // [H][L], oldest to newest
+    const float* conv_bias;   // [H] or null
+    const float* in_bias;     // [3H] (B, C, X) or null
+    float* state;             // this layer's state: [slot][L-1][H] float32
+    long long slot_stride;
+    const int* slots;         // per token (a step of single tokens: token i is request i)
+    const int* seg_pos0;      // per token: its position (0: the request starts, the history is zero)
+    int L, H;
+};
 
 __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -73,7 +89,8 @@ template <int NT, int EPI, bool NORM, int ROWS, int XC>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, const float* __restrict__ norm_w,
                    float eps, const bf16* __restrict__ W, void* __restrict__ out, const float* __restrict__ bias,
-                   int M, int N, int K, int ldk, int S, float* __restrict__ ws, int* __restrict__ tickets) {
+                   int M, int N, int K, int ldk, int S, float* __restrict__ ws, int* __restrict__ tickets,
+                   const ConvEpi cv) {
     // K: this block's share of the inner size; ldk: the row pitch of W and x (K * S)
     constexpr int RSLOTS = ROWS / 8;                      // 16-byte pieces per thread and chunk
     constexpr int STAGES = SK_STAGES_FOR(ROWS);           // ring depth: 80 KB of W in flight per block
@@ -117,8 +134,9 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
             const int c = chunk_of(p_i);
             if (c < n_chunks) {
                 const bf16* src = wbase + (size_t)p_tile * ROWS * ldk + (size_t)c * 32;
-                cp_async16(slot + p_stage * stage_stride, src);
-                if (RSLOTS == 2) cp_async16(slot + p_stage * stage_stride + SK_WARPS * 32, src + (size_t)8 * ldk);
+#pragma unroll
+                for (int rs = 0; rs < RSLOTS; ++rs)
+                    cp_async16(slot + p_stage * stage_stride + rs * SK_WARPS * 32, src + (size_t)(8 * rs) * ldk);
             }
             ++p_item;
             if (++p_i == CH) { p_i = 0; p_tile += gdim; }
@@ -197,8 +215,12 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
         for (int j = 0; j < NT; ++j) xq[i][j] = load_x(chunk_of(i), j, true);
 
     float acc[NT][4];
+    float acc2[NT][4];                                    // rows 16..23 of a 24-row tile (upper half unused)
 #pragma unroll
-    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int j = 0; j < NT; ++j) {
+        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        acc2[j][0] = acc2[j][1] = acc2[j][2] = acc2[j][3] = 0.f;
+    }
 
     int c_stage = 0, buf = 0;
     for (int tk = 0; tk < my_tiles; ++tk) {
@@ -222,7 +244,8 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                 }
                 cp_async_wait<STAGES - 1>();              // the oldest group (this item) has landed
                 const uint4 fa = slot[c_stage * stage_stride];
-                const uint4 fb = RSLOTS == 2 ? slot[c_stage * stage_stride + SK_WARPS * 32] : make_uint4(0, 0, 0, 0);
+                const uint4 fb = RSLOTS >= 2 ? slot[c_stage * stage_stride + SK_WARPS * 32] : make_uint4(0, 0, 0, 0);
+                const uint4 fc = RSLOTS == 3 ? slot[c_stage * stage_stride + 2 * SK_WARPS * 32] : make_uint4(0, 0, 0, 0);
                 if (++c_stage == STAGES) c_stage = 0;
                 issue();                                  // refill the slot with the item SK_STAGES ahead
                 if (c < n_chunks) {
@@ -230,6 +253,10 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                     for (int j = 0; j < NT; ++j) {
                         mma16816(acc[j], fa.x, fb.x, fa.y, fb.y, xb[j].x, xb[j].y);
                         mma16816(acc[j], fa.z, fb.z, fa.w, fb.w, xb[j].z, xb[j].w);
+                        if (RSLOTS == 3) {
+                            mma16816(acc2[j], fc.x, 0u, fc.y, 0u, xb[j].x, xb[j].y);
+                            mma16816(acc2[j], fc.z, 0u, fc.w, 0u, xb[j].z, xb[j].w);
+                        }
                     }
                 }
             }
@@ -239,9 +266,14 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
         for (int j = 0; j < NT; ++j) {
             part[buf][w][g][j * 8 + 2 * t] = acc[j][0];
             part[buf][w][g][j * 8 + 2 * t + 1] = acc[j][1];
-            if (ROWS == 16) {
+            if (ROWS >= 16) {
                 part[buf][w][(g + 8) % ROWS][j * 8 + 2 * t] = acc[j][2];
                 part[buf][w][(g + 8) % ROWS][j * 8 + 2 * t + 1] = acc[j][3];
+            }
+            if (ROWS == 24) {
+                part[buf][w][(g + 16) % ROWS][j * 8 + 2 * t] = acc2[j][0];
+                part[buf][w][(g + 16) % ROWS][j * 8 + 2 * t + 1] = acc2[j][1];
+                acc2[j][0] = acc2[j][1] = 0.f;
             }
             acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
         }
@@ -266,7 +298,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
             __syncthreads();
         }
         const int n0 = tile * ROWS;
-        if (EPI != EPI_SWIGLU && !NORM && S > 1) {
+        if (EPI != EPI_SWIGLU && EPI != EPI_CONV && !NORM && S > 1) {
             // this block's partial tile -> workspace; the last of the S blocks adds them up
             constexpr int TILE = ROWS * NT * 8;
             float* wsp = ws + (size_t)tile * S * TILE;
@@ -297,6 +329,40 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                     else if (EPI == EPI_F32) reinterpret_cast<float*>(out)[o] = v;
                     else reinterpret_cast<float*>(out)[o] += v + (bias ? bias[n0 + r] : 0.f);
                 }
+            }
+        } else if (EPI == EPI_CONV) {
+            // 8 channels per token: rows r, r + 8, r + 16 are B, C, X of channel tile * 8 + r (ROWS == 24)
+            for (int idx = threadIdx.x; idx < 8 * NT * 8; idx += blockDim.x) {
+                const int r = idx & 7, m = idx >> 3;
+                if (m >= M) continue;
+                float b = 0.f, cg = 0.f, xv = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < SK_WARPS; ++ww) {
+                    b += part[buf][ww][r][m];
+                    cg += part[buf][ww][(r + 8) % ROWS][m];
+                    xv += part[buf][ww][(r + 16) % ROWS][m];
+                }
+                if (NORM && folded) { b *= rinv[m]; cg *= rinv[m]; xv *= rinv[m]; }
+                // the projection's output is a bfloat16 tensor wherever it is stored: round as a store would
+                b = __bfloat162float(__float2bfloat16_rn(b));
+                cg = __bfloat162float(__float2bfloat16_rn(cg));
+                xv = __bfloat162float(__float2bfloat16_rn(xv));
+                const int ch = tile * 8 + r, H = cv.H, L = cv.L;
+                if (cv.in_bias) { b += cv.in_bias[ch]; cg += cv.in_bias[H + ch]; xv += cv.in_bias[2 * H + ch]; }
+                const float bx = b * xv;
+                float* st = cv.state + (size_t)cv.slots[m] * cv.slot_stride + ch;
+                const bool fresh = cv.seg_pos0[m] == 0;
+                const float* tp = cv.taps + (size_t)ch * L;
+                float y = 0.f;
+                for (int q = 0; q < L - 1; ++q) {
+                    const float hq = fresh ? 0.f : st[(size_t)q * H];
+                    y += hq * tp[q];
+                    if (q > 0) st[(size_t)(q - 1) * H] = hq;      // the history moves up by one place
+                }
+                st[(size_t)(L - 2) * H] = bx;
+                y += bx * tp[L - 1];
+                if (cv.conv_bias) y += cv.conv_bias[ch];
+                reinterpret_cast<bf16*>(out)[(size_t)m * H + ch] = __float2bfloat16_rn(cg * y);
             }
         } else if (EPI == EPI_SWIGLU) {
             // 8 outputs per token: row r is gate, row r + 8 is up (ROWS == 16)
@@ -340,7 +406,7 @@ GESSO_API int gesso_skinny_gemm_takes(int M, int N, int K) {
 
 template <int NT, int EPI, bool NORM, int ROWS, int XC>
 static int launch_one(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
-                      const float* bias, int M, int N, int K, int S, void* ws, cudaStream_t stream) {
+                      const float* bias, int M, int N, int K, int S, void* ws, const ConvEpi& cv, cudaStream_t stream) {
     static bool configured = false;   // once per instantiation, outside any stream capture
     if (!configured) {
         cudaFuncSetAttribute(skinny_gemm_kernel<NT, EPI, NORM, ROWS, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -352,17 +418,18 @@ static int launch_one(const void* x, const float* h_in, const float* norm_w, flo
     const int blocks = per_share * S;
     launch_pdl(skinny_gemm_kernel<NT, EPI, NORM, ROWS, XC>, dim3(blocks), dim3(SK_WARPS * 32), SK_RING_BYTES(ROWS), stream,
                (const bf16*)x, h_in, norm_w, eps, (const bf16*)W, out, bias, M, N, K / S, K, S,
-               (float*)((int*)ws + SK_TICKETS), (int*)ws);
+               (float*)((int*)ws + SK_TICKETS), (int*)ws, cv);
     return launch_status();
 }
 
 template <int NT, int EPI, bool NORM>
 static int launch_shape(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
-                        const float* bias, int M, int N, int K, void* ws, long long ws_bytes, cudaStream_t stream) {
+                        const float* bias, int M, int N, int K, void* ws, long long ws_bytes, const ConvEpi& cv,
+                        cudaStream_t stream) {
     // token-side fragments stay in registers when a warp has at most 8 chunks per tile (K <= 2048)
     auto cacheable = [](int k) { return k / 32 <= 8 * SK_WARPS && k % (32 * SK_WARPS) == 0 && NT * (k / (32 * SK_WARPS)) <= 16; };
     int S = 1;
-    if (!cacheable(K) && !NORM && EPI != EPI_SWIGLU && ws != nullptr && N / 8 <= SK_TICKETS) {
+    if (!cacheable(K) && !NORM && EPI != EPI_SWIGLU && EPI != EPI_CONV && ws != nullptr && N / 8 <= SK_TICKETS) {
         // split K over S blocks per tile, the smallest S whose share is cacheable and fits the workspace
         for (int s = 2; s <= 16; s *= 2) {
             // sized for 16 token rows whatever M is: the choice of S must not depend on the batch
@@ -374,7 +441,12 @@ static int launch_shape(const void* x, const float* h_in, const float* norm_w, f
     const bool cache_x = cacheable(Ks);
     const bool small_rows = EPI != EPI_SWIGLU && (N / 16) * S < SK_MAX_BLOCKS && N % 8 == 0;
     const int xc = cache_x ? Ks / (32 * SK_WARPS) : 0;
-#define GO(ROWS, XC) return launch_one<NT, EPI, NORM, ROWS, XC>(x, h_in, norm_w, eps, W, out, bias, M, N, K, S, ws, stream)
+#define GO(ROWS, XC) return launch_one<NT, EPI, NORM, ROWS, XC>(x, h_in, norm_w, eps, W, out, bias, M, N, K, S, ws, cv, stream)
+    if constexpr (EPI == EPI_CONV) {
+        if (xc == 8) GO(24, 8);
+        if (xc == 4) GO(24, 4);
+        GO(24, 0);
+    } else {
     if (EPI != EPI_SWIGLU && small_rows) {
         if (xc == 8) GO(8, 8);
         if (xc == 4) GO(8, 4);
@@ -385,25 +457,28 @@ static int launch_shape(const void* x, const float* h_in, const float* norm_w, f
     if (xc == 4) GO(16, 4);
     if (xc == 2) GO(16, 2);
     GO(16, 0);
+    }
 #undef GO
 }
 
 template <int NT>
 static int launch_skinny(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
                          const float* bias, int M, int N, int K, int epi, void* ws, long long ws_bytes,
-                         cudaStream_t stream) {
+                         const ConvEpi& cv, cudaStream_t stream) {
     const bool norm = h_in != nullptr;
-#define GO(E, NM) return launch_shape<NT, E, NM>(x, h_in, norm_w, eps, W, out, bias, M, N, K, ws, ws_bytes, stream)
+#define GO(E, NM) return launch_shape<NT, E, NM>(x, h_in, norm_w, eps, W, out, bias, M, N, K, ws, ws_bytes, cv, stream)
     if (norm) {
         if (epi == EPI_BF16) GO(EPI_BF16, true);
         else if (epi == EPI_F32) GO(EPI_F32, true);
         else if (epi == EPI_SWIGLU) GO(EPI_SWIGLU, true);
+        else if (epi == EPI_CONV) GO(EPI_CONV, true);
         else return GESSO_ERR_UNSUPPORTED;
     } else {
         if (epi == EPI_BF16) GO(EPI_BF16, false);
         else if (epi == EPI_F32) GO(EPI_F32, false);
         else if (epi == EPI_RESID) GO(EPI_RESID, false);
         else if (epi == EPI_SWIGLU) GO(EPI_SWIGLU, false);
+        else if (epi == EPI_CONV) GO(EPI_CONV, false);
         else return GESSO_ERR_UNSUPPORTED;
     }
 #undef GO
@@ -419,7 +494,28 @@ GESSO_API int gesso_skinny_gemm(const void* x, const float* h_in, const float* n
     if (!gesso_skinny_gemm_takes(M, N, K)) return GESSO_ERR_BAD_SIZE;
     if ((x == nullptr) == (h_in == nullptr)) return GESSO_ERR_UNSUPPORTED;
     if (h_in && M > 16) return GESSO_ERR_BAD_SIZE;      // the fused norm is for a handful of rows
+    if (epi == EPI_CONV) return GESSO_ERR_UNSUPPORTED;   // has an entry point of its own
     if (ws_bytes < (long long)SK_TICKETS * 4) ws = nullptr;
-    if (M <= 8) return launch_skinny<1>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, ws, ws_bytes, stream);
-    return launch_skinny<2>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, ws, ws_bytes, stream);
+    const ConvEpi none = {};
+    if (M <= 8) return launch_skinny<1>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, ws, ws_bytes, none, stream);
+    return launch_skinny<2>(x, h_in, norm_w, eps, W, out, bias, M, N, K, epi, ws, ws_bytes, none, stream);
+}
+
+GESSO_API int gesso_skinny_conv_takes(int M, int H, int K, int L) {
+    return M >= 1 && M <= 16 && H >= 8 && H % 8 == 0 && K >= 32 && K % 32 == 0 && L >= 2 && L <= 8;
+}
+
+// The input projection of the short convolution with the convolution in its epilogue, for a step of
+// single tokens (token i belongs to request i).  W: bf16 [3H, K] packed in groups of 24 rows (B, C, X
+// of 8 channels); x or h_in/norm_w as above; y: bf16 [M, H]; state: this layer's [slot][L-1][H] float32.
+GESSO_API int gesso_skinny_gemm_conv(const void* x, const float* h_in, const float* norm_w, float eps, const void* W,
+                                     void* y, int M, int H, int K, const float* taps, const float* conv_bias,
+                                     const float* in_bias, float* state, long long slot_stride, const int* slots,
+                                     const int* seg_pos0, int L, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (!gesso_skinny_conv_takes(M, H, K, L)) return GESSO_ERR_BAD_SIZE;
+    if ((x == nullptr) == (h_in == nullptr)) return GESSO_ERR_UNSUPPORTED;
+    const ConvEpi cv = {taps, conv_bias, in_bias, state, slot_stride, slots, seg_pos0, L, H};
+    if (M <= 8) return launch_skinny<1>(x, h_in, norm_w, eps, W, y, nullptr, M, 3 * H, K, EPI_CONV, nullptr, 0, cv, stream);
+    return launch_skinny<2>(x, h_in, norm_w, eps, W, y, nullptr, M, 3 * H, K, EPI_CONV, nullptr, 0, cv, stream);
 }

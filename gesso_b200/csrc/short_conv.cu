@@ -12,13 +12,21 @@
 // (one thread per (portion, channel), which owns that slot column) rewrites it afterwards.
 // When every portion is short (decoding), `mix_update_small` does both in one launch with the
 // same ownership.
+//
+// `packed` rows of bcx hold the three parts in groups of 24 columns (B, C, X of 8 channels), the order in
+// which the packed input projection (whose decoding form has this convolution in its epilogue) gives them.
 #include "common.cuh"
+
+// column of part p (0 = B, 1 = C, 2 = X) of channel c in a row of bcx
+__device__ __forceinline__ int bcx_col(int part, int c, int H, int packed) {
+    return packed ? 24 * (c >> 3) + 8 * part + (c & 7) : part * H + c;
+}
 
 template <typename T>
 __device__ __forceinline__ float bx_at(const T* __restrict__ bcx, const float* __restrict__ in_bias,
-                                       int tok, int c, int H) {
+                                       int tok, int c, int H, int packed) {
     const T* row = bcx + (size_t)tok * 3 * H;
-    float b = to_f32(row[c]), x = to_f32(row[2 * H + c]);
+    float b = to_f32(row[bcx_col(0, c, H, packed)]), x = to_f32(row[bcx_col(2, c, H, packed)]);
     if (in_bias) { b += in_bias[c]; x += in_bias[2 * H + c]; }
     return b * x;
 }
@@ -30,7 +38,7 @@ __global__ void conv_mix_kernel(const T* __restrict__ bcx, const float* __restri
                                 const float* __restrict__ state, long long slot_stride,
                                 const int* __restrict__ seg_of_token, const int* __restrict__ seg_start,
                                 const int* __restrict__ seg_pos0, const int* __restrict__ slots,
-                                T* __restrict__ out, int n_tokens, int H, int L) {
+                                T* __restrict__ out, int n_tokens, int H, int L, int packed) {
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int t = blockIdx.x;
     if (c >= H || t >= n_tokens) return;
@@ -44,14 +52,14 @@ __global__ void conv_mix_kernel(const T* __restrict__ bcx, const float* __restri
         const int back = (L - 1) - p;          // how many tokens before t
         float v;
         if (back > pos) v = 0.f;               // before the start of the sequence
-        else if (back <= off) v = bx_at(bcx, in_bias, t - back, c, H);
+        else if (back <= off) v = bx_at(bcx, in_bias, t - back, c, H, packed);
         else v = st[(size_t)((L - 1) - (back - off)) * H + c];
         y += v * w[p];
     }
-    y += bx_at(bcx, in_bias, t, c, H) * w[L - 1];
+    y += bx_at(bcx, in_bias, t, c, H, packed) * w[L - 1];
     if (conv_bias) y += conv_bias[c];
     const T* row = bcx + (size_t)t * 3 * H;
-    float cg = to_f32(row[H + c]);
+    float cg = to_f32(row[bcx_col(1, c, H, packed)]);
     if (in_bias) cg += in_bias[H + c];
     out[(size_t)t * H + c] = from_f32<T>(cg * y);
 }
@@ -98,7 +106,7 @@ __global__ void conv_mix_vec_kernel(const T* __restrict__ bcx, const float* __re
                                     const float* __restrict__ state, long long slot_stride,
                                     const int* __restrict__ seg_of_token, const int* __restrict__ seg_start,
                                     const int* __restrict__ seg_pos0, const int* __restrict__ slots,
-                                    T* __restrict__ out, int n_tokens, int H, int L) {
+                                    T* __restrict__ out, int n_tokens, int H, int L, int packed) {
     constexpr int V = ConvVec<T>::N;
     const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     const int t = blockIdx.x;
@@ -119,8 +127,8 @@ __global__ void conv_mix_vec_kernel(const T* __restrict__ bcx, const float* __re
         } else if (back <= off) {
             const T* row = bcx + (size_t)(t - back) * 3 * H;
             float b[V], x[V];
-            load_vec<T>(row + c0, b);
-            load_vec<T>(row + 2 * H + c0, x);
+            load_vec<T>(row + bcx_col(0, c0, H, packed), b);
+            load_vec<T>(row + bcx_col(2, c0, H, packed), x);
 #pragma unroll
             for (int v = 0; v < V; ++v) {
                 if (in_bias) { b[v] += in_bias[c0 + v]; x[v] += in_bias[2 * H + c0 + v]; }
@@ -135,7 +143,7 @@ __global__ void conv_mix_vec_kernel(const T* __restrict__ bcx, const float* __re
         for (int v = 0; v < V; ++v) y[v] += val[v] * taps[(size_t)(c0 + v) * L + p];
     }
     float cg[V];
-    load_vec<T>(bcx + (size_t)t * 3 * H + H + c0, cg);
+    load_vec<T>(bcx + (size_t)t * 3 * H + bcx_col(1, c0, H, packed), cg);
 #pragma unroll
     for (int v = 0; v < V; ++v) {
         if (conv_bias) y[v] += conv_bias[c0 + v];
@@ -149,7 +157,7 @@ template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ bcx, const float* __restrict__ in_bias,
                                          float* __restrict__ state, long long slot_stride,
                                          const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
-                                         const int* __restrict__ slots, int n_segs, int H, int L) {
+                                         const int* __restrict__ slots, int n_segs, int H, int L, int packed) {
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int s = blockIdx.x;
     if (c >= H || s >= n_segs) return;
@@ -162,7 +170,7 @@ __global__ void conv_state_update_kernel(const T* __restrict__ bcx, const float*
         const int back = (L - 1) - q;          // 1 = last token of the portion
         float v;
         if (back > pos_end) v = 0.f;
-        else if (back <= n) v = bx_at(bcx, in_bias, t0 + n - back, c, H);
+        else if (back <= n) v = bx_at(bcx, in_bias, t0 + n - back, c, H, packed);
         else v = st[(size_t)(q + n) * H + c];
         st[(size_t)q * H + c] = v;
     }
@@ -176,7 +184,7 @@ __global__ void conv_mix_update_small_kernel(const T* __restrict__ bcx, const fl
                                              float* __restrict__ state, long long slot_stride,
                                              const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
                                              const int* __restrict__ slots, T* __restrict__ out, int n_segs,
-                                             int H, int L) {
+                                             int H, int L, int packed) {
     // let the successor in first (it only prefetches what no running kernel writes until its own wait)
     pdl_launch_dependents();
     pdl_wait();
@@ -194,7 +202,7 @@ __global__ void conv_mix_update_small_kernel(const T* __restrict__ bcx, const fl
     }
     for (int i = 0; i < n; ++i) {
         const int t = t0 + i;
-        const float bx = bx_at(bcx, in_bias, t, c, H);
+        const float bx = bx_at(bcx, in_bias, t, c, H, packed);
         float y = 0.f;
 #pragma unroll
         for (int p = 0; p < LMAX; ++p)
@@ -206,7 +214,7 @@ __global__ void conv_mix_update_small_kernel(const T* __restrict__ bcx, const fl
         y += bx * wl;
         if (conv_bias) y += conv_bias[c];
         const T* row = bcx + (size_t)t * 3 * H;
-        float cg = to_f32(row[H + c]);
+        float cg = to_f32(row[bcx_col(1, c, H, packed)]);
         if (in_bias) cg += in_bias[H + c];
         out[(size_t)t * H + c] = from_f32<T>(cg * y);
 #pragma unroll
@@ -225,9 +233,9 @@ GESSO_API int gesso_short_conv(const void* bcx, int dtype, const float* in_bias,
                                const float* conv_bias, float* state, long long slot_stride,
                                const int* seg_of_token, const int* seg_start, const int* seg_pos0,
                                const int* slots, void* out, int n_tokens, int n_segs, int max_seg_len,
-                               int H, int L, cudaStream_t stream) {
+                               int H, int L, int packed, cudaStream_t stream) {
     if (n_tokens <= 0 || n_segs <= 0) return 0;
-    if (L < 2 || H <= 0) return GESSO_ERR_BAD_SIZE;
+    if (L < 2 || H <= 0 || (packed && H % 8 != 0)) return GESSO_ERR_BAD_SIZE;
     if (dtype != GESSO_F32 && dtype != GESSO_BF16) return GESSO_ERR_BAD_DTYPE;
     const int threads = 128;
     const int cblocks = (H + threads - 1) / threads;
@@ -236,11 +244,11 @@ GESSO_API int gesso_short_conv(const void* bcx, int dtype, const float* in_bias,
         if (dtype == GESSO_F32)
             launch_pdl(conv_mix_update_small_kernel<float, 8>, grid, dim3(threads), 0, stream,
                 (const float*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_start, seg_pos0, slots,
-                (float*)out, n_segs, H, L);
+                (float*)out, n_segs, H, L, packed);
         else
             launch_pdl(conv_mix_update_small_kernel<bf16, 8>, grid, dim3(threads), 0, stream,
                 (const bf16*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_start, seg_pos0, slots,
-                (bf16*)out, n_segs, H, L);
+                (bf16*)out, n_segs, H, L, packed);
         return launch_status();
     }
     dim3 grid(n_tokens, cblocks), sgrid(n_segs, cblocks);
@@ -252,30 +260,30 @@ GESSO_API int gesso_short_conv(const void* bcx, int dtype, const float* in_bias,
         if (dtype == GESSO_F32) {
             conv_mix_vec_kernel<float><<<vgrid, vthreads, 0, stream>>>(
                 (const float*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_of_token, seg_start, seg_pos0, slots,
-                (float*)out, n_tokens, H, L);
+                (float*)out, n_tokens, H, L, packed);
             conv_state_update_kernel<float><<<sgrid, threads, 0, stream>>>((const float*)bcx, in_bias, state, slot_stride,
-                                                                           seg_start, seg_pos0, slots, n_segs, H, L);
+                                                                           seg_start, seg_pos0, slots, n_segs, H, L, packed);
         } else {
             conv_mix_vec_kernel<bf16><<<vgrid, vthreads, 0, stream>>>(
                 (const bf16*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_of_token, seg_start, seg_pos0, slots,
-                (bf16*)out, n_tokens, H, L);
+                (bf16*)out, n_tokens, H, L, packed);
             conv_state_update_kernel<bf16><<<sgrid, threads, 0, stream>>>((const bf16*)bcx, in_bias, state, slot_stride,
-                                                                          seg_start, seg_pos0, slots, n_segs, H, L);
+                                                                          seg_start, seg_pos0, slots, n_segs, H, L, packed);
         }
         return launch_status();
     }
     if (dtype == GESSO_F32) {
         conv_mix_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, in_bias, taps, conv_bias, state,
                                                              slot_stride, seg_of_token, seg_start, seg_pos0, slots,
-                                                             (float*)out, n_tokens, H, L);
+                                                             (float*)out, n_tokens, H, L, packed);
         conv_state_update_kernel<float><<<sgrid, threads, 0, stream>>>((const float*)bcx, in_bias, state, slot_stride,
-                                                                       seg_start, seg_pos0, slots, n_segs, H, L);
+                                                                       seg_start, seg_pos0, slots, n_segs, H, L, packed);
     } else {
         conv_mix_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, in_bias, taps, conv_bias, state,
                                                             slot_stride, seg_of_token, seg_start, seg_pos0, slots,
-                                                            (bf16*)out, n_tokens, H, L);
+                                                            (bf16*)out, n_tokens, H, L, packed);
         conv_state_update_kernel<bf16><<<sgrid, threads, 0, stream>>>((const bf16*)bcx, in_bias, state, slot_stride,
-                                                                      seg_start, seg_pos0, slots, n_segs, H, L);
+                                                                      seg_start, seg_pos0, slots, n_segs, H, L, packed);
     }
     return launch_status();
 }

@@ -110,8 +110,9 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Ten
 def short_conv(bcx: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Tensor,
                conv_bias: Optional[torch.Tensor], state: torch.Tensor, seg_of_token: torch.Tensor,
                seg_start: torch.Tensor, seg_pos0: torch.Tensor, slots: torch.Tensor,
-               n_segs: int, max_seg_len: int) -> torch.Tensor:
-    """Gated FIR over ``bcx`` [N, 3H]; ``state`` is this layer's view [slots, L-1, H] (float32)."""
+               n_segs: int, max_seg_len: int, packed: bool = False) -> torch.Tensor:
+    """Gated FIR over ``bcx`` [N, 3H]; ``state`` is this layer's view [slots, L-1, H] (float32).
+    ``packed``: the columns of ``bcx`` come in groups of 24 (see :func:`pack_bcx`)."""
     _cuda_contig(bcx, "bcx")
     _cuda_contig(taps, "taps", torch.float32)
     N, H3 = bcx.shape
@@ -127,8 +128,54 @@ def short_conv(bcx: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.T
     _lib.check(_lib.library().gesso_short_conv(
         _p(bcx), _dt(bcx), _p(in_bias), _p(taps), _p(conv_bias), _p(state), state.stride(0),
         _p(seg_of_token), _p(seg_start), _p(seg_pos0), _p(slots), _p(out), N, n_segs, max_seg_len,
-        H, L, _stream()), "short_conv")
+        H, L, 1 if packed else 0, _stream()), "short_conv")
     return out
+
+
+def pack_bcx(w_in: torch.Tensor) -> torch.Tensor:
+    """The short convolution's input projection [3H, K] (rows B, then C, then X) in groups of 24 rows:
+    B, C and X of 8 channels (the layout whose convolution the skinny matrix product can run in its
+    epilogue).  H % 8 == 0."""
+    H3, K = w_in.shape
+    H = H3 // 3
+    return w_in.reshape(3, H // 8, 8, K).permute(1, 0, 2, 3).reshape(H3, K).contiguous()
+
+
+def skinny_conv_takes(M: int, w_in: torch.Tensor, x_dtype, L: int) -> bool:
+    H3, K = w_in.shape
+    return (w_in.dtype == torch.bfloat16 and x_dtype == torch.bfloat16 and w_in.is_contiguous()
+            and 1 <= M <= SKINNY_MAX_ROWS and H3 % 24 == 0 and K % 32 == 0 and 2 <= L <= 8)
+
+
+def linear_conv(x, w_in_packed: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Tensor,
+                conv_bias: Optional[torch.Tensor], state: torch.Tensor, seg_pos0: torch.Tensor,
+                slots: torch.Tensor) -> torch.Tensor:
+    """Input projection and gated FIR in one kernel for a step of single tokens (token i is request i):
+    ``x`` is a bfloat16 tensor or a :class:`LazyNorm` of at most 16 rows, ``w_in_packed`` from
+    :func:`pack_bcx`; returns y [M, H] and shifts bx into ``state`` [slots, L-1, H]."""
+    H3, K = w_in_packed.shape
+    H, L = taps.shape
+    _need(H3 == 3 * H, "packed input projection must have three rows per channel")
+    _need(state.dtype == torch.float32 and state.is_cuda and state.dim() == 3 and state.shape[1] == L - 1
+          and state.shape[2] == H and state.stride(2) == 1 and state.stride(1) == H,
+          "conv state must be [slots, L-1, H] float32 with dense rows")
+    _cuda_contig(taps, "taps", torch.float32)
+    _cuda_contig(seg_pos0, "seg_pos0", torch.int32)
+    _cuda_contig(slots, "slots", torch.int32)
+    x = _skinny_input(x)
+    M = x.shape[0]
+    _need(slots.numel() >= M and seg_pos0.numel() >= M, "one slot and one position per token")
+    if isinstance(x, LazyNorm):
+        _cuda_contig(x.h, "h", torch.float32)
+        args = (None, _p(x.h), _p(x.weight), x.eps)
+    else:
+        _cuda_contig(x, "x", torch.bfloat16)
+        args = (_p(x), None, None, 0.0)
+    y = torch.empty((M, H), dtype=torch.bfloat16, device=w_in_packed.device)
+    _lib.check(_lib.library().gesso_skinny_gemm_conv(
+        *args, _p(w_in_packed), _p(y), M, H, K, _p(taps), _p(conv_bias), _p(in_bias), _p(state), state.stride(0),
+        _p(slots), _p(seg_pos0), L, _stream()), "skinny_gemm_conv")
+    return y
 
 
 # ---- attention ---------------------------------------------------------------------------------

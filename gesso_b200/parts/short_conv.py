@@ -14,6 +14,8 @@ from __future__ import annotations
 
 from typing import Dict
 
+import torch
+
 from .. import ops
 from ..errors import invalid
 from .base import Mixer, ParamDecl, StateNeed
@@ -57,15 +59,26 @@ class ShortConv(Mixer):
         self.b_in = tensors.get("in_proj.bias")
         self.b_conv = tensors.get("conv.bias")
         self.b_out = tensors.get("out_proj.bias")
+        # bfloat16 runs keep the input projection in groups of 24 rows (B, C, X of 8 channels): decoding
+        # steps then run the convolution in the projection's epilogue, and longer steps read the
+        # projection's output in the same grouping
+        self.packed = self.w_in.dtype == torch.bfloat16 and self.hidden % 8 == 0
+        if self.packed:
+            self.w_in = ops.pack_bcx(self.w_in)
 
     def fold_input_scale(self, scale) -> bool:
         self.w_in = ops.fold_norm_weight(self.w_in, scale)
         return True
 
     def forward(self, x, ctx, cache, residual=None):
-        bcx = ops.linear(x, self.w_in, out_dtype=x.dtype)
-        y = ops.short_conv(bcx, self.b_in, self.taps, self.b_conv, cache.state, ctx.seg_of_token,
-                           ctx.seg_start, ctx.seg_pos0, cache.slots, ctx.n_segs, ctx.max_seg_len)
+        if self.packed and ctx.decode_only and ops.skinny_conv_takes(x.shape[0], self.w_in, x.dtype, self.kernel):
+            y = ops.linear_conv(x, self.w_in, self.b_in, self.taps, self.b_conv, cache.state, ctx.seg_pos0,
+                                cache.slots)
+        else:
+            bcx = ops.linear(x, self.w_in, out_dtype=x.dtype)
+            y = ops.short_conv(bcx, self.b_in, self.taps, self.b_conv, cache.state, ctx.seg_of_token,
+                               ctx.seg_start, ctx.seg_pos0, cache.slots, ctx.n_segs, ctx.max_seg_len,
+                               packed=self.packed)
         if residual is not None:
             d = ops.linear_residual(y, self.w_out, residual, self.b_out)
             return (None, None) if d is None else (d, self.b_out)

@@ -150,6 +150,90 @@ def test_short_conv_carried_state(dtype, H, L, bias):
     assert torch.equal(st_a, st_b)
 
 
+@pytest.mark.parametrize("H,L,bias", [(64, 3, False), (40, 4, True), (8, 2, False)])
+def test_short_conv_packed_layout(H, L, bias):
+    """The same convolution from rows of bcx laid out in groups of 24 columns (B, C, X of 8 channels)."""
+    from gesso_b200 import ops
+    g = torch.Generator().manual_seed(H + L)
+    T = 41
+    taps = torch.randn(H, L, generator=g).to(DEV)
+    in_b = torch.randn(3 * H, generator=g).to(DEV) if bias else None
+    cv_b = torch.randn(H, generator=g).to(DEV) if bias else None
+    bcx = torch.randn(T, 3 * H, generator=g).to(torch.bfloat16).to(DEV)
+    packed = bcx.reshape(T, 3, H // 8, 8).permute(0, 2, 1, 3).reshape(T, 3 * H).contiguous()
+    # pack_bcx permutes the rows of the projection the same way
+    w = torch.arange(3 * H, dtype=torch.float32).reshape(3 * H, 1).repeat(1, 2)
+    assert torch.equal(ops.pack_bcx(w)[:, 0], torch.arange(3 * H, dtype=torch.float32)
+                       .reshape(3, H // 8, 8).permute(1, 0, 2).reshape(-1))
+    for cuts in ([T], [9, 1, 1, 3, 27]):
+        st_a = torch.zeros((1, L - 1, H), device=DEV)
+        st_b = torch.zeros((1, L - 1, H), device=DEV)
+        pos = 0
+        for n in cuts:
+            args = (i32([0] * n), i32([0, n]), i32([pos]), i32([0]), 1, n)
+            a = ops.short_conv(bcx[pos:pos + n].contiguous(), in_b, taps, cv_b, st_a, *args)
+            b = ops.short_conv(packed[pos:pos + n].contiguous(), in_b, taps, cv_b, st_b, *args, packed=True)
+            assert torch.equal(a, b) and torch.equal(st_a, st_b)
+            pos += n
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 11, 16])
+@pytest.mark.parametrize("H,K,L,bias", [(64, 64, 3, False), (2048, 2048, 3, False), (40, 96, 4, True),
+                                        (8, 32, 2, False), (48, 8192, 3, True)])
+def test_skinny_projection_with_conv_epilogue(M, H, K, L, bias):
+    """Input projection + gated FIR + state shift in one kernel (a step of single tokens) against the
+    projection followed by the convolution kernel, and against the formulas; fresh and running requests
+    in one step, slots in any order, two steps in a row."""
+    from gesso_b200 import ops
+    g = torch.Generator().manual_seed(M * 100 + H + K + L)
+    w = (torch.randn(3 * H, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    wp = ops.pack_bcx(w)
+    taps = torch.randn(H, L, generator=g).to(DEV)
+    in_b = torch.randn(3 * H, generator=g).to(DEV) if bias else None
+    cv_b = torch.randn(H, generator=g).to(DEV) if bias else None
+    assert ops.skinny_conv_takes(M, wp, torch.bfloat16, L)
+    slots = torch.randperm(M + 3, generator=g)[:M].tolist()
+    st_fused = torch.randn(M + 3, L - 1, H, generator=g).to(DEV)
+    st_split = st_fused.clone()
+    st_ref = st_fused.double().cpu()
+    pos = [0 if i % 3 == 0 else 5 + i for i in range(M)]           # every third request starts here
+    for step in range(2):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+        y = ops.linear_conv(x, wp, in_b, taps, cv_b, st_fused, i32(pos), i32(slots))
+        bcx = ops.linear(x, w)
+        y2 = ops.short_conv(bcx, in_b, taps, cv_b, st_split, i32(list(range(M))), i32(list(range(M + 1))),
+                            i32(pos), i32(slots), M, 1)
+        # the plain formulas on the rounded projection (src/Inference/lfm2.jl:253-271)
+        r = (x.double() @ w.double().T).to(torch.bfloat16).double().cpu()
+        if bias:
+            r = r + in_b.double().cpu()
+        B, C, X = r[:, :H], r[:, H:2 * H], r[:, 2 * H:]
+        want = torch.zeros(M, H, dtype=torch.float64)
+        for i in range(M):
+            hist = torch.zeros(L - 1, H, dtype=torch.float64) if pos[i] == 0 else st_ref[slots[i]].clone()
+            bx = B[i] * X[i]
+            yv = (hist * taps.double().cpu().T[:L - 1]).sum(0) + bx * taps.double().cpu()[:, L - 1]
+            if bias:
+                yv = yv + cv_b.double().cpu()
+            want[i] = C[i] * yv
+            st_ref[slots[i]] = torch.cat([hist[1:], bx[None]])
+        assert rel_err(y, want) < BF16_EPS
+        assert rel_err(y2, want) < BF16_EPS
+        assert rel_err(y, y2.double()) < BF16_EPS
+        used = torch.tensor(slots)
+        assert rel_err(st_fused[used.to(DEV)], st_ref[used]) < 1e-2 and rel_err(st_split[used.to(DEV)], st_ref[used]) < 1e-2
+        assert rel_err(st_fused, st_split.double()) < 1e-2
+        pos = [p + 1 for p in pos]
+    # a norm in the prologue (weight folded into the matrix by the caller, or applied here)
+    h = torch.randn(M, K, generator=g).to(DEV)
+    nw = (1 + 0.1 * torch.randn(K, generator=g)).to(DEV)
+    st1, st2 = st_fused.clone(), st_fused.clone()
+    y1 = ops.linear_conv(ops.LazyNorm(h, nw, 1e-5, torch.bfloat16), wp, in_b, taps, cv_b, st1, i32(pos), i32(slots))
+    y2 = ops.linear_conv(ops.add_rmsnorm(h, None, None, nw, 1e-5, torch.bfloat16), wp, in_b, taps, cv_b, st2,
+                         i32(pos), i32(slots))
+    assert rel_err(y1, y2.double()) < 2 * BF16_EPS
+
+
 def test_short_conv_tap_order_identity():
     """All-ones B, C, X with taps [2, -1, 3] gives [3, 2, 4, 4] (the newest tap is on the current
     token; test/test_lfm25.jl:79-90 without its norm factor); reversed taps give something else."""
