@@ -139,9 +139,10 @@ def pack_step(entries: List[StepEntry], starts: List[int], slots: List[int],
         pos[cur:cur + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
         seg[cur:cur + n] = i
         seg_start[i] = cur
-        for w in e.want:
-            rows[r] = cur + w
-            r += 1
+        k = len(e.want)
+        if k:
+            rows[r:r + k] = np.asarray(e.want, dtype=np.int64) + cur
+            r += k
         cur += n
     seg_start[layout.n_segs] = cur
     _pack_tail(entries, starts, slots, tables, layout, out, o)

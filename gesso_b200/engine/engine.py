@@ -112,11 +112,14 @@ class Engine:
         return self.cache.length(req_id)
 
     # ---- the step ----------------------------------------------------------------------------
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, entries: Sequence[StepEntry]) -> List[StepEntry]:
+        """Check the entries; returns them with tokens and wanted places as integer arrays (one
+        conversion serves the checks and the packing of long portions)."""
         if not entries:
             raise invalid("step: no entries")
         seen = set()
         V = self.model.vocab_size
+        out = []
         for e in entries:
             if e.req_id in seen:
                 raise invalid(f"step: request {e.req_id!r} appears twice in one step")
@@ -126,12 +129,21 @@ class Engine:
             n = len(e.tokens)
             if n < 1:
                 raise invalid(f"step: request {e.req_id!r} brings no tokens")
-            for t in e.tokens:
-                if not (0 <= int(t) < V):
-                    raise invalid(f"step: token id {t} of request {e.req_id!r} is outside the vocabulary (0..{V - 1})")
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise invalid(f"step: wanted place {w} of request {e.req_id!r} is outside its {n} tokens")
+            try:
+                toks = np.asarray(e.tokens, dtype=np.int64)
+                want = np.asarray(e.want, dtype=np.int64)
+            except (TypeError, ValueError, OverflowError):
+                raise invalid(f"step: tokens and wanted places of request {e.req_id!r} must be integers") from None
+            if toks.ndim != 1 or want.ndim != 1:
+                raise invalid(f"step: tokens and wanted places of request {e.req_id!r} must be flat lists")
+            if toks.min() < 0 or toks.max() >= V:
+                t = int(toks[(toks < 0) | (toks >= V)][0])
+                raise invalid(f"step: token id {t} of request {e.req_id!r} is outside the vocabulary (0..{V - 1})")
+            if want.size and (want.min() < 0 or want.max() >= n):
+                w = int(want[(want < 0) | (want >= n)][0])
+                raise invalid(f"step: wanted place {w} of request {e.req_id!r} is outside its {n} tokens")
+            out.append(StepEntry(e.req_id, toks, want))
+        return out
 
     def _pinned_buffer(self, n: int):
         i = self._pinned_next
@@ -172,7 +184,7 @@ class Engine:
         """Validate, reserve pages, zero fresh slots and pack the step's metadata on the host."""
         if entries and all(len(e.tokens) == 1 for e in entries):
             return self._prepare_single_tokens(entries)
-        self._validate(entries)
+        entries = self._validate(entries)
         for e in entries:
             n = len(e.tokens)
             if self.cache.length(e.req_id) + n > self.max_positions:
@@ -204,7 +216,8 @@ class Engine:
         pack_step(list(entries), starts, slots, tables, layout, host.numpy()[:size])
         max_seg = max(len(e.tokens) for e in entries)
         max_kv = max(s + len(e.tokens) for s, e in zip(starts, entries))
-        self._all_rows = all(list(e.want) == list(range(len(e.tokens))) for e in entries)
+        self._all_rows = all(len(e.want) == len(e.tokens) and bool((e.want == np.arange(len(e.tokens))).all())
+                             for e in entries)
         return layout, slot_i, host[:size], max_seg, max_kv
 
     def _upload(self, buf: torch.Tensor, slot_i: int, host: torch.Tensor) -> None:

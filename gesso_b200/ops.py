@@ -183,8 +183,10 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
                        eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                        positions: torch.Tensor, seg_of_token: torch.Tensor, block_table: torch.Tensor,
                        k_pages: torch.Tensor, v_pages: torch.Tensor, nh: int, nkv: int, hd: int,
-                       write_kv: bool, status: torch.Tensor) -> torch.Tensor:
-    """Norm + rotate q and k, write k and v into their pages; returns q as [N, nh, hd]."""
+                       write_kv: bool, status: torch.Tensor, tiles=None) -> torch.Tensor:
+    """Norm + rotate q and k, write k and v into their pages; returns q as [N, nh, hd].  ``tiles`` =
+    (seg_start, seg_pos0, tile_seg, tile_q0) of a step with prompt portions lets bfloat16 runs take the
+    kernel that works by 64-token tiles (wide loads, v written along the slots of its transposed page)."""
     _cuda_contig(qkv, "qkv")
     N = qkv.shape[0]
     heads = nh + 2 * nkv if write_kv else nh
@@ -203,6 +205,14 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
         _cuda_contig(sin, "sin", torch.float32)
         _need(cos.shape[1] == hd // 2, "rotary table width must be half the head size")
     q_out = torch.empty((N, nh, hd), dtype=qkv.dtype, device=qkv.device)
+    if (tiles is not None and write_kv and qkv.dtype == torch.bfloat16 and tiles[2].numel() > 0
+            and _lib.library().gesso_qk_rope_store_tiles_takes(hd, page_size, nh, nkv)):
+        seg_start, seg_pos0, tile_seg, tile_q0 = tiles
+        _lib.check(_lib.library().gesso_qk_norm_rope_store_tiles(
+            _p(qkv), _p(q_w), _p(k_w), float(eps), _p(cos), _p(sin), _p(seg_start), _p(seg_pos0), _p(tile_seg),
+            _p(tile_q0), tile_seg.numel(), _p(block_table), block_table.shape[1], page_size, _p(q_out),
+            _p(k_pages), _p(v_pages), nh, nkv, hd, _p(status), _stream()), "qk_norm_rope_store_tiles")
+        return q_out
     _lib.check(_lib.library().gesso_qk_norm_rope_store(
         _p(qkv), _dt(qkv), _p(q_w), _p(k_w), float(eps), _p(cos), _p(sin), _p(positions),
         _p(seg_of_token), _p(block_table), block_table.shape[1], page_size, _p(q_out), _p(k_pages),
@@ -430,6 +440,11 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
                                                 _p(ids), _p(bad), _stream()), "sample_rows")
     return ids, bad
 
+
+_lib.declare("gesso_qk_rope_store_tiles_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
+_lib.declare("gesso_qk_norm_rope_store_tiles", [_lib.P, _lib.P, _lib.P, _lib.F, _lib.P, _lib.P, _lib.P, _lib.P, _lib.P,
+                                                _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.I,
+                                                _lib.I, _lib.I, _lib.P, _lib.P])
 
 # ---- tensor-core attention (bfloat16) ------------------------------------------------------------
 _lib.declare("gesso_attention_tc_takes", [_lib.I, _lib.I, _lib.I, _lib.I])

@@ -330,6 +330,72 @@ def test_qk_norm_rope_store(dtype, nh, nkv, hd, page):
     assert int(status.item()) == 1 and torch.equal(kp, before)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 32, 16), (6, 3, 64, 16), (2, 2, 128, 32), (32, 8, 64, 8), (3, 1, 64, 24)])
+def test_qk_norm_rope_store_by_tiles(nh, nkv, hd, page):
+    """The kernel for prompt portions (64-token tiles, v written along the slots of its transposed page)
+    against the formulas: portions that start inside a page and inside a group of 8 positions, end
+    anywhere, span several tiles, beside single tokens; stale values around the written slots stay."""
+    from gesso_b200 import ops
+    from gesso_b200.engine.batch import QUERY_TILE
+    from gesso_b200.parts.rope import rope_tables
+    g = torch.Generator().manual_seed(nh * 100 + hd + page)
+    lens, starts = [150, 1, 67, 2, 9], [3, 40, 0, 250, 121]
+    N, S = sum(lens), len(lens)
+    ctx_len = 320
+    qkv = torch.randn(N, (nh + 2 * nkv) * hd, generator=g).to(torch.bfloat16)
+    qw = torch.rand(hd, generator=g) + 0.5
+    kw = torch.rand(hd, generator=g) + 0.5
+    theta, eps = 54321.0, 1e-6
+    cos, sin = rope_tables(theta, hd, ctx_len)
+    positions = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)])
+    seg = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)])
+    seg_start = [0]
+    for n in lens:
+        seg_start.append(seg_start[-1] + n)
+    tile_seg, tile_q0 = [], []
+    for i, n in enumerate(lens):
+        for q0 in range(0, n, QUERY_TILE):
+            tile_seg.append(i)
+            tile_q0.append(q0)
+    max_pages = (ctx_len + page - 1) // page
+    n_pages = S * max_pages
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    bt = torch.full((S, max_pages), -1, dtype=torch.int32)
+    for i, (s0, n) in enumerate(zip(starts, lens)):
+        for p in range((s0 + n + page - 1) // page):
+            bt[i, p] = perm.pop()
+    kp = torch.full((n_pages, nkv, page, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    vp = torch.full((n_pages, nkv, hd, page), 7.0, dtype=torch.bfloat16, device=DEV)
+    kp0, vp0 = kp.clone(), vp.clone()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert ops._lib.library().gesso_qk_rope_store_tiles_takes(hd, page, nh, nkv)
+    args = (qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, cos.to(DEV), sin.to(DEV), i32(positions.tolist()),
+            i32(seg.tolist()), bt.to(DEV))
+    tiles = (i32(seg_start), i32(starts), i32(tile_seg), i32(tile_q0))
+    q = ops.qk_norm_rope_store(*args, kp, vp, nh, nkv, hd, True, status, tiles=tiles)
+    kp1, vp1 = kp0.clone(), vp0.clone()
+    q1 = ops.qk_norm_rope_store(*args, kp1, vp1, nh, nkv, hd, True, status)      # one warp per (token, head)
+    x = qkv.double()
+    qr = P.rope(P.rmsnorm(x[:, :nh * hd].reshape(N, nh, hd), qw.double(), eps), positions.tolist(), theta)
+    assert rel_err(q, qr) < BF16_EPS and rel_err(q, q1.double()) < BF16_EPS
+    assert rel_err(kp, kp1.double()) < BF16_EPS
+    assert torch.equal(vp, vp1)                       # values are copied: identical, stale slots included
+    written = torch.zeros(n_pages, page, dtype=torch.bool)
+    for tkn in range(N):
+        s0, pos = int(seg[tkn]), int(positions[tkn])
+        written[int(bt[s0, pos // page]), pos % page] = True
+    kc, k0 = kp.cpu(), kp0.cpu()
+    for pg in range(n_pages):
+        for sl in range(page):
+            if not written[pg, sl]:
+                assert torch.equal(kc[pg, :, sl], k0[pg, :, sl])
+    assert int(status.item()) == 0
+    bt2 = bt.clone()
+    bt2[0, (3 + 70) // page] = -1                      # a page of the long portion is missing
+    ops.qk_norm_rope_store(args[0], *args[1:8], bt2.to(DEV), kp, vp, nh, nkv, hd, True, status, tiles=tiles)
+    assert int(status.item()) == 1
+
+
 # ---- attention -----------------------------------------------------------------------------------
 def attention_reference(q, ks, vs, seg_lens_new, window):
     """q [N, nh, hd]; per request: all keys/values so far (the new tokens are the last ones)."""
