@@ -7,17 +7,22 @@
 //   TMA warp      Q once (3-D tensor map [token][head][feature], 128-byte swizzle); per key block 8
 //                 K pages ([slot][feature] rows of 128 bytes, 128-byte swizzle) and 8 V pages
 //                 ([feature][slot] rows of 32 bytes, 32-byte swizzle) into a two-stage ring;
-//   MMA thread    S[128 x 128] = Q K^T   (tcgen05.mma, M 128, N 128, K 4 x 16) into tensor memory;
-//                 O_blk[128 x 64] = P V  (A operand P read from tensor memory, B = one V page per
-//                 K = 16 step);
-//   4 softmax warps  one thread per query row: tcgen05.ld of its S row, scale by log2(e)/sqrt(d),
-//                 causal / window mask, running maximum and sum (no shuffles: a row is one thread),
-//                 P as packed bfloat16 back to tensor memory (tcgen05.st), then O += O_blk with the
-//                 running rescale, all in float32 registers.
+//   MMA thread    S[128 x 128] = Q K^T   (tcgen05.mma, M 128, N 128, K 4 x 16) into tensor memory, issued
+//                 for block j+1 as soon as the softmax warps hold S of block j in registers;
+//                 O[128 x 64] += P V     (A operand P read from tensor memory, B = one V page per K = 16
+//                 step), accumulated in tensor memory over all blocks;
+//   8 softmax warps  two threads per query row, 64 of the 128 scores each (one tcgen05.ld, no second
+//                 pass): mask, maximum (the two halves meet through shared memory), base-2 exponentials
+//                 with log2(e)/sqrt(d) folded into one multiply-add, sum, P as packed bfloat16 back to
+//                 tensor memory (tcgen05.st).
+// The running maximum is only raised when a block exceeds it by more than 8 (a factor 256, far inside
+// the range of bfloat16 and float32): then the row of O in tensor memory and the running sum are scaled
+// down, which after the first blocks is rare; the result O / l is the same function either way.
 // Formulas: scores q.k/sqrt(d), query at position p reads keys max(0, p-window+1)..p, softmax, weighted
-// sum of values (src/Inference/Inference.jl:1201-1207, 1414-1457).  All waits are bounded and
-// report through the status word.  Two blocks fit an SM (80 KB of shared memory, 256 tensor-memory
-// columns each), so one block's softmax overlaps the other's tensor work.
+// sum of values (src/Inference/Inference.jl:1201-1207, 1414-1457).  All waits are bounded mbarrier
+// waits that report through the status word (no block-wide barrier between the roles).  Two blocks fit
+// an SM (80 KB of shared memory, 256 tensor-memory columns each), so one block's softmax overlaps the
+// other's tensor work.
 #include <math.h>
 
 #include "tcgen05.cuh"
@@ -25,18 +30,21 @@
 #define FA_HD 64
 #define FA_BK 128
 #define FA_STAGES 2
-#define FA_THREADS 192
+#define FA_THREADS 320                 // warp 0: TMA, warp 1: MMA, warps 2..9: softmax
 #define FA_LOG2E 1.4426950408889634f
+#define FA_RAISE 8.f                   // the reference maximum follows the true one at this distance
 
 struct __align__(1024) FaSmem {
     bf16 q[128 * FA_HD];                       // 16 KB
     bf16 k[FA_STAGES][FA_BK * FA_HD];          // 16 KB per stage: 8 pages x [16][64]
     bf16 v[FA_STAGES][FA_BK * FA_HD];          // 16 KB per stage: 8 pages x [64][16]
-    unsigned long long q_full, full[FA_STAGES], empty[FA_STAGES], s_full, p_ready, o_full;
+    unsigned long long q_full, full[FA_STAGES], empty[FA_STAGES], s_full, s_free, p_ready, o_full, pair[4];
+    float xmax[2][2][128];                     // [block parity][half][row]: the halves' maxima
+    float xsum[2][128];                        // [half][row]: the halves' sums, at the end
     unsigned tmem_base;
 };
 
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(FA_THREADS, 2)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                                  int max_pages, int page_size, const int* __restrict__ seg_start,
@@ -67,11 +75,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         mbar_init(&s.q_full, 1);
         for (int i = 0; i < FA_STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
         mbar_init(&s.s_full, 1);
-        mbar_init(&s.p_ready, 128);
+        mbar_init(&s.s_free, 256);
+        mbar_init(&s.p_ready, 256);
         mbar_init(&s.o_full, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&s.pair[i], 64);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) {       // S: columns 0..127, P: 128..191 (bfloat16 pairs), O_blk: 192..255
+    if (warp == 1) {       // S: columns 0..127, P: 128..191 (bfloat16 pairs), O: 192..255
         tmem_alloc(&s.tmem_base, 256);
         tmem_relinquish();
     }
@@ -120,114 +130,147 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             bool ok = mbar_wait(&s.q_full, 0);
             if (!ok) atomicExch(status, 13);
             const unsigned long long dq = make_desc(smem_u32(s.q));
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                const int st = j % FA_STAGES;
-                if (!mbar_wait(&s.full[st], (j / FA_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
-                tc_fence_after();
-                const unsigned long long dk = make_desc(smem_u32(s.k[st]));
+            auto issue_s = [&](int j) {          // S = Q K_j^T, K_j in stage j % 2
+                const unsigned long long dk = make_desc(smem_u32(s.k[j % FA_STAGES]));
 #pragma unroll
                 for (int k = 0; k < FA_HD / 16; ++k) umma_f16(tm_s, dq + 2 * k, dk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
                 umma_commit(&s.s_full);
-                // the softmax warps turn S into P (and have taken the previous O_blk before that)
+            };
+            if (ok) {
+                if (!mbar_wait(&s.full[0], 0)) { atomicExch(status, 14); ok = false; }
+                else { tc_fence_after(); issue_s(0); }
+            }
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int st = j % FA_STAGES;
+                if (j + 1 < n_blocks) {
+                    // the scores of the next block, as soon as its keys are here and S is free again
+                    if (!mbar_wait(&s.full[(j + 1) % FA_STAGES], ((j + 1) / FA_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
+                    if (!mbar_wait(&s.s_free, j & 1)) { atomicExch(status, 19); ok = false; break; }
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
                 if (!mbar_wait(&s.p_ready, j & 1)) { atomicExch(status, 15); ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < FA_BK / 16; ++kk)
                     umma_f16_ts(tm_o, tm_p + 8 * kk, make_desc_sw32(smem_u32(s.v[st] + kk * 16 * FA_HD)), idesc_o,
-                                kk > 0 ? 1u : 0u);
+                                (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(&s.o_full);
                 umma_commit(&s.empty[st]);
             }
-            if (!ok) { umma_commit(&s.s_full); umma_commit(&s.o_full); }
         }
     } else {
-        // ---- softmax: one thread per query row ----
-        const int qw = warp & 3;
-        const int r = qw * 32 + lane;                     // row = token * G + head
+        // ---- softmax: two threads per query row, 64 scores each ----
+        const int q4 = warp & 3;                          // the quarter of tensor-memory lanes this warp may touch
+        const int half = (warp - 2) >> 2;                 // which 64 of the block's 128 keys
+        const int r = q4 * 32 + lane;                     // row = token * G + head
         const int tok = r / G, hg = r % G;
         const bool valid = tok < rows_tok;
         const int pos = p0 + q0 + min(tok, rows_tok - 1);
         const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-        const unsigned lane_base = (unsigned)(qw * 32) << 16;
-        float o[FA_HD];
-#pragma unroll
-        for (int d = 0; d < FA_HD; ++d) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f;
+        const unsigned lane_base = (unsigned)(q4 * 32) << 16;
+        float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
+        // a wait that ran out ends the whole warp: the tensor-memory loads and stores below are warp-wide
+        auto wait_all = [&](void* bar, unsigned parity, int code) -> bool {
+            const bool got = mbar_wait(bar, parity);
+            if (__all_sync(0xffffffffu, got)) return true;
+            if (lane == 0) atomicExch(status, code);
+            return false;
+        };
         for (int j = 0; j < n_blocks && ok; ++j) {
-            const int key0 = (kb0 + j) * FA_BK;
-            if (!mbar_wait(&s.s_full, j & 1)) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
+            const int key0 = (kb0 + j) * FA_BK + half * 64;
+            if (!wait_all(&s.s_full, j & 1, 16)) { ok = false; break; }
             tc_fence_after();
-            const bool need_mask = key0 + FA_BK - 1 > pos_first || key0 < lo;
-            // pass 1: the row maximum of this block
+            unsigned v[64];
+            tmem_ld32(tm_s + lane_base + half * 64, reinterpret_cast<unsigned(&)[32]>(v[0]));
+            tmem_ld32(tm_s + lane_base + half * 64 + 32, reinterpret_cast<unsigned(&)[32]>(v[32]));
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&s.s_free);                       // S may be overwritten by the next block's scores
+            const bool need_mask = key0 + 63 > pos || key0 < lo;
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < FA_BK; c += 32) {
-                unsigned v[32];
-                tmem_ld32(tm_s + lane_base + c, v);
-                tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __uint_as_float(v[i]) * scale_log2;
-                    if (need_mask) { const int key = key0 + c + i; if (key > pos || key < lo) x = -INFINITY; }
-                    mx = fmaxf(mx, x);
+            for (int i = 0; i < 64; ++i) {
+                float x = __uint_as_float(v[i]);
+                if (need_mask) {
+                    const int key = key0 + i;
+                    if (key > pos || key < lo) { x = -INFINITY; v[i] = __float_as_uint(x); }
+                }
+                mx = fmaxf(mx, x);
+            }
+            // the other half of the row
+            s.xmax[j & 1][half][r] = mx;
+            mbar_arrive(&s.pair[q4]);
+            if (!wait_all(&s.pair[q4], j & 1, 18)) { ok = false; break; }
+            const float m_blk = fmaxf(mx, s.xmax[j & 1][half ^ 1][r]) * scale_log2;
+            // O += P V of the block before has finished: P may be rewritten, O may be rescaled
+            if (j > 0) {
+                if (!wait_all(&s.o_full, (j - 1) & 1, 17)) { ok = false; break; }
+                tc_fence_after();
+            }
+            // raise the reference maximum?  (both threads of a row decide alike; the warp acts as one,
+            // rows that stay are scaled by 1)
+            const bool raise = m_blk > m_ref + FA_RAISE;
+            const float alpha = (raise && m_ref != -INFINITY) ? ex2_approx(m_ref - m_blk) : 1.f;
+            if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+                for (int c = 0; c < 32; c += 16) {        // seldom taken: keep its registers few
+                    unsigned o[16];
+                    tmem_ld16(tm_o + lane_base + half * 32 + c, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st16(tm_o + lane_base + half * 32 + c, o);
                 }
             }
-            const float m_new = fmaxf(m, mx);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = exp2f(m - m_use);
-            m = m_new;
-            // pass 2: probabilities, their sum, P as packed bfloat16 into tensor memory
+            l *= alpha;
+            if (raise) m_ref = m_blk;
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             float l_blk = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < FA_BK; c += 32) {
-                unsigned v[32];
-                tmem_ld32(tm_s + lane_base + c, v);
-                tmem_ld_wait();
-                unsigned pk[16];
+            unsigned pk[32];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float x0 = __uint_as_float(v[i]) * scale_log2, x1 = __uint_as_float(v[i + 1]) * scale_log2;
-                    if (need_mask) {
-                        const int key = key0 + c + i;
-                        if (key > pos || key < lo) x0 = -INFINITY;
-                        if (key + 1 > pos || key + 1 < lo) x1 = -INFINITY;
-                    }
-                    const float e0 = exp2f(x0 - m_use), e1 = exp2f(x1 - m_use);
-                    l_blk += e0 + e1;
-                    __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-                    pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
-                }
-                tmem_st16(tm_p + lane_base + c / 2, pk);
+            for (int i = 0; i < 64; i += 2) {
+                const float e0 = ex2_approx(fmaf(__uint_as_float(v[i]), scale_log2, -m_use));
+                const float e1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), scale_log2, -m_use));
+                l_blk += e0 + e1;
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
             }
-            l = l * alpha + l_blk;
+            l += l_blk;
+            tmem_st32(tm_p + lane_base + half * 32, pk);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&s.p_ready);
-            // O_blk = P V of this block
-            if (!mbar_wait(&s.o_full, j & 1)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < FA_HD; c += 32) {
-                unsigned v[32];
-                tmem_ld32(tm_o + lane_base + c, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c + i] = o[c + i] * alpha + __uint_as_float(v[i]);
-            }
         }
-        if (ok && valid) {
-            const float inv = 1.f / l;
-            bf16* dst = out + ((size_t)(t0 + q0 + tok) * nh + (size_t)kvh * G + hg) * FA_HD;
+        if (ok) {
+            // the last O += P V, the other half's sum, and out = O / l
+            if (!wait_all(&s.o_full, (n_blocks - 1) & 1, 17)) ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            s.xsum[half][r] = l;
+            mbar_arrive(&s.pair[q4]);
+            if (!wait_all(&s.pair[q4], n_blocks & 1, 18)) ok = false;
+        }
+        if (ok) {
+            const float inv = 1.f / (l + s.xsum[half ^ 1][r]);
+            unsigned o[32];
+            tmem_ld32(tm_o + lane_base + half * 32, o);
+            tmem_ld_wait();
+            if (valid) {
+                bf16* dst = out + ((size_t)(t0 + q0 + tok) * nh + (size_t)kvh * G + hg) * FA_HD + half * 32;
 #pragma unroll
-            for (int d = 0; d < FA_HD; d += 8) {
-                unsigned pk[4];
+                for (int d = 0; d < 32; d += 8) {
+                    unsigned w4[4];
 #pragma unroll
-                for (int i = 0; i < 8; i += 2) {
-                    __nv_bfloat162 b2 = __floats2bfloat162_rn(o[d + i] * inv, o[d + i + 1] * inv);
-                    pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
+                    for (int i = 0; i < 8; i += 2) {
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[d + i]) * inv,
+                                                                  __uint_as_float(o[d + i + 1]) * inv);
+                        w4[i / 2] = *reinterpret_cast<unsigned*>(&b2);
+                    }
+                    *reinterpret_cast<uint4*>(dst + d) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                 }
-                *reinterpret_cast<uint4*>(dst + d) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
         }
     }
