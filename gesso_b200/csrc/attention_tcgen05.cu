@@ -111,7 +111,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const int st = j % FA_STAGES;
             const int next_page = lookup(j + 1);
             if (lane == 0) {
-                if (!mbar_wait(&s.empty[st], ((j / FA_STAGES) & 1) ^ 1)) { atomicExch(status, 12); ok = false; }
+                if (!mbar_wait_idle(&s.empty[st], ((j / FA_STAGES) & 1) ^ 1)) { atomicExch(status, 12); ok = false; }
                 else mbar_expect_tx(&s.full[st], 2 * FA_BK * FA_HD * sizeof(bf16));
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -127,7 +127,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (elect_one()) {
             constexpr unsigned idesc_s = make_idesc(128, FA_BK);
             constexpr unsigned idesc_o = make_idesc(128, FA_HD);
-            bool ok = mbar_wait(&s.q_full, 0);
+            bool ok = mbar_wait_idle(&s.q_full, 0);
             if (!ok) atomicExch(status, 13);
             const unsigned long long dq = make_desc(smem_u32(s.q));
             auto issue_s = [&](int j) {          // S = Q K_j^T, K_j in stage j % 2
@@ -137,19 +137,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 umma_commit(&s.s_full);
             };
             if (ok) {
-                if (!mbar_wait(&s.full[0], 0)) { atomicExch(status, 14); ok = false; }
+                if (!mbar_wait_idle(&s.full[0], 0)) { atomicExch(status, 14); ok = false; }
                 else { tc_fence_after(); issue_s(0); }
             }
             for (int j = 0; j < n_blocks && ok; ++j) {
                 const int st = j % FA_STAGES;
                 if (j + 1 < n_blocks) {
                     // the scores of the next block, as soon as its keys are here and S is free again
-                    if (!mbar_wait(&s.full[(j + 1) % FA_STAGES], ((j + 1) / FA_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
-                    if (!mbar_wait(&s.s_free, j & 1)) { atomicExch(status, 19); ok = false; break; }
+                    if (!mbar_wait_idle(&s.full[(j + 1) % FA_STAGES], ((j + 1) / FA_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
+                    if (!mbar_wait_idle(&s.s_free, j & 1)) { atomicExch(status, 19); ok = false; break; }
                     tc_fence_after();
                     issue_s(j + 1);
                 }
-                if (!mbar_wait(&s.p_ready, j & 1)) { atomicExch(status, 15); ok = false; break; }
+                if (!mbar_wait_idle(&s.p_ready, j & 1)) { atomicExch(status, 15); ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < FA_BK / 16; ++kk)
@@ -188,17 +188,22 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(&s.s_free);                       // S may be overwritten by the next block's scores
-            const bool need_mask = key0 + 63 > pos || key0 < lo;
-            float mx = -INFINITY;
+            // masking is a pass of its own behind a warp-wide branch: most blocks lie wholly inside the
+            // visible range, and their inner loops then carry no compare at all
+            if (__any_sync(0xffffffffu, key0 + 63 > pos || key0 < lo)) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                float x = __uint_as_float(v[i]);
-                if (need_mask) {
+                for (int i = 0; i < 64; ++i) {
                     const int key = key0 + i;
-                    if (key > pos || key < lo) { x = -INFINITY; v[i] = __float_as_uint(x); }
+                    if (key > pos || key < lo) v[i] = 0xff800000u;      // -inf
                 }
-                mx = fmaxf(mx, x);
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(v[i + u]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the other half of the row
             s.xmax[j & 1][half][r] = mx;
             mbar_arrive(&s.pair[q4]);
@@ -227,17 +232,17 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             l *= alpha;
             if (raise) m_ref = m_blk;
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            float l_blk = 0.f;
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
             unsigned pk[32];
 #pragma unroll
             for (int i = 0; i < 64; i += 2) {
                 const float e0 = ex2_approx(fmaf(__uint_as_float(v[i]), scale_log2, -m_use));
                 const float e1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), scale_log2, -m_use));
-                l_blk += e0 + e1;
+                l4[(i >> 1) & 3] += e0 + e1;
                 __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
                 pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
             }
-            l += l_blk;
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             tmem_st32(tm_p + lane_base + half * 32, pk);
             tmem_st_wait();
             tc_fence_before();

@@ -36,6 +36,15 @@ __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// The same for a thread that waits most of the time (a producer, the MMA issuer): it sleeps between
+// polls, so that its warp does not take issue slots from the warps that compute beside it.
+__device__ __forceinline__ bool mbar_wait_idle(void* bar, unsigned parity) {
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(64);
+    }
+    return false;
+}
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, void* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
