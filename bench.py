@@ -84,7 +84,7 @@ class ClockSampler(threading.Thread):
                     self.samples.append([x.strip() for x in out[0].split(",")])
             except Exception:
                 pass
-            self.stop_flag.wait(0.2)
+            self.stop_flag.wait(0.05)
 
     def summary(self):
         self.stop_flag.set()
