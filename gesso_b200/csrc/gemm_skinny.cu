@@ -207,7 +207,6 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     // once; otherwise a slot is refilled right after it is used, XD items ahead, so that the L2
     // latency of the activations never sits between the arrival of W and the MMA.
     constexpr int XD = XC > 0 ? XC : 4;
-    const int CH_pad = ((CH + XD - 1) / XD) * XD;
     uint4 xq[XD][NT];
 #pragma unroll
     for (int i = 0; i < XD; ++i)
@@ -236,9 +235,10 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
 #pragma unroll
                 for (int j = 0; j < NT; ++j) xb[j] = xq[ii][j];
                 if (XC == 0) {
+                    // slot ii serves the items ii, ii + XD, ... of a tile, then item ii of the next tile
                     int ni = i + XD;
-                    const bool wrapped = ni >= CH_pad;
-                    if (wrapped) ni = ii;                 // the same slot of the next tile
+                    const bool wrapped = ni >= CH;
+                    if (wrapped) ni = ii;
 #pragma unroll
                     for (int j = 0; j < NT; ++j) xq[ii][j] = load_x(chunk_of(ni), j, tk == 0 && !wrapped);
                 }

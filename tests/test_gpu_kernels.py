@@ -584,6 +584,40 @@ def test_skinny_gemm_epilogues(M, N, K):
         assert rel_err(plain, packed) < 1e-6
 
 
+@pytest.mark.parametrize("M", [1, 7, 8, 13, 16])
+@pytest.mark.parametrize("H,F", [(2048, 8192), (1536, 6144), (2048, 4096), (256, 10240), (2560, 5120)])
+def test_skinny_feed_forward_of_few_tokens(M, H, F):
+    """The feed-forward of a decoding step at widths where a block walks several tiles (folded norm +
+    gate/up product + SwiGLU, then the down product with its inner size split over blocks and the
+    residual add) against the formulas.  Inner sizes of 6 and 10 chunks per warp (1536, 2560) take the
+    path whose token-side fragments are reloaded tile after tile."""
+    from gesso_b200 import ops
+    g = torch.Generator().manual_seed(M + H + F)
+    gate = (torch.randn(F, H, generator=g) / math.sqrt(H)).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(F, H, generator=g) / math.sqrt(H)).to(torch.bfloat16).to(DEV)
+    w1 = ops.pack_gate_up(gate, up)
+    w2 = (torch.randn(H, F, generator=g) / math.sqrt(F)).to(torch.bfloat16).to(DEV)
+    for rep in range(2):
+        h = torch.randn(M, H, generator=g).to(DEV)
+        h_two = h.clone()
+        a = ops.linear_swiglu(ops.LazyNorm(h_two, None, 1e-5, torch.bfloat16), w1, True)
+        assert ops.linear_residual(a, w2, h_two, None) is None
+        # the kernel feeds bf16(h) to the tensor cores and divides by the root mean square afterwards
+        hb = h.to(torch.bfloat16).double()
+        rinv = 1.0 / torch.sqrt((h.double() ** 2).mean(dim=1, keepdim=True) + 1e-5)
+        gg, uu = (hb @ gate.double().T) * rinv, (hb @ up.double().T) * rinv
+        act = ((gg / (1 + torch.exp(-gg))) * uu)
+        assert rel_err(a, act) < BF16_EPS
+        want = h.double() + a.double() @ w2.double().T
+        assert rel_err(h_two, want) < 1e-5
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16).to(DEV)              # plain input, no norm
+    gg, uu = x.double() @ gate.double().T, x.double() @ up.double().T
+    assert rel_err(ops.linear_swiglu(x, w1, True), (gg / (1 + torch.exp(-gg))) * uu) < BF16_EPS
+    # the lm_head shape at those widths: many tiles per block, float32 output
+    wv = (torch.randn(8192, H, generator=g) / math.sqrt(H)).to(torch.bfloat16).to(DEV)
+    assert rel_err(ops.linear(x, wv, out_dtype=torch.float32), x.double() @ wv.double().T) < 2e-6
+
+
 @pytest.mark.parametrize("M", [1, 5, 8, 16])
 @pytest.mark.parametrize("N,K", [(64, 64), (6144, 2048), (32, 8192)])
 def test_skinny_gemm_fused_norm(M, N, K):
