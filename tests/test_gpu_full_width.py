@@ -1,5 +1,6 @@
 """Replay at the layer widths of LFM2-1.2B (hidden 2048, 32 heads / 8 kv heads of 64, feed-forward
-8192, vocabulary 65536, 3 taps; three layers: conv, attention, conv) against the plain implementation.
+8192), LFM2-350M (1024, 16 / 8, 4608) and LFM2-700M (1536, 24 / 8, 6912), vocabulary 65536, 3 taps;
+three layers each: conv, attention, conv; against the plain implementation.
 
 The tiny configurations never reach the kernels that serve these widths: the tensor-memory matrix
 product and flash attention of steps with a thousand tokens and more, the skinny product with its
@@ -12,13 +13,18 @@ import trace_tools as tt
 
 pytestmark = pytest.mark.gpu
 
-WIDE = {
-    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
-    "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 3,
-    "num_attention_heads": 32, "num_key_value_heads": 8, "full_attn_idxs": [1],
-    "conv_L_cache": 3, "conv_bias": False, "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True,
-    "block_multiple_of": 256, "norm_eps": 1e-5, "rope_theta": 1000000.0, "tie_embedding": True,
-}
+def wide_config(hidden, heads, block_ff):
+    return {
+        "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+        "vocab_size": 65536, "hidden_size": hidden, "num_hidden_layers": 3,
+        "num_attention_heads": heads, "num_key_value_heads": 8, "full_attn_idxs": [1],
+        "conv_L_cache": 3, "conv_bias": False, "block_ff_dim": block_ff, "block_auto_adjust_ff_dim": True,
+        "block_multiple_of": 256, "norm_eps": 1e-5, "rope_theta": 1000000.0, "tie_embedding": True,
+    }
+
+
+WIDE = {"1.2B": wide_config(2048, 32, 12288), "350M": wide_config(1024, 16, 6656), "700M": wide_config(1536, 24, 10240)}
+VOCAB = 65536
 TOL = {"float32": 1e-4, "bfloat16": 32 * 2.0 ** -9}
 LONG, SIDE, LATE = 1100, 300, 256
 # places of the long request whose logits are compared: the first tokens, borders of pages, of
@@ -27,13 +33,13 @@ PLACES = sorted(set([0, 1, 2, 15, 16, 63, 64, 127, 128, 129, 511, 512, 699, 700,
                     + list(range(LONG - 32, LONG))))
 
 
-@pytest.fixture(scope="module")
-def wide(tmp_path_factory):
+@pytest.fixture(scope="module", params=["1.2B", "350M", "700M"])
+def wide(request, tmp_path_factory):
     from gesso_b200.weights import write_random_model
     from plain_lfm2 import PlainModel
     d = str(tmp_path_factory.mktemp("model_wide"))
-    write_random_model(d, WIDE, 5, dtype="bfloat16", style="fan_in")
-    reqs = tt.make_requests(WIDE["vocab_size"], [LONG, SIDE, LATE], seed=77)
+    write_random_model(d, WIDE[request.param], 5, dtype="bfloat16", style="fan_in")
+    reqs = tt.make_requests(VOCAB, [LONG, SIDE, LATE], seed=77)
     plain = PlainModel(d)
     side_places = [0, 149, 150, 151, SIDE - 1]
     late_places = [0, 99, 100, LATE - 1]
@@ -116,7 +122,7 @@ def test_full_width_replay(schedule, dtype, wide, loaded, tmp_path):
     d, reqs, ref = wide
     tb, max_tokens = build(schedule, reqs)
     eng = tt.run_in_process(loaded(dtype), tb, max_tokens, str(tmp_path))
-    rows = tt.read_rows(tb, str(tmp_path), WIDE["vocab_size"])
+    rows = tt.read_rows(tb, str(tmp_path), VOCAB)
     want = {(rid, pos) for rid in ((0, 1, 2) if schedule == "mixed" else (0,)) for pos in ref[rid]}
     assert set(rows) == want
     worst = 0.0
