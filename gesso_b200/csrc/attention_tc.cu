@@ -2,8 +2,9 @@
 // flash kernel for steps with prompt portions.  Head sizes 32, 64, 96, 128; page sizes that are
 // multiples of 16.  Other sizes are refused (the caller then takes the FP32-arithmetic kernel).
 //
-// Both kernels read K and V fragments straight from the cache pages into registers, with no
-// shared-memory staging and no transposition:
+// Both kernels take K and V fragments from the cache pages as they lie, with no transposition (the
+// decode kernel through a per-thread ring of asynchronous copies, the prefill kernel straight into
+// registers):
 //   * scores S = Q K^T use mma.m16n8k16 with K as the B operand: b(k = feature, n = key) is two
 //     consecutive features of one K row, so a thread reads 16 contiguous bytes of a K row and
 //     uses them for two k16 steps.  The sum over features is order-free, so features are assigned
@@ -432,176 +433,6 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     }
 }
 
-// ================================ prefill: flash, keys and values staged in shared memory ==========
-// For the common head layouts (head 64 with 2, 4 or 8 query heads per kv head; head 128 with 1, 2 or
-// 4).  A block owns a 64-token tile of one request and ALL query heads of one kv group: warp w handles
-// the 16 queries (w & 3) and the HPW heads of head group (w >> 2), so one copy of K and V serves every
-// head of the group.  K and V blocks travel global -> shared memory with asynchronous 16-byte copies,
-// FS_KB key blocks per stage and FS_STAGES stages deep, and the fragments are then read from shared
-// memory with the same slot assignment as above.  K rows are stored with the 16-byte chunk index
-// XOR-ed by 4 for odd keys, which makes the quarter-warp fragment reads bank-conflict free; V^T rows
-// are read 128 contiguous bytes per half-warp and need no swizzle.
-#define FS_KB 4          // 16-key blocks per stage (64 keys)
-#define FS_STAGES 3
-
-template <int HD>
-__device__ __forceinline__ void load_block_smem(KVFrag<HD>& f, const bf16* __restrict__ ks,
-                                                const bf16* __restrict__ vs, int g, int t) {
-    // ks: [16 keys][HD] with swizzled chunks; vs: [HD][16 keys]
-    const int key_a = 4 * (g >> 1) + (g & 1), key_b = key_a + 2;      // same parity: same swizzle
-    const int sw = (key_a & 1) << 2;
-#pragma unroll
-    for (int c = 0; c < HD / 32; ++c) {
-        const int chunk = (4 * c + t) ^ sw;
-        f.k[0][c] = *reinterpret_cast<const uint4*>(ks + key_a * HD + chunk * 8);
-        f.k[1][c] = *reinterpret_cast<const uint4*>(ks + key_b * HD + chunk * 8);
-    }
-#pragma unroll
-    for (int j = 0; j < HD / 8; ++j) f.v[j] = *reinterpret_cast<const uint2*>(vs + (8 * j + g) * 16 + 4 * t);
-}
-
-__device__ __forceinline__ void fs_cp_async16(void* smem_dst, const void* gmem_src) {
-    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src));
-}
-
-template <int HD, int HPW, int NHG>
-__global__ void __launch_bounds__(128 * NHG)
-prefill_attention_smem_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
-                              const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
-                              int page_size, const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
-                              const int* __restrict__ tile_seg, const int* __restrict__ tile_q0,
-                              bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2) {
-    extern __shared__ __align__(16) unsigned char fs_smem[];
-    constexpr int BLOCK_ELEMS = 16 * HD;                       // one K (or V) block
-    constexpr int STAGE_ELEMS = 2 * FS_KB * BLOCK_ELEMS;       // K blocks then V blocks
-    bf16* stages = reinterpret_cast<bf16*>(fs_smem);
-    constexpr int NTHREADS = 128 * NHG;
-
-    // long tiles first: the queries at the end of a prompt have the most keys to read
-    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
-    const int G = nh / nkv;
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int wq = w & 3, hg = w >> 2;
-    const int seg = tile_seg[tile];
-    const int t0 = seg_start[seg], n = seg_start[seg + 1] - t0;
-    const int tq0 = tile_q0[tile];
-    const int p0 = seg_pos0[seg];
-    const int* bt = block_table + (size_t)seg * max_pages;
-    // the block walks the key blocks that any of its queries reads
-    const int tile_rows = min(64, n - tq0);
-    const int tile_first = p0 + tq0, tile_last = p0 + tq0 + tile_rows - 1;
-    const int cta_first_block = (window > 0 ? max(0, tile_first - window + 1) : 0) / 16;
-    const int cta_last_block = tile_last / 16;
-    const int n_stages_total = (cta_last_block - cta_first_block + FS_KB) / FS_KB;
-
-    // this warp's queries
-    const int q0 = tq0 + 16 * wq;
-    const bool active = q0 < n;
-    const int rows = active ? min(16, n - q0) : 1;
-    const int ra = min(g, rows - 1), rb = min(g + 8, rows - 1);
-    const int qa = active ? q0 : tq0;                          // an idle warp mirrors the tile's first rows
-    const int pos_a = p0 + qa + ra, pos_b = p0 + qa + rb;
-    const int lo_a = window > 0 ? max(0, pos_a - window + 1) : 0;
-    const int lo_b = window > 0 ? max(0, pos_b - window + 1) : 0;
-    const int pos_first = p0 + qa, pos_last = p0 + qa + rows - 1;
-    const int w_first_block = (window > 0 ? max(0, pos_first - window + 1) : 0) / 16;
-    const int w_last_block = pos_last / 16;
-    const int head0 = kvh * G + hg * HPW;
-
-    uint4 qf[HPW][HD / 32], qg[HPW][HD / 32];
-    float o[HPW][HD / 8][4], m[HPW][2], l[HPW][2];
-#pragma unroll
-    for (int h = 0; h < HPW; ++h) {
-        const bf16* pa = q + ((size_t)(t0 + qa + ra) * nh + head0 + h) * HD + 8 * t;
-        const bf16* pb = q + ((size_t)(t0 + qa + rb) * nh + head0 + h) * HD + 8 * t;
-#pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-            qf[h][c] = *reinterpret_cast<const uint4*>(pa + 32 * c);
-            qg[h][c] = *reinterpret_cast<const uint4*>(pb + 32 * c);
-        }
-        m[h][0] = m[h][1] = -INFINITY;
-        l[h][0] = l[h][1] = 0.f;
-#pragma unroll
-        for (int j = 0; j < HD / 8; ++j) o[h][j][0] = o[h][j][1] = o[h][j][2] = o[h][j][3] = 0.f;
-    }
-
-    // asynchronous copy of stage `si` (key blocks cta_first_block + si*FS_KB ...) into ring slot si % FS_STAGES
-    auto issue_stage = [&](int si) {
-        if (si < n_stages_total) {
-            bf16* dst = stages + (size_t)(si % FS_STAGES) * STAGE_ELEMS;
-            constexpr int PIECES = STAGE_ELEMS / 8;            // 16-byte pieces per stage
-            for (int pc = threadIdx.x; pc < PIECES; pc += NTHREADS) {
-                const int is_v = pc >= PIECES / 2;
-                const int pp = is_v ? pc - PIECES / 2 : pc;
-                const int blk = pp / (BLOCK_ELEMS / 8), off = pp % (BLOCK_ELEMS / 8);   // 16-byte piece inside the block
-                const int b = cta_first_block + si * FS_KB + blk;
-                if (b > cta_last_block) continue;
-                const int key0 = b * 16;
-                const int page = bt[key0 / page_size];
-                if (page < 0) {
-                    // given back behind a window: every key of it is masked; fill with zeros so that a
-                    // zero probability never meets a stale non-finite value
-                    bf16* z = is_v ? dst + FS_KB * BLOCK_ELEMS + blk * BLOCK_ELEMS + off * 8 : dst + blk * BLOCK_ELEMS + off * 8;
-                    *reinterpret_cast<uint4*>(z) = make_uint4(0, 0, 0, 0);
-                    continue;
-                }
-                const int sub = key0 % page_size;
-                const size_t pk = (size_t)page * nkv + kvh;
-                if (!is_v) {
-                    // K: rows of HD elements; piece `off` = key r, chunk ch
-                    const int r = off / (HD / 8), ch = off % (HD / 8);
-                    const bf16* src = k_pages + (pk * page_size + sub + r) * HD + ch * 8;
-                    fs_cp_async16(dst + blk * BLOCK_ELEMS + r * HD + ((ch ^ ((r & 1) << 2)) * 8), src);
-                } else {
-                    // V^T: [HD][page_size]; row d holds 16 keys = 2 pieces
-                    const int d = off / 2, half = off % 2;
-                    const bf16* src = v_pages + (pk * HD + d) * page_size + sub + half * 8;
-                    fs_cp_async16(dst + FS_KB * BLOCK_ELEMS + blk * BLOCK_ELEMS + d * 16 + half * 8, src);
-                }
-            }
-        }
-        asm volatile("cp.async.commit_group;\n" ::);
-    };
-#pragma unroll
-    for (int si = 0; si < FS_STAGES - 1; ++si) issue_stage(si);
-
-    for (int si = 0; si < n_stages_total; ++si) {
-        asm volatile("cp.async.wait_group %0;\n" ::"n"(FS_STAGES - 2));
-        __syncthreads();                   // stage si has landed for every thread; slot (si-1) is free again
-        issue_stage(si + FS_STAGES - 1);
-        const bf16* st = stages + (size_t)(si % FS_STAGES) * STAGE_ELEMS;
-#pragma unroll 1
-        for (int blk = 0; blk < FS_KB; ++blk) {
-            const int b = cta_first_block + si * FS_KB + blk;
-            if (!active || b < w_first_block || b > w_last_block) continue;
-            KVFrag<HD> f;
-            load_block_smem<HD>(f, st + blk * BLOCK_ELEMS, st + FS_KB * BLOCK_ELEMS + blk * BLOCK_ELEMS, g, t);
-            const bool need_mask = (b * 16 + 15 > pos_first) || (window > 0 && b * 16 < max(lo_a, lo_b));
-#pragma unroll
-            for (int h = 0; h < HPW; ++h)
-                attend_block<HD>(f, qf[h], qg[h], o[h], m[h], l[h], b * 16, t, pos_a, pos_b, lo_a, lo_b, scale_log2,
-                                 need_mask);
-        }
-    }
-    asm volatile("cp.async.wait_group 0;\n" ::);
-    if (!active) return;
-#pragma unroll
-    for (int h = 0; h < HPW; ++h) {
-        const float la = quad_sum(l[h][0]), lb = quad_sum(l[h][1]);
-        const float ia = 1.f / la, ib = 1.f / lb;
-        bf16* oa = out + ((size_t)(t0 + q0 + g) * nh + head0 + h) * HD + 2 * t;
-        bf16* ob = out + ((size_t)(t0 + q0 + g + 8) * nh + head0 + h) * HD + 2 * t;
-#pragma unroll
-        for (int j = 0; j < HD / 8; ++j) {
-            if (g < rows)
-                *reinterpret_cast<__nv_bfloat162*>(oa + 8 * j) = __floats2bfloat162_rn(o[h][j][0] * ia, o[h][j][1] * ia);
-            if (g + 8 < rows)
-                *reinterpret_cast<__nv_bfloat162*>(ob + 8 * j) = __floats2bfloat162_rn(o[h][j][2] * ib, o[h][j][3] * ib);
-        }
-    }
-}
-
 // ---- launchers -------------------------------------------------------------------------------------
 GESSO_API int gesso_attention_tc_takes(int hd, int page_size, int nh, int nkv) {
     if (!(hd == 32 || hd == 64 || hd == 96 || hd == 128)) return 0;
@@ -656,39 +487,12 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
 GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const void* v_pages,
                                       const int* block_table, int max_pages, int page_size, const int* seg_start,
                                       const int* seg_pos0, const int* tile_seg, const int* tile_q0, int n_tiles,
-                                      void* out, int nh, int nkv, int hd, int window, float scale, int variant,
-                                      cudaStream_t stream) {
-    // variant: 0 = the default choice (fragments from global memory: measured 91 vs 76 TFLOP/s at 2,048
-    // tokens, 137 vs 124 at 8,192), 1 = fragments from global memory, 2 = staged in shared memory
+                                      void* out, int nh, int nkv, int hd, int window, float scale, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
     if (nkv > 65535) return GESSO_ERR_BAD_SIZE;
     const float scale_log2 = scale * LOG2E;
-    // the shared-memory staged kernel for the common head layouts
-#define GOS(HD, HPW, NHG)                                                                                     \
-    do {                                                                                                      \
-        constexpr int smem = FS_STAGES * 2 * FS_KB * 16 * HD * (int)sizeof(bf16);                             \
-        static bool configured = false;                                                                       \
-        if (!configured) {                                                                                    \
-            cudaFuncSetAttribute(prefill_attention_smem_kernel<HD, HPW, NHG>,                                 \
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                          \
-            configured = true;                                                                                \
-        }                                                                                                     \
-        prefill_attention_smem_kernel<HD, HPW, NHG><<<dim3(n_tiles, nkv), 128 * NHG, smem, stream>>>(         \
-            (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,    \
-            seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, window, scale_log2);                 \
-        return launch_status();                                                                               \
-    } while (0)
-    if (variant == 2) {
-    if (hd == 64 && G == 2) GOS(64, 2, 1);
-    if (hd == 64 && G == 4) GOS(64, 2, 2);
-    if (hd == 64 && G == 8) GOS(64, 2, 4);
-    if (hd == 128 && G == 1) GOS(128, 1, 1);
-    if (hd == 128 && G == 2) GOS(128, 1, 2);
-    if (hd == 128 && G == 4) GOS(128, 1, 4);
-    }
-#undef GOS
 #define GO(HD, HPW)                                                                                          \
     prefill_attention_kernel<HD, HPW><<<dim3(n_tiles, nkv, G / HPW), 128, 0, stream>>>(                      \
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,       \

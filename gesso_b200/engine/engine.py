@@ -155,9 +155,9 @@ class Engine:
         return i, self._pinned[i]
 
     def _prepare_single_tokens(self, entries: Sequence[StepEntry]):
-        """:meth:`_prepare` for a step of single tokens (decoding): one pass over the entries."""
+        """:meth:`_prepare` for a step of single tokens (decoding): the checks here, then one call of the
+        native manager reserves every request's next position and packs the step's metadata."""
         V = self.model.vocab_size
-        seen = set()
         for e in entries:
             tok = e.tokens[0]
             if not (0 <= tok < V):
@@ -165,24 +165,26 @@ class Engine:
             for w in e.want:
                 if w != 0:
                     raise invalid(f"step: wanted place {w} of request {e.req_id!r} is outside its 1 tokens")
-            seen.add(e.req_id)
-        if len(seen) != len(entries):
-            raise invalid("step: a request appears twice in one step")
-        starts, slots, fresh, tables = self.cache.reserve_single_tokens([e.req_id for e in entries])
-        for slot in fresh:
-            self.device_cache.zero_slot(slot)
+            if not self.cache.is_live(e.req_id):
+                raise invalid(f"step: request {e.req_id!r} is not live (admit it first)")
         n = len(entries)
-        layout = StepLayout(n_tokens=n, n_segs=n, n_rows=sum(len(e.want) for e in entries),
+        layout = StepLayout(n_tokens=n, n_segs=n, n_rows=sum(1 for e in entries if len(e.want)),
                             n_groups=len(self.cache.groups), max_pages=self.cache.max_pages_per_request, n_tiles=n)
         size = layout.offsets()["_end"]
         slot_i, host = self._pinned_buffer(size)
-        pack_step(list(entries), starts, slots, tables, layout, host.numpy()[:size])
+        fresh, max_kv, _, written = self.cache.stage_single_tokens(
+            [e.req_id for e in entries], [int(e.tokens[0]) for e in entries], [len(e.want) > 0 for e in entries],
+            host.numpy()[:size])
+        if written != size:
+            raise GessoError(ErrorCode.INTERNAL, f"step metadata: {written} ints packed, layout has {size}")
+        for slot in fresh:
+            self.device_cache.zero_slot(slot)
         self._all_rows = layout.n_rows == n
-        return layout, slot_i, host[:size], 1, max(starts) + 1
+        return layout, slot_i, host[:size], 1, max_kv
 
     def _prepare(self, entries: Sequence[StepEntry]):
         """Validate, reserve pages, zero fresh slots and pack the step's metadata on the host."""
-        if entries and all(len(e.tokens) == 1 for e in entries):
+        if entries and all(len(e.tokens) == 1 and len(e.want) <= 1 for e in entries):
             return self._prepare_single_tokens(entries)
         entries = self._validate(entries)
         for e in entries:
@@ -268,8 +270,11 @@ class Engine:
             before = launch_count()
             logits = self.model.forward(ctx, self.views(ctx))
             self.launches += launch_count() - before
-        for e in entries:
-            self.cache.commit(e.req_id, len(e.tokens))
+        if max_seg == 1:
+            self.cache.commit_single_tokens([e.req_id for e in entries])
+        else:
+            for e in entries:
+                self.cache.commit(e.req_id, len(e.tokens))
         self.steps_run += 1
         self.tokens_run += layout.n_tokens
         return logits
@@ -298,8 +303,7 @@ class Engine:
         staged.host.numpy()[at:at + len(tokens)] = tokens
         self._all_rows = staged.all_rows
         logits = self._step_graph(staged.layout, staged.slot_i, staged.host, staged.max_kv)
-        for rid in staged.req_ids:
-            self.cache.commit(rid, 1)
+        self.cache.commit_single_tokens(staged.req_ids)
         self.steps_run += 1
         self.staged_steps_run += 1
         self.tokens_run += staged.layout.n_tokens

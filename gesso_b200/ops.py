@@ -452,7 +452,7 @@ _lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, 
                                         _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P, _lib.P,
                                         _lib.P, _lib.P])
 _lib.declare("gesso_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
-                                         _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P])
+                                         _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.P])
 
 SM_COUNT = 148   # B200
 
@@ -505,7 +505,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
 def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_table: torch.Tensor, seg_start: torch.Tensor, seg_pos0: torch.Tensor,
                       tile_seg: torch.Tensor, tile_q0: torch.Tensor, window: Optional[int],
-                      scale: float, variant: int = 0) -> torch.Tensor:
+                      scale: float) -> torch.Tensor:
     _cuda_contig(q, "q", torch.bfloat16)
     N, nh, hd = q.shape
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
@@ -513,7 +513,7 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     _lib.check(_lib.library().gesso_prefill_attention(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(seg_start),
         _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), _p(out), nh, nkv, hd, int(window or 0),
-        float(scale), int(variant), _stream()), "prefill_attention")
+        float(scale), _stream()), "prefill_attention")
     return out
 
 
