@@ -291,30 +291,42 @@ class Engine:
         layout, slot_i, host, _, max_kv = self._prepare_single_tokens(entries)
         return StagedStep(tuple(req_ids), layout, slot_i, host, max_kv, self._all_rows)
 
-    def step_staged(self, staged: StagedStep, tokens: Sequence[int]) -> torch.Tensor:
-        """Run a staged step with its tokens (one per request, in the staged order); logits of every request."""
-        V = self.model.vocab_size
-        if len(tokens) != len(staged.req_ids):
-            raise invalid("step: a staged step takes one token per request")
-        for rid, tok in zip(staged.req_ids, tokens):
-            if not (0 <= tok < V):
-                raise invalid(f"step: token id {tok} of request {rid!r} is outside the vocabulary (0..{V - 1})")
+    def step_staged(self, staged: StagedStep, tokens: Optional[Sequence[int]] = None,
+                    device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Run a staged step with its tokens (one per request, in the staged order); logits of every
+        request.  The tokens come from the host (``tokens``) or straight from the device
+        (``device_tokens``: int32 ids that an earlier selection left there), in which case the step
+        starts without the host ever having seen them."""
+        n = len(staged.req_ids)
         at = staged.layout.offsets()["token_ids"]
-        staged.host.numpy()[at:at + len(tokens)] = tokens
+        if device_tokens is None:
+            V = self.model.vocab_size
+            if tokens is None or len(tokens) != n:
+                raise invalid("step: a staged step takes one token per request")
+            for rid, tok in zip(staged.req_ids, tokens):
+                if not (0 <= tok < V):
+                    raise invalid(f"step: token id {tok} of request {rid!r} is outside the vocabulary (0..{V - 1})")
+            staged.host.numpy()[at:at + n] = tokens
+        elif device_tokens.dtype != torch.int32 or device_tokens.numel() != n or not device_tokens.is_cuda:
+            raise invalid("step: device tokens must be one int32 id per request on the device")
         self._all_rows = staged.all_rows
-        logits = self._step_graph(staged.layout, staged.slot_i, staged.host, staged.max_kv)
+        logits = self._step_graph(staged.layout, staged.slot_i, staged.host, staged.max_kv,
+                                  device_tokens=device_tokens, token_at=at)
         self.cache.commit_single_tokens(staged.req_ids)
         self.steps_run += 1
         self.staged_steps_run += 1
         self.tokens_run += staged.layout.n_tokens
         return logits
 
-    def _step_graph(self, layout: StepLayout, slot_i: int, host: torch.Tensor, max_kv: int):
+    def _step_graph(self, layout: StepLayout, slot_i: int, host: torch.Tensor, max_kv: int,
+                    device_tokens: Optional[torch.Tensor] = None, token_at: int = 0):
         key = (layout.n_segs, layout.n_rows, self._all_rows)
         g = self._graphs.get(key)
         if g is None:
             buf = torch.zeros((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
             self._upload(buf, slot_i, host)
+            if device_tokens is not None:
+                buf[token_at:token_at + device_tokens.numel()].copy_(device_tokens)
             ctx = StepContext(layout, buf, self.status, 1, self.max_positions, self._all_rows)
             views = self.views(ctx)
             # One eager run first: libraries initialise lazily, and capture records rather than runs,
@@ -342,6 +354,8 @@ class Engine:
             return logits
         graph, buf, out, n_launch = g
         self._upload(buf, slot_i, host)
+        if device_tokens is not None:
+            buf[token_at:token_at + device_tokens.numel()].copy_(device_tokens)     # device to device, in stream order
         graph.replay()
         self.launches += n_launch
         return out

@@ -109,7 +109,7 @@ class StepPlan:
 
 class Scheduler:
     def __init__(self, engine, select: Callable, *, max_batch: int = 8, max_tokens_per_step: int = 2048,
-                 prefill_chunk: int = 512, vocab_size: Optional[int] = None):
+                 prefill_chunk: int = 512, vocab_size: Optional[int] = None, pipeline: bool = True):
         if max_batch < 1 or max_tokens_per_step < 1 or prefill_chunk < 1:
             raise invalid("scheduler: max_batch, max_tokens_per_step and prefill_chunk must be >= 1")
         self.engine = engine
@@ -126,6 +126,8 @@ class Scheduler:
         self.steps = 0
         self.preemptions = 0
         self._staged = None                       # the next decoding step, prepared while this one runs
+        self._inflight = None                     # (requests, selection) of a step whose tokens are not read yet
+        self.pipeline = pipeline
 
     # ---- adding --------------------------------------------------------------------------------
     def add(self, req: Request) -> Request:
@@ -156,7 +158,7 @@ class Scheduler:
 
     @property
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._inflight is not None)
 
     # ---- planning (pure bookkeeping: no device work) ------------------------------------------------
     def _left(self, r: Request) -> int:
@@ -282,8 +284,58 @@ class Scheduler:
         r.state, r.status, r.error = FINISHED, status, error
 
     # ---- running a step ---------------------------------------------------------------------------
+    def _digest(self, requests: List[Request], tokens: List[object]) -> List[Tuple[Request, int]]:
+        """Take the selected tokens in: append, call hooks, finish what has ended."""
+        emitted: List[Tuple[Request, int]] = []
+        for r, tok in zip(requests, tokens):
+            if isinstance(tok, Exception):
+                self._finish(r, FAILED, tok)
+                continue
+            r.generated.append(int(tok))
+            emitted.append((r, int(tok)))
+            stop_by_hook = False
+            if r.on_token is not None:
+                try:
+                    stop_by_hook = r.on_token(int(tok)) is False
+                except Exception as e:      # a failing callback fails only its request
+                    self._finish(r, FAILED, GessoError(ErrorCode.RUNTIME, f"on_token raised: {e!r}"))
+                    continue
+            if int(tok) in r.eos_ids:
+                self._finish(r, EOS)
+            elif int(tok) in r.stop_ids or stop_by_hook:
+                self._finish(r, STOP)
+            elif len(r.generated) >= r.max_new_tokens:
+                self._finish(r, COMPLETE)
+            elif len(r.prompt) + len(r.generated) > self.cache.max_positions:
+                # the sampled token would not fit the context (src/Inference/session.jl:903-909)
+                self._finish(r, COMPLETE)
+        return emitted
+
+    def _stage_next(self, requests: List[Request], pending_tokens: int) -> None:
+        """While the device runs, prepare the decoding step after the ones in flight if it will most
+        likely be the same requests with one more token each (``pending_tokens``: tokens per request that
+        are selected but not digested yet); only the sampled ids are missing then."""
+        self._staged = None
+        stage = getattr(self.engine, "stage_single_tokens", None)
+        if (stage is None or self.waiting or len(requests) != len(self.running)
+                or any(r.state != RUNNING or r.cancelled
+                       or len(r.generated) + pending_tokens + 1 > r.max_new_tokens for r in requests)):
+            return
+        try:
+            self._staged = stage([r.req_id for r in requests])
+        except GessoError:
+            self._staged = None               # no page or no room: the ordinary path decides
+
     def step(self) -> List[Tuple[Request, int]]:
-        """Plan, run and digest one step; returns the (request, token) pairs emitted by it."""
+        """Plan, run and digest one step; returns the (request, token) pairs emitted by it.
+
+        Steady decoding runs one step ahead of the host: the next step is launched with the token ids
+        that the selection kernel left on the device, before the host has read them, so the device never
+        waits for the host between two steps.  What a call returns is then the step before the one it
+        launched.  A request that turns out to have ended is simply part of one step too many, whose
+        result for it is dropped."""
+        if self._inflight is not None:
+            return self._advance()
         plan = self.plan()
         if not plan.entries:
             return []
@@ -302,41 +354,53 @@ class Scheduler:
         self.steps += 1
         for r, _, n in plan.entries:
             r.fed += n
-        # While the device runs this step, prepare the next one if it will most likely be the same
-        # requests with one more token each; only their sampled ids are missing then.
-        stage = getattr(self.engine, "stage_single_tokens", None)
-        if (stage is not None and decoding and not self.waiting and len(samplers) == len(self.running)
-                and all(len(r.generated) + 1 < r.max_new_tokens and not r.cancelled for r in samplers)):
-            try:
-                self._staged = stage([r.req_id for r in samplers])
-            except GessoError:
-                self._staged = None               # no page or no room: the ordinary path decides
-        emitted: List[Tuple[Request, int]] = []
-        if samplers:
-            tokens = self.select(logits, samplers)
-            for r, tok in zip(samplers, tokens):
-                if isinstance(tok, Exception):
-                    self._finish(r, FAILED, tok)
-                    continue
-                r.generated.append(int(tok))
-                emitted.append((r, int(tok)))
-                stop_by_hook = False
-                if r.on_token is not None:
-                    try:
-                        stop_by_hook = r.on_token(int(tok)) is False
-                    except Exception as e:      # a failing callback fails only its request
-                        self._finish(r, FAILED, GessoError(ErrorCode.RUNTIME, f"on_token raised: {e!r}"))
-                        continue
-                if int(tok) in r.eos_ids:
-                    self._finish(r, EOS)
-                elif int(tok) in r.stop_ids or stop_by_hook:
-                    self._finish(r, STOP)
-                elif len(r.generated) >= r.max_new_tokens:
-                    self._finish(r, COMPLETE)
-                elif len(r.prompt) + len(r.generated) > self.cache.max_positions:
-                    # the sampled token would not fit the context (src/Inference/session.jl:903-909)
-                    self._finish(r, COMPLETE)
+        if decoding:
+            self._stage_next(samplers, pending_tokens=1)
+        if not samplers:
+            return []
+        launch = getattr(self.select, "launch", None)
+        if launch is not None and self.pipeline and self._staged is not None:
+            # the selection is launched, not awaited: the next call takes it from there
+            self._inflight = (samplers, launch(logits, samplers))
+            return self._advance()
+        return self._digest(samplers, self.select(logits, samplers))
+
+    def _advance(self) -> List[Tuple[Request, int]]:
+        """One turn of the pipelined decoding: launch the step after the one in flight from the ids on the
+        device, then wait for the one in flight and digest it."""
+        requests, pending = self._inflight
+        staged, self._staged = self._staged, None
+        ahead = None
+        if (staged is not None and staged.req_ids == tuple(r.req_id for r in requests) and not self.waiting
+                and not any(r.cancelled for r in requests)):
+            logits = self.engine.step_staged(staged, device_tokens=pending.ids)
+            self.steps += 1
+            for r in requests:
+                r.fed += 1
+            ahead = self.select.launch(logits, requests)
+        emitted = self._digest(requests, self.select.wait(pending))
+        if ahead is None:
+            self._inflight = None                     # back to one step at a time
+            return emitted
+        if any(r.state != RUNNING or r.cancelled for r in requests) or self.waiting:
+            # somebody ended (or arrived): the step ahead has run with the old batch; take what it
+            # gives to the requests that go on, drop the rest
+            tokens = self.select.wait(ahead)
+            alive = [(r, t) for r, t in zip(requests, tokens) if r.state == RUNNING]
+            emitted += self._digest([r for r, _ in alive], [t for _, t in alive])
+            self._inflight = None
+            return emitted
+        self._inflight = (requests, ahead)
+        self._stage_next(requests, pending_tokens=1)
         return emitted
+
+    def drain(self) -> List[Tuple[Request, int]]:
+        """Wait for a step that is still in flight and digest it (before the scheduler is left alone)."""
+        if self._inflight is None:
+            return []
+        requests, pending = self._inflight
+        self._inflight, self._staged = None, None
+        return self._digest(requests, self.select.wait(pending))
 
     def run(self, max_steps: Optional[int] = None) -> None:
         n = 0
@@ -346,7 +410,7 @@ class Scheduler:
             n += 1
             if max_steps is not None and n >= max_steps:
                 break
-            if (len(self.waiting), len(self.running), self.steps) == before and not self.running:
+            if (len(self.waiting), len(self.running), self.steps) == before and not self.running and self.waiting:
                 # nothing ran and nothing is live: the head of the queue cannot be admitted
                 r = self.waiting.pop(0)
                 self._finish(r, FAILED, resource(f"request {r.req_id!r} cannot be admitted"))

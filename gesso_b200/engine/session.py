@@ -29,7 +29,7 @@ import numpy as np
 import torch
 
 from ..errors import ErrorCode, GessoError, invalid
-from ..sampling.sampler import SamplingParams, select_tokens
+from ..sampling.sampler import SamplingParams, select_launch, select_tokens, select_wait
 from .batch import StepEntry
 from .engine import Engine
 from .scheduler import CANCELLED, COMPLETE, EOS, FAILED, STOP, Request, Scheduler
@@ -63,8 +63,21 @@ class BatchResult:
     error: Optional[Exception] = None
 
 
-def _select(logits, requests):
-    return select_tokens(logits, [r.sampling for r in requests], [r.rng for r in requests])
+class _Select:
+    """Token selection for the scheduler: at once, or launched now and awaited later (the scheduler runs
+    steady decoding one step ahead of the host)."""
+
+    def __call__(self, logits, requests):
+        return select_tokens(logits, [r.sampling for r in requests], [r.rng for r in requests])
+
+    def launch(self, logits, requests):
+        return select_launch(logits, [r.sampling for r in requests], [r.rng for r in requests])
+
+    def wait(self, pending):
+        return select_wait(pending)
+
+
+_select = _Select()
 
 
 class Session:

@@ -95,15 +95,80 @@ def sample_host(row: np.ndarray, params: SamplingParams, rng: SplitMix64) -> int
 
 
 _pinned: dict = {}
+_pinned_turn: dict = {}
 
 
 def _pinned_rows(R: int) -> torch.Tensor:
-    """A pinned [2, R] int32 host buffer (ids and flags), kept per row count: the copy back needs no
-    staging through pageable memory."""
-    buf = _pinned.get(R)
-    if buf is None:
-        buf = _pinned[R] = torch.empty((2, R), dtype=torch.int32, pin_memory=True)
-    return buf
+    """A pinned [2, R] int32 host buffer (ids and flags): the copy back needs no staging through pageable
+    memory.  Four buffers per row count take turns, so that a selection that is still awaited keeps its
+    buffer while the next ones are launched."""
+    bufs = _pinned.get(R)
+    if bufs is None:
+        bufs = _pinned[R] = [torch.empty((2, R), dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        _pinned_turn[R] = 0
+    _pinned_turn[R] = (_pinned_turn[R] + 1) % len(bufs)
+    return bufs[_pinned_turn[R]]
+
+
+class PendingSelection:
+    """A selection that has been launched: the ids stay on the device (``ids``: int32 [R], for a next
+    step that starts before the host has read them) and are on their way to pinned host memory."""
+
+    def __init__(self, both: torch.Tensor, host: torch.Tensor, event: "torch.cuda.Event", rows: int):
+        self.both, self.host, self.event, self.rows = both, host, event, rows
+
+    @property
+    def ids(self) -> torch.Tensor:
+        return self.both[0]
+
+
+def select_launch(logits: torch.Tensor, params: Sequence[SamplingParams],
+                  rngs: Sequence[Optional[SplitMix64]]) -> Optional[PendingSelection]:
+    """Launch the selection of one token per row of ``logits`` [R, V] (device, float32) and the copy of
+    the result to the host, without waiting for either.  Sampled rows draw exactly one uniform number
+    from their request's generator, now."""
+    R = logits.shape[0]
+    if R == 0:
+        return None
+    ids, bad = ops.argmax_rows(logits)
+    sampled = [i for i, p in enumerate(params) if not p.greedy]
+    if not sampled and ids.data_ptr() + 4 * R == bad.data_ptr():
+        # all greedy: ids and flags sit in one buffer, one copy brings both
+        both = ids.new_empty(0).set_(ids.untyped_storage(), ids.storage_offset(), (2, R))
+    else:
+        if sampled:
+            dev = logits.device
+            # temperature, top-p, the uniform numbers and the pick mask in one pinned buffer, one copy
+            hp = torch.empty((4, R), dtype=torch.float64, pin_memory=True)
+            a = hp.numpy()
+            for i in range(R):
+                g = params[i].greedy
+                a[0, i] = 1.0 if g else params[i].temperature
+                a[1, i] = params[i].top_p
+                a[2, i] = 0.0 if g else rngs[i].unit()
+                a[3, i] = 0.0 if g else 1.0
+            dp = hp.to(dev, non_blocking=True)
+            sids, sbad = ops.sample_rows(logits, dp[0].contiguous(), dp[1].contiguous(), dp[2].contiguous())
+            pick = dp[3] > 0.5
+            ids = torch.where(pick, sids, ids)
+            bad = torch.where(pick, sbad, bad)
+        both = torch.stack([ids, bad])
+    host = _pinned_rows(R)
+    host.copy_(both, non_blocking=True)
+    event = torch.cuda.Event()
+    event.record()
+    return PendingSelection(both, host, event, R)
+
+
+def select_wait(pending: Optional[PendingSelection]) -> List[object]:
+    """The tokens of a launched selection: an ``int`` per row, or a :class:`GessoError` for a row whose
+    logits are not finite (the caller fails that request only)."""
+    if pending is None:
+        return []
+    pending.event.synchronize()
+    host = pending.host.numpy()
+    return [GessoError(ErrorCode.NUMERICAL_INSTABILITY, "nonfinite logits; no token may be emitted")
+            if host[1, i] else int(host[0, i]) for i in range(pending.rows)]
 
 
 def select_tokens(logits: torch.Tensor, params: Sequence[SamplingParams],
@@ -114,38 +179,4 @@ def select_tokens(logits: torch.Tensor, params: Sequence[SamplingParams],
     finite (the caller fails that request only).  Sampled rows draw exactly one uniform number from
     their request's generator.
     """
-    R = logits.shape[0]
-    if R == 0:
-        return []
-    ids, bad = ops.argmax_rows(logits)
-    sampled = [i for i, p in enumerate(params) if not p.greedy]
-    if not sampled and ids.data_ptr() + 4 * R == bad.data_ptr():
-        # all greedy: ids and flags sit in one buffer, one copy brings both
-        both = ids.new_empty(0).set_(ids.untyped_storage(), ids.storage_offset(), (2, R))
-        pinned = _pinned_rows(R)
-        pinned.copy_(both, non_blocking=True)
-        torch.cuda.current_stream(ids.device).synchronize()
-        host = pinned.numpy()
-        return [GessoError(ErrorCode.NUMERICAL_INSTABILITY, "nonfinite logits; no token may be emitted")
-                if host[1, i] else int(host[0, i]) for i in range(R)]
-    if sampled:
-        temp = torch.tensor([params[i].temperature if not params[i].greedy else 1.0 for i in range(R)],
-                            dtype=torch.float64)
-        top_p = torch.tensor([params[i].top_p for i in range(R)], dtype=torch.float64)
-        u = torch.tensor([rngs[i].unit() if not params[i].greedy else 0.0 for i in range(R)],
-                         dtype=torch.float64)
-        dev = logits.device
-        sids, sbad = ops.sample_rows(logits, temp.to(dev), top_p.to(dev), u.to(dev))
-        pick = torch.zeros((R,), dtype=torch.bool)
-        pick[sampled] = True
-        pick = pick.to(dev)
-        ids = torch.where(pick, sids, ids)
-        bad = torch.where(pick, sbad, bad)
-    host = torch.stack([ids, bad]).to("cpu").numpy()
-    out: List[object] = []
-    for i in range(R):
-        if host[1, i]:
-            out.append(GessoError(ErrorCode.NUMERICAL_INSTABILITY, "nonfinite logits; no token may be emitted"))
-        else:
-            out.append(int(host[0, i]))
-    return out
+    return select_wait(select_launch(logits, params, rngs))

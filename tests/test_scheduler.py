@@ -268,3 +268,117 @@ def test_staging_yields_to_page_pressure():
     assert a.status == COMPLETE and b.status == COMPLETE
     assert a.ids == solo([1, 2, 3], 9) and b.ids == solo([4, 5, 6], 3)
     assert eng.cache.pages_in_use() == [0]
+
+
+# ---- steady decoding one step ahead of the host ---------------------------------------------------------
+class PipelinedEngine(FakeEngine):
+    """A stand-in that keeps every request's history itself (as a cache would), so that a step can be
+    launched from ids the host has not seen: 'logits' are the histories after the step."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.history = {}
+        self.from_device = 0
+
+    def admit(self, rid):
+        super().admit(rid)
+        self.history[rid] = []
+
+    def release(self, rid):
+        super().release(rid)
+        self.history.pop(rid, None)
+
+    def step(self, entries):
+        super().step(entries)
+        for e in entries:
+            self.history[e.req_id] += [int(t) for t in e.tokens]
+        return [list(self.history[e.req_id]) for e in entries if e.want]
+
+    def stage_single_tokens(self, req_ids):
+        self.cache.reserve_single_tokens(list(req_ids))
+
+        class Staged:
+            pass
+        st = Staged()
+        st.req_ids = tuple(req_ids)
+        return st
+
+    def step_staged(self, staged, tokens=None, device_tokens=None):
+        if device_tokens is not None:
+            tokens, self.from_device = device_tokens, self.from_device + 1
+        for rid, t in zip(staged.req_ids, tokens):
+            self.history[rid].append(int(t))
+        self.cache.commit_single_tokens(list(staged.req_ids))
+        self.cache.check_invariants()
+        self.log.append([(rid, [int(t)], [0]) for rid, t in zip(staged.req_ids, tokens)])
+        return [list(self.history[rid]) for rid in staged.req_ids]
+
+
+class HistorySelect:
+    """next token = a function of the whole history, as `next_token` computes it from a request."""
+
+    @staticmethod
+    def pick(history):
+        return (sum(history) * 31 + len(history)) % 97
+
+    def __call__(self, logits, requests):
+        return [self.pick(h) for h in logits]
+
+    def launch(self, logits, requests):
+        class Pending:
+            pass
+        p = Pending()
+        p.ids = [self.pick(h) for h in logits]
+        return p
+
+    def wait(self, pending):
+        return list(pending.ids)
+
+
+def test_pipelined_decoding_gives_the_same_tokens():
+    prompts, news = [[1, 2, 3], [9] * 11, [4]], (12, 7, 9)
+    eng = PipelinedEngine()
+    s = Scheduler(eng, HistorySelect(), vocab_size=100, max_batch=3, prefill_chunk=4)
+    reqs = [s.add(Request(p, n)) for p, n in zip(prompts, news)]
+    s.run()
+    for p, r, n in zip(prompts, reqs, news):
+        assert r.status == COMPLETE and r.ids == solo(p, n)
+    assert eng.from_device > 5                       # steps were launched from ids the host had not read
+    assert eng.cache.pages_in_use() == [0] and eng.cache.slots_in_use() == 0 and not s.has_work
+
+
+def test_pipelined_decoding_drops_the_step_too_many():
+    """A request ends on a stop id while the next step is already running with it; the others go on."""
+    eng = PipelinedEngine()
+    s = Scheduler(eng, HistorySelect(), vocab_size=100, max_batch=2)
+    full_a, full_b = solo([5, 6, 7], 14), solo([8, 1], 14)
+    a = s.add(Request([5, 6, 7], 14, stop_ids=[full_a[3 + 6]]))       # its 7th new token stops it
+    b = s.add(Request([8, 1], 14))
+    late = None
+    for i in range(40):
+        if not s.has_work:
+            break
+        s.step()
+        if i == 9:
+            late = s.add(Request([3, 3, 3, 3], 5))                   # an arrival in the middle of the pipeline
+    assert a.status == STOP and a.ids == full_a[:3 + 7]
+    assert b.status == COMPLETE and b.ids == full_b
+    assert late.status == COMPLETE and late.ids == solo([3, 3, 3, 3], 5)
+    assert eng.from_device > 0 and eng.cache.pages_in_use() == [0]
+
+
+def test_pipelined_decoding_with_cancel_and_hooks():
+    eng = PipelinedEngine()
+    s = Scheduler(eng, HistorySelect(), vocab_size=100, max_batch=2)
+    seen = []
+    a = s.add(Request([5, 6, 7], 20, on_token=lambda t: (seen.append(t), len(seen) < 5)[1]))
+    b = s.add(Request([2, 2], 20))
+    for i in range(60):
+        if not s.has_work:
+            break
+        s.step()
+        if i == 8:
+            b.cancel()
+    assert a.status == STOP and a.ids == solo([5, 6, 7], 20)[:3 + 5] and len(seen) == 5
+    assert b.status == CANCELLED and b.ids == solo([2, 2], 20)[:len(b.ids)]
+    assert eng.cache.pages_in_use() == [0] and not s.has_work
