@@ -16,8 +16,9 @@ One JSON line is printed:
   before); inputs of a step are larger than L2 (all weights are read once per step);
 * ``e2e``: the same through the Python entry point (``Session.open_batch`` + ``step()``): host token
   ids in, sampled ids out, every step's metadata copied from pinned host memory and its ids read back;
-* ``prefill``: one request of 2,048 tokens, logits at its last position; ``frac`` = flops / time / the
-  bf16 peak;
+* ``prefill``: one request of 2,048 tokens, logits at its last position, best of five after two warm-up
+  runs (the engine replays a captured graph for a portion of a length it has seen before); ``frac`` =
+  flops / time / the bf16 peak;
 * ``roofline``: bytes a decode step has to read (every weight once + the cache of the live requests)
   / its time, against the measured copy bandwidth;
 * ``points``: decode tokens per second at batch 1 and 64.

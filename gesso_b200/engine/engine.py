@@ -92,6 +92,7 @@ class Engine:
         self.use_graphs = use_graphs and getattr(model, "graph_safe", True)
         self.max_graph_batch = 256
         self._graphs: Dict = {}
+        self._portion_shapes: Dict = {}           # how often a single-portion step of a shape has come
         self._graph_pool = None
         # ring of pinned staging buffers; an event per buffer says when its copy has left it
         self._pinned: List[Optional[torch.Tensor]] = [None] * 4
@@ -257,12 +258,15 @@ class Engine:
 
         A step of single tokens only (decoding) replays a CUDA graph captured for its batch size:
         the metadata goes into the graph's fixed buffer and the whole layer loop is one launch.
-        The logits of such a step live in the graph's output buffer and are valid until the next
-        step of the same shape.
+        So does a step that is one prompt portion of a length seen before (the portions of a chunked
+        prompt) with few wanted rows.  The logits of such a step live in the graph's output buffer and
+        are valid until the next step of the same shape.
         """
         layout, slot_i, host, max_seg, max_kv = self._prepare(entries)
         if self.use_graphs and max_seg == 1 and layout.n_segs <= self.max_graph_batch:
             logits = self._step_graph(layout, slot_i, host, max_kv)
+        elif self.use_graphs and self._portion_graph_wanted(layout):
+            logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg)
         else:
             buf = torch.empty((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
             self._upload(buf, slot_i, host)
@@ -318,16 +322,28 @@ class Engine:
         self.tokens_run += staged.layout.n_tokens
         return logits
 
+    def _portion_graph_wanted(self, layout: StepLayout) -> bool:
+        """One prompt portion of at least 64 tokens with at most 16 wanted rows, of a length that has come
+        before (a graph is captured at the second step of a shape, and for at most 8 shapes)."""
+        if layout.n_segs != 1 or layout.n_tokens < 64 or layout.n_rows > 16:
+            return False
+        key = (layout.n_tokens, layout.n_segs, layout.n_rows, self._all_rows)
+        if key in self._graphs:
+            return True
+        seen = self._portion_shapes.get(key, 0)
+        self._portion_shapes[key] = seen + 1
+        return seen >= 1 and sum(1 for k in self._graphs if k[0] > k[1]) < 8
+
     def _step_graph(self, layout: StepLayout, slot_i: int, host: torch.Tensor, max_kv: int,
-                    device_tokens: Optional[torch.Tensor] = None, token_at: int = 0):
-        key = (layout.n_segs, layout.n_rows, self._all_rows)
+                    device_tokens: Optional[torch.Tensor] = None, token_at: int = 0, max_seg: int = 1):
+        key = (layout.n_tokens, layout.n_segs, layout.n_rows, self._all_rows)
         g = self._graphs.get(key)
         if g is None:
             buf = torch.zeros((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
             self._upload(buf, slot_i, host)
             if device_tokens is not None:
                 buf[token_at:token_at + device_tokens.numel()].copy_(device_tokens)
-            ctx = StepContext(layout, buf, self.status, 1, self.max_positions, self._all_rows)
+            ctx = StepContext(layout, buf, self.status, max_seg, self.max_positions, self._all_rows)
             views = self.views(ctx)
             # One eager run first: libraries initialise lazily, and capture records rather than runs,
             # so this run is also the one that produces the step's result.

@@ -107,6 +107,31 @@ def test_decoding_steps_staged_ahead_keep_the_tokens(dtype, models, plain_models
     assert s.stats()["pages_in_use"] == [0]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_portion_shapes_replay_a_graph(dtype, models):
+    """Prompt portions of a length that has come before run as a captured graph: three requests with
+    prompts of one length (a chunked prompt's full portions) give, position by position, the logits of
+    an engine that launches every kernel itself."""
+    from gesso_b200.engine import Engine, StepEntry
+    model = models("c", dtype)
+    prompts = prompts_for("c", [96, 96, 96, 96], seed=21)
+    outs = {}
+    for graphs in (False, True):
+        eng = Engine(model, max_positions=256, page_size=16, num_pages=40, max_requests=2, use_graphs=graphs)
+        res = []
+        for i, p in enumerate(prompts):
+            eng.admit(i)
+            res.append(eng.step([StepEntry(i, p, [0, 95])]).clone())
+            res.append(eng.step([StepEntry(i, p[:70], [69])]).clone())       # a second portion shape, positions 96..
+            eng.release(i)
+        outs[graphs] = res
+        eng.check_status()
+        if graphs:
+            assert sum(1 for k in eng._graphs if k[0] > k[1]) == 2            # both shapes were captured
+    for a, b in zip(outs[False], outs[True]):
+        assert torch.equal(a, b)
+
+
 def test_sampled_ids_follow_the_plain_sampler(models, plain_models):
     import gesso_b200
     from plain_lfm2 import PlainSampler
