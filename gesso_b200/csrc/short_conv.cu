@@ -153,6 +153,81 @@ __global__ void conv_mix_vec_kernel(const T* __restrict__ bcx, const float* __re
     store_vec(out + (size_t)t * H + c0, y);
 }
 
+// The same for runs of TB consecutive tokens per thread (long portions, at most 4 taps): the products
+// B*X of the last L-1 tokens stay in registers from one token to the next, so a token costs one read of
+// its own B, C and X instead of L reads of B and X; the history is fetched afresh only at the start of a
+// run and where a new portion begins inside it.
+template <typename T, int TB, int L>
+__global__ void conv_mix_run_kernel(const T* __restrict__ bcx, const float* __restrict__ in_bias,
+                                    const float* __restrict__ taps, const float* __restrict__ conv_bias,
+                                    const float* __restrict__ state, long long slot_stride,
+                                    const int* __restrict__ seg_of_token, const int* __restrict__ seg_start,
+                                    const int* __restrict__ seg_pos0, const int* __restrict__ slots,
+                                    T* __restrict__ out, int n_tokens, int H, int packed) {
+    constexpr int V = ConvVec<T>::N;
+    const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    const int tbeg = blockIdx.x * TB, tend = min(n_tokens, tbeg + TB);
+    if (c0 >= H || tbeg >= n_tokens) return;
+    float w[L][V], hist[L - 1][V];
+#pragma unroll
+    for (int p = 0; p < L; ++p)
+#pragma unroll
+        for (int v = 0; v < V; ++v) w[p][v] = taps[(size_t)(c0 + v) * L + p];
+    for (int t = tbeg; t < tend; ++t) {
+        const int s = seg_of_token[t];
+        const int off = t - seg_start[s];
+        const int pos = seg_pos0[s] + off;
+        const T* row = bcx + (size_t)t * 3 * H;
+        if (t == tbeg || off == 0) {
+            // hist[q] = bx of the token (L-1-q) places before t, for the taps q = 0 .. L-2 (oldest first)
+            const float* st = state + (size_t)slots[s] * slot_stride;
+#pragma unroll
+            for (int q = 0; q < L - 1; ++q) {
+                const int back = (L - 1) - q;
+                if (back > pos) {
+#pragma unroll
+                    for (int v = 0; v < V; ++v) hist[q][v] = 0.f;
+                } else if (back <= off) {
+                    const T* prow = row - (size_t)back * 3 * H;
+                    float b[V], x[V];
+                    load_vec<T>(prow + bcx_col(0, c0, H, packed), b);
+                    load_vec<T>(prow + bcx_col(2, c0, H, packed), x);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        if (in_bias) { b[v] += in_bias[c0 + v]; x[v] += in_bias[2 * H + c0 + v]; }
+                        hist[q][v] = b[v] * x[v];
+                    }
+                } else {
+                    const float* sp = st + (size_t)((L - 1) - (back - off)) * H + c0;
+#pragma unroll
+                    for (int v = 0; v < V; ++v) hist[q][v] = sp[v];
+                }
+            }
+        }
+        float b[V], x[V], cg[V], y[V];
+        load_vec<T>(row + bcx_col(0, c0, H, packed), b);
+        load_vec<T>(row + bcx_col(2, c0, H, packed), x);
+        load_vec<T>(row + bcx_col(1, c0, H, packed), cg);
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            if (in_bias) { b[v] += in_bias[c0 + v]; x[v] += in_bias[2 * H + c0 + v]; cg[v] += in_bias[H + c0 + v]; }
+            const float cur = b[v] * x[v];
+            // taps oldest to newest, in the order of the other kernels
+            float acc = 0.f;
+#pragma unroll
+            for (int q = 0; q < L - 1; ++q) acc += hist[q][v] * w[q][v];
+            acc += cur * w[L - 1][v];
+            if (conv_bias) acc += conv_bias[c0 + v];
+            y[v] = acc * cg[v];
+            // the history moves up by one place and takes this token's product at its newest place
+#pragma unroll
+            for (int q = 0; q < L - 2; ++q) hist[q][v] = hist[q + 1][v];
+            hist[L - 2][v] = cur;
+        }
+        store_vec(out + (size_t)t * H + c0, y);
+    }
+}
+
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ bcx, const float* __restrict__ in_bias,
                                          float* __restrict__ state, long long slot_stride,
@@ -257,6 +332,26 @@ GESSO_API int gesso_short_conv(const void* bcx, int dtype, const float* in_bias,
         // 16 bytes of channels per thread
         const int vthreads = 128;
         dim3 vgrid(n_tokens, (H / vec + vthreads - 1) / vthreads);
+        if (L <= 4 && n_tokens >= 256) {
+            // long portions: runs of 8 tokens per thread with the history in registers
+            constexpr int TB = 8;
+            dim3 rgrid((n_tokens + TB - 1) / TB, (H / vec + vthreads - 1) / vthreads);
+#define RUN(T, LL)                                                                                              \
+    conv_mix_run_kernel<T, TB, LL><<<rgrid, vthreads, 0, stream>>>(                                             \
+        (const T*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_of_token, seg_start, seg_pos0, slots,   \
+        (T*)out, n_tokens, H, packed)
+            if (dtype == GESSO_F32) {
+                if (L == 2) RUN(float, 2); else if (L == 3) RUN(float, 3); else RUN(float, 4);
+                conv_state_update_kernel<float><<<sgrid, threads, 0, stream>>>(
+                    (const float*)bcx, in_bias, state, slot_stride, seg_start, seg_pos0, slots, n_segs, H, L, packed);
+            } else {
+                if (L == 2) RUN(bf16, 2); else if (L == 3) RUN(bf16, 3); else RUN(bf16, 4);
+                conv_state_update_kernel<bf16><<<sgrid, threads, 0, stream>>>(
+                    (const bf16*)bcx, in_bias, state, slot_stride, seg_start, seg_pos0, slots, n_segs, H, L, packed);
+            }
+#undef RUN
+            return launch_status();
+        }
         if (dtype == GESSO_F32) {
             conv_mix_vec_kernel<float><<<vgrid, vthreads, 0, stream>>>(
                 (const float*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_of_token, seg_start, seg_pos0, slots,

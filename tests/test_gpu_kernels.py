@@ -150,6 +150,47 @@ def test_short_conv_carried_state(dtype, H, L, bias):
     assert torch.equal(st_a, st_b)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,L,bias,packed", [(64, 3, False, True), (200, 4, True, False), (8, 2, False, True),
+                                             (328, 3, True, True)])
+def test_short_conv_long_portions(dtype, H, L, bias, packed):
+    """Steps of hundreds of tokens (each thread walks runs of 8 tokens with the history in registers):
+    three requests in one step whose borders fall inside a run, one of them starting at position 0 and
+    the others carrying state from an earlier step; then a second long step.  Against the formulas."""
+    from gesso_b200 import ops
+    if packed and dtype != torch.bfloat16:
+        pytest.skip("the packed layout belongs to bfloat16 runs")
+    g = torch.Generator().manual_seed(H + 7 * L)
+    lens1, lens2 = [5, 9, 0], [397, 313, 61]          # first a short step (carried state), then a long one
+    T = [a + b_ for a, b_ in zip(lens1, lens2)]
+    taps = torch.randn(H, L, generator=g).to(DEV)
+    in_b = torch.randn(3 * H, generator=g).to(DEV) if bias else None
+    cv_b = torch.randn(H, generator=g).to(DEV) if bias else None
+    seqs = [torch.randn(t_, 3 * H, generator=g).to(dtype).to(DEV) for t_ in T]
+    want = [conv_reference(s_, in_b, taps, cv_b) for s_ in seqs]
+
+    def lay(x):       # rows as the (packed) projection gives them
+        return x.reshape(-1, 3, H // 8, 8).permute(0, 2, 1, 3).reshape(-1, 3 * H).contiguous() if packed else x
+    state = torch.full((4, L - 1, H), 3.0, device=DEV)           # stale values: position 0 must ignore them
+    slots = [2, 0, 3]
+    out1 = ops.short_conv(lay(torch.cat([seqs[0][:5], seqs[1][:9]])), in_b, taps, cv_b, state, i32([0] * 5 + [1] * 9),
+                          i32([0, 5, 14]), i32([0, 0]), i32(slots[:2]), 2, 9, packed=packed)
+    bcx = lay(torch.cat([seqs[0][5:], seqs[1][9:], seqs[2]]))
+    n = lens2
+    out2 = ops.short_conv(bcx, in_b, taps, cv_b, state, i32([0] * n[0] + [1] * n[1] + [2] * n[2]),
+                          i32([0, n[0], n[0] + n[1], sum(n)]), i32([5, 9, 0]), i32(slots), 3, max(n), packed=packed)
+    tol = 2e-6 if dtype == torch.float32 else BF16_EPS
+    assert rel_err(out1[:5], want[0][:5]) < tol and rel_err(out1[5:], want[1][:9]) < tol
+    assert rel_err(out2[:n[0]], want[0][5:]) < tol
+    assert rel_err(out2[n[0]:n[0] + n[1]], want[1][9:]) < tol
+    assert rel_err(out2[n[0] + n[1]:], want[2]) < tol
+    # the state after the long step: the last L-1 products of every request
+    for k, slot in enumerate(slots):
+        r = seqs[k].double().cpu() + (in_b.double().cpu() if bias else 0)
+        bx = (r[:, :H] * r[:, 2 * H:])[-(L - 1):]
+        assert rel_err(state[slot], bx) < 1e-6
+
+
 @pytest.mark.parametrize("H,L,bias", [(64, 3, False), (40, 4, True), (8, 2, False)])
 def test_short_conv_packed_layout(H, L, bias):
     """The same convolution from rows of bcx laid out in groups of 24 columns (B, C, X of 8 channels)."""
