@@ -85,8 +85,8 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = u;
 }
 
-#define NORM_VEC_THREADS 256
-#define NORM_VEC_MAX 8
+#define NORM_VEC_THREADS 512
+#define NORM_VEC_MAX 4
 
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(NORM_VEC_THREADS)
