@@ -175,3 +175,57 @@ __host__ __device__ constexpr unsigned make_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
+
+// ---- a pair of blocks (a cluster of two) working on one tile: cta_group::2 ----------------------------
+// In the shared::cluster window a block's shared-memory addresses carry its rank in the pair in bit 24;
+// clearing that bit addresses the same object in the even (leader) block.
+#define PAIR_LEADER_MASK 0xFEFFFFFFu
+
+__device__ __forceinline__ unsigned cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(void* smem_dst, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_dst)), "r"(cols));
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::);
+}
+__device__ __forceinline__ void tmem_dealloc_pair(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols));
+}
+// TMA load into this block's shared memory whose bytes are counted on the LEADER block's barrier
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int c0, int c1, void* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
+            "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar) & PAIR_LEADER_MASK), "r"(c0), "r"(c1)
+        : "memory");
+}
+// D[tmem of both blocks] (+)= A * B with M = 256 (128 rows from each block's shared memory) and each block
+// holding half of B's rows; issued by one thread of the leader block
+__device__ __forceinline__ void umma_f16_pair(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
+                                              unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
+        "r"(0u)
+        : "memory");
+}
+// when the MMAs issued so far have finished, one arrival on the barrier at this address in both blocks
+__device__ __forceinline__ void umma_commit_pair(void* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::
+            "r"(smem_u32(bar)), "h"((unsigned short)3)
+        : "memory");
+}
+// one arrival on the leader block's barrier, from either block
+__device__ __forceinline__ void mbar_arrive_leader(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(smem_u32(bar) & PAIR_LEADER_MASK) : "memory");
+}

@@ -541,6 +541,11 @@ def check_tc_status(device="cuda") -> None:
         raise GessoError(ErrorCode.RUNTIME, f"tcgen05 matrix product: a pipeline wait ran out (role code {code})")
 
 
+_lib.declare("gesso_gemm_tcgen05_pair_takes", [_lib.I, _lib.I, _lib.I])
+_lib.declare("gesso_gemm_tcgen05_pair", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P])
+TC_PAIR = os.environ.get("GESSO_TC_PAIR", "1") != "0"
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epi: int = EPI_BF16, out: Optional[torch.Tensor] = None,
                  bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x [M,K] @ w [N,K]^T`` on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory).
@@ -559,8 +564,14 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epi: int = EPI_BF16, out: Opt
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
     else:
         out = torch.empty((M, N), dtype=torch.bfloat16 if epi == EPI_BF16 else torch.float32, device=x.device)
-    _lib.check(_lib.library().gesso_gemm_tcgen05(_p(x), _p(w), _p(out), _p(bias), M, N, K, epi,
-                                                 _p(tc_status_tensor(x.device)), _stream()), "gemm_tcgen05")
+    lib = _lib.library()
+    # from 256 rows and columns on, two blocks share a 256 x 256 tile (a third less operand traffic per SM)
+    if TC_PAIR and lib.gesso_gemm_tcgen05_pair_takes(M, N, K):
+        _lib.check(lib.gesso_gemm_tcgen05_pair(_p(x), _p(w), _p(out), _p(bias), M, N, K, epi,
+                                               _p(tc_status_tensor(x.device)), _stream()), "gemm_tcgen05_pair")
+    else:
+        _lib.check(lib.gesso_gemm_tcgen05(_p(x), _p(w), _p(out), _p(bias), M, N, K, epi,
+                                          _p(tc_status_tensor(x.device)), _stream()), "gemm_tcgen05")
     return out
 
 

@@ -21,10 +21,17 @@ def case(M, N, K, seed=0):
     return x, w, x.double() @ w.double().T
 
 
+@pytest.mark.parametrize("pair", [True, False])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 64), (128, 128, 256), (256, 512, 512), (2048, 2048, 2048),
-                                   (300, 384, 200), (130, 1032, 72), (1000, 6144, 2048), (128, 2048, 8192), (40, 256, 128), (17, 64, 96)])
-def test_tcgen05_gemm(M, N, K):
+                                   (300, 384, 200), (130, 1032, 72), (1000, 6144, 2048), (128, 2048, 8192), (40, 256, 128),
+                                   (17, 64, 96), (256, 256, 64), (2040, 16384, 2048), (520, 264, 8192)])
+def test_tcgen05_gemm(M, N, K, pair, monkeypatch):
+    """Both kernels: one block per 128 x 256 tile, and (from 256 rows and columns on) two blocks per
+    256 x 256 tile; every epilogue; sizes with ragged last tiles in every direction."""
     from gesso_b200 import ops
+    monkeypatch.setattr(ops, "TC_PAIR", pair)
+    if pair and not ops._lib.library().gesso_gemm_tcgen05_pair_takes(M, N, K):
+        pytest.skip("below the pair kernel's sizes: the single-block kernel runs either way")
     x, w, want = case(M, N, K)
     got = ops.gemm_tcgen05(x, w, ops.EPI_F32)
     ops.check_tc_status()
