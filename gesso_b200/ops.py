@@ -317,7 +317,21 @@ def tc_takes(M: int, w: torch.Tensor, x_dtype) -> bool:
     rows, inner and output sizes that are multiples of 8 (16-byte rows for TMA and vector stores)."""
     N, K = w.shape
     return (w.dtype == torch.bfloat16 and x_dtype == torch.bfloat16 and w.is_contiguous() and M >= TC_MIN_ROWS
-            and N >= 8 and N % 8 == 0 and K >= 8 and K % 8 == 0 and w.data_ptr() % 16 == 0)
+            and N >= 8 and N % 8 == 0 and K >= 8 and K % 8 == 0 and w.data_ptr() % 16 == 0
+            and _tc_wave_efficiency(M, N) >= TC_MIN_WAVE_EFFICIENCY)
+
+
+# The tcgen05 kernels walk whole tiles, one wave of (pairs of) SMs after the other; where the last wave is
+# mostly empty (few tokens times a narrow output) the library's smaller tiles and split-K variants win.
+TC_MIN_WAVE_EFFICIENCY = 0.8
+
+
+def _tc_wave_efficiency(M: int, N: int) -> float:
+    if M >= 256 and N >= 256:
+        tiles, slots = -(-M // 256) * -(-N // 256), SM_COUNT // 2          # pairs of blocks, 256 x 256 tiles
+    else:
+        tiles, slots = -(-M // 128) * -(-N // 256), SM_COUNT
+    return tiles / (-(-tiles // slots) * slots)
 
 
 _skinny_ws = {}
