@@ -219,6 +219,37 @@ def test_long_decoding_token_by_token(dtype, tol, models, plain_models):
     eng.check_status()
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL32), ("bfloat16", TOL16)])
+def test_long_context(dtype, tol, model_dirs, plain_models):
+    """5,000 tokens: the prompt in portions of 2,048, then 24 tokens one by one at positions near 5,000
+    (hundreds of pages per request, many key splits, rotation angles at large positions), beside a short
+    request that shares the steps."""
+    import gesso_b200
+    from gesso_b200.engine import Engine, StepEntry
+    model = gesso_b200.load(model_dirs["a"], dtype=dtype, max_positions=5120)
+    ids = prompts_for("a", [5000], seed=12)[0]
+    other = prompts_for("a", [40], seed=13)[0]
+    plain = plain_models["a"]
+    ref = plain.logits(ids).numpy()
+    ref_o = plain.logits(other).numpy()
+    eng = Engine(model, max_positions=5120, page_size=16, num_pages=330, max_requests=2)
+    eng.admit("long")
+    eng.admit("short")
+    scale, scale_o = max(1.0, float(np.abs(ref).max())), max(1.0, float(np.abs(ref_o).max()))
+    head = len(ids) - 24
+    for at in range(0, head, 2048):
+        n = min(2048, head - at)
+        out = eng.step([StepEntry("long", ids[at:at + n], [0, n - 1])]).cpu().numpy()
+        assert float(np.abs(out[0] - ref[at]).max()) <= tol * scale, f"position {at}"
+        assert float(np.abs(out[1] - ref[at + n - 1]).max()) <= tol * scale, f"position {at + n - 1}"
+    eng.step([StepEntry("short", other[:16], [])])
+    for k in range(24):
+        out = eng.step([StepEntry("short", [other[16 + k]], [0]), StepEntry("long", [ids[head + k]], [0])]).cpu().numpy()
+        assert float(np.abs(out[0] - ref_o[16 + k]).max()) <= tol * scale_o, f"short request, position {16 + k}"
+        assert float(np.abs(out[1] - ref[head + k]).max()) <= tol * scale, f"position {head + k}"
+    eng.check_status()
+
+
 @pytest.mark.parametrize("name", ["a", "b", "c"])
 def test_first_tokens_of_a_sequence(name, models, plain_models):
     """Prompts of 1, 2, 3 tokens, whole and token by token: the conv history is shorter than its
