@@ -32,6 +32,9 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
               "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 
 
+_SLOW_FIRST = ("attention_generic", "gemm_skinny_")
+
+
 def _say(msg: str) -> None:
     print(f"[gesso_b200 build] {msg}", file=sys.stderr, flush=True)
 
@@ -114,15 +117,17 @@ def build(verbose: bool = True, ptxas_info: bool = False) -> str:
             objs = [os.path.join(out_dir, s[:-3] + ".o") for s in srcs]
             logs = {}
             with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs), os.cpu_count() or 2)) as pool:
-                futs = {pool.submit(_compile_one, nvcc, s, o, extra): s for s, o in zip(srcs, objs)}
+                # the files with the most template instantiations take longest and start first
+                order = sorted(zip(srcs, objs), key=lambda so: (not so[0].startswith(_SLOW_FIRST), so[0]))
+                futs = {pool.submit(_compile_one, nvcc, s, o, extra): s for s, o in order}
                 pending = set(futs)
                 while pending:
-                    done, pending = cf.wait(pending, timeout=10.0)
+                    done, pending = cf.wait(pending, timeout=10.0, return_when=cf.FIRST_COMPLETED)
                     for f in done:
                         logs[futs[f]] = f.result()
                         if verbose:
                             _say(f"  {futs[f]} done ({time.time() - t0:.0f}s)")
-                    if pending and verbose:
+                    if pending and not done and verbose:
                         _say(f"  still compiling {len(pending)} file(s) ... {time.time() - t0:.0f}s")
             tmp_lib = lib + f".tmp{os.getpid()}"
             p = subprocess.run([nvcc] + ARCH_FLAGS + ["-shared", "-o", tmp_lib] + objs,
