@@ -22,6 +22,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
+from .. import ops
 from ..csrc.lib import launch_count
 from ..errors import ErrorCode, GessoError, invalid, resource
 from .batch import StepContext, StepEntry, StepLayout, count_tiles, pack_step
@@ -94,6 +95,7 @@ class Engine:
         self._graphs: Dict = {}
         self._portion_shapes: Dict = {}           # how often a single-portion step of a shape has come
         self._graph_pool = None
+        self._capture_stream = None
         # ring of pinned staging buffers; an event per buffer says when its copy has left it
         self._pinned: List[Optional[torch.Tensor]] = [None] * 4
         self._pinned_events: List[Optional[torch.cuda.Event]] = [None] * 4
@@ -351,7 +353,10 @@ class Engine:
             logits = self.model.forward(ctx, views)
             n_launch = launch_count() - before
             self.launches += n_launch
-            torch.cuda.current_stream().synchronize()
+            if self._capture_stream is None:
+                self._capture_stream = torch.cuda.Stream(self.model.rt.device)
+            ops.ensure_workspaces(self.model.rt.device, self._capture_stream)
+            torch.cuda.synchronize(self.model.rt.device)
             graph = torch.cuda.CUDAGraph()
             # No garbage collection while the stream records: a collected object that owns device
             # resources (an older engine's graphs, for one) would free them in the middle of the
@@ -359,7 +364,7 @@ class Engine:
             gc_was_on = gc.isenabled()
             gc.disable()
             try:
-                with torch.cuda.graph(graph, pool=self._graph_pool):
+                with torch.cuda.graph(graph, pool=self._graph_pool, stream=self._capture_stream):
                     out = self.model.forward(ctx, views)
             finally:
                 if gc_was_on:

@@ -348,6 +348,14 @@ def _skinny_workspace(device) -> torch.Tensor:
     return ws
 
 
+def ensure_workspaces(device, stream) -> None:
+    """Create the zeroed workspace of the skinny matrix product for ``stream`` now (on the current stream),
+    so that a graph captured on ``stream`` does not record its allocation and zero fill."""
+    with torch.cuda.stream(stream):
+        _skinny_workspace(device)
+    torch.cuda.current_stream(device).wait_stream(stream)
+
+
 def _skinny(x, w, out, bias, epi):
     """x: bfloat16 tensor or LazyNorm with at most SKINNY_NORM_MAX_ROWS rows."""
     N, K = w.shape
@@ -389,6 +397,8 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch
         _skinny(_skinny_input(x), w, out, None, EPI_BF16 if out_dtype == torch.bfloat16 else EPI_F32)
         return out
     x = _as_tensor(x)
+    if few_takes(M, w, x.dtype) and out_dtype in (torch.bfloat16, torch.float32):
+        return gemm_tcgen05_few(x, w, EPI_BF16 if out_dtype == torch.bfloat16 else EPI_F32)
     if tc_takes(M, w, x.dtype) and out_dtype in (torch.bfloat16, torch.float32):
         return gemm_tcgen05(x, w, EPI_BF16 if out_dtype == torch.bfloat16 else EPI_F32)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
@@ -408,6 +418,9 @@ def linear_residual(x, w: torch.Tensor, h: torch.Tensor, bias: Optional[torch.Te
         _cuda_contig(h, "h", torch.float32)
         _skinny(_as_tensor(x), w, h, bias, EPI_RESID)
         return None
+    if few_takes(M, w, x.dtype) and tuple(h.shape) == (M, w.shape[0]):
+        gemm_tcgen05_few(_as_tensor(x), w, EPI_RESID, out=h, bias=bias)
+        return None
     # Steps of many tokens hand the product on as a pending bfloat16 delta: the next norm kernel adds
     # it while it reads the residual stream anyway, which moves fewer bytes than a read-modify-write
     # of the float32 stream in the product's epilogue (measured: 15.7 vs 38.7 us at 2040 x 2048 x 2048).
@@ -421,6 +434,8 @@ def linear_swiglu(x, w_gate_up: torch.Tensor, packed: bool) -> torch.Tensor:
         out = torch.empty((M, w_gate_up.shape[0] // 2), dtype=torch.bfloat16, device=w_gate_up.device)
         _skinny(_skinny_input(x), w_gate_up, out, None, EPI_SWIGLU)
         return out
+    if packed and few_takes(M, w_gate_up, x.dtype) and w_gate_up.shape[0] % 16 == 0:
+        return gemm_tcgen05_few(_as_tensor(x), w_gate_up, EPI_SWIGLU)
     if packed and tc_takes(M, w_gate_up, x.dtype) and w_gate_up.shape[0] % 16 == 0:
         return gemm_tcgen05(_as_tensor(x), w_gate_up, EPI_SWIGLU)
     return swiglu(linear(x, w_gate_up, out_dtype=x.dtype), packed)
@@ -558,6 +573,52 @@ def check_tc_status(device="cuda") -> None:
 _lib.declare("gesso_gemm_tcgen05_pair_takes", [_lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_gemm_tcgen05_pair", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P])
 TC_PAIR = os.environ.get("GESSO_TC_PAIR", "1") != "0"
+
+
+_lib.declare("gesso_gemm_tcgen05_few_takes", [_lib.I, _lib.I, _lib.I])
+_lib.declare("gesso_gemm_tcgen05_few", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P,
+                                        _lib.P])
+FEW_MAX_ROWS = 128
+# The few-row tcgen05 product (17 .. 128 tokens; W streamed once, SwiGLU or the residual add in the
+# epilogue) is an option, GESSO_TC_FEW=1, for matrices of TC_FEW_MIN_BYTES or more.  Alone it ties with
+# the library at 64 rows (14.9 us against 12.8 + 3.5 for the SwiGLU kernel at 16384 x 2048, 48 against
+# 53 us at 65536 x 2048, 13.1 against 13.0 at 2048 x 8192; smaller matrices lose: 11.5 against 6.7 us at
+# 6144 x 2048, a cluster's exchange through shared memory costs about 3 us), but inside a decoding step
+# of 64 requests the library's kernels came out 1 to 3 % ahead (their start overlaps the preceding
+# kernel; a block of this one holds a whole SM), so they are the default.
+TC_FEW = os.environ.get("GESSO_TC_FEW", "0") == "1"
+TC_FEW_MIN_BYTES = int(float(os.environ.get("GESSO_TC_FEW_MIN_MB", "32")) * (1 << 20))
+
+
+def few_takes(M: int, w: torch.Tensor, x_dtype) -> bool:
+    """Whether the few-row tcgen05 matrix product takes this product: bfloat16 operands, 17 .. 128 rows,
+    an inner size that is a multiple of 8 (16-byte rows for TMA), a matrix of TC_FEW_MIN_BYTES or more."""
+    N, K = w.shape
+    return (TC_FEW and w.dtype == torch.bfloat16 and x_dtype == torch.bfloat16 and w.is_contiguous()
+            and SKINNY_MAX_ROWS < M <= FEW_MAX_ROWS and N >= 8 and K >= 8 and K % 8 == 0 and w.data_ptr() % 16 == 0
+            and N * K * 2 >= TC_FEW_MIN_BYTES)
+
+
+def gemm_tcgen05_few(x: torch.Tensor, w: torch.Tensor, epi: int = EPI_BF16, out: Optional[torch.Tensor] = None,
+                     bias: Optional[torch.Tensor] = None, cluster: int = 0) -> torch.Tensor:
+    """``x [M,K] @ w [N,K]^T`` for at most 128 rows on the tcgen05 tensor cores with the operands swapped
+    (128 rows of ``w`` per MMA, the tokens on its N side); ``epi`` and ``out`` as in :func:`gemm_tcgen05`.
+    ``cluster``: blocks that share a tile along K (0: the kernel chooses; 1, 2, 4, 8: where that fits)."""
+    _cuda_contig(x, "x", torch.bfloat16)
+    _cuda_contig(w, "w", torch.bfloat16)
+    M, K = x.shape
+    N, K2 = w.shape
+    _need(K == K2, f"inner sizes differ: {K} vs {K2}")
+    if epi == EPI_RESID:
+        _need(out is not None and out.dtype == torch.float32 and tuple(out.shape) == (M, N), "residual must be float32 [M,N]")
+        _cuda_contig(out, "out")
+    elif epi == EPI_SWIGLU:
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    else:
+        out = torch.empty((M, N), dtype=torch.bfloat16 if epi == EPI_BF16 else torch.float32, device=x.device)
+    _lib.check(_lib.library().gesso_gemm_tcgen05_few(_p(x), _p(w), _p(out), _p(bias), M, N, K, epi, int(cluster),
+                                                     _p(tc_status_tensor(x.device)), _stream()), "gemm_tcgen05_few")
+    return out
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epi: int = EPI_BF16, out: Optional[torch.Tensor] = None,

@@ -134,3 +134,14 @@ def test_full_width_replay(schedule, dtype, wide, loaded, tmp_path):
             f"{schedule}/{dtype}: request {rid} position {pos}: max error {err:.3e} > {TOL[dtype]:.1e} * {scale:.2f}"
         worst = max(worst, err / scale)
     print(f"full width {schedule}/{dtype}: worst {worst:.3e}")
+
+
+@pytest.mark.parametrize("schedule", ["portions", "mixed"])
+def test_full_width_replay_few_row_product(schedule, wide, loaded, tmp_path, monkeypatch):
+    """The same replays with the optional few-row tcgen05 product serving every matrix of the steps of
+    17 .. 128 tokens (portions of 33, 30 and 100 tokens, 150 + ... mixed steps)."""
+    from gesso_b200 import ops
+    monkeypatch.setattr(ops, "TC_FEW", True)
+    monkeypatch.setattr(ops, "TC_FEW_MIN_BYTES", 0)
+    test_full_width_replay(schedule, "bfloat16", wide, loaded, tmp_path)
+    ops.check_tc_status()

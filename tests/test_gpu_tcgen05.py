@@ -50,6 +50,55 @@ def test_tcgen05_gemm(M, N, K, pair, monkeypatch):
     ops.check_tc_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(17, 128, 64), (32, 128, 64), (64, 256, 256), (17, 64, 96), (64, 2048, 2048),
+                                   (64, 6144, 2048), (64, 16384, 2048), (64, 2048, 8192), (100, 1536, 6912),
+                                   (128, 2048, 2048), (33, 504, 200), (48, 72, 72), (128, 65536, 2048), (20, 3072, 1024),
+                                   (96, 264, 8192), (1, 128, 64), (5, 2048, 512)])
+def test_tcgen05_few_rows(M, N, K):
+    """The few-row product (W on the MMA's M side): every epilogue, tiles that one block finishes alone
+    and tiles summed from the parts of a cluster's blocks, ragged sizes in every direction."""
+    from gesso_b200 import ops
+    x, w, want = case(M, N, K)
+    for _ in range(2):
+        got = ops.gemm_tcgen05_few(x, w, ops.EPI_F32)
+        ops.check_tc_status()
+        assert rel_err(got, want) < 3e-5
+    assert torch.equal(got, ops.gemm_tcgen05_few(x, w, ops.EPI_F32))       # the order of the sum is fixed
+    assert rel_err(ops.gemm_tcgen05_few(x, w, ops.EPI_BF16), want) < BF16_EPS
+    h = torch.randn(M, N, device=DEV)
+    bias = torch.randn(N, device=DEV)
+    h0 = h.clone()
+    ops.gemm_tcgen05_few(x, w, ops.EPI_RESID, out=h, bias=bias)
+    assert rel_err(h, h0.double() + want + bias.double()) < 3e-5
+    if N % 16 == 0:
+        F = N // 2
+        a = ops.gemm_tcgen05_few(x, ops.pack_gate_up(w[:F].contiguous(), w[F:].contiguous()), ops.EPI_SWIGLU)
+        gg, uu = want[:, :F], want[:, F:]
+        assert rel_err(a, (gg / (1 + torch.exp(-gg))) * uu) < BF16_EPS
+    ops.check_tc_status()
+
+
+@pytest.mark.parametrize("cluster", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_tcgen05_few_rows_clusters(cluster):
+    """Every cluster size on one product; one large weight far along K and one near its start must each
+    be counted once, whichever block of the cluster multiplies that part of K."""
+    from gesso_b200 import ops
+    M, N, K = 40, 256, 8192
+    x = torch.ones(M, K, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(N, K, dtype=torch.bfloat16, device=DEV)
+    w[130, 8000] = 64.0
+    w[3, 70] = -2.0
+    got = ops.gemm_tcgen05_few(x, w, ops.EPI_F32, cluster=cluster)
+    ops.check_tc_status()
+    want = torch.zeros(M, N, device=DEV)
+    want[:, 130], want[:, 3] = 64.0, -2.0
+    assert torch.equal(got, want)
+    x, w, want = case(100, 2048, 6912)
+    got = ops.gemm_tcgen05_few(x, w, ops.EPI_F32, cluster=cluster)
+    ops.check_tc_status()
+    assert rel_err(got, want) < 3e-5
+
+
 # ---- flash prefill attention on tcgen05 --------------------------------------------------------------
 @pytest.mark.parametrize("window", [None, 50, 200])
 @pytest.mark.parametrize("nh,nkv,page", [(8, 2, 16), (32, 8, 16), (4, 2, 32), (8, 1, 16), (16, 1, 32)])
