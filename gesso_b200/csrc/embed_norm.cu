@@ -133,11 +133,87 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, cons
     }
 }
 
+// The same for steps of many rows: a warp per row, the whole row in registers (VPL float4 per lane), no
+// block-wide barrier between the sum of squares and the scaling; four rows per block.
+#define NORM_WARP_ROWS 4
+template <typename TD, typename TO, int VPL>
+__global__ void __launch_bounds__(NORM_WARP_ROWS * 32)
+add_rmsnorm_warp_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ delta_bias,
+                        const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
+                        int n_rows) {
+    constexpr int H = VPL * 128;
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * NORM_WARP_ROWS + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const int src = rows ? rows[r] : r;
+    float* hrow = h + (size_t)src * H;
+    const TD* drow = delta ? delta + (size_t)src * H : nullptr;
+    float4 x[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) x[v] = load4(hrow + (v * 32 + lane) * 4);
+    if (drow) {
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int i = (v * 32 + lane) * 4;
+            float4 d = load4(drow + i);
+            if (delta_bias) {
+                const float4 b = load4(delta_bias + i);
+                d.x += b.x; d.y += b.y; d.z += b.z; d.w += b.w;
+            }
+            x[v].x += d.x; x[v].y += d.y; x[v].z += d.z; x[v].w += d.w;
+            if (!rows) store4(hrow + i, x[v]);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) ss += x[v].x * x[v].x + x[v].y * x[v].y + x[v].z * x[v].z + x[v].w * x[v].w;
+    ss = warp_sum(ss);
+    const float denom = sqrtf(ss / (float)H + eps);
+    TO* orow = out + (size_t)r * H;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+        const int i = (v * 32 + lane) * 4;
+        const float4 ww = w ? load4(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        store4(orow + i, make_float4((x[v].x / denom) * ww.x, (x[v].y / denom) * ww.y, (x[v].z / denom) * ww.z,
+                                     (x[v].w / denom) * ww.w));
+    }
+}
+
+template <typename TD, typename TO>
+static bool launch_norm_warp(float* h, const void* delta, const float* delta_bias, const float* w, float eps, void* out,
+                             const int* rows, int n_rows, int H, cudaStream_t stream) {
+    const int grid = (n_rows + NORM_WARP_ROWS - 1) / NORM_WARP_ROWS;
+#define WLAUNCH(VPL)                                                                                         \
+    add_rmsnorm_warp_kernel<TD, TO, VPL><<<grid, NORM_WARP_ROWS * 32, 0, stream>>>(h, (const TD*)delta, delta_bias, w, \
+                                                                                   eps, (TO*)out, rows, n_rows)
+    switch (H) {
+        case 512: WLAUNCH(4); return true;
+        case 1024: WLAUNCH(8); return true;
+        case 1536: WLAUNCH(12); return true;
+        case 2048: WLAUNCH(16); return true;
+        case 2560: WLAUNCH(20); return true;
+        default: return false;
+    }
+#undef WLAUNCH
+}
+
 GESSO_API int gesso_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* delta_bias,
                                 const float* w, float eps, void* out, int out_dtype, const int* rows,
                                 int n_rows, int H, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return GESSO_ERR_BAD_SIZE;
+    if (n_rows >= 256) {      // many rows: a warp per row, for the widths it is compiled for
+        bool done = false;
+        if (delta_dtype == GESSO_F32 && out_dtype == GESSO_F32)
+            done = launch_norm_warp<float, float>(h, delta, delta_bias, w, eps, out, rows, n_rows, H, stream);
+        else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_BF16)
+            done = launch_norm_warp<bf16, bf16>(h, delta, delta_bias, w, eps, out, rows, n_rows, H, stream);
+        else if (delta_dtype == GESSO_F32 && out_dtype == GESSO_BF16)
+            done = launch_norm_warp<float, bf16>(h, delta, delta_bias, w, eps, out, rows, n_rows, H, stream);
+        else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_F32)
+            done = launch_norm_warp<bf16, float>(h, delta, delta_bias, w, eps, out, rows, n_rows, H, stream);
+        if (done) return launch_status();
+    }
     if (H % 4 == 0 && H <= 4 * NORM_VEC_THREADS * NORM_VEC_MAX) {
 #define VLAUNCH(TD, TO)                                                                             \
     add_rmsnorm_vec_kernel<TD, TO><<<n_rows, NORM_VEC_THREADS, 0, stream>>>(h, (const TD*)delta, delta_bias, w, eps, \

@@ -54,16 +54,21 @@ class DeviceCache:
             # not meet a NaN left in fresh memory
             self.kv.append(torch.zeros((len(owners), 2, max(pages, 1), need.n_kv_heads, page_size,
                                         need.head_dim), dtype=dt, device=dev))
+        # One buffer for all fixed-size state, a slot's entries side by side (each padded to 128 bytes),
+        # so that a fresh slot is zeroed by one fill; entry i is the view [slots, *shape] into it.
+        sizes = [int(np.prod(need.shape)) for need, _ in plan.state_entries]
+        offsets = np.concatenate([[0], np.cumsum([-(-n // 32) * 32 for n in sizes])]).astype(int)
+        self._state_flat = torch.zeros((max(num_slots, 1), max(int(offsets[-1]), 1)), dtype=torch.float32, device=dev)
         self.state: List[torch.Tensor] = [
-            torch.zeros((max(num_slots, 1),) + tuple(need.shape), dtype=torch.float32, device=dev)
-            for need, _ in plan.state_entries]
+            self._state_flat[:, off:off + n].view((self._state_flat.shape[0],) + tuple(need.shape))
+            for (need, _), off, n in zip(plan.state_entries, offsets, sizes)]
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.kv + self.state)
+        return sum(t.numel() * t.element_size() for t in self.kv + [self._state_flat])
 
     def zero_slot(self, slot: int) -> None:
-        for s in self.state:
-            s[slot].zero_()
+        if self.state:
+            self._state_flat[slot].zero_()
 
 
 class Engine:

@@ -55,6 +55,35 @@ def test_embed_and_add_rmsnorm(dtype, H):
     assert rel_err(out, P.rmsnorm(h1.double().cpu(), w.double().cpu(), 1e-5)) < 2e-6
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,N", [(512, 257), (1024, 300), (1536, 1001), (2048, 2040), (2560, 256), (2048, 255), (640, 400)])
+def test_add_rmsnorm_many_rows(dtype, H, N):
+    """Steps of 256 rows and more use a warp per row at the widths that kernel is compiled for (a number
+    of rows that is no multiple of four; 255 rows and width 640 take the other kernels)."""
+    from gesso_b200 import ops
+    g = torch.Generator().manual_seed(H + N)
+    h = torch.randn(N, H, generator=g).to(DEV)
+    h[N // 2] *= 100.0                                   # one row far larger than the others
+    delta = torch.randn(N, H, generator=g).to(dtype).to(DEV)
+    bias = torch.randn(H, generator=g).to(DEV)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(DEV)
+    h0 = h.clone()
+    out = ops.add_rmsnorm(h, delta, bias, w, 1e-5, dtype)
+    want_h = h0.double() + delta.double() + bias.double()
+    assert rel_err(h, want_h) < 1e-6
+    want = P.rmsnorm(want_h.cpu(), w.double().cpu(), 1e-5)
+    err = ((out.double().cpu() - want).abs() / want.abs().clamp_min(1.0)).max()
+    assert float(err) < (2e-6 if dtype == torch.float32 else BF16_EPS)
+    rows = i32(list(range(N - 1, -1, -1)))               # every row, backwards; h untouched
+    h1 = h.clone()
+    sel = ops.add_rmsnorm(h, delta, None, w, 1e-6, torch.float32, rows=rows)
+    assert torch.equal(h, h1)
+    want = P.rmsnorm((h1.double() + delta.double()).cpu().flip(0), w.double().cpu(), 1e-6)
+    assert rel_err(sel, want) < 2e-6
+    out = ops.add_rmsnorm(h, None, None, w, 1e-5, torch.float32)
+    assert rel_err(out, P.rmsnorm(h1.double().cpu(), w.double().cpu(), 1e-5)) < 2e-6
+
+
 def test_rmsnorm_rows_per_head():
     from gesso_b200 import ops
     x = torch.randn(11, 5, 24, device=DEV)
