@@ -77,10 +77,24 @@ argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict
     const float* r = logits + (size_t)row * V;
     float best = -INFINITY;
     int bi = 0x7fffffff, bad = 0;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        const float v = r[i];
-        if (!isfinite(v)) bad = 1;
-        if (v > best) { best = v; bi = i; }
+    pdl_launch_dependents();
+    pdl_wait();                 // the logits come from the kernel before
+    if (((V | per) & 3) == 0 && (((size_t)logits) & 15) == 0) {
+        // 16-byte reads; a thread meets its elements in ascending order, so ">" keeps the lowest id of a tie
+        for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(r + i);
+            if (!isfinite(v.x) || !isfinite(v.y) || !isfinite(v.z) || !isfinite(v.w)) bad = 1;
+            if (v.x > best) { best = v.x; bi = i; }
+            if (v.y > best) { best = v.y; bi = i + 1; }
+            if (v.z > best) { best = v.z; bi = i + 2; }
+            if (v.w > best) { best = v.w; bi = i + 3; }
+        }
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            const float v = r[i];
+            if (!isfinite(v)) bad = 1;
+            if (v > best) { best = v; bi = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -106,6 +120,8 @@ argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict
 __global__ void argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx,
                                     int* __restrict__ ids, int* __restrict__ nonfinite) {
     const int row = blockIdx.x, lane = threadIdx.x;     // 32 threads, one per slice
+    pdl_launch_dependents();
+    pdl_wait();
     float best = pval[row * ARGMAX_SPLIT + lane];
     int bi = pidx[(row * ARGMAX_SPLIT + lane) * 2], bad = pidx[(row * ARGMAX_SPLIT + lane) * 2 + 1];
 #pragma unroll
@@ -127,8 +143,10 @@ GESSO_API int gesso_argmax_rows(const float* logits, int n_rows, int V, int* ids
         argmax_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, ids, nonfinite);
         return launch_status();
     }
-    argmax_partial_kernel<<<dim3(ARGMAX_SPLIT, n_rows), 256, 0, stream>>>(logits, V, scratch_val, scratch_idx);
-    argmax_final_kernel<<<n_rows, 32, 0, stream>>>(scratch_val, scratch_idx, ids, nonfinite);
+    launch_pdl(argmax_partial_kernel, dim3(ARGMAX_SPLIT, n_rows), dim3(256), 0, stream, logits, V, scratch_val,
+               scratch_idx);
+    launch_pdl(argmax_final_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)scratch_val,
+               (const int*)scratch_idx, ids, nonfinite);
     return launch_status();
 }
 

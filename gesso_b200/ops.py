@@ -338,10 +338,16 @@ _skinny_ws = {}
 SKINNY_WS_BYTES = 16 * 1024 + 4 * 1024 * 1024
 
 
+def _device_index(device) -> int:
+    """``cuda`` and ``cuda:0`` name the same device: workspaces are kept by index."""
+    d = torch.device(device)
+    return d.index if d.index is not None else torch.cuda.current_device()
+
+
 def _skinny_workspace(device) -> torch.Tensor:
     """Tickets and partial tiles for skinny products that are split along K: one zeroed buffer per
     device and stream (launches on one stream run in order, so they can share it)."""
-    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
+    key = (_device_index(device), torch.cuda.current_stream(device).cuda_stream)
     ws = _skinny_ws.get(key)
     if ws is None:
         ws = _skinny_ws[key] = torch.zeros((SKINNY_WS_BYTES,), dtype=torch.uint8, device=device)
@@ -555,7 +561,7 @@ _tc_status = {}
 
 def tc_status_tensor(device) -> torch.Tensor:
     """One int32 per device that the tcgen05 kernel writes when one of its bounded waits runs out."""
-    key = str(device)
+    key = _device_index(device)
     if key not in _tc_status:
         _tc_status[key] = torch.zeros((1,), dtype=torch.int32, device=device)
     return _tc_status[key]

@@ -29,6 +29,15 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture(autouse=True)
+def seeded(request):
+    """Every test draws its random inputs from a seed of its own name, whatever ran before it."""
+    import zlib
+    import torch
+    torch.manual_seed(zlib.crc32(request.node.nodeid.encode()))
+    yield
+
+
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
     """Tiny model folders (config.json + model.safetensors), made once per session in a temp folder."""
