@@ -37,7 +37,7 @@ _SIGNATURES = {
     "gesso_skinny_gemm": [P, P, P, F, P, P, P, I, I, I, I, P, LL, P],
     "gesso_gemm_f32": [P, I, P, I, P, P, I, I, I, P],
     "gesso_argmax_rows": [P, I, I, P, P, P, P, P],
-    "gesso_sample_rows": [P, I, I, P, P, P, P, P, P],
+    "gesso_sample_rows": [P, I, I, P, P, P, P, P, P, P],
 }
 
 _REFUSALS = {-2: "unsupported dtype", -3: "a size this kernel does not take",

@@ -12,7 +12,10 @@
 // from the host's splitmix64 stream of the request, so a request's tokens do not depend on the
 // batch it is in.  No sort is needed: the kept set and the drawn id are both "first position in
 // descending order at which the running mass crosses a target", which is found by narrowing the
-// 64-bit pattern of the weight eight bits at a time (positive doubles order like their bits).
+// 64-bit pattern of the weight eight bits at a time (positive doubles order like their bits).  The
+// weights are computed once into a scratch row (float64, read back from L2 by the later passes).  A
+// cluster of eight blocks works on a row, each on an eighth of the ids; what the blocks must agree on
+// (the total, a byte pass's histogram) they read from one another's shared memory.
 #include <math.h>
 
 #include "common.cuh"
@@ -172,39 +175,164 @@ __device__ __forceinline__ double weight_of(float logit, float hi, double inv_t)
     return exp(((double)logit - (double)hi) * inv_t);
 }
 
+// The weight of element i: from the row's cache of weights (written by the first pass) if there is one.
+struct Weights {
+    const float* row;
+    const double* cache;
+    float hi;
+    double inv_t;
+    __device__ __forceinline__ double operator()(int i) const {
+        return cache ? __ldcg(cache + i) : weight_of(row[i], hi, inv_t);
+    }
+};
+
+// ---- a cluster of SAMPLE_CLUSTER blocks per row: block r works on the r-th slice of the ids ----------
+#define SAMPLE_CLUSTER 8      // at most; fewer blocks per row when there are many rows (see the launch)
+#define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+
+__device__ __forceinline__ unsigned sample_blocks() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ unsigned sample_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// every warp arrives as one: its threads have converged before
+__device__ __forceinline__ void sample_cluster_sync() {
+    __syncthreads();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// reads of another block's shared memory (the address of the same object in block `rank`)
+__device__ __forceinline__ unsigned peer_addr(const void* p, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"((unsigned)__cvta_generic_to_shared(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ double peer_f64(const void* p, unsigned rank) {
+    double v;
+    asm volatile("ld.shared::cluster.f64 %0, [%1];\n" : "=d"(v) : "r"(peer_addr(p, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ int peer_i32(const void* p, unsigned rank) {
+    int v;
+    asm volatile("ld.shared::cluster.s32 %0, [%1];\n" : "=r"(v) : "r"(peer_addr(p, rank)) : "memory");
+    return v;
+}
+
+// One byte pass's histogram: mass, elements and highest id per byte value.
+struct ByteHist {
+    double mass[256];
+    int count[256];
+    int last[256];
+};
+
+struct CrossShared {
+    ByteHist mine[2];          // this block's slice (two copies: peers may still read the pass before)
+    ByteHist all;              // the whole row: the blocks' histograms added in rank order
+    double red[33];
+    double exchange[2];        // a value each block shows its peers (two copies, as above)
+    unsigned long long prefix;
+    double above, mass;
+    int id, done;
+    int cnt[SAMPLE_THREADS];
+};
+
 // Finds, in descending order of weight (ties: ascending id), the first element at which the
 // running mass exceeds `target` (strict: running > target) or reaches it (running >= target).
-// Returns through shared memory: the element's id and the running mass up to and including it.
-// Every thread of the block must call it.  hist[256] doubles, red[33] doubles of shared memory.
+// Returns the element's id and the running mass up to and including it.  Every thread of every
+// block of the cluster must call it; all blocks return the same result.
+//
+// The weight's bit pattern is narrowed from the top byte down.  `prefix` holds the bytes fixed so
+// far; `above` is the mass of all weights whose pattern is larger than any with this prefix.  Each
+// warp keeps a histogram of its own over its part of the block's slice: in a step of 32 elements
+// the lanes with the same byte value form a group (match.any), the group's first lane adds the
+// group's weights up in lane order and adds the sum to the warp's histogram (all 32 lanes with one
+// value, the usual case in the top bytes, take a butterfly instead).  The warps' histograms are
+// added in warp order, the blocks' in rank order (read from the peers' shared memory), so the sums
+// do not depend on timing.  As soon as the chosen value holds a single element, that element is
+// the answer and the remaining bytes are skipped.
 struct CrossResult { int id; double mass; };
 
-__device__ CrossResult descending_cross(const float* __restrict__ row, int V, float hi, double inv_t,
-                                        double target, bool strict, double* hist, double* red,
-                                        unsigned long long* s_prefix, double* s_above, int* s_id,
-                                        double* s_mass) {
-    // Narrow the weight's bit pattern from the top byte down.  `prefix` holds the bytes fixed so
-    // far; `above` is the mass of all weights whose pattern is larger than any with this prefix.
-    if (threadIdx.x == 0) { *s_prefix = 0ull; *s_above = 0.0; }
+__device__ CrossResult descending_cross(const Weights& W, int V, int lo, int hi_id, double target, bool strict,
+                                        CrossShared& sh, ByteHist* wh_all, unsigned& round) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned C = sample_blocks();
+    ByteHist& wh = wh_all[warp];
+    if (threadIdx.x == 0) { sh.prefix = 0ull; sh.above = 0.0; sh.done = 0; }
     __syncthreads();
     for (int byte = 7; byte >= 0; --byte) {
-        for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0.0;
-        __syncthreads();
-        const unsigned long long prefix = *s_prefix;
+        for (int b = lane; b < 256; b += 32) { wh.mass[b] = 0.0; wh.count[b] = 0; wh.last[b] = -1; }
+        __syncwarp();
+        const unsigned long long prefix = sh.prefix;
         const int shift = byte * 8;
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
-            const double w = weight_of(row[i], hi, inv_t);
+        for (int base = lo + warp * 32; base < hi_id; base += SAMPLE_THREADS) {
+            const int i = base + lane;
+            const bool valid = i < hi_id;
+            const double w = valid ? W(i) : 0.0;
             const unsigned long long bits = (unsigned long long)__double_as_longlong(w);
-            const bool match = byte == 7 || ((bits >> (shift + 8)) == (prefix >> (shift + 8)));
-            if (match) atomicAdd(&hist[(bits >> shift) & 0xff], w);
+            const bool match = valid && (byte == 7 || ((bits >> (shift + 8)) == (prefix >> (shift + 8))));
+            const int b = match ? (int)((bits >> shift) & 0xff) : -1;
+            const int b0 = __shfl_sync(0xffffffffu, b, 0);
+            if (__all_sync(0xffffffffu, b == b0)) {
+                if (b0 < 0) continue;                        // nobody matches
+                double sum = w;                              // fixed butterfly: the same sum every time
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (lane == 0) { wh.mass[b0] += sum; wh.count[b0] += 32; wh.last[b0] = base + 31; }
+            } else {
+                const unsigned grp = __match_any_sync(0xffffffffu, b);
+                unsigned m = match ? grp : 0u;
+                double sum = 0.0;
+                while (__any_sync(0xffffffffu, m != 0u)) {
+                    const int src = m ? __ffs(m) - 1 : lane;
+                    const double v = __shfl_sync(0xffffffffu, w, src);
+                    if (m) { sum += v; m &= m - 1; }
+                }
+                if (match && lane == __ffs(grp) - 1) {
+                    wh.mass[b] += sum;
+                    wh.count[b] += __popc(grp);
+                    wh.last[b] = base + (31 - __clz(grp));     // bases ascend: the last write is the highest id
+                }
+            }
+            __syncwarp();
         }
         __syncthreads();
+        ByteHist& mine = sh.mine[round & 1];
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+            double mass = 0.0;
+            int count = 0, last = -1;
+            for (int k = 0; k < SAMPLE_WARPS; ++k) {
+                mass += wh_all[k].mass[b];
+                count += wh_all[k].count[b];
+                last = max(last, wh_all[k].last[b]);
+            }
+            mine.mass[b] = mass; mine.count[b] = count; mine.last[b] = last;
+        }
+        sample_cluster_sync();                     // every block's histogram of this pass is written
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+            double mass = 0.0;
+            int count = 0, last = -1;
+            for (unsigned r = 0; r < C; ++r) {
+                mass += peer_f64(&mine.mass[b], r);
+                count += peer_i32(&mine.count[b], r);
+                last = max(last, peer_i32(&mine.last[b], r));
+            }
+            sh.all.mass[b] = mass; sh.all.count[b] = count; sh.all.last[b] = last;
+        }
+        ++round;
+        __syncthreads();
         if (threadIdx.x == 0) {
-            double run = *s_above;
+            double run = sh.above;
             int pick = -1, last_occupied = 0;
             double run_before_last = run;
             for (int b = 255; b >= 0; --b) {
-                if (hist[b] <= 0.0) continue;
-                const double next = run + hist[b];
+                if (sh.all.count[b] <= 0) continue;
+                const double next = run + sh.all.mass[b];
                 const bool crossed = strict ? (next > target) : (next >= target);
                 if (crossed) { pick = b; break; }
                 last_occupied = b;
@@ -213,15 +341,28 @@ __device__ CrossResult descending_cross(const float* __restrict__ row, int V, fl
             }
             // if nothing crossed (rounding), the walk ends in the smallest occupied bucket
             if (pick < 0) { pick = last_occupied; run = run_before_last; }
-            *s_above = run;
-            *s_prefix = prefix | ((unsigned long long)pick << shift);
+            sh.above = run;
+            sh.prefix = prefix | ((unsigned long long)pick << shift);
+            if (sh.all.count[pick] == 1) {        // one element left: it is the answer
+                sh.id = sh.all.last[pick];
+                sh.mass = run + sh.all.mass[pick];
+                sh.done = 1;
+            }
         }
         __syncthreads();
+        if (sh.done) {
+            CrossResult r;
+            r.id = sh.id;
+            r.mass = sh.mass;
+            __syncthreads();
+            return r;
+        }
     }
-    // All weights equal to the found pattern tie; they are taken in ascending id order.
-    const unsigned long long pat = *s_prefix;
+    // All weights equal to the found pattern tie; they are taken in ascending id order.  Every block
+    // does this part over the whole row by itself (it is rare, and all arrive at the same answer).
+    const unsigned long long pat = sh.prefix;
     const double wv = __longlong_as_double((long long)pat);
-    const double above = *s_above;
+    const double above = sh.above;
     // how many of the tied elements are needed for the running mass to cross
     long long need;
     if (wv > 0.0) {
@@ -237,61 +378,79 @@ __device__ CrossResult descending_cross(const float* __restrict__ row, int V, fl
     const int i0 = threadIdx.x * chunk, i1 = min(V, i0 + chunk);
     int cnt = 0;
     for (int i = i0; i < i1; ++i)
-        if ((unsigned long long)__double_as_longlong(weight_of(row[i], hi, inv_t)) == pat) ++cnt;
-    // inclusive scan of cnt over threads (hist reused as int scratch is avoided: use red as doubles)
-    __shared__ int s_cnt[SAMPLE_THREADS];
-    s_cnt[threadIdx.x] = cnt;
+        if ((unsigned long long)__double_as_longlong(W(i)) == pat) ++cnt;
+    sh.cnt[threadIdx.x] = cnt;
     __syncthreads();
     if (threadIdx.x == 0) {
         long long run = 0, total = 0;
-        for (int t = 0; t < (int)blockDim.x; ++t) total += s_cnt[t];
+        for (int t = 0; t < (int)blockDim.x; ++t) total += sh.cnt[t];
         if (need > total) need = total;          // rounding: take the last tie
         int owner = 0;
         long long before = 0;
         for (int t = 0; t < (int)blockDim.x; ++t) {
-            if (run + s_cnt[t] >= need) { owner = t; before = run; break; }
-            run += s_cnt[t];
+            if (run + sh.cnt[t] >= need) { owner = t; before = run; break; }
+            run += sh.cnt[t];
         }
-        *s_id = owner;
-        *s_mass = above + (double)need * wv;
-        red[0] = (double)(need - before);        // rank inside the owner's chunk
+        sh.id = owner;
+        sh.mass = above + (double)need * wv;
+        sh.red[0] = (double)(need - before);     // rank inside the owner's chunk
     }
     __syncthreads();
-    const int owner = *s_id;
-    const long long rank = (long long)red[0];
+    const int owner = sh.id;
+    const long long rank = (long long)sh.red[0];
     __syncthreads();
     if ((int)threadIdx.x == owner) {
         long long seen = 0;
         int found = i1 - 1;
         for (int i = i0; i < i1; ++i)
-            if ((unsigned long long)__double_as_longlong(weight_of(row[i], hi, inv_t)) == pat) {
+            if ((unsigned long long)__double_as_longlong(W(i)) == pat) {
                 if (++seen == rank) { found = i; break; }
             }
-        *s_id = found;
+        sh.id = found;
     }
     __syncthreads();
     CrossResult r;
-    r.id = *s_id;
-    r.mass = *s_mass;
+    r.id = sh.id;
+    r.mass = sh.mass;
     __syncthreads();
     return r;
 }
 
-// One block per row.  u[row] in [0,1).  top_p[row] in (0,1]; temperature[row] > 0.
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+// Every block shows `v` to its peers; returns the values of all blocks (the same in every block).
+__device__ void cluster_gather(double v, double (&out)[SAMPLE_CLUSTER], CrossShared& sh, unsigned& round) {
+    double* slot = &sh.exchange[round & 1];
+    if (threadIdx.x == 0) *slot = v;
+    sample_cluster_sync();
+    const unsigned C = sample_blocks();
+    for (unsigned r = 0; r < SAMPLE_CLUSTER; ++r) out[r] = r < C ? peer_f64(slot, r) : 0.0;
+    ++round;
+    sample_cluster_sync();      // all have read: a block may leave after this without a peer still reading it
+}
+
+// A cluster of 1, 2, 4 or 8 blocks per row (the launch's cluster size).  u[row] in [0,1).  top_p[row] in (0,1]; temperature[row] > 0.
+// wcache: [rows, V] float64 scratch for the weights (computed once, read by the later passes), or null
+// (every pass then computes them again).
+__global__ void __launch_bounds__(SAMPLE_THREADS, 1)
 sample_rows_kernel(const float* __restrict__ logits, int V, const double* __restrict__ temperature,
                    const double* __restrict__ top_p, const double* __restrict__ u, int* __restrict__ ids,
-                   int* __restrict__ nonfinite) {
-    __shared__ double hist[256];
-    __shared__ double red[33];
+                   int* __restrict__ nonfinite, double* __restrict__ wcache) {
+    extern __shared__ unsigned char sample_smem[];
+    ByteHist* wh_all = reinterpret_cast<ByteHist*>(sample_smem);      // one histogram per warp
+    __shared__ CrossShared sh;
     __shared__ float s_max[33];
-    __shared__ unsigned long long s_prefix;
-    __shared__ double s_above, s_mass;
-    __shared__ int s_id, s_bad;
-    const int rowi = blockIdx.x;
+    __shared__ double s_part[SAMPLE_THREADS];
+    __shared__ int s_bad;
+    const int C = (int)sample_blocks();
+    const int rowi = blockIdx.x / C;
+    const unsigned rank = sample_rank();
+    unsigned round = 0;                          // exchanges with the peers so far (picks the copy to write)
     const float* row = logits + (size_t)rowi * V;
+    // this block's slice of the ids, in whole steps of 32
+    const int per = ((V + C - 1) / C + 31) / 32 * 32;
+    const int lo = min(V, (int)rank * per), hi_id = min(V, lo + per);
     if (threadIdx.x == 0) s_bad = 0;
     __syncthreads();
+    // the maximum and the check for non-finite values: every block over the whole row
     float hi = -INFINITY;
     int bad = 0;
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
@@ -310,49 +469,68 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const double* __rest
     }
     __syncthreads();
     hi = s_max[32];
-    if (s_bad) {
-        if (threadIdx.x == 0) { nonfinite[rowi] = 1; ids[rowi] = 0; }
+    if (s_bad) {                                 // the same in every block: nobody waits at a barrier below
+        if (threadIdx.x == 0 && rank == 0) { nonfinite[rowi] = 1; ids[rowi] = 0; }
         return;
     }
     const double inv_t = 1.0 / temperature[rowi];
+    double* row_cache = wcache ? wcache + (size_t)rowi * V : nullptr;
     double part = 0.0;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) part += weight_of(row[i], hi, inv_t);
-    const double total = block_sum_d(part, red);
+    for (int i = lo + threadIdx.x; i < hi_id; i += blockDim.x) {
+        const double w = weight_of(row[i], hi, inv_t);
+        if (row_cache) __stcg(row_cache + i, w);
+        part += w;
+    }
+    const double slice_total = block_sum_d(part, sh.red);
+    double totals[SAMPLE_CLUSTER];
+    cluster_gather(slice_total, totals, sh, round);       // its barrier also publishes the cached weights
+    double total = 0.0;
+    for (int r = 0; r < SAMPLE_CLUSTER; ++r) total += totals[r];
+    const Weights W = {row, row_cache, hi, inv_t};
     const double p = top_p[rowi];
     const double r01 = u[rowi];
 
     if (p >= 1.0) {
-        // walk in id order: thread chunks are contiguous id ranges
-        const int chunk = (V + blockDim.x - 1) / blockDim.x;
-        const int i0 = threadIdx.x * chunk, i1 = min(V, i0 + chunk);
+        // walk in id order: the slice that holds the draw, then its thread chunks, then its elements
+        const double r = r01 * total;
+        double run = 0.0;
+        int slice = -1;
+        for (int k = 0; k < SAMPLE_CLUSTER; ++k) {
+            if (r < run + totals[k]) { slice = k; break; }
+            run += totals[k];
+        }
+        if (slice < 0) {                         // rounding: the last id
+            if (threadIdx.x == 0 && rank == 0) { ids[rowi] = V - 1; nonfinite[rowi] = 0; }
+            return;
+        }
+        if ((int)rank != slice) return;
+        const int n = hi_id - lo;
+        const int chunk = (n + (int)blockDim.x - 1) / (int)blockDim.x;
+        const int i0 = min(hi_id, lo + (int)threadIdx.x * chunk), i1 = min(hi_id, i0 + chunk);
         double mine = 0.0;
-        for (int i = i0; i < i1; ++i) mine += weight_of(row[i], hi, inv_t);
-        __shared__ double s_part[SAMPLE_THREADS];
+        for (int i = i0; i < i1; ++i) mine += W(i);
         s_part[threadIdx.x] = mine;
         __syncthreads();
         if (threadIdx.x == 0) {
-            const double r = r01 * total;
-            double run = 0.0;
             int owner = -1;
             for (int t = 0; t < (int)blockDim.x; ++t) {
                 if (r < run + s_part[t]) { owner = t; break; }
                 run += s_part[t];
             }
-            s_id = owner;
-            s_above = run;
+            sh.id = owner;
+            sh.above = run;
         }
         __syncthreads();
-        const int owner = s_id;
-        if (owner < 0) {
-            if (threadIdx.x == 0) { ids[rowi] = V - 1; nonfinite[rowi] = 0; }
+        const int owner = sh.id;
+        if (owner < 0) {                         // rounding: the slice's last id
+            if (threadIdx.x == 0) { ids[rowi] = hi_id - 1; nonfinite[rowi] = 0; }
             return;
         }
         if ((int)threadIdx.x == owner) {
-            const double r = r01 * total;
-            double acc = s_above;
+            double acc = sh.above;
             int found = i1 - 1;
             for (int i = i0; i < i1; ++i) {
-                acc += weight_of(row[i], hi, inv_t);
+                acc += W(i);
                 if (r < acc) { found = i; break; }
             }
             ids[rowi] = found;
@@ -361,19 +539,53 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const double* __rest
         return;
     }
     // nucleus: kept mass = running mass at the first position where it reaches top_p * total
-    const CrossResult cut = descending_cross(row, V, hi, inv_t, p * total, false, hist, red, &s_prefix, &s_above,
-                                             &s_id, &s_mass);
+    const CrossResult cut = descending_cross(W, V, lo, hi_id, p * total, false, sh, wh_all, round);
     const double r = r01 * cut.mass;
-    const CrossResult pick = descending_cross(row, V, hi, inv_t, r, true, hist, red, &s_prefix, &s_above, &s_id,
-                                              &s_mass);
-    if (threadIdx.x == 0) { ids[rowi] = pick.id; nonfinite[rowi] = 0; }
+    const CrossResult pick = descending_cross(W, V, lo, hi_id, r, true, sh, wh_all, round);
+    if (threadIdx.x == 0 && rank == 0) { ids[rowi] = pick.id; nonfinite[rowi] = 0; }
+    sample_cluster_sync();                       // no block leaves while a peer may still read its shared memory
 }
 
+// wcache: n_rows * V doubles of scratch, or null.
 GESSO_API int gesso_sample_rows(const float* logits, int n_rows, int V, const double* temperature,
-                                const double* top_p, const double* u, int* ids, int* nonfinite,
+                                const double* top_p, const double* u, int* ids, int* nonfinite, double* wcache,
                                 cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0) return GESSO_ERR_BAD_SIZE;
-    sample_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, top_p, u, ids, nonfinite);
+    const size_t smem = sizeof(ByteHist) * SAMPLE_WARPS;
+    static bool configured = false;
+    static int max_clusters[SAMPLE_CLUSTER + 1];     // clusters of that many blocks the device runs at once
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(SAMPLE_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (!configured) {
+        if (cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        for (int c = 2; c <= SAMPLE_CLUSTER; c *= 2) {
+            attr[0].val.clusterDim.x = c;
+            cfg.gridDim = dim3(c);
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, sample_rows_kernel, &cfg) != cudaSuccess) {
+                cudaGetLastError();
+                n = 0;
+            }
+            max_clusters[c] = n;
+        }
+        configured = true;
+    }
+    // the most blocks per row with which all rows still run at the same time
+    int C = 1;
+    for (int c = SAMPLE_CLUSTER; c >= 2; c /= 2)
+        if (n_rows <= max_clusters[c]) { C = c; break; }
+    attr[0].val.clusterDim.x = C;
+    cfg.gridDim = dim3(n_rows * C);
+    cudaLaunchKernelEx(&cfg, sample_rows_kernel, logits, V, temperature, top_p, u, ids, nonfinite, wcache);
     return launch_status();
 }

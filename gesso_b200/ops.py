@@ -40,7 +40,9 @@ def _p(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of the current stream of the current device (the public accessor builds a Stream
+    # object and resolves the device by name: ten times the cost, paid once per kernel launch)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 def _need(cond: bool, msg: str) -> None:
@@ -49,10 +51,11 @@ def _need(cond: bool, msg: str) -> None:
 
 
 def _cuda_contig(t: torch.Tensor, name: str, dtype=None) -> None:
+    if t.is_cuda and t.is_contiguous() and (dtype is None or t.dtype == dtype):
+        return
     _need(t.is_cuda, f"{name} must be a CUDA tensor")
     _need(t.is_contiguous(), f"{name} must be contiguous")
-    if dtype is not None:
-        _need(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
+    _need(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
 
 
 # ---- embedding / norms ---------------------------------------------------------------------
@@ -347,7 +350,8 @@ def _device_index(device) -> int:
 def _skinny_workspace(device) -> torch.Tensor:
     """Tickets and partial tiles for skinny products that are split along K: one zeroed buffer per
     device and stream (launches on one stream run in order, so they can share it)."""
-    key = (_device_index(device), torch.cuda.current_stream(device).cuda_stream)
+    idx = _device_index(device)
+    key = (idx, torch._C._cuda_getCurrentRawStream(idx))
     ws = _skinny_ws.get(key)
     if ws is None:
         ws = _skinny_ws[key] = torch.zeros((SKINNY_WS_BYTES,), dtype=torch.uint8, device=device)
@@ -471,8 +475,10 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
     _need(temperature.numel() == R and top_p.numel() == R and u.numel() == R, "one parameter per row")
     ids = torch.empty((R,), dtype=torch.int32, device=logits.device)
     bad = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    # the weights of a row are computed once into this scratch and read back by the later passes
+    wcache = torch.empty((R, V), dtype=torch.float64, device=logits.device) if R * V <= (1 << 27) else None
     _lib.check(_lib.library().gesso_sample_rows(_p(logits), R, V, _p(temperature), _p(top_p), _p(u),
-                                                _p(ids), _p(bad), _stream()), "sample_rows")
+                                                _p(ids), _p(bad), _p(wcache), _stream()), "sample_rows")
     return ids, bad
 
 

@@ -622,6 +622,28 @@ def test_sampler_matches_the_plain_rule(V):
         assert got == want_host == want_plain
 
 
+@pytest.mark.parametrize("V", [503, 65536, 50001])
+@pytest.mark.parametrize("rows", [1, 20, 40, 100])
+def test_sampler_rows_do_not_depend_on_the_batch(V, rows):
+    """The kernel gives a row 8, 4, 2 or 1 blocks by the number of rows in the call; a row's id must be the
+    same whichever it is: the 12 rows checked against the plain rule above, repeated to `rows` rows."""
+    from gesso_b200 import ops
+    g = torch.Generator().manual_seed(V)
+    logits = 3.0 * torch.randn(12, V, generator=g)
+    logits[3] = 0.25
+    logits[4, 7] = 40.0
+    logits[5, :] = torch.round(logits[5, :])
+    t = torch.tensor([[0.7, 1.3, 0.05][i % 3] for i in range(12)], dtype=torch.float64)
+    p = torch.tensor([[1.0, 0.9, 0.5, 0.999][i % 4] for i in range(12)], dtype=torch.float64)
+    u = torch.rand(12, generator=g, dtype=torch.float64)
+    base, bad = ops.sample_rows(logits.to(DEV), t.to(DEV), p.to(DEV), u.to(DEV))
+    assert bad.tolist() == [0] * 12
+    idx = [i % 12 for i in range(rows)]
+    got, bad = ops.sample_rows(logits[idx].contiguous().to(DEV), t[idx].to(DEV), p[idx].to(DEV), u[idx].to(DEV))
+    assert bad.tolist() == [0] * rows
+    assert got.tolist() == [base.tolist()[i] for i in idx]
+
+
 def test_sampler_low_temperature_is_argmax_and_nucleus_keeps_the_top_set():
     from gesso_b200.sampling import SamplingParams, SplitMix64, select_tokens
     V = 1000
