@@ -170,12 +170,25 @@ add_rmsnorm_warp_kernel(float* __restrict__ h, const TD* __restrict__ delta, con
     ss = warp_sum(ss);
     const float denom = sqrtf(ss / (float)H + eps);
     TO* orow = out + (size_t)r * H;
+    if constexpr (sizeof(TO) == 2) {
+        // bfloat16 output: one reciprocal and a multiplication per element (the last bit of the float32
+        // quotient is far below the output's rounding); the float32 output keeps the division
+        const float inv = 1.f / denom;
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-        const int i = (v * 32 + lane) * 4;
-        const float4 ww = w ? load4(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
-        store4(orow + i, make_float4((x[v].x / denom) * ww.x, (x[v].y / denom) * ww.y, (x[v].z / denom) * ww.z,
-                                     (x[v].w / denom) * ww.w));
+        for (int v = 0; v < VPL; ++v) {
+            const int i = (v * 32 + lane) * 4;
+            const float4 ww = w ? load4(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+            store4(orow + i, make_float4((x[v].x * inv) * ww.x, (x[v].y * inv) * ww.y, (x[v].z * inv) * ww.z,
+                                         (x[v].w * inv) * ww.w));
+        }
+    } else {
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int i = (v * 32 + lane) * 4;
+            const float4 ww = w ? load4(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+            store4(orow + i, make_float4((x[v].x / denom) * ww.x, (x[v].y / denom) * ww.y, (x[v].z / denom) * ww.z,
+                                         (x[v].w / denom) * ww.w));
+        }
     }
 }
 
