@@ -26,6 +26,7 @@
 #include <math.h>
 
 #include "tcgen05.cuh"
+#include "tensor_map.cuh"
 
 #define FA_HD 64
 #define FA_BK 128
@@ -288,22 +289,6 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 }
 
 // ---- host side ------------------------------------------------------------------------------------------
-typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static FaEncodeFn fa_encode_fn() {
-    static FaEncodeFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (FaEncodeFn)p;
-    }
-    return fn;
-}
-
 GESSO_API int gesso_attention_tcgen05_takes(int hd, int page_size, int nh, int nkv) {
     if (hd != FA_HD || page_size < 16 || page_size % 16 != 0 || nkv <= 0 || nh % nkv != 0) return 0;
     const int G = nh / nkv;
@@ -319,7 +304,7 @@ GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages
                                               int window, float scale, int* status, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!gesso_attention_tcgen05_takes(FA_HD, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
-    FaEncodeFn fn = fa_encode_fn();
+    TensorMapEncodeFn fn = tensor_map_encoder();
     if (!fn) return GESSO_ERR_UNSUPPORTED;
     const int G = nh / nkv, TOK = 128 / G;
     CUtensorMap mq, mk, mv;

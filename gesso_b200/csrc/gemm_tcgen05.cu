@@ -25,6 +25,7 @@
 
 #include "tcgen05.cuh"
 #include "gemm_tcgen05_epilogue.cuh"
+#include "tensor_map.cuh"
 
 #define TC_BM 128
 #define TC_BK 64
@@ -161,36 +162,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---- host side ------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// A row-major [rows, K] bfloat16 matrix, tiles of box_rows x 64 elements, 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return GESSO_ERR_UNSUPPORTED;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(bf16)};
-    const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : GESSO_ERR_UNSUPPORTED;
-}
-
 GESSO_API int gesso_gemm_tcgen05_takes(int M, int N, int K) {
     // TMA: 16-byte aligned rows (K % 8); vector stores: N % 8 (bfloat16) / N % 4 (float32)
     return M >= 1 && N >= 8 && N % 8 == 0 && K >= 8 && K % 8 == 0;
@@ -223,9 +194,9 @@ GESSO_API int gesso_gemm_tcgen05(const void* A, const void* W, void* out, const 
     if (((size_t)A & 15) || ((size_t)W & 15) || ((size_t)out & 15)) return GESSO_ERR_BAD_SIZE;
     const bool wide = N % 256 == 0 || N >= 1024;
     CUtensorMap ma, mw;
-    int r = make_map(&ma, A, M, K, TC_BM);
+    int r = make_matrix_map(&ma, A, M, K, TC_BM);
     if (r) return r;
-    r = make_map(&mw, W, N, K, wide ? 256 : 128);
+    r = make_matrix_map(&mw, W, N, K, wide ? 256 : 128);
     if (r) return r;
 #define GO(BN, ST)                                                                                              \
     switch (epi) {                                                                                              \

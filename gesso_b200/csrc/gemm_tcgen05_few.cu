@@ -33,6 +33,7 @@
 
 #include "tcgen05.cuh"
 #include "gemm_tcgen05_epilogue.cuh"
+#include "tensor_map.cuh"
 
 #define FW_BN 128            // rows of W per tile
 #define FW_BK 64
@@ -277,36 +278,6 @@ gemm_tcgen05_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 }
 
 // ---- host side ------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn few_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// A row-major [rows, K] bfloat16 matrix, tiles of box_rows x 64 elements, 128-byte swizzle.
-static int few_make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-    EncodeTiledFn fn = few_encode_fn();
-    if (!fn) return GESSO_ERR_UNSUPPORTED;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(bf16)};
-    const cuuint32_t box[2] = {FW_BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : GESSO_ERR_UNSUPPORTED;
-}
-
 static int few_mt(int M) { return M <= 16 ? 16 : (M + 15) / 16 * 16; }
 
 GESSO_API int gesso_gemm_tcgen05_few_takes(int M, int N, int K) {
@@ -391,9 +362,9 @@ GESSO_API int gesso_gemm_tcgen05_few(const void* A, const void* W, void* out, co
     if (epi == TC_EPI_SWIGLU && N % 16 != 0) return GESSO_ERR_BAD_SIZE;
     if (((size_t)A & 15) || ((size_t)W & 15)) return GESSO_ERR_BAD_SIZE;
     CUtensorMap mw, ma;
-    int r = few_make_map(&mw, W, N, K, FW_BN);
+    int r = make_matrix_map(&mw, W, N, K, FW_BN);
     if (r) return r;
-    r = few_make_map(&ma, A, M, K, few_mt(M));
+    r = make_matrix_map(&ma, A, M, K, few_mt(M));
     if (r) return r;
     switch (epi) {
         case TC_EPI_BF16: return launch_few<TC_EPI_BF16>(mw, ma, out, bias, M, N, K, cluster, status, stream);

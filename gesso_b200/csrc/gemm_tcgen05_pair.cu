@@ -19,6 +19,7 @@
 
 #include "tcgen05.cuh"
 #include "gemm_tcgen05_epilogue.cuh"
+#include "tensor_map.cuh"
 
 #define TP_BM 128            // rows of C per block (256 per pair)
 #define TP_BN 256            // columns of C per pair; each block stages 128 rows of W
@@ -152,36 +153,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 }
 
 // ---- host side ------------------------------------------------------------------------------------------
-typedef CUresult (*TpEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static TpEncodeFn tp_encode_fn() {
-    static TpEncodeFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (TpEncodeFn)p;
-    }
-    return fn;
-}
-
-// A row-major [rows, K] bfloat16 matrix, tiles of 128 rows x 64 elements, 128-byte swizzle.
-static int tp_make_map(CUtensorMap* map, const void* base, int rows, int K) {
-    TpEncodeFn fn = tp_encode_fn();
-    if (!fn) return GESSO_ERR_UNSUPPORTED;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(bf16)};
-    const cuuint32_t box[2] = {TP_BK, 128};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : GESSO_ERR_UNSUPPORTED;
-}
-
 // The pair kernel takes what the single-block kernel takes, and pays from 256 rows and 256 columns on.
 GESSO_API int gesso_gemm_tcgen05_pair_takes(int M, int N, int K) {
     return M >= 256 && N >= 256 && N % 8 == 0 && K >= 8 && K % 8 == 0;
@@ -213,9 +184,9 @@ GESSO_API int gesso_gemm_tcgen05_pair(const void* A, const void* W, void* out, c
     if (epi == TC_EPI_SWIGLU && N % 16 != 0) return GESSO_ERR_BAD_SIZE;
     if (((size_t)A & 15) || ((size_t)W & 15) || ((size_t)out & 15)) return GESSO_ERR_BAD_SIZE;
     CUtensorMap ma, mw;
-    int r = tp_make_map(&ma, A, M, K);
+    int r = make_matrix_map(&ma, A, M, K, 128);
     if (r) return r;
-    r = tp_make_map(&mw, W, N, K);
+    r = make_matrix_map(&mw, W, N, K, 128);
     if (r) return r;
     switch (epi) {
         case TC_EPI_BF16: return tp_launch<TC_EPI_BF16>(ma, mw, out, bias, M, N, K, status, stream);
