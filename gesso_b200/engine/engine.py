@@ -25,7 +25,7 @@ from ..cache.manager import CacheManager
 from .. import ops
 from ..csrc.lib import launch_count
 from ..errors import ErrorCode, GessoError, invalid, resource
-from .batch import StepContext, StepEntry, StepLayout, count_tiles, pack_step
+from .batch import QUERY_TILE, StepContext, StepEntry, StepLayout, count_tiles, pack_step
 from .model import Model, PagedView, StateView
 
 
@@ -52,13 +52,17 @@ class DeviceCache:
         for (need, owners), pages in zip(plan.paged_groups, num_pages):
             # zero-filled: a masked key multiplies its value row by an exact zero, which must
             # not meet a NaN left in fresh memory
-            self.kv.append(torch.zeros((len(owners), 2, max(pages, 1), need.n_kv_heads, page_size,
+            # one page more than the manager hands out: the scratch page of padded steps
+            self.kv.append(torch.zeros((len(owners), 2, max(pages, 1) + 1, need.n_kv_heads, page_size,
                                         need.head_dim), dtype=dt, device=dev))
+        self.scratch_pages = [max(pages, 1) for pages in num_pages]
+        self.scratch_slot = max(num_slots, 1)
         # One buffer for all fixed-size state, a slot's entries side by side (each padded to 128 bytes),
         # so that a fresh slot is zeroed by one fill; entry i is the view [slots, *shape] into it.
         sizes = [int(np.prod(need.shape)) for need, _ in plan.state_entries]
         offsets = np.concatenate([[0], np.cumsum([-(-n // 32) * 32 for n in sizes])]).astype(int)
-        self._state_flat = torch.zeros((max(num_slots, 1), max(int(offsets[-1]), 1)), dtype=torch.float32, device=dev)
+        self._state_flat = torch.zeros((max(num_slots, 1) + 1, max(int(offsets[-1]), 1)), dtype=torch.float32,
+                                       device=dev)       # the last slot is the scratch slot of padded steps
         self.state: List[torch.Tensor] = [
             self._state_flat[:, off:off + n].view((self._state_flat.shape[0],) + tuple(need.shape))
             for (need, _), off, n in zip(plan.state_entries, offsets, sizes)]
@@ -101,6 +105,8 @@ class Engine:
         self._portion_shapes: Dict = {}           # how often a single-portion step of a shape has come
         self._graph_pool = None
         self._capture_stream = None
+        self._padded_rows = None      # set by _prepare for a step that was filled up to a padded shape
+        self.padded_steps_run = 0
         # ring of pinned staging buffers; an event per buffer says when its copy has left it
         self._pinned: List[Optional[torch.Tensor]] = [None] * 4
         self._pinned_events: List[Optional[torch.cuda.Event]] = [None] * 4
@@ -192,6 +198,7 @@ class Engine:
 
     def _prepare(self, entries: Sequence[StepEntry]):
         """Validate, reserve pages, zero fresh slots and pack the step's metadata on the host."""
+        self._padded_rows = None
         if entries and all(len(e.tokens) == 1 and len(e.want) <= 1 for e in entries):
             return self._prepare_single_tokens(entries)
         entries = self._validate(entries)
@@ -217,6 +224,11 @@ class Engine:
                 self.device_cache.zero_slot(slots[-1])
         n_groups = len(self.cache.groups)
         tables = [[self.cache.block_table_row(e.req_id, g) for e in entries] for g in range(n_groups)]
+        max_seg = max(len(e.tokens) for e in entries)
+        max_kv = max(s + len(e.tokens) for s, e in zip(starts, entries))
+        padded = self._padded_shape(entries)
+        if padded is not None:
+            return self._pack_padded(list(entries), starts, slots, tables, padded, max_kv)
         layout = StepLayout(n_tokens=sum(len(e.tokens) for e in entries), n_segs=len(entries),
                             n_rows=sum(len(e.want) for e in entries), n_groups=n_groups,
                             max_pages=self.cache.max_pages_per_request,
@@ -224,11 +236,64 @@ class Engine:
         size = layout.offsets()["_end"]
         slot_i, host = self._pinned_buffer(size)
         pack_step(list(entries), starts, slots, tables, layout, host.numpy()[:size])
-        max_seg = max(len(e.tokens) for e in entries)
-        max_kv = max(s + len(e.tokens) for s, e in zip(starts, entries))
         self._all_rows = all(len(e.want) == len(e.tokens) and bool((e.want == np.arange(len(e.tokens))).all())
                              for e in entries)
         return layout, slot_i, host[:size], max_seg, max_kv
+
+    # ---- mixed steps in a few padded shapes, so that they replay graphs -------------------------------
+    # A mixed step's kernels are launched one by one from the host unless its shape has a graph, and the
+    # shapes of mixed steps hardly ever repeat.  So a mixed step whose padded shape has come before is
+    # filled up to that shape with stand-in requests: single tokens and one portion of token id 0 at
+    # position 0, all on a scratch state slot and a scratch cache page that no request owns.  They are
+    # ordinary entries to every kernel (what they compute is never read), so no kernel knows of padding.
+    # Segments go up to a multiple of 8 (at least one stand-in), tokens to a multiple of 64, the wanted
+    # rows to the number of segments, the attention tiles to the most that shape can have.
+    def _padded_shape(self, entries):
+        S, T = len(entries), sum(len(e.tokens) for e in entries)
+        if (not self.use_graphs or S < 2 or T > 8192 or T == S or any(len(e.want) > 1 for e in entries)):
+            return None
+        S_b = -(-(S + 1) // 8) * 8
+        T_b = -(-(T + S_b - S) // 64) * 64
+        key = (T_b, S_b, S_b, False)
+        if key not in self._graphs:
+            seen = self._portion_shapes.get(key, 0)
+            self._portion_shapes[key] = seen + 1
+            if seen < 1 or sum(1 for k in self._graphs if k[0] > k[1] > 1) >= 48:
+                return None          # first time (or too many shapes already): as it is, launched one by one
+        return T_b, S_b
+
+    def _pack_padded(self, entries, starts, slots, tables, shape, max_kv):
+        T_b, S_b = shape
+        S, T = len(entries), sum(len(e.tokens) for e in entries)
+        R = sum(len(e.want) for e in entries)
+        k = S_b - S                                   # stand-ins: k - 1 single tokens and one portion
+        portion = T_b - T - (k - 1)                   # >= 1
+        dc = self.device_cache
+        pad = [StepEntry(None, np.zeros((1,), dtype=np.int32), np.zeros((1,), dtype=np.int64)) for _ in range(k - 1)]
+        # the portion wants what is left of the S_b rows (the same place over and over)
+        pad.append(StepEntry(None, np.zeros((portion,), dtype=np.int32),
+                             np.zeros((S_b - R - (k - 1),), dtype=np.int64)))
+        n_groups = len(self.cache.groups)
+        max_pages = self.cache.max_pages_per_request
+        rows = [np.full((max_pages,), dc.scratch_pages[g], dtype=np.int32) for g in range(n_groups)]
+        all_entries = entries + pad
+        starts = list(starts) + [0] * k
+        slots = list(slots) + [dc.scratch_slot] * k
+        tables = [list(tables[g]) + [rows[g]] * k for g in range(n_groups)]
+        layout = StepLayout(n_tokens=T_b, n_segs=S_b, n_rows=S_b, n_groups=n_groups, max_pages=max_pages,
+                            n_tiles=T_b // QUERY_TILE + S_b)
+        size = layout.offsets()["_end"]
+        slot_i, host = self._pinned_buffer(size)
+        out = host.numpy()[:size]
+        pack_step(all_entries, starts, slots, tables, layout, out)
+        # the tiles that this step does not have repeat the stand-in portion's first one
+        o = layout.offsets()
+        used = count_tiles(len(e.tokens) for e in all_entries)
+        out[o["tile_seg"] + used:o["tile_seg"] + layout.n_tiles] = S_b - 1
+        out[o["tile_q0"] + used:o["tile_q0"] + layout.n_tiles] = 0
+        self._all_rows = False
+        self._padded_rows = R
+        return layout, slot_i, host[:size], T_b, max_kv
 
     def _upload(self, buf: torch.Tensor, slot_i: int, host: torch.Tensor) -> None:
         buf.copy_(host, non_blocking=True)
@@ -266,11 +331,17 @@ class Engine:
         A step of single tokens only (decoding) replays a CUDA graph captured for its batch size:
         the metadata goes into the graph's fixed buffer and the whole layer loop is one launch.
         So does a step that is one prompt portion of a length seen before (the portions of a chunked
-        prompt) with few wanted rows.  The logits of such a step live in the graph's output buffer and
-        are valid until the next step of the same shape.
+        prompt) with few wanted rows, and a mixed step whose padded shape has come before (see
+        ``_padded_shape``).  The logits of such a step live in the graph's output buffer and are valid
+        until the next step of the same shape.
         """
         layout, slot_i, host, max_seg, max_kv = self._prepare(entries)
-        if self.use_graphs and max_seg == 1 and layout.n_segs <= self.max_graph_batch:
+        if self._padded_rows is not None:
+            # a mixed step filled up to a shape that has a graph (or gets one now)
+            logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg)
+            logits = logits[:self._padded_rows] if self._padded_rows else None
+            self.padded_steps_run += 1
+        elif self.use_graphs and max_seg == 1 and layout.n_segs <= self.max_graph_batch:
             logits = self._step_graph(layout, slot_i, host, max_kv)
         elif self.use_graphs and self._portion_graph_wanted(layout):
             logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg)
@@ -287,7 +358,7 @@ class Engine:
             for e in entries:
                 self.cache.commit(e.req_id, len(e.tokens))
         self.steps_run += 1
-        self.tokens_run += layout.n_tokens
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
 
     def stage_single_tokens(self, req_ids: Sequence[Hashable]) -> Optional[StagedStep]:
@@ -339,7 +410,7 @@ class Engine:
             return True
         seen = self._portion_shapes.get(key, 0)
         self._portion_shapes[key] = seen + 1
-        return seen >= 1 and sum(1 for k in self._graphs if k[0] > k[1]) < 8
+        return seen >= 1 and sum(1 for k in self._graphs if k[0] > k[1] == 1) < 8
 
     def _step_graph(self, layout: StepLayout, slot_i: int, host: torch.Tensor, max_kv: int,
                     device_tokens: Optional[torch.Tensor] = None, token_at: int = 0, max_seg: int = 1):
@@ -394,7 +465,8 @@ class Engine:
 
     def stats(self) -> Dict[str, object]:
         return {
-            "steps": self.steps_run, "staged_steps": self.staged_steps_run, "tokens": self.tokens_run,
+            "steps": self.steps_run, "staged_steps": self.staged_steps_run, "padded_steps": self.padded_steps_run,
+            "tokens": self.tokens_run,
             "pages_in_use": self.cache.pages_in_use(), "pages_free": self.cache.free_pages(),
             "slots_in_use": self.cache.slots_in_use(), "cache_bytes": self.device_cache.bytes(),
             "live_requests": len(self.cache.live_requests()),

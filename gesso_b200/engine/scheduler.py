@@ -44,7 +44,7 @@ WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 COMPLETE, EOS, STOP, CANCELLED, FAILED = "complete", "eos", "stop", "cancelled", "failed"
 
 
-@dataclass
+@dataclass(eq=False)      # a request is itself: membership tests must not compare prompts element by element
 class Request:
     prompt: List[int]
     max_new_tokens: int = 8

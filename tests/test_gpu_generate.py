@@ -132,6 +132,65 @@ def test_repeated_portion_shapes_replay_a_graph(dtype, models):
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL32), ("bfloat16", TOL16)])
+def test_mixed_steps_in_padded_shapes_replay_graphs(dtype, tol, models, plain_models):
+    """Mixed steps whose padded shape has come before are filled up with stand-in requests (scratch slot,
+    scratch page) and replay a graph: portions of changing length beside a changing number of single
+    tokens, requests that end and others that take over their pages; every wanted row against the plain
+    implementation, and the same rows as an engine that launches every kernel itself."""
+    from gesso_b200.engine import Engine, StepEntry
+    model = models("c", dtype)
+    plain = plain_models["c"]
+    seqs = prompts_for("c", [150, 90, 61, 33, 120], seed=31)
+    want_rows = {i: plain.logits(seq, list(range(len(seq)))).numpy() for i, seq in enumerate(seqs)}
+
+    def run(graphs):
+        eng = Engine(model, max_positions=256, page_size=16, num_pages=30, max_requests=4, use_graphs=graphs)
+        fed = {i: 0 for i in range(len(seqs))}
+        got = []
+        for i in (0, 1, 2):
+            eng.admit(i)
+        live, waiting = [0, 1, 2], [3, 4]
+        portion_of, sizes, turn = 0, [17, 5, 30, 2, 9, 23, 3, 12], 0
+        while live:
+            entries, places = [], []
+            # one request feeds a portion, the others one token each
+            if portion_of not in live:
+                portion_of = live[0]
+            for i in live:
+                n = min(sizes[turn % len(sizes)] if i == portion_of else 1, len(seqs[i]) - fed[i])
+                entries.append(StepEntry(i, seqs[i][fed[i]:fed[i] + n], [n - 1]))
+                places.append((i, fed[i] + n - 1))
+                fed[i] += n
+            turn += 1
+            portion_of = live[(live.index(portion_of) + 1) % len(live)]
+            logits = eng.step(entries)
+            got.append((places, logits.clone()))
+            for i in [i for i in live if fed[i] == len(seqs[i])]:
+                eng.release(i)
+                live.remove(i)
+                if waiting:
+                    j = waiting.pop(0)
+                    eng.admit(j)
+                    live.append(j)
+        eng.check_status()
+        return eng, got
+
+    eng, got = run(True)
+    assert eng.stats()["padded_steps"] >= 10
+    for places, logits in got:
+        for row, (i, pos) in enumerate(places):
+            ref = want_rows[i][pos]
+            err = float(np.abs(logits[row].cpu().numpy().astype(np.float64) - ref).max())
+            assert err <= tol * max(1.0, float(np.abs(ref).max())), (i, pos, err)
+    _, plain_run = run(False)
+    for (pa, la), (pb, lb) in zip(got, plain_run):
+        assert pa == pb
+        # the stand-ins change the shapes some kernels are chosen by, not what a row is made of
+        assert float((la - lb).abs().max()) <= tol * max(1.0, float(lb.abs().max()))
+    assert eng.stats()["pages_in_use"] == [0]
+
+
 def test_sampled_ids_follow_the_plain_sampler(models, plain_models):
     import gesso_b200
     from plain_lfm2 import PlainSampler
