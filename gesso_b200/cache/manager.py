@@ -292,6 +292,42 @@ class CacheManager:
             raise invalid("step: the metadata buffer is too small for this step")
         raise GessoError(ErrorCode.INTERNAL, f"cache manager: staging a decoding step failed ({e})")
 
+    def reserve_step(self, req_ids: Sequence[Hashable], n_new: Sequence[int]):
+        """The pages of a whole step in one native call: ``n_new[i]`` more positions for request i, for
+        all requests or for none.  Returns ``(starts, slots, fresh_slots, longest sequence after the
+        step, block-table rows per group)``; the state of the fresh slots must be zeroed before the step."""
+        n = len(req_ids)
+        rids = (ctypes.c_int64 * n)(*[self._h(r) for r in req_ids])
+        news = (ctypes.c_int * n)(*[int(k) for k in n_new])
+        starts, slots, fresh = (ctypes.c_int * n)(), (ctypes.c_int * n)(), (ctypes.c_int * n)()
+        info = (ctypes.c_int * 4)()
+        e = self._lib.gesso_cm_reserve_step(self._cm, rids, news, n, starts, slots, fresh, info)
+        if e == 0:
+            rows = [[self._rows[rid][g] for rid in req_ids] for g in range(len(self.groups))]
+            return list(starts), list(slots), list(fresh[:info[0]]), info[1], rows
+        if e == _E_PAGES:
+            self._lib.gesso_cm_last_short(self._cm, self._ibuf)
+            raise resource(f"step needs {self._ibuf[1]} pages of group {self.groups[self._ibuf[0]].name}, "
+                           f"{self._ibuf[2]} free")
+        if e == _E_CONTEXT:
+            rid = req_ids[info[0]]
+            raise resource(f"request {rid!r}: {self.length(rid)}+{n_new[info[0]]} positions exceed the context "
+                           f"length {self.max_positions}")
+        if e == _E_BAD_ARG and 0 <= info[0] < n and list(req_ids).count(req_ids[info[0]]) > 1:
+            raise invalid("step: a request appears twice in one step")
+        raise GessoError(ErrorCode.INTERNAL, f"cache manager: reserving a step failed ({e})")
+
+    def commit_step(self, req_ids: Sequence[Hashable], n_new: Sequence[int]) -> None:
+        """``n_new[i]`` positions of request i were written."""
+        n = len(req_ids)
+        rids = (ctypes.c_int64 * n)(*[self._h(r) for r in req_ids])
+        news = (ctypes.c_int * n)(*[int(k) for k in n_new])
+        e = self._lib.gesso_cm_commit_step(self._cm, rids, news, n)
+        if e != 0:
+            raise GessoError(ErrorCode.INTERNAL, f"cache manager: commit of a step failed ({e})")
+        for r, k in zip(req_ids, n_new):
+            self._length[r] += int(k)
+
     def commit(self, req_id: Hashable, n_new: int) -> None:
         """``n_new`` positions were written; windowed groups give back what no query will read."""
         e = self._lib.gesso_cm_commit(self._cm, self._h(req_id), int(n_new))

@@ -245,6 +245,64 @@ HOST_API int gesso_cm_commit_many(void* cm, const int64_t* rids, int n, int n_ne
     return OK;
 }
 
+// A whole step at once: the pages for n_new[i] more positions of request i, for all requests or for none.
+// starts[i] = the request's length now, slots[i] = its state slot; fresh_slots receives the slots whose
+// state must be zeroed before the step; info[0] = their count (or the index of the offending request),
+// info[1] = the longest sequence after the step.
+HOST_API int gesso_cm_reserve_step(void* cm, const int64_t* rids, const int* n_new, int n, int* starts, int* slots,
+                                   int* fresh_slots, int* info) {
+    Manager* m = static_cast<Manager*>(cm);
+    if (n <= 0) return E_BAD_ARG;
+    const int G = (int)m->pools.size();
+    std::vector<Request*> reqs(n);
+    std::vector<int> need(G, 0);
+    for (int i = 0; i < n; ++i) {
+        Request* r = m->find(rids[i]);
+        if (!r) { info[0] = i; return E_NOT_LIVE; }
+        for (int j = 0; j < i; ++j)
+            if (reqs[j] == r) { info[0] = i; return E_BAD_ARG; }     // a request twice in one step
+        if (n_new[i] < 0) { info[0] = i; return E_BAD_ARG; }
+        if (r->length + n_new[i] > m->max_positions) { info[0] = i; return E_CONTEXT; }
+        const int wantp = m->pages_for(r->length + n_new[i]);
+        for (int g = 0; g < G; ++g)
+            if (wantp > r->n_pages[g]) need[g] += wantp - r->n_pages[g];
+        reqs[i] = r;
+    }
+    for (int g = 0; g < G; ++g)
+        if (need[g] > m->pools[g].free_count()) {
+            m->short_group = g;
+            m->short_need = need[g];
+            m->short_free = m->pools[g].free_count();
+            return E_PAGES;
+        }
+    int n_fresh = 0, max_kv = 0;
+    for (int i = 0; i < n; ++i) {
+        Request& r = *reqs[i];
+        const int e = m->grow(r, m->pages_for(r.length + n_new[i]));
+        if (e < 0) return e;
+        if (r.length + n_new[i] > r.reserved) r.reserved = r.length + n_new[i];
+        if (r.fresh) {
+            r.fresh = false;
+            fresh_slots[n_fresh++] = r.slot;
+        }
+        starts[i] = r.length;
+        slots[i] = r.slot;
+        if (r.length + n_new[i] > max_kv) max_kv = r.length + n_new[i];
+    }
+    info[0] = n_fresh;
+    info[1] = max_kv;
+    return OK;
+}
+
+// n_new[i] positions of request i were written
+HOST_API int gesso_cm_commit_step(void* cm, const int64_t* rids, const int* n_new, int n) {
+    for (int i = 0; i < n; ++i) {
+        const int e = gesso_cm_commit(cm, rids[i], n_new[i]);
+        if (e < 0) return e;
+    }
+    return OK;
+}
+
 // the block table of a request in a group: a pointer to max_pages ints that stays valid (and up to date)
 // until the request is released; *n_used entries are in use
 HOST_API const int* gesso_cm_row(void* cm, int64_t rid, int group, int* n_used) {

@@ -96,6 +96,8 @@ _SIGNATURES = {
     "gesso_cm_live": ([c_void_p, _LP, c_int], c_int),
     "gesso_cm_last_short": ([c_void_p, _IP], None),
     "gesso_cm_check": ([c_void_p], c_int),
+    "gesso_cm_reserve_step": ([c_void_p, _LP, _IP, c_int, _IP, _IP, _IP, _IP], c_int),
+    "gesso_cm_commit_step": ([c_void_p, _LP, _IP, c_int], c_int),
     "gesso_cm_stage_single": ([c_void_p, _LP, c_int, c_void_p, c_void_p, c_void_p, c_int, _IP, _IP], c_int),
 }
 

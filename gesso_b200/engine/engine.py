@@ -202,30 +202,13 @@ class Engine:
         if entries and all(len(e.tokens) == 1 and len(e.want) <= 1 for e in entries):
             return self._prepare_single_tokens(entries)
         entries = self._validate(entries)
-        for e in entries:
-            n = len(e.tokens)
-            if self.cache.length(e.req_id) + n > self.max_positions:
-                raise resource(f"request {e.req_id!r}: {self.cache.length(e.req_id)}+{n} positions exceed "
-                               f"the context length {self.max_positions}")
-        # all-or-nothing across the batch: check the total need before handing out any page
-        need = [0] * len(self.cache.groups)
-        for e in entries:
-            for g, k in enumerate(self.cache.pages_needed(e.req_id, len(e.tokens))):
-                need[g] += k
-        for g, (k, free) in enumerate(zip(need, self.cache.free_pages())):
-            if k > free:
-                raise resource(f"step needs {k} pages of group {self.cache.groups[g].name}, {free} free")
-        starts, slots = [], []
-        for e in entries:
-            self.cache.reserve(e.req_id, len(e.tokens))
-            starts.append(self.cache.length(e.req_id))
-            slots.append(self.cache.slot(e.req_id))
-            if self.cache.take_fresh(e.req_id):
-                self.device_cache.zero_slot(slots[-1])
+        # all-or-nothing across the batch, in one native call: every request's pages, or none and an error
+        starts, slots, fresh, max_kv, tables = self.cache.reserve_step([e.req_id for e in entries],
+                                                                       [len(e.tokens) for e in entries])
+        for slot in fresh:
+            self.device_cache.zero_slot(slot)
         n_groups = len(self.cache.groups)
-        tables = [[self.cache.block_table_row(e.req_id, g) for e in entries] for g in range(n_groups)]
         max_seg = max(len(e.tokens) for e in entries)
-        max_kv = max(s + len(e.tokens) for s, e in zip(starts, entries))
         padded = self._padded_shape(entries)
         if padded is not None:
             return self._pack_padded(list(entries), starts, slots, tables, padded, max_kv)
@@ -355,8 +338,7 @@ class Engine:
         if max_seg == 1:
             self.cache.commit_single_tokens([e.req_id for e in entries])
         else:
-            for e in entries:
-                self.cache.commit(e.req_id, len(e.tokens))
+            self.cache.commit_step([e.req_id for e in entries], [len(e.tokens) for e in entries])
         self.steps_run += 1
         self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits

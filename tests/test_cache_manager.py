@@ -184,3 +184,43 @@ def test_single_token_reservation_equals_the_general_one():
     assert c.pages_in_use() == [0]
     with pytest.raises(GessoError):
         c.reserve_single_tokens(["nobody"])
+
+
+def test_step_reservation_equals_the_general_one():
+    """``reserve_step`` (a whole mixed step in one native call) hands out the same pages as ``reserve``
+    request by request, is all or nothing, refuses a request named twice and reports fresh slots once."""
+    a, b = make(num_pages=20, page_size=4, slots=3, ctx=40, window=6), make(num_pages=20, page_size=4, slots=3, ctx=40, window=6)
+    for m in (a, b):
+        for r in ("x", "y", "z"):
+            m.admit(r)
+    fresh_seen = []
+    for news in ([5, 1, 9], [1, 1, 1], [3, 7, 1], [8, 2, 4]):
+        starts, slots, fresh, max_kv, rows = a.reserve_step(["x", "y", "z"], news)
+        fresh_seen += fresh
+        for r, k in zip(("x", "y", "z"), news):
+            b.reserve(r, k)
+        assert starts == [b.length(r) for r in ("x", "y", "z")] and slots == [b.slot(r) for r in ("x", "y", "z")]
+        assert max_kv == max(b.length(r) + k for r, k in zip(("x", "y", "z"), news))
+        for g in range(2):
+            for i, r in enumerate(("x", "y", "z")):
+                assert a.block_table(r, g) == b.block_table(r, g)
+                assert rows[g][i].tolist()[:len(b.block_table(r, g))] == b.block_table(r, g)
+        a.commit_step(["x", "y", "z"], news)
+        for r, k in zip(("x", "y", "z"), news):
+            b.commit(r, k)
+        assert [a.length(r) for r in ("x", "y", "z")] == [b.length(r) for r in ("x", "y", "z")]
+        a.check_invariants()
+    assert sorted(fresh_seen) == [0, 1, 2]
+    c = make(num_pages=3, page_size=4, slots=3, ctx=40)
+    for r in ("x", "y"):
+        c.admit(r)
+    with pytest.raises(GessoError):
+        c.reserve_step(["x", "y"], [9, 5])          # 3 + 2 pages wanted, 3 there: nobody gets any
+    assert c.pages_in_use() == [0]
+    with pytest.raises(GessoError):
+        c.reserve_step(["x", "x"], [1, 1])
+    with pytest.raises(GessoError):
+        c.reserve_step(["x", "y"], [41, 1])         # beyond the context length
+    assert c.pages_in_use() == [0]
+    c.reserve_step(["x", "y"], [8, 4])
+    assert c.pages_in_use() == [3]
