@@ -51,7 +51,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  int max_pages, int page_size, const int* __restrict__ seg_start,
                                  const int* __restrict__ seg_pos0, const int* __restrict__ tile_seg,
                                  const int* __restrict__ tile_q0, bf16* __restrict__ out, int nh, int nkv, int G,
-                                 int window, float scale_log2, int* __restrict__ status) {
+                                 int window, float scale_log2, int num_pages, int* __restrict__ status) {
     extern __shared__ unsigned char fa_raw[];
     FaSmem& s = *reinterpret_cast<FaSmem*>(((size_t)fa_raw + 1023) & ~(size_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -101,10 +101,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             mbar_expect_tx(&s.q_full, 128 * FA_HD * sizeof(bf16));
             tma_load_3d(s.q, &map_q, 0, kvh * G, t0 + q0, &s.q_full);
         }
+        // A page beyond the sequence or given back behind a window is wholly masked.  Its probabilities
+        // are exact zeros, but 0 x NaN is NaN and such a page may hold anything, so nothing of it is
+        // read: its loads start past the last row of the tensor map, where TMA fills in zeros.
         auto lookup = [&](int j) -> int {
             const int key0 = (kb0 + j) * FA_BK + lane * 16;
-            int page = (lane < FA_BK / 16 && j < n_blocks && key0 <= pos_last) ? bt[key0 / page_size] : 0;
-            return page < 0 ? 0 : page;      // beyond the sequence or behind a window: masked, any valid page will do
+            return (lane < FA_BK / 16 && j < n_blocks && key0 <= pos_last) ? bt[key0 / page_size] : -1;
         };
         int page = lookup(0);
         bool ok = true;
@@ -118,8 +120,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (ok && lane < FA_BK / 16) {
                 const int sl = ((kb0 + j) * FA_BK + lane * 16) % page_size;
-                tma_load_2d(s.k[st] + lane * 16 * FA_HD, &map_k, 0, (page * nkv + kvh) * page_size + sl, &s.full[st]);
-                tma_load_2d(s.v[st] + lane * 16 * FA_HD, &map_v, sl, (page * nkv + kvh) * FA_HD, &s.full[st]);
+                const int pg = page < 0 ? num_pages : page;          // num_pages: the first row past the end
+                tma_load_2d(s.k[st] + lane * 16 * FA_HD, &map_k, 0, (pg * nkv + kvh) * page_size + sl, &s.full[st]);
+                tma_load_2d(s.v[st] + lane * 16 * FA_HD, &map_v, sl, (pg * nkv + kvh) * FA_HD, &s.full[st]);
             }
             page = next_page;
         }
@@ -349,6 +352,6 @@ GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages
     const dim3 grid(n_tiles * (64 / TOK), nkv);
     prefill_attention_tcgen05_kernel<<<grid, FA_THREADS, smem, stream>>>(
         mq, mk, mv, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, G,
-        window, scale * FA_LOG2E, status);
+        window, scale * FA_LOG2E, num_pages, status);
     return launch_status();
 }

@@ -68,6 +68,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
 extern int gesso_pdl_enabled;   // runtime.cu; set through gesso_set_pdl()
+extern "C" int gesso_sm_count();  // runtime.cu; streaming multiprocessors of the current device
 
 template <typename... KArgs, typename... Args>
 static inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

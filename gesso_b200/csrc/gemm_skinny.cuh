@@ -397,7 +397,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
 }
 
 #define SK_RING_BYTES(ROWS) (SK_STAGES_FOR(ROWS) * ((ROWS) / 8) * SK_WARPS * 32 * 16)
-#define SK_MAX_BLOCKS (2 * 148)
+#define SK_MAX_BLOCKS (2 * gesso_sm_count())
 
 #define SK_TICKETS 4096                                  // tiles a split product may have (ints at the head of the workspace)
 

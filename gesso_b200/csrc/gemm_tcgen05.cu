@@ -30,7 +30,7 @@
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
-#define TC_SMS 148
+#define TC_SMS gesso_sm_count()
 
 template <int BN, int STAGES>
 struct __align__(1024) TcSmem {

@@ -39,7 +39,7 @@
 #define FW_BK 64
 #define FW_EPI_WARPS 16       // four per quarter of the tensor-memory lanes, each with every fourth group of 8 tokens
 #define FW_THREADS (64 + 32 * FW_EPI_WARPS)
-#define FW_SMS 148
+#define FW_SMS gesso_sm_count()
 #define FW_MAX_ROWS 128      // tokens
 #define FW_MAX_STAGES 10
 #define FW_RING_BYTES (192 * 1024)

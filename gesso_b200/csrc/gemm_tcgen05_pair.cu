@@ -170,7 +170,8 @@ static int tp_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, co
         configured = true;
     }
     const int tiles = ((N + TP_BN - 1) / TP_BN) * ((M + 2 * TP_BM - 1) / (2 * TP_BM));
-    const int pairs = tiles < 74 ? tiles : 74;
+    const int max_pairs = gesso_sm_count() / 2;            // one pair of blocks per two SMs
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
     gemm_tcgen05_pair_kernel<EPI><<<dim3(2 * pairs), TP_THREADS, smem, stream>>>(ma, mw, out, bias, M, N, K, status);
     return launch_status();
 }

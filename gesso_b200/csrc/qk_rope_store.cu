@@ -11,6 +11,14 @@
 // normed, rotated K and the raw V (src/Inference/Inference.jl:2417-2421).  Page layouts:
 // K [page][kv head][slot][feature], V [page][kv head][feature][slot].
 //
+// Pages are handed from request to request as they are, so the slots behind a request's last
+// position hold whatever the page's last owner left, a NaN or an infinity included.  The tensor-core
+// attention kernels multiply masked probabilities (exact zeros) with the V slots of the whole 16-key
+// block that holds the last position, and 0 x NaN is NaN.  So the writer keeps this invariant: the
+// V slots between a request's last written position and the end of that position's 16-slot block
+// are zero.  The token that ends a request's portion in a step writes those zeros along with its own
+// values (the same 32-byte sectors); no other token of the step touches them.
+//
 // One warp per (token, head).  Everything is float32 inside; stores round to the run type.
 #include "common.cuh"
 
@@ -48,8 +56,15 @@ __global__ void qk_norm_rope_store_kernel(
         if (!is_k) {
             // v is stored transposed inside its page, [head size][page size], so that the attention
             // kernels read the values of consecutive keys of one feature as one contiguous piece
-            T* vt = v_pages + ((size_t)page * nkv + kvh) * hd * page_size + (pos % page_size);
-            for (int j = lane; j < hd; j += 32) vt[(size_t)j * page_size] = src[j];
+            const int slot = pos % page_size;
+            T* vt = v_pages + ((size_t)page * nkv + kvh) * hd * page_size + slot;
+            // the last token of its request in this step clears the rest of its 16-slot block
+            const bool last = t == n_tokens - 1 || seg_of_token[t + 1] != s;
+            const int clear = last ? min(page_size, ((slot >> 4) + 1) << 4) - slot : 1;
+            for (int j = lane; j < hd; j += 32) {
+                vt[(size_t)j * page_size] = src[j];
+                for (int z = 1; z < clear; ++z) vt[(size_t)j * page_size + z] = from_f32<T>(0.f);
+            }
             return;
         }
         dst = k_pages + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd;
@@ -190,6 +205,17 @@ qk_norm_rope_store_tile_kernel(
             *reinterpret_cast<uint4*>(dst) = make_uint4(u[0], u[1], u[2], u[3]);
         } else {
             for (int p = lo; p < hi; ++p) dst[p - p_lo] = vt[p - pos0][j];
+        }
+    }
+    // the tile that ends the portion clears the rest of the last position's 16-slot block
+    if (q0 + rows == n) {
+        const int last = pos0 + rows - 1, slot = last % page_size;
+        const int clear = min(page_size, ((slot >> 4) + 1) << 4) - slot - 1;
+        const int page = bt[last / page_size];
+        if (clear > 0 && page >= 0) {
+            bf16* dst = v_pages + ((size_t)page * nkv + kvh) * HD * page_size + slot + 1;
+            for (int idx = threadIdx.x; idx < HD * clear; idx += 256)
+                dst[(size_t)(idx / clear) * page_size + idx % clear] = __float2bfloat16_rn(0.f);
         }
     }
 }

@@ -50,9 +50,11 @@ class DeviceCache:
         dev, dt = model.rt.device, model.dtype
         self.kv: List[torch.Tensor] = []
         for (need, owners), pages in zip(plan.paged_groups, num_pages):
-            # zero-filled: a masked key multiplies its value row by an exact zero, which must
-            # not meet a NaN left in fresh memory
-            # one page more than the manager hands out: the scratch page of padded steps
+            # Pages go from request to request as they are.  The tensor-core attention kernels multiply
+            # masked probabilities (exact zeros) with the V slots of the 16-slot block that holds a
+            # request's last position; the cache writer keeps those slots zero (qk_rope_store.cu), and
+            # wholly masked pages are never read.  Zero-filled here only so that fresh memory is defined.
+            # One page more than the manager hands out: the scratch page of padded steps.
             self.kv.append(torch.zeros((len(owners), 2, max(pages, 1) + 1, need.n_kv_heads, page_size,
                                         need.head_dim), dtype=dt, device=dev))
         self.scratch_pages = [max(pages, 1) for pages in num_pages]
@@ -93,7 +95,16 @@ class Engine:
         self.cache = CacheManager(groups, self.page_size, [self.num_pages] * len(groups),
                                   max_requests, self.max_positions)
         self.device_cache = DeviceCache(model, self.page_size, [self.num_pages] * len(groups), max_requests)
-        self.status = torch.zeros((1,), dtype=torch.int32, device=model.rt.device)
+        # What kernels report instead of trapping: [0] a position without a cache page, [1] a tcgen05
+        # pipeline wait that ran out.  Read back after steps (status_read_launch / status_read_finish,
+        # or check_status); a word that is set fails the requests of the steps since the last read.
+        self.status_words = torch.zeros((2,), dtype=torch.int32, device=model.rt.device)
+        self.status = self.status_words[0:1]
+        self._tc_status = self.status_words[1:2]
+        self._unchecked: set = set()          # requests of steps whose status has not been read yet
+        self._broken: Dict[Hashable, str] = {}     # requests that took part in a failed step: release only
+        self._status_host = [torch.zeros((2,), dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._status_turn = 0
         self.steps_run = 0
         self.staged_steps_run = 0
         self.tokens_run = 0
@@ -118,6 +129,8 @@ class Engine:
 
     def release(self, req_id: Hashable) -> None:
         self.cache.release(req_id)
+        self._broken.pop(req_id, None)
+        self._unchecked.discard(req_id)
 
     def is_live(self, req_id: Hashable) -> bool:
         return self.cache.is_live(req_id)
@@ -140,6 +153,8 @@ class Engine:
             seen.add(e.req_id)
             if not self.cache.is_live(e.req_id):
                 raise invalid(f"step: request {e.req_id!r} is not live (admit it first)")
+            if self._broken and e.req_id in self._broken:
+                raise self._broken_error(e.req_id)
             n = len(e.tokens)
             if n < 1:
                 raise invalid(f"step: request {e.req_id!r} brings no tokens")
@@ -181,6 +196,8 @@ class Engine:
                     raise invalid(f"step: wanted place {w} of request {e.req_id!r} is outside its 1 tokens")
             if not self.cache.is_live(e.req_id):
                 raise invalid(f"step: request {e.req_id!r} is not live (admit it first)")
+            if self._broken and e.req_id in self._broken:
+                raise self._broken_error(e.req_id)
         n = len(entries)
         layout = StepLayout(n_tokens=n, n_segs=n, n_rows=sum(1 for e in entries if len(e.want)),
                             n_groups=len(self.cache.groups), max_pages=self.cache.max_pages_per_request, n_tiles=n)
@@ -317,28 +334,40 @@ class Engine:
         prompt) with few wanted rows, and a mixed step whose padded shape has come before (see
         ``_padded_shape``).  The logits of such a step live in the graph's output buffer and are valid
         until the next step of the same shape.
+
+        A step that raises after its kernels have started has written part of its keys, values and
+        state: its requests can only be released (a later step with one of them is refused).
         """
+        # a refusal here (bad entries, no pages: all requests' pages are reserved or none) leaves every
+        # request as it was
         layout, slot_i, host, max_seg, max_kv = self._prepare(entries)
-        if self._padded_rows is not None:
-            # a mixed step filled up to a shape that has a graph (or gets one now)
-            logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg)
-            logits = logits[:self._padded_rows] if self._padded_rows else None
-            self.padded_steps_run += 1
-        elif self.use_graphs and max_seg == 1 and layout.n_segs <= self.max_graph_batch:
-            logits = self._step_graph(layout, slot_i, host, max_kv)
-        elif self.use_graphs and self._portion_graph_wanted(layout):
-            logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg)
-        else:
-            buf = torch.empty((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
-            self._upload(buf, slot_i, host)
-            ctx = StepContext(layout, buf, self.status, max_seg, max_kv, self._all_rows)
-            before = launch_count()
-            logits = self.model.forward(ctx, self.views(ctx))
-            self.launches += launch_count() - before
-        if max_seg == 1:
-            self.cache.commit_single_tokens([e.req_id for e in entries])
-        else:
-            self.cache.commit_step([e.req_id for e in entries], [len(e.tokens) for e in entries])
+        req_ids = [e.req_id for e in entries]
+        self._unchecked.update(req_ids)
+        try:
+            with ops.tc_status_scope(self._tc_status):
+                if self._padded_rows is not None:
+                    # a mixed step filled up to a shape that has a graph (or gets one now)
+                    logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg)
+                    logits = logits[:self._padded_rows] if self._padded_rows else None
+                    self.padded_steps_run += 1
+                elif self.use_graphs and max_seg == 1 and layout.n_segs <= self.max_graph_batch:
+                    logits = self._step_graph(layout, slot_i, host, max_kv)
+                elif self.use_graphs and self._portion_graph_wanted(layout):
+                    logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg)
+                else:
+                    buf = torch.empty((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
+                    self._upload(buf, slot_i, host)
+                    ctx = StepContext(layout, buf, self.status, max_seg, max_kv, self._all_rows)
+                    before = launch_count()
+                    logits = self.model.forward(ctx, self.views(ctx))
+                    self.launches += launch_count() - before
+            if max_seg == 1:
+                self.cache.commit_single_tokens(req_ids)
+            else:
+                self.cache.commit_step(req_ids, [len(e.tokens) for e in entries])
+        except Exception as e:
+            self._mark_broken(req_ids, f"a step it took part in failed ({type(e).__name__}: {e})")
+            raise
         self.steps_run += 1
         self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
@@ -374,9 +403,15 @@ class Engine:
         elif device_tokens.dtype != torch.int32 or device_tokens.numel() != n or not device_tokens.is_cuda:
             raise invalid("step: device tokens must be one int32 id per request on the device")
         self._all_rows = staged.all_rows
-        logits = self._step_graph(staged.layout, staged.slot_i, staged.host, staged.max_kv,
-                                  device_tokens=device_tokens, token_at=at)
-        self.cache.commit_single_tokens(staged.req_ids)
+        self._unchecked.update(staged.req_ids)
+        try:
+            with ops.tc_status_scope(self._tc_status):
+                logits = self._step_graph(staged.layout, staged.slot_i, staged.host, staged.max_kv,
+                                          device_tokens=device_tokens, token_at=at)
+            self.cache.commit_single_tokens(staged.req_ids)
+        except Exception as e:
+            self._mark_broken(staged.req_ids, f"a step it took part in failed ({type(e).__name__}: {e})")
+            raise
         self.steps_run += 1
         self.staged_steps_run += 1
         self.tokens_run += staged.layout.n_tokens
@@ -439,11 +474,55 @@ class Engine:
         self.launches += n_launch
         return out
 
+    # ---- what the kernels reported ----------------------------------------------------------------
+    def _mark_broken(self, req_ids, why: str) -> None:
+        for rid in req_ids:
+            if self.cache.is_live(rid):
+                self._broken[rid] = why
+
+    def _broken_error(self, req_id) -> GessoError:
+        return GessoError(ErrorCode.RUNTIME, f"step: request {req_id!r} cannot go on: {self._broken[req_id]}; "
+                          "what it holds in the cache is not valid any more, release it")
+
+    def _status_error(self, words) -> Optional[GessoError]:
+        if int(words[0]) != 0:
+            return GessoError(ErrorCode.RUNTIME, "a kernel met a position without a cache page; the step's results "
+                              "are not valid")
+        if int(words[1]) != 0:
+            return ops.tc_wait_error(int(words[1]))
+        return None
+
+    def status_read_launch(self):
+        """Start the copy of the status words to pinned host memory, behind everything launched so far,
+        without waiting.  Returns a ticket for :meth:`status_read_finish`."""
+        self._status_turn = (self._status_turn + 1) % len(self._status_host)
+        host = self._status_host[self._status_turn]
+        host.copy_(self.status_words, non_blocking=True)
+        covered, self._unchecked = self._unchecked, set()
+        return host, covered
+
+    def status_read_finish(self, ticket, synchronize: bool = False):
+        """Look at a launched read.  The caller has waited for something that was put on the stream after
+        the read (the sampled ids' copy), or asks for ``synchronize``.  ``None`` if all is well; else
+        ``(error, requests)``: the live requests of the steps the read covers, which are now marked and can
+        only be released; the words are cleared for the steps to come."""
+        host, covered = ticket
+        if synchronize:
+            torch.cuda.current_stream(self.model.rt.device).synchronize()
+        error = self._status_error(host.numpy())
+        if error is None:
+            return None
+        self.status_words.zero_()
+        hit = [rid for rid in covered if self.cache.is_live(rid)]
+        self._mark_broken(hit, str(error))
+        return error, hit
+
     def check_status(self) -> None:
-        """Raise if a kernel recorded a position without a page (synchronises)."""
-        if int(self.status.item()) != 0:
-            self.status.zero_()
-            raise GessoError(ErrorCode.INTERNAL, "a kernel met a position without a cache page")
+        """Raise if a kernel reported a position without a page or an exhausted wait since the last read
+        (synchronises).  The requests of the steps since then are marked: they can only be released."""
+        res = self.status_read_finish(self.status_read_launch(), synchronize=True)
+        if res is not None:
+            raise res[0]
 
     def stats(self) -> Dict[str, object]:
         return {

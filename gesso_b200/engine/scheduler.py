@@ -24,6 +24,11 @@ decisions are its own:
   The oldest request is never preempted, and a request that could not fit an empty pool is refused
   when it is added, so the queue always makes progress.
 * **Finish**: pages and slot go back to the pools in the same step.
+* **A step that fails** (the engine raises, or a kernel reports through the engine's status words that
+  what it computed is not valid) fails the requests of that step only: they end with status ``failed``
+  and their pages go back; the queue goes on (a failure is terminal for its own request only,
+  src/Runtime/Runtime.jl:151-153, 175-178).  The status words travel back with the sampled ids, so
+  reading them costs no wait of its own.
 
 The scheduler needs of its engine only ``cache`` (a CacheManager), ``admit``, ``release``,
 ``step(entries) -> logits`` and a ``select(logits, requests) -> tokens`` function, so its decisions
@@ -94,6 +99,9 @@ class Request:
 
     def cancel(self) -> None:
         self.cancelled = True
+
+
+_FAILED_STEP = object()      # what Scheduler._run returns for a step that raised
 
 
 @dataclass
@@ -284,10 +292,61 @@ class Scheduler:
         r.state, r.status, r.error = FINISHED, status, error
 
     # ---- running a step ---------------------------------------------------------------------------
+    # ---- failures of a step ---------------------------------------------------------------------------
+    def _fail(self, requests, error: Exception) -> None:
+        if not isinstance(error, GessoError):
+            error = GessoError(ErrorCode.RUNTIME, f"the step failed: {type(error).__name__}: {error}")
+        for r in requests:
+            if r.state == RUNNING:
+                self._finish(r, FAILED, error)
+
+    def _run(self, requests: List[Request], call):
+        """Run one engine step; if it raises, its requests fail (and are released) and ``_FAILED_STEP``
+        comes back."""
+        try:
+            return call()
+        except Exception as e:      # not BaseException: an interrupt goes through
+            self._fail(requests, e)
+            self._staged = None
+            return _FAILED_STEP
+
+    def _status_launch(self):
+        launch = getattr(self.engine, "status_read_launch", None)
+        return None if launch is None else launch()
+
+    def _status_finish(self, ticket) -> None:
+        """What the kernels of the steps since the last read reported: their requests fail."""
+        if ticket is None:
+            return
+        res = self.engine.status_read_finish(ticket)
+        if res is not None:
+            error, req_ids = res
+            hit = set(req_ids)
+            self._fail([r for r in self.running if r.req_id in hit], error)
+            self._staged = None
+
+    def _select_now(self, logits, requests: List[Request]) -> List[object]:
+        ticket = self._status_launch()
+        tokens = self.select(logits, requests)
+        self._status_finish(ticket)
+        return tokens
+
+    def _select_launch(self, logits, requests: List[Request]):
+        ticket = self._status_launch()          # before the ids' copy: it has landed when they have
+        return self.select.launch(logits, requests), ticket
+
+    def _select_wait(self, pending) -> List[object]:
+        selection, ticket = pending
+        tokens = self.select.wait(selection)
+        self._status_finish(ticket)
+        return tokens
+
     def _digest(self, requests: List[Request], tokens: List[object]) -> List[Tuple[Request, int]]:
         """Take the selected tokens in: append, call hooks, finish what has ended."""
         emitted: List[Tuple[Request, int]] = []
         for r, tok in zip(requests, tokens):
+            if r.state != RUNNING:
+                continue                    # failed with its step: what was selected for it is dropped
             if isinstance(tok, Exception):
                 self._finish(r, FAILED, tok)
                 continue
@@ -347,11 +406,14 @@ class Scheduler:
                 samplers.append(r)
         staged, self._staged = self._staged, None
         decoding = len(samplers) == len(entries) and all(n == 1 for _, _, n in plan.entries)
+        step_requests = [r for r, _, _ in plan.entries]
         if staged is not None and decoding and staged.req_ids == tuple(e.req_id for e in entries):
-            logits = self.engine.step_staged(staged, [e.tokens[0] for e in entries])
+            logits = self._run(step_requests, lambda: self.engine.step_staged(staged, [e.tokens[0] for e in entries]))
         else:
-            logits = self.engine.step(entries)
+            logits = self._run(step_requests, lambda: self.engine.step(entries))
         self.steps += 1
+        if logits is _FAILED_STEP:
+            return []
         for r, _, n in plan.entries:
             r.fed += n
         if decoding:
@@ -361,9 +423,9 @@ class Scheduler:
         launch = getattr(self.select, "launch", None)
         if launch is not None and self.pipeline and self._staged is not None:
             # the selection is launched, not awaited: the next call takes it from there
-            self._inflight = (samplers, launch(logits, samplers))
+            self._inflight = (samplers, self._select_launch(logits, samplers))
             return self._advance()
-        return self._digest(samplers, self.select(logits, samplers))
+        return self._digest(samplers, self._select_now(logits, samplers))
 
     def _advance(self) -> List[Tuple[Request, int]]:
         """One turn of the pipelined decoding: launch the step after the one in flight from the ids on the
@@ -371,21 +433,27 @@ class Scheduler:
         requests, pending = self._inflight
         staged, self._staged = self._staged, None
         ahead = None
+        ahead_error = None
         if (staged is not None and staged.req_ids == tuple(r.req_id for r in requests) and not self.waiting
                 and not any(r.cancelled for r in requests)):
-            logits = self.engine.step_staged(staged, device_tokens=pending.ids)
-            self.steps += 1
-            for r in requests:
-                r.fed += 1
-            ahead = self.select.launch(logits, requests)
-        emitted = self._digest(requests, self.select.wait(pending))
+            try:
+                logits = self.engine.step_staged(staged, device_tokens=pending[0].ids)
+                self.steps += 1
+                for r in requests:
+                    r.fed += 1
+                ahead = self._select_launch(logits, requests)
+            except Exception as e:
+                ahead_error = e                   # the step in flight is still good: digest it first
+        emitted = self._digest(requests, self._select_wait(pending))
+        if ahead_error is not None:
+            self._fail(requests, ahead_error)
         if ahead is None:
             self._inflight = None                     # back to one step at a time
             return emitted
         if any(r.state != RUNNING or r.cancelled for r in requests) or self.waiting:
             # somebody ended (or arrived): the step ahead has run with the old batch; take what it
             # gives to the requests that go on, drop the rest
-            tokens = self.select.wait(ahead)
+            tokens = self._select_wait(ahead)
             alive = [(r, t) for r, t in zip(requests, tokens) if r.state == RUNNING]
             emitted += self._digest([r for r, _ in alive], [t for _, t in alive])
             self._inflight = None
@@ -400,7 +468,7 @@ class Scheduler:
             return []
         requests, pending = self._inflight
         self._inflight, self._staged = None, None
-        return self._digest(requests, self.select.wait(pending))
+        return self._digest(requests, self._select_wait(pending))
 
     def run(self, max_steps: Optional[int] = None) -> None:
         n = 0

@@ -94,12 +94,15 @@ class Session:
         self.max_tokens_per_step = max_tokens_per_step
         self.prefill_chunk = prefill_chunk
         self._busy = False
+        self._open_batch: Optional[Scheduler] = None         # a stream opened by open_batch that still has work
         self._last_logits: Optional[torch.Tensor] = None     # [V], of the solo sequence's last position
         self.last_scheduler: Optional[Scheduler] = None
 
     # ---- guards ------------------------------------------------------------------------------------
     def _enter(self):
-        if self._busy:
+        if self._open_batch is not None and not self._open_batch.has_work:
+            self._open_batch = None                   # the stream a caller stepped has run dry
+        if self._busy or self._open_batch is not None:
             raise GessoError(ErrorCode.INVALID_PLAN, "Session is busy: it is not re-entrant")
         self._busy = True
 
@@ -129,11 +132,16 @@ class Session:
             self.engine.admit(_SOLO)
             try:
                 logits = self.engine.step([StepEntry(_SOLO, tokens, list(range(len(tokens))))])
+                ticket = self.engine.status_read_launch()
+                host = logits.to("cpu").numpy()          # waits for the step, and so for the status words
+                bad = self.engine.status_read_finish(ticket)
+                if bad is not None:
+                    raise bad[0]
             except Exception:
                 self.reset()
                 raise
             self._last_logits = logits[-1]
-            return logits.to("cpu").numpy()
+            return host
         finally:
             self._leave()
 
@@ -143,7 +151,12 @@ class Session:
         try:
             if self._last_logits is None:
                 raise invalid("decode: nothing was prefilled")
+            ticket = self.engine.status_read_launch()    # of the step that made these logits
             tok = _select_greedy(self._last_logits)
+            bad = self.engine.status_read_finish(ticket)
+            if bad is not None:
+                self.reset()
+                raise bad[0]
             if tok in self._eos(None):
                 return tok
             if self.engine.length(_SOLO) >= self.context_length:
@@ -172,8 +185,9 @@ class Session:
     def run_batch(self, requests: Sequence[BatchRequest]) -> List[BatchResult]:
         """All requests as one continuously batched stream; one result per request, in order.
 
-        A request that fails (bad prompt, a callback that raises, non-finite logits) is terminal for
-        itself only (src/Runtime/Runtime.jl:151-153, 175-178)."""
+        A request that fails (bad prompt, a callback that raises, non-finite logits, a step of the
+        engine that raised or whose kernels reported an invalid result) is terminal for itself only
+        (src/Runtime/Runtime.jl:151-153, 175-178): the others go on and every request gets a result."""
         self._enter()
         try:
             self.reset()
@@ -198,10 +212,17 @@ class Session:
                     results[i] = BatchResult([int(t) for t in br.prompt], FAILED, e)
             try:
                 sched.run()
-            except Exception:
-                for r in list(sched.running):
-                    sched._finish(r, FAILED)
-                raise
+            except BaseException as e:
+                # the scheduler itself gave up (a step's own failure never gets here): nobody is left
+                # holding pages, and everybody still gets a result unless the caller interrupted
+                err = e if isinstance(e, GessoError) else GessoError(
+                    ErrorCode.INTERNAL, f"the scheduler stopped: {type(e).__name__}: {e}")
+                for r in list(sched.running) + list(sched.waiting):
+                    if r in sched.waiting:
+                        sched.waiting.remove(r)
+                    sched._finish(r, FAILED, err)
+                if not isinstance(e, Exception):
+                    raise
             for i, req in live:
                 results[i] = BatchResult(req.ids, req.status or FAILED, req.error)
             return results
@@ -211,7 +232,17 @@ class Session:
     def open_batch(self, requests: Sequence[BatchRequest]) -> Scheduler:
         """The same stream as :meth:`run_batch`, stepped by the caller: returns the scheduler with the
         requests added; every ``step()`` of it runs one engine step and returns the (request, token)
-        pairs it emitted, until ``has_work`` is false."""
+        pairs it emitted, until ``has_work`` is false.  Until then the session is busy: a second call is
+        refused, as while ``run_batch`` runs."""
+        self._enter()
+        try:
+            sched = self._open(requests)
+        finally:
+            self._leave()
+        self._open_batch = sched if sched.has_work else None
+        return sched
+
+    def _open(self, requests: Sequence[BatchRequest]) -> Scheduler:
         self.reset()
         sched = Scheduler(self.engine, _select, max_batch=self.max_batch,
                           max_tokens_per_step=self.max_tokens_per_step, prefill_chunk=self.prefill_chunk,
@@ -224,6 +255,16 @@ class Session:
             br._request = req
             sched.add(req)
         return sched
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """The raw step (:meth:`Engine.step`): ``entries`` of (request id, next tokens, wanted places) run as
+        one batch from the cache; float32 logits ``[wanted, vocab]`` on the device.  The caller admits and
+        releases its requests through ``session.engine``."""
+        self._enter()
+        try:
+            return self.engine.step(entries)
+        finally:
+            self._leave()
 
     def stats(self):
         s = self.engine.stats()

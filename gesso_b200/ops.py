@@ -22,9 +22,18 @@ from .errors import ErrorCode, GessoError
 
 F32, BF16 = 0, 1
 
-# The library matrix product accumulates in float32 from start to end: no bfloat16 intermediate sums
-# (split-K partials rounded to 16 bits cost about a digit of accuracy).
-torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
+def _library_mm(x: torch.Tensor, w_t: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """The library matrix product with float32 accumulation from start to end: no bfloat16 intermediate
+    sums (split-K partials rounded to 16 bits cost about a digit of accuracy).  The process-wide switch
+    is set for the call only and put back."""
+    flag = torch.backends.cuda.matmul
+    was = flag.allow_bf16_reduced_precision_reduction
+    flag.allow_bf16_reduced_precision_reduction = False
+    try:
+        return torch.mm(x, w_t) if out_dtype is None else torch.mm(x, w_t, out_dtype=out_dtype)
+    finally:
+        flag.allow_bf16_reduced_precision_reduction = was
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -331,9 +340,9 @@ TC_MIN_WAVE_EFFICIENCY = 0.8
 
 def _tc_wave_efficiency(M: int, N: int) -> float:
     if M >= 256 and N >= 256:
-        tiles, slots = -(-M // 256) * -(-N // 256), SM_COUNT // 2          # pairs of blocks, 256 x 256 tiles
+        tiles, slots = -(-M // 256) * -(-N // 256), sm_count() // 2        # pairs of blocks, 256 x 256 tiles
     else:
-        tiles, slots = -(-M // 128) * -(-N // 256), SM_COUNT
+        tiles, slots = -(-M // 128) * -(-N // 256), sm_count()
     return tiles / (-(-tiles // slots) * slots)
 
 
@@ -414,8 +423,8 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         _cuda_contig(x, "x")
         if out_dtype == torch.bfloat16:
-            return torch.mm(x, w.t())
-        return torch.mm(x, w.t(), out_dtype=torch.float32)
+            return _library_mm(x, w.t())
+        return _library_mm(x, w.t(), torch.float32)
     c = gemm_f32(x, w)
     return c if out_dtype == torch.float32 else c.to(out_dtype)
 
@@ -495,7 +504,17 @@ _lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, 
 _lib.declare("gesso_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
                                          _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.P])
 
-SM_COUNT = 148   # B200
+_lib.declare("gesso_sm_count", [])
+_sm_count = 0
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (148 on a B200), asked of the device once."""
+    global _sm_count
+    if _sm_count == 0:
+        _sm_count = int(_lib.library().gesso_sm_count())
+        _need(_sm_count > 0, "cannot read the device's multiprocessor count")
+    return _sm_count
 
 
 def fast_attention_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
@@ -511,7 +530,7 @@ def decode_splits(n_segs: int, nkv: int, max_kv_len: int) -> int:
     """How many ways the keys of a request are split so that about DECODE_BLOCKS_PER_SM blocks per SM
     are busy."""
     blocks = (max_kv_len + 15) // 16
-    want = (DECODE_BLOCKS_PER_SM * SM_COUNT) // (n_segs * nkv)      # rounded down: all blocks resident at once
+    want = (DECODE_BLOCKS_PER_SM * sm_count()) // (n_segs * nkv)      # rounded down: all blocks resident at once
     # at least 16 blocks (256 keys) per split: finer splits cost more in their set-up and in the merge of
     # the parts than they win (one request at 4,096 keys: 1,393 tokens/s with 16 splits, 1,226 with 37)
     return max(1, min(want, (blocks + 15) // 16))
@@ -565,23 +584,50 @@ _lib.declare("gesso_gemm_tcgen05_takes", [_lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_gemm_tcgen05", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P])
 
 _tc_status = {}
+_tc_status_scope: list = []
 
 
 def tc_status_tensor(device) -> torch.Tensor:
-    """One int32 per device that the tcgen05 kernel writes when one of its bounded waits runs out."""
+    """The int32 word that a tcgen05 kernel writes when one of its bounded waits runs out: the word of
+    the innermost :class:`tc_status_scope` (an engine's own, so that a step's failure is seen by the
+    engine that ran it), else one word per device."""
+    if _tc_status_scope:
+        return _tc_status_scope[-1]
     key = _device_index(device)
     if key not in _tc_status:
         _tc_status[key] = torch.zeros((1,), dtype=torch.int32, device=device)
     return _tc_status[key]
 
 
+class tc_status_scope:
+    """``with tc_status_scope(word):`` every tcgen05 kernel launched (or captured into a graph) inside
+    reports an exhausted wait to ``word`` (int32 [1] on the device)."""
+
+    def __init__(self, word: torch.Tensor):
+        self.word = word
+
+    def __enter__(self):
+        _tc_status_scope.append(self.word)
+        return self.word
+
+    def __exit__(self, *exc):
+        _tc_status_scope.pop()
+        return False
+
+
+def tc_wait_error(code: int) -> GessoError:
+    return GessoError(ErrorCode.RUNTIME, f"a tcgen05 kernel gave up on a pipeline wait (role code {code}); "
+                      "what it computed is not valid")
+
+
 def check_tc_status(device="cuda") -> None:
-    """Raise if a tcgen05 matrix product gave up on a wait since the last check (synchronises)."""
+    """Raise if a tcgen05 kernel gave up on a wait since the last check (synchronises).  Kernels
+    launched by an engine's steps report to the engine instead (``Engine.check_status``)."""
     st = tc_status_tensor(device)
     code = int(st.item())
     if code != 0:
         st.zero_()
-        raise GessoError(ErrorCode.RUNTIME, f"tcgen05 matrix product: a pipeline wait ran out (role code {code})")
+        raise tc_wait_error(code)
 
 
 _lib.declare("gesso_gemm_tcgen05_pair_takes", [_lib.I, _lib.I, _lib.I])

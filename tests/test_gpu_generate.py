@@ -227,16 +227,98 @@ def test_stops_hooks_and_failures(models):
     assert s.engine.cache.pages_in_use() == [0]
 
 
-def test_pages_run_out_preemption_keeps_the_tokens(models, plain_models):
-    """A pool too small for everybody: requests are preempted and recomputed, ids do not change."""
+def test_a_status_word_set_during_a_step_fails_that_steps_requests_only(models):
+    """The kernels report a position without a page, or a pipeline wait that ran out, through the engine's
+    status words instead of trapping.  The words come back with the sampled ids; when one is set the
+    requests of the steps it covers end as failed (what was sampled for them is dropped, their pages go
+    back) and the others go on (src/Runtime/Runtime.jl:151-153, 175-178).  The word is set from the host
+    here, between two steps: no kernel is made to fail."""
     import gesso_b200
+    model = models("c", "bfloat16")
+    prompts = prompts_for("c", [9, 30, 4, 12], seed=5)
+    alone = [gesso_b200.Session(model, context_length=128, max_batch=1).generate(p, 8) for p in prompts]
+    for word in (0, 1):
+        s = gesso_b200.Session(model, context_length=128, max_batch=2)
+        sched = s.open_batch([gesso_b200.BatchRequest(p, max_new_tokens=8) for p in prompts])
+        with pytest.raises(gesso_b200.GessoError):
+            s.generate(prompts[0], 1)                   # the session is busy while its stream is open
+        reqs = list(sched.waiting)
+        for _ in range(3):
+            sched.step()
+        assert [r.state for r in reqs] == ["running", "running", "waiting", "waiting"]
+        s.engine.status_words[word] = 7                 # as a kernel of the next step would
+        sched.run()
+        assert [r.status for r in reqs] == ["failed", "failed", "complete", "complete"]
+        for r in reqs[:2]:
+            assert r.error.code == gesso_b200.ErrorCode.RUNTIME and 1 <= len(r.generated) < 8
+        assert ("tcgen05" in str(reqs[0].error)) == (word == 1)
+        assert [r.ids for r in reqs[2:]] == alone[2:]
+        assert int(s.engine.status_words.abs().sum().item()) == 0          # cleared for the steps to come
+        assert s.engine.cache.pages_in_use() == [0] and s.engine.cache.slots_in_use() == 0
+        assert s.generate(prompts[0], 8) == alone[0]    # and the session is free again
+
+
+def test_a_request_of_a_failed_step_can_only_be_released(models):
+    """Driving the engine directly: after a step that failed, or whose status was bad, its requests have
+    keys, values and state of a half-run step in the cache; a further step with one of them is refused."""
+    import gesso_b200
+    from gesso_b200.engine import Engine, StepEntry
     model = models("a", "float32")
-    prompts = prompts_for("a", [30, 28, 25, 20], seed=8)
+    eng = Engine(model, max_positions=64, max_requests=3)
+    for rid in ("x", "y", "z"):
+        eng.admit(rid)
+    eng.step([StepEntry("x", [1, 2, 3], [2]), StepEntry("y", [4, 5], [])])
+    eng.check_status()                                   # all well
+    eng.step([StepEntry("y", [6], [0])])
+    eng.status[0] = 1
+    with pytest.raises(gesso_b200.GessoError, match="without a cache page"):
+        eng.check_status()
+    with pytest.raises(gesso_b200.GessoError, match="cannot go on"):
+        eng.step([StepEntry("y", [7], [0]), StepEntry("z", [1], [0])])
+    assert eng.length("z") == 0                          # the refused step touched nobody
+    out = eng.step([StepEntry("x", [4], [0]), StepEntry("z", [1, 2], [1])])      # x was not part of the bad step
+    assert out.shape[0] == 2 and bool(torch.isfinite(out).all())
+    eng.check_status()
+    eng.release("y")
+    eng.admit("y")                                       # a new request under the old name starts clean
+    eng.step([StepEntry("y", [4, 5, 6], [2])])
+    eng.check_status()
+    # a step that raises inside the engine (the model's forward here) marks its requests too
+    real = model.forward
+    try:
+        model.forward = lambda ctx, views: (_ for _ in ()).throw(RuntimeError("forward broke"))
+        with pytest.raises(RuntimeError, match="forward broke"):
+            eng.step([StepEntry("z", [3, 4], [1])])
+    finally:
+        model.forward = real
+    with pytest.raises(gesso_b200.GessoError, match="cannot go on"):
+        eng.step([StepEntry("z", [5], [0])])
+    for rid in ("x", "y", "z"):
+        eng.release(rid)
+    eng.cache.check_invariants()
+    assert eng.cache.pages_in_use() == [0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pages_run_out_preemption_keeps_the_tokens(dtype, models, plain_models):
+    """A pool too small for everybody: requests are preempted and recomputed.  In float32 the ids are the
+    plain model's.  In bfloat16 (model "c", head size 32: the tensor-core attention kernels) a recomputed
+    prefix runs as a prompt portion where the first run decoded token by token, other kernels and other
+    roundings, so every token must be a near-maximum of the plain logits."""
+    import gesso_b200
+    name = "a" if dtype == "float32" else "c"
+    model = models(name, dtype)
+    prompts = prompts_for(name, [30, 28, 25, 20], seed=8)
     s = gesso_b200.Session(model, context_length=64, page_size=16, num_pages=7, max_batch=4, prefill_chunk=16)
     res = s.run_batch([gesso_b200.BatchRequest(p, max_new_tokens=30) for p in prompts])
     assert s.stats()["preemptions"] >= 1
     for p, r in zip(prompts, res):
-        assert r.status == "complete" and r.ids == plain_models["a"].greedy(p, 30)
+        assert r.status == "complete" and len(r.ids) == len(p) + 30
+        if dtype == "float32":
+            assert r.ids == plain_models[name].greedy(p, 30)
+        else:
+            near_max(plain_models[name], r.ids, len(p), TOL16)
+    assert s.engine.cache.pages_in_use() == [0]
 
 
 # ---- prefill / decode of a Session ----------------------------------------------------------------------

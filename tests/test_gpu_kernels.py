@@ -334,11 +334,13 @@ def test_short_conv_nan_stays_in_its_channel():
 # ---- q/k norm, rotation, cache write -------------------------------------------------------------------
 def build_cache(seqs_k, seqs_v, nkv, hd, page_size, dtype, shuffle_seed=0):
     """Paged K [pages, nkv, slot, hd] and V [pages, nkv, hd, slot] holding the given sequences on
-    shuffled pages; returns (k_pages, v_pages, block_table)."""
+    shuffled pages; returns (k_pages, v_pages, block_table).  Every slot that no sequence owns holds
+    NaN, as a page may that a failed request gave back; only the V slots between a sequence's end and
+    the end of that 16-slot block are zero, which is what the cache writer guarantees."""
     n_pages = sum((len(k) + page_size - 1) // page_size for k in seqs_k) + 3
     perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(shuffle_seed)).tolist()
-    kp = torch.randn(n_pages, nkv, page_size, hd).to(dtype)      # stale finite values on unused slots
-    vp = torch.randn(n_pages, nkv, hd, page_size).to(dtype)
+    kp = torch.full((n_pages, nkv, page_size, hd), float("nan")).to(dtype)
+    vp = torch.full((n_pages, nkv, hd, page_size), float("nan")).to(dtype)
     max_pages = max((len(k) + page_size - 1) // page_size for k in seqs_k) + 1
     bt = torch.full((len(seqs_k), max_pages), -1, dtype=torch.int32)
     nxt = 0
@@ -351,11 +353,29 @@ def build_cache(seqs_k, seqs_v, nkv, hd, page_size, dtype, shuffle_seed=0):
             n = rows.stop - rows.start
             kp[page, :, :n] = k[rows].to(dtype).transpose(0, 1)
             vp[page, :, :, :n] = v[rows].to(dtype).permute(1, 2, 0)
+            if rows.stop == len(k):
+                vp[page, :, :, n:min(page_size, -(-n // 16) * 16)] = 0
     return kp.to(DEV), vp.to(DEV), bt.to(DEV)
 
 
+def check_v_tails(vp, bt, starts, lens, page):
+    """What the writer leaves behind a portion's last position: zeros up to the end of that position's
+    16-slot block (the attention kernels multiply those slots with masked, zero probabilities), and
+    the slots after that block, and every slot before the portion, as they were (NaN here)."""
+    v = vp.float().cpu()
+    for i, (s0, n) in enumerate(zip(starts, lens)):
+        last = s0 + n - 1
+        slot = last % page
+        end = min(page, (slot // 16 + 1) * 16)
+        pg = int(bt[i, last // page])
+        assert torch.isfinite(v[pg, :, :, :slot + 1][..., max(0, slot + 1 - n):]).all()
+        assert (v[pg, :, :, slot + 1:end] == 0).all(), "the rest of the last 16-slot block must be zero"
+        assert torch.isnan(v[pg, :, :, end:]).all(), "slots behind that block are not the writer's"
+        assert torch.isnan(v[int(bt[i, s0 // page]), :, :, :s0 % page]).all(), "slots before the portion stay"
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 16), (3, 1, 24, 8), (6, 3, 64, 16), (2, 2, 128, 32)])
+@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 16), (3, 1, 24, 8), (6, 3, 64, 16), (2, 2, 128, 32), (2, 1, 32, 48)])
 def test_qk_norm_rope_store(dtype, nh, nkv, hd, page):
     from gesso_b200 import ops
     from gesso_b200.parts.rope import rope_tables
@@ -375,11 +395,12 @@ def test_qk_norm_rope_store(dtype, nh, nkv, hd, page):
     for i, (s, n) in enumerate(zip(starts, lens)):
         for p in range((s + n + page - 1) // page):
             bt[i, p] = free.pop()
-    kp = torch.zeros(n_pages, nkv, page, hd, dtype=dtype, device=DEV)
-    vp = torch.zeros(n_pages, nkv, hd, page, dtype=dtype, device=DEV)
+    kp = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=dtype, device=DEV)
+    vp = torch.full((n_pages, nkv, hd, page), float("nan"), dtype=dtype, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     q = ops.qk_norm_rope_store(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, cos.to(DEV), sin.to(DEV), i32(positions.tolist()),
                                i32(seg.tolist()), bt.to(DEV), kp, vp, nh, nkv, hd, True, status)
+    check_v_tails(vp, bt, starts, lens, page)
     x = qkv.double()
     qr = P.rope(P.rmsnorm(x[:, :nh * hd].reshape(N, nh, hd), qw.double(), eps), positions.tolist(), theta)
     kr = P.rope(P.rmsnorm(x[:, nh * hd:(nh + nkv) * hd].reshape(N, nkv, hd), kw.double(), eps), positions.tolist(), theta)
@@ -398,7 +419,8 @@ def test_qk_norm_rope_store(dtype, nh, nkv, hd, page):
     before = kp.clone()
     ops.qk_norm_rope_store(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, cos.to(DEV), sin.to(DEV), i32(positions.tolist()),
                            i32(seg.tolist()), bt2.to(DEV), kp, vp, nh, nkv, hd, True, status)
-    assert int(status.item()) == 1 and torch.equal(kp, before)
+    bits = torch.int32 if dtype == torch.float32 else torch.int16
+    assert int(status.item()) == 1 and torch.equal(kp.view(bits), before.view(bits))
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 32, 16), (6, 3, 64, 16), (2, 2, 128, 32), (32, 8, 64, 8), (3, 1, 64, 24)])
@@ -435,8 +457,8 @@ def test_qk_norm_rope_store_by_tiles(nh, nkv, hd, page):
     for i, (s0, n) in enumerate(zip(starts, lens)):
         for p in range((s0 + n + page - 1) // page):
             bt[i, p] = perm.pop()
-    kp = torch.full((n_pages, nkv, page, hd), 7.0, dtype=torch.bfloat16, device=DEV)
-    vp = torch.full((n_pages, nkv, hd, page), 7.0, dtype=torch.bfloat16, device=DEV)
+    kp = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vp = torch.full((n_pages, nkv, hd, page), float("nan"), dtype=torch.bfloat16, device=DEV)
     kp0, vp0 = kp.clone(), vp.clone()
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     assert ops._lib.library().gesso_qk_rope_store_tiles_takes(hd, page, nh, nkv)
@@ -450,16 +472,17 @@ def test_qk_norm_rope_store_by_tiles(nh, nkv, hd, page):
     qr = P.rope(P.rmsnorm(x[:, :nh * hd].reshape(N, nh, hd), qw.double(), eps), positions.tolist(), theta)
     assert rel_err(q, qr) < BF16_EPS and rel_err(q, q1.double()) < BF16_EPS
     assert rel_err(kp, kp1.double()) < BF16_EPS
-    assert torch.equal(vp, vp1)                       # values are copied: identical, stale slots included
+    # values are copied: identical, the cleared tails and the untouched slots (NaN) included
+    assert torch.equal(vp.view(torch.int16), vp1.view(torch.int16))
+    check_v_tails(vp, bt, starts, lens, page)
     written = torch.zeros(n_pages, page, dtype=torch.bool)
     for tkn in range(N):
         s0, pos = int(seg[tkn]), int(positions[tkn])
         written[int(bt[s0, pos // page]), pos % page] = True
-    kc, k0 = kp.cpu(), kp0.cpu()
+    kc = kp.float().cpu()
     for pg in range(n_pages):
         for sl in range(page):
-            if not written[pg, sl]:
-                assert torch.equal(kc[pg, :, sl], k0[pg, :, sl])
+            assert bool(torch.isnan(kc[pg, :, sl]).all()) != bool(written[pg, sl]), "K: written slots only"
     assert int(status.item()) == 0
     bt2 = bt.clone()
     bt2[0, (3 + 70) // page] = -1                      # a page of the long portion is missing
@@ -534,6 +557,69 @@ def test_decode_attention_split_kv(window, nh, nkv, hd, page, splits):
     for _ in range(2):      # twice with one workspace: the tickets of the first launch must have been reset
         out = ops.decode_attention(q.to(DEV), kp, vp, bt, i32(positions.tolist()), window,
                                    1.0 / math.sqrt(hd), splits, ws)
+        assert rel_err(out, want) < 2 * BF16_EPS
+
+
+def attention_reference_new_rows(q, ks, vs, new_lens, window=None):
+    """The same as :func:`attention_reference` for long sequences: only the rows of the new tokens
+    are computed (scores [n, keys] per head instead of [keys, keys])."""
+    outs, cur = [], 0
+    nh, nkv = q.shape[1], ks[0].shape[1]
+    for k, v, n in zip(ks, vs, new_lens):
+        Lk = k.shape[0]
+        qq, kk, vv = q[cur:cur + n].double(), k.double(), v.double()
+        pos = torch.arange(Lk - n, Lk)[:, None]
+        key = torch.arange(Lk)[None, :]
+        mask = key > pos
+        if window is not None:
+            mask = mask | (key < pos - window + 1)
+        o = torch.zeros(n, nh, q.shape[2], dtype=torch.float64)
+        for h in range(nh):
+            g = h // (nh // nkv)
+            sc = (qq[:, h] @ kk[:, g].T) / math.sqrt(q.shape[2])      # Inference.jl:1201-1207
+            sc = sc.masked_fill(mask, float("-inf"))
+            pr = torch.exp(sc - sc.max(dim=-1, keepdim=True).values)  # :1414-1430
+            o[:, h] = (pr / pr.sum(dim=-1, keepdim=True)) @ vv[:, g]  # :1449-1457
+        outs.append(o)
+        cur += n
+    return torch.cat(outs).reshape(q.shape[0], -1)
+
+
+def test_new_rows_reference_is_the_plain_one():
+    q, ks, vs, *_ = make_attention_case(4, 2, 32, 16, torch.float32, [70, 9], [13, 2], 5)
+    for window in (None, 20):
+        assert rel_err(attention_reference_new_rows(q, ks, vs, [13, 2], window),
+                       attention_reference(q, ks, vs, [13, 2], window)) < 1e-12
+
+
+def test_split_counts_of_the_benchmark_shapes():
+    """What the decoding steps of the benchmark run with (LFM2-1.2B: 8 kv heads, context 4,096): one
+    request has its keys split 16 ways, eight requests 4 ways, sixty-four not at all.  The tests below
+    and the long-context replay run exactly these."""
+    from gesso_b200 import ops
+    assert ops.decode_splits(1, 8, 4096) == 16
+    assert ops.decode_splits(8, 8, 4096) == 4
+    assert ops.decode_splits(64, 8, 4096) == 1
+
+
+@pytest.mark.parametrize("splits", [1, 4, 9, 16, 37])
+def test_decode_attention_at_the_benchmark_context(splits):
+    """Head 64, 32 query heads on 8 kv heads, 16-slot pages, up to 4,096 keys (256 pages a request):
+    the split counts the benchmark's steps use (16 at batch 1, 4 at batch 8, 1 at batch 64), and odd
+    ones whose parts do not divide the blocks evenly.  Lengths end at page and split borders."""
+    from gesso_b200 import ops
+    nh, nkv, hd, page = 32, 8, 64, 16
+    kv_lens = [4096, 4095, 4081, 2049, 256, 4080, 1, 3000]
+    new_lens = [1] * len(kv_lens)
+    q, ks, vs, kp, vp, bt, positions, seg, starts = make_attention_case(nh, nkv, hd, page, torch.bfloat16, kv_lens,
+                                                                         new_lens, 40 + splits)
+    want = attention_reference_new_rows(q, ks, vs, new_lens)
+    S = len(kv_lens)
+    ws = (torch.empty(S * nh * splits * hd, device=DEV), torch.empty(S * nh * splits * 2, device=DEV),
+          torch.zeros(S * nkv, dtype=torch.int32, device=DEV))
+    for _ in range(2):
+        out = ops.decode_attention(q.to(DEV), kp, vp, bt, i32(positions.tolist()), None, 1.0 / math.sqrt(hd), splits, ws)
+        assert torch.isfinite(out).all()
         assert rel_err(out, want) < 2 * BF16_EPS
 
 

@@ -1,0 +1,98 @@
+"""Replay at the benchmark's own shapes: LFM2-1.2B layer widths (hidden 2048, 32 heads on 8 kv heads of
+64, feed-forward 8192, vocabulary 65536), context 4,096 with 16-slot pages, against the plain
+implementation, in float32 and bfloat16.
+
+What the benchmark times and the shorter replays never reach: a prompt portion of the tcgen05 flash
+attention that starts at position 2,048 and reads more than 2,048 keys through a block table of 256
+pages; rotary angles at positions 2,048-4,095 in the tile kernel; decoding steps at a context of
+4,096, whose captured graphs split one request's keys 16 ways and eight requests' keys 4 ways
+(``ops.decode_splits``; graphs are captured for the engine's position limit), with tickets over all
+those parts.  Two layers (short convolution, then attention) keep the float64 plain model affordable.
+
+One request of 4,096 tokens is fed as portions of 2,048 and 1,984 tokens, then 32 tokens one by one
+alone (batch 1), then its last 32 tokens beside seven short requests that decode with it (batch 8)."""
+import numpy as np
+import pytest
+
+import trace_tools as tt
+
+pytestmark = pytest.mark.gpu
+
+VOCAB = 65536
+CONFIG = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": VOCAB, "hidden_size": 2048, "num_hidden_layers": 2,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "full_attn_idxs": [1],
+    "conv_L_cache": 3, "conv_bias": False, "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True,
+    "block_multiple_of": 256, "norm_eps": 1e-5, "rope_theta": 1000000.0, "tie_embedding": True,
+}
+CONTEXT = 4096
+LONG = 4096
+SHORT = [37 + 32, 16 + 32, 64 + 32, 129 + 32, 5 + 32, 48 + 32, 250 + 32]       # prompt + 32 decoded tokens
+TOL = {"float32": 1e-4, "bfloat16": 32 * 2.0 ** -9}
+# places of the long request whose logits are compared: around the start of the second portion, borders
+# of pages, of 64-token tiles, of 128-key blocks and of the 256-key parts of a 16-way split, the end of
+# the second portion, and the last 64 (decoded one by one)
+PLACES = sorted(set([0, 1, 2047, 2048, 2049, 2063, 2064, 2111, 2112, 2175, 2176, 2303, 2304, 3071, 3072, 3839, 3840,
+                     4030, 4031] + list(range(LONG - 64, LONG))))
+
+
+@pytest.fixture(scope="module")
+def case(tmp_path_factory):
+    from gesso_b200.weights import write_random_model
+    from plain_lfm2 import PlainModel
+    d = str(tmp_path_factory.mktemp("model_long"))
+    write_random_model(d, CONFIG, 11, dtype="bfloat16", style="fan_in")
+    reqs = tt.make_requests(VOCAB, [LONG] + SHORT, seed=123)
+    plain = PlainModel(d)
+    ref = {0: dict(zip(PLACES, plain.logits(reqs[0], PLACES).numpy()))}
+    for i, n in enumerate(SHORT, start=1):
+        places = [n - 33, n - 17, n - 1]                  # the last prompt token, two decoded ones
+        ref[i] = dict(zip(places, plain.logits(reqs[i], places).numpy()))
+    del plain
+    return d, reqs, ref
+
+
+def build(reqs, ref):
+    A = reqs[0]
+    tb = tt.TraceBuilder()
+    want = lambda rid, p, n: [i for i in range(n) if p + i in ref[rid]]
+    tb.add_step([(0, A[:2048], 0, want(0, 0, 2048))])
+    tb.add_step([(0, A[2048:4032], 2048, want(0, 2048, 1984))])          # a portion from position 2,048
+    for p in range(4032, 4064):                                          # alone: batch 1, 16-way split
+        tb.add_step([(0, A[p:p + 1], p, want(0, p, 1))])
+    # the seven short prompts in one step of portions, the long request left out of it
+    tb.add_step([(i, reqs[i][:n - 32], 0, want(i, 0, n - 32)) for i, n in enumerate(SHORT, start=1)])
+    for k in range(32):                                                  # eight single tokens: 4-way split
+        p = 4064 + k
+        entries = [(i, reqs[i][n - 32 + k:n - 31 + k], n - 32 + k, want(i, n - 32 + k, 1))
+                   for i, n in enumerate(SHORT, start=1)]
+        entries.insert(k % 8, (0, A[p:p + 1], p, want(0, p, 1)))         # the long request at every place of the batch
+        tb.add_step(entries, end=list(range(8)) if k == 31 else [])
+    return tb, tt.round_up(LONG) + sum(tt.round_up(n) for n in SHORT)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_at_the_benchmark_context(dtype, case, tmp_path):
+    import gesso_b200
+    from gesso_b200 import ops
+    d, reqs, ref = case
+    tb, max_tokens = build(reqs, ref)
+    model = gesso_b200.load(d, dtype=dtype, max_positions=CONTEXT)
+    eng = tt.run_in_process(model, tb, max_tokens, str(tmp_path), max_requests=8)
+    assert eng.max_positions == CONTEXT
+    if dtype == "bfloat16":
+        # the graphs of the single-token steps were captured for these split counts
+        assert ops.decode_splits(1, 8, eng.max_positions) == 16 and ops.decode_splits(8, 8, eng.max_positions) == 4
+        ops.check_tc_status()
+    rows = tt.read_rows(tb, str(tmp_path), VOCAB)
+    assert set(rows) == {(rid, pos) for rid in ref for pos in ref[rid]}
+    worst = 0.0
+    for (rid, pos), got in sorted(rows.items()):
+        r = ref[rid][pos]
+        scale = max(1.0, float(np.abs(r).max()))
+        err = float(np.abs(got.astype(np.float64) - r).max())
+        assert np.isfinite(got).all() and err <= TOL[dtype] * scale, \
+            f"{dtype}: request {rid} position {pos}: max error {err:.3e} > {TOL[dtype]:.1e} * {scale:.2f}"
+        worst = max(worst, err / scale)
+    print(f"benchmark context {dtype}: worst {worst:.3e}")

@@ -94,6 +94,24 @@ def test_schedules_agree_closely(dtype, loaded, plain_logits, tmp_path):
             assert err <= bound * scale, f"{sched} differs from whole at request/position {key}: {err:.3e}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,schedule", [("a", "mixed"), ("b", "mixed"), ("c", "mixed"), ("c", "portions"),
+                                           ("c", "tail_decode")])
+def test_what_a_free_page_holds_never_reaches_a_request(name, schedule, dtype, loaded, plain_logits, tmp_path):
+    """Pages and state slots go from request to request as they are.  Whatever the last owner left in
+    them, non-finite values included (a request whose activations overflowed ends, its pages do not
+    get cleaned), a new request starts from nothing and never sees another's rows
+    (src/Inference/Inference.jl:147-148, src/Inference/generate_state.jl:188-192).  Every free page
+    and slot is filled with NaN before the first step; the mixed replay uses pages again.  Model "c"
+    has head size 32, so its bfloat16 runs take the tensor-core attention kernels."""
+    reqs, ref = plain_logits(name)
+    tb, max_tokens = SCHEDULES[schedule](reqs)
+    model = loaded(name, dtype)
+    tt.run_in_process(model, tb, max_tokens, str(tmp_path), prepare=tt.poison_free_memory)
+    rows = tt.read_rows(tb, str(tmp_path), model.vocab_size)
+    tt.compare_with_plain(rows, ref, TOL[dtype], f"poisoned pages {name}/{schedule}/{dtype}")
+
+
 def test_trace_run_program(model_dirs, plain_logits, tmp_path):
     """The program itself, as a user runs it: a subprocess fed through standard input."""
     reqs, ref = plain_logits("a")

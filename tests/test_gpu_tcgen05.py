@@ -123,3 +123,29 @@ def test_tcgen05_prefill_attention(window, nh, nkv, page):
     want = K.attention_reference(q, ks, vs, new_lens, window)
     assert torch.isfinite(out).all()
     assert rel_err(out, want) < 2 * BF16_EPS
+
+
+def test_tcgen05_prefill_attention_late_portion():
+    """The benchmark's head layout (32 query heads on 8 kv heads of 64, 16-slot pages) with portions
+    that start deep inside a sequence: 2,048 tokens from position 2,048 (every query reads more than
+    2,048 keys over 256 pages), a short portion that ends at key 4,096, and one beside them that
+    starts at a position that is no multiple of anything."""
+    import test_gpu_kernels as K
+    from gesso_b200 import ops
+    from gesso_b200.engine.batch import QUERY_TILE
+    nh, nkv, hd, page = 32, 8, 64, 16
+    kv_lens, new_lens = [4096, 4096, 2500], [2048, 33, 131]
+    q, ks, vs, kp, vp, bt, positions, seg, starts = K.make_attention_case(nh, nkv, hd, page, torch.bfloat16, kv_lens,
+                                                                           new_lens, 91)
+    tile_seg, tile_q0 = [], []
+    for s, n in enumerate(new_lens):
+        for q0 in range(0, n, QUERY_TILE):
+            tile_seg.append(s)
+            tile_q0.append(q0)
+    pos0 = [L - n for L, n in zip(kv_lens, new_lens)]
+    out = ops.prefill_attention_tcgen05(q.to(DEV), kp, vp, bt, K.i32(starts), K.i32(pos0), K.i32(tile_seg), K.i32(tile_q0),
+                                        None, 1.0 / math.sqrt(hd))
+    ops.check_tc_status()
+    want = K.attention_reference_new_rows(q, ks, vs, new_lens)
+    assert torch.isfinite(out).all()
+    assert rel_err(out, want) < 2 * BF16_EPS

@@ -382,3 +382,92 @@ def test_pipelined_decoding_with_cancel_and_hooks():
     assert a.status == STOP and a.ids == solo([5, 6, 7], 20)[:3 + 5] and len(seen) == 5
     assert b.status == CANCELLED and b.ids == solo([2, 2], 20)[:len(b.ids)]
     assert eng.cache.pages_in_use() == [0] and not s.has_work
+
+
+# ---- a step that fails is terminal for its own requests only (src/Runtime/Runtime.jl:151-153, 175-178) ----
+class FailingEngine(FakeEngine):
+    """Raises in the steps whose numbers are in ``raise_at``; reports a bad status word after the steps in
+    ``bad_status_at`` (through the same two calls the real engine offers)."""
+
+    def __init__(self, raise_at=(), bad_status_at=(), **kw):
+        super().__init__(**kw)
+        self.raise_at, self.bad_status_at = set(raise_at), set(bad_status_at)
+        self.n = 0
+        self.unchecked = set()
+        self.bad = False
+
+    def step(self, entries):
+        k = self.n
+        self.n += 1
+        if k in self.raise_at:
+            raise GessoError(ErrorCode.LAUNCH, f"step {k}: a kernel refused its sizes")
+        out = super().step(entries)
+        self.unchecked.update(e.req_id for e in entries)
+        if k in self.bad_status_at:
+            self.bad = True
+        return out
+
+    def status_read_launch(self):
+        ticket = (self.bad, self.unchecked)
+        self.bad, self.unchecked = False, set()
+        return ticket
+
+    def status_read_finish(self, ticket):
+        bad, covered = ticket
+        if not bad:
+            return None
+        return GessoError(ErrorCode.RUNTIME, "a kernel reported an invalid result"), \
+            [rid for rid in covered if self.cache.is_live(rid)]
+
+
+def test_a_step_that_raises_fails_its_requests_and_the_queue_goes_on():
+    prompts = [[1, 2, 3], [4, 5], [6, 7, 8, 9], [10]]
+    # two live at a time; step 1 is the first decoding step of the first two requests
+    eng, s = make(FailingEngine(raise_at={1}), max_batch=2)
+    reqs = [s.add(Request(p, 4)) for p in prompts]
+    s.run()
+    assert [r.status for r in reqs] == [FAILED, FAILED, COMPLETE, COMPLETE]
+    for r in reqs[:2]:
+        assert isinstance(r.error, GessoError) and r.error.code == ErrorCode.LAUNCH and "step 1" in str(r.error)
+        assert len(r.generated) == 1              # what it had been given before the step failed stays
+    for p, r in zip(prompts[2:], reqs[2:]):
+        assert r.ids == solo(p, 4)
+    assert eng.cache.pages_in_use() == [0] and eng.cache.slots_in_use() == 0
+    eng.cache.check_invariants()
+    assert not s.has_work
+
+
+def test_a_foreign_exception_in_a_step_is_wrapped_and_contained():
+    class Boom(FailingEngine):
+        def step(self, entries):
+            if self.n == 0:
+                self.n += 1
+                raise RuntimeError("CUDA out of memory")
+            return super().step(entries)
+    eng, s = make(Boom(), max_batch=1)
+    a, b = s.add(Request([1, 2], 3)), s.add(Request([3], 3))
+    s.run()
+    assert a.status == FAILED and a.error.code == ErrorCode.RUNTIME and "out of memory" in str(a.error)
+    assert b.status == COMPLETE and b.ids == solo([3], 3)
+    assert eng.cache.pages_in_use() == [0]
+
+
+def test_a_bad_status_word_fails_the_requests_of_the_steps_it_covers():
+    # step 0: the prompts of r0 and r1 (both sample); the status read with their ids is bad
+    eng, s = make(FailingEngine(bad_status_at={0}), max_batch=2)
+    reqs = [s.add(Request(p, 3)) for p in ([1, 2, 3], [4, 5], [6])]
+    s.run()
+    assert [r.status for r in reqs] == [FAILED, FAILED, COMPLETE]
+    assert all(r.error.code == ErrorCode.RUNTIME and r.generated == [] for r in reqs[:2])    # the ids were dropped
+    assert reqs[2].ids == solo([6], 3)
+    assert eng.cache.pages_in_use() == [0] and eng.cache.slots_in_use() == 0
+
+
+def test_a_bad_status_of_a_step_without_samples_is_seen_at_the_next_read():
+    # prompt of 9 in portions of 4: steps 0 and 1 sample nothing, so nothing is read; the word set in step 0
+    # is seen with the ids of step 2 and fails the request then
+    eng, s = make(FailingEngine(bad_status_at={0}), prefill_chunk=4, max_batch=1)
+    a, b = s.add(Request(list(range(9)), 2)), s.add(Request([7], 2))
+    s.run()
+    assert a.status == FAILED and a.generated == [] and len(eng.log) >= 3
+    assert b.status == COMPLETE and b.ids == solo([7], 2)

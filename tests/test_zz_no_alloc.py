@@ -47,12 +47,21 @@ def test_static_argmax_matches_the_regular_entry_point_twice_in_a_row():
         x = x.cuda()
         bufs.append((x, torch.full((x.shape[0],), -7, dtype=torch.int32, device="cuda"),
                      torch.full((x.shape[0],), -7, dtype=torch.int32, device="cuda")))
+    # the set-up call: the first call on a device looks the scratch array's address up, and the driver loads
+    # the kernels' code at their first launch; neither is what the calls below may do
+    warm = torch.zeros(2, 65536, device="cuda")
+    warm_small = torch.zeros(2, 503, device="cuda")
+    for w in (warm, warm_small):
+        assert call(fn, w, torch.zeros(2, dtype=torch.int32, device="cuda"),
+                    torch.zeros(2, dtype=torch.int32, device="cuda")) == 0
     torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
+    before = torch.cuda.memory_allocated()         # torch's own allocator ...
+    free_before, _ = torch.cuda.mem_get_info()     # ... and the driver's view: a cudaMalloc inside would show here
     for x, ids, bad in bufs:                       # two calls in a row, the second reuses the scratch
         assert call(fn, x, ids, bad) == 0
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    assert torch.cuda.mem_get_info()[0] == free_before, "the device's free memory changed: something allocated"
     for x, ids, bad in bufs:
         want_ids, want_bad = ops.argmax_rows(x)
         assert torch.equal(ids, want_ids) and torch.equal(bad, want_bad)

@@ -121,9 +121,13 @@ def trace_mixed(reqs, seed: int, max_live: int = 4, decode_tail: int = 12,
 
 
 # ---- running and comparing --------------------------------------------------------------------------
-def run_in_process(model, tb: TraceBuilder, max_tokens: int, out_dir: str, page_size: int = 16):
+def run_in_process(model, tb: TraceBuilder, max_tokens: int, out_dir: str, page_size: int = 16, prepare=None,
+                   max_requests: int = 4):
+    """Replay ``tb`` on a fresh engine; ``prepare(engine)`` may touch the engine before the first step."""
     from gesso_b200.engine import trace
-    eng = trace.make_engine(model, max_tokens, page_size=page_size)
+    eng = trace.make_engine(model, max_tokens, page_size=page_size, max_requests=max_requests)
+    if prepare is not None:
+        prepare(eng)
     sink = io.StringIO()
     trace.replay(eng, io.StringIO(tb.text()), out_dir, done=sink)
     assert sink.getvalue().count("done ") == len(tb.steps)
@@ -163,3 +167,12 @@ def compare_with_plain(rows, plain_logits: List[np.ndarray], tol: float, what: s
                 f"{what}: request {rid} position {pos} (of {len(ref)}): max error {err:.3e} "
                 f"> {tol:.1e} * {scale:.3f}; first bad position of this request")
     return worst
+
+
+def poison_free_memory(eng) -> None:
+    """Fill every cache page and every state slot with NaN, as requests that went non-finite may have
+    left them (on a fresh engine every page and slot is free, so this touches nothing a request owns)."""
+    assert eng.cache.live_requests() == []
+    for kv in eng.device_cache.kv:
+        kv.fill_(float("nan"))
+    eng.device_cache._state_flat.fill_(float("nan"))
