@@ -263,34 +263,19 @@ class CacheManager:
         rows = [[self._rows[rid][g] for rid in req_ids] for g in range(len(self.groups))]
         return starts, slots, fresh, rows
 
-    def stage_single_tokens(self, req_ids: Sequence[Hashable], tokens: Optional[Sequence[int]],
-                            want: Sequence[bool], out: np.ndarray):
-        """:meth:`reserve_single_tokens` and the packing of the step's metadata into ``out`` (int32, the
-        layout of :class:`~gesso_b200.engine.batch.StepLayout` for single tokens) in one native call.
-        Returns ``(fresh_slots, longest sequence after the step, wanted rows, ints written)``."""
-        n = len(req_ids)
-        rids = (ctypes.c_int64 * n)(*[self._h(r) for r in req_ids])
-        toks = None if tokens is None else (ctypes.c_int * n)(*tokens)
-        wants = (ctypes.c_int * n)(*[1 if w else 0 for w in want])
-        fresh = (ctypes.c_int * n)()
-        info = (ctypes.c_int * 4)()
-        e = self._lib.gesso_cm_stage_single(self._cm, rids, n, toks, wants, ctypes.c_void_p(out.ctypes.data),
-                                            int(out.size), fresh, info)
-        if e == 0:
-            return list(fresh[:info[0]]), info[1], info[2], info[3]
-        if e == _E_PAGES:
-            self._lib.gesso_cm_last_short(self._cm, self._ibuf)
-            raise resource(f"step needs {self._ibuf[1]} pages of group {self.groups[self._ibuf[0]].name}, "
-                           f"{self._ibuf[2]} free")
-        if e == _E_CONTEXT:
-            rid = req_ids[info[0]]
-            raise resource(f"request {rid!r}: {self.length(rid)}+1 positions exceed the context length "
-                           f"{self.max_positions}")
-        if e == _E_BAD_ARG and 0 <= info[0] < n and list(req_ids).count(req_ids[info[0]]) > 1:
-            raise invalid("step: a request appears twice in one step")
-        if e == _E_BAD_ARG:
-            raise invalid("step: the metadata buffer is too small for this step")
-        raise GessoError(ErrorCode.INTERNAL, f"cache manager: staging a decoding step failed ({e})")
+    # ---- for the step packer (csrc/host/step_packer.cpp), which drives the native manager itself ---------
+    def handle(self, req_id: Hashable) -> Optional[int]:
+        """The native handle of a live request, ``None`` if it is not live."""
+        return self._handle.get(req_id)
+
+    def native(self):
+        """The native manager, for calls that take it as an argument."""
+        return self._cm
+
+    def last_short(self) -> str:
+        """Which group ran short in the refusal just returned, in words."""
+        self._lib.gesso_cm_last_short(self._cm, self._ibuf)
+        return f"{self._ibuf[1]} pages of group {self.groups[self._ibuf[0]].name}, {self._ibuf[2]} free"
 
     def reserve_step(self, req_ids: Sequence[Hashable], n_new: Sequence[int]):
         """The pages of a whole step in one native call: ``n_new[i]`` more positions for request i, for

@@ -1,4 +1,4 @@
-// The cache manager's bookkeeping and the packing of a decoding step's metadata, on the host.
+// The cache manager's bookkeeping, on the host.
 //
 // Keys and values live in pages of `page_size` positions.  Layers with the same need form a group;
 // a group has a page pool of its own and every request one block table per group, so one page id
@@ -379,82 +379,5 @@ HOST_API int gesso_cm_check(void* cm) {
         slot_seen[s] = 1;
     }
     if ((int)m->reqs.size() != m->slots.count - m->slots.free_count()) return fail(-1, 6, (int)m->reqs.size());
-    return OK;
-}
-
-// ---- a decoding step: one more position for each request, and its packed metadata ----------------------
-// Reserves (all or none) and fills `out` in the step's layout for single tokens
-//   token_ids[n] positions[n] seg_of_token[n] seg_start[n+1] seg_pos0[n] slots[n] logit_rows[R] tile_seg[n]
-//   tile_q0[n] block_table[g][n][max_pages] for each group g
-// where R = the number of requests with want[i] != 0 (logit row i for each).  tokens may be null (filled in
-// later).  fresh_slots receives the slots whose state must be zeroed before the step; info[0] = their count,
-// info[1] = the longest sequence after the step, info[2] = R, info[3] = ints written.
-HOST_API int gesso_cm_stage_single(void* cm, const int64_t* rids, int n, const int* tokens, const int* want, int* out,
-                                   int out_cap, int* fresh_slots, int* info) {
-    Manager* m = static_cast<Manager*>(cm);
-    if (n <= 0) return E_BAD_ARG;
-    const int G = (int)m->pools.size();
-    std::vector<Request*> reqs(n);
-    std::vector<int> need(G, 0);
-    int R = 0;
-    for (int i = 0; i < n; ++i) {
-        Request* r = m->find(rids[i]);
-        if (!r) { info[0] = i; return E_NOT_LIVE; }
-        for (int j = 0; j < i; ++j)
-            if (reqs[j] == r) { info[0] = i; return E_BAD_ARG; }     // a request twice in one step
-        if (r->length + 1 > m->max_positions) { info[0] = i; return E_CONTEXT; }
-        const int wantp = m->pages_for(r->length + 1);
-        for (int g = 0; g < G; ++g)
-            if (wantp > r->n_pages[g]) need[g] += wantp - r->n_pages[g];
-        reqs[i] = r;
-        R += want[i] != 0;
-    }
-    for (int g = 0; g < G; ++g)
-        if (need[g] > m->pools[g].free_count()) {
-            m->short_group = g;
-            m->short_need = need[g];
-            m->short_free = m->pools[g].free_count();
-            return E_PAGES;
-        }
-    const long long total = 3LL * n + (n + 1) + 2LL * n + R + 2LL * n + (long long)G * n * m->max_pages;
-    if (total > out_cap) return E_BAD_ARG;
-    int* tok = out;
-    int* pos = tok + n;
-    int* seg = pos + n;
-    int* seg_start = seg + n;
-    int* seg_pos0 = seg_start + n + 1;
-    int* slots = seg_pos0 + n;
-    int* rows = slots + n;
-    int* tile_seg = rows + R;
-    int* tile_q0 = tile_seg + n;
-    int* bt = tile_q0 + n;
-    int n_fresh = 0, max_kv = 0, row = 0;
-    for (int i = 0; i < n; ++i) {
-        Request& r = *reqs[i];
-        const int e = m->grow(r, m->pages_for(r.length + 1));
-        if (e < 0) return e;
-        if (r.length + 1 > r.reserved) r.reserved = r.length + 1;
-        if (r.fresh) {
-            r.fresh = false;
-            fresh_slots[n_fresh++] = r.slot;
-        }
-        tok[i] = tokens ? tokens[i] : 0;
-        pos[i] = r.length;
-        seg[i] = i;
-        seg_start[i] = i;
-        seg_pos0[i] = r.length;
-        slots[i] = r.slot;
-        tile_seg[i] = i;
-        tile_q0[i] = 0;
-        if (want[i]) rows[row++] = i;
-        if (r.length + 1 > max_kv) max_kv = r.length + 1;
-        for (int g = 0; g < G; ++g)
-            std::memcpy(bt + ((size_t)g * n + i) * m->max_pages, r.rows[g].data(), sizeof(int) * m->max_pages);
-    }
-    seg_start[n] = n;
-    info[0] = n_fresh;
-    info[1] = max_kv;
-    info[2] = R;
-    info[3] = (int)total;
     return OK;
 }

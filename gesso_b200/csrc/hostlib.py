@@ -1,5 +1,5 @@
 """Builds and loads the host runtime library (``host/*.cpp``: the cache manager's bookkeeping and the
-packing of a decoding step), plain C++ behind a C ABI.
+packing of a step's metadata), plain C++ behind a C ABI.
 
 It is compiled with the system C++ compiler into ``_build/libgesso_host.so`` at the first use (a
 second or two) and rebuilt when a source changes.  It needs neither a GPU nor ``nvcc``, so the
@@ -98,7 +98,8 @@ _SIGNATURES = {
     "gesso_cm_check": ([c_void_p], c_int),
     "gesso_cm_reserve_step": ([c_void_p, _LP, _IP, c_int, _IP, _IP, _IP, _IP], c_int),
     "gesso_cm_commit_step": ([c_void_p, _LP, _IP, c_int], c_int),
-    "gesso_cm_stage_single": ([c_void_p, _LP, c_int, c_void_p, c_void_p, c_void_p, c_int, _IP, _IP], c_int),
+    "gesso_step_prepare": ([c_void_p, _LP, _IP, c_int, _IP, _IP, _IP, _IP, c_int, _IP, c_int, c_int, c_int, c_int,
+                            _IP, c_void_p, c_int, _IP, _IP], c_int),
 }
 
 

@@ -4,29 +4,66 @@ A step is a list of *entries*: (request, its next tokens, the places among them 
 logits are wanted).  A prompt portion is an entry with several tokens, a decoded token an
 entry with one; they share one token axis of ``N = sum(n_tokens)`` rows.  The device-side
 description (:class:`StepContext`) is built on the host into one pinned int32 buffer and
-copied with a single transfer:
+copied with a single transfer.
 
-``token_ids[N]  positions[N]  seg_of_token[N]  seg_start[S+1]  seg_pos0[S]  slots[S]
-logit_rows[R]  tile_seg[NT]  tile_q0[NT]  block_table[g][S][max_pages] for each paged group g``
+**The layout of that buffer is decided here and nowhere else.**  :data:`CORE_FIELDS` lists the
+fields every step has, in order, each with the axis it runs along; the block tables of the paged
+groups follow, then any fields registered with :func:`register_step_field` (a mixer that needs one
+more array per segment, token, wanted row or tile adds a line there and a function that fills it).
+:meth:`StepLayout.offsets` turns the table into offsets; the native packer
+(``csrc/host/step_packer.cpp``) is handed those offsets and only knows what goes *into* a core
+field, and :class:`StepContext` cuts the device buffer by the same offsets.
 
-(``tile_*`` list the 64-token query tiles of the step for the prefill attention kernel; a tile never
-crosses a request)
-
-(the reference's only per-pass metadata is the position vector,
-src/Inference/Inference.jl:2322-2323, because it runs one sequence at a time).
+``tile_*`` list the 64-token query tiles of the step for the prefill attention kernel; a tile never
+crosses a request.  (The reference's only per-pass metadata is the position vector,
+src/Inference/Inference.jl:2322-2323, because it runs one sequence at a time.)
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Sequence
+from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 from ..cache.manager import FREED
+from ..csrc import hostlib
+from ..errors import ErrorCode, GessoError, invalid, resource
 
 
 QUERY_TILE = 64   # tokens per query tile of the prefill attention kernel
+
+# (name, axis): what every step carries.  The order is the field numbering of csrc/host/step_packer.cpp.
+CORE_FIELDS: Tuple[Tuple[str, str], ...] = (
+    ("token_ids", "token"),        # token ids
+    ("positions", "token"),        # absolute position of every token
+    ("seg_of_token", "token"),     # segment (entry) of every token
+    ("seg_start", "seg+1"),        # first token of every segment, and the total
+    ("seg_pos0", "seg"),           # position of a segment's first token
+    ("slots", "seg"),              # state slot of a segment's request
+    ("logit_rows", "row"),         # tokens whose logits are wanted
+    ("tile_seg", "tile"),          # the step's query tiles: segment ...
+    ("tile_q0", "tile"),           # ... and first token inside the segment
+)
+
+# fields added from outside: name -> (axis, fill(entries, view)); they follow the block tables
+_EXTRA_FIELDS: Dict[str, Tuple[str, Callable]] = {}
+
+
+def register_step_field(name: str, axis: str, fill: Callable[[List["StepEntry"], np.ndarray], None]) -> None:
+    """One more int32 array in every step's metadata: ``axis`` is ``token``, ``seg``, ``seg+1``, ``row`` or
+    ``tile``; ``fill(entries, view)`` writes it on the host (``entries`` include the stand-ins of a padded
+    step, whose ``req_id`` is ``None``).  Parts read it as ``ctx.extra[name]``."""
+    if axis not in ("token", "seg", "seg+1", "row", "tile"):
+        raise invalid(f"step field {name!r}: unknown axis {axis!r}")
+    if name in _EXTRA_FIELDS or any(name == n for n, _ in CORE_FIELDS) or name.startswith("block_table"):
+        raise invalid(f"step field {name!r} exists already")
+    _EXTRA_FIELDS[name] = (axis, fill)
+
+
+def unregister_step_field(name: str) -> None:
+    _EXTRA_FIELDS.pop(name, None)
 
 
 def count_tiles(lengths) -> int:
@@ -51,19 +88,32 @@ class StepLayout:
     max_pages: int
     n_tiles: int = 0
 
+    def _axis(self, axis: str) -> int:
+        return {"token": self.n_tokens, "seg": self.n_segs, "seg+1": self.n_segs + 1, "row": self.n_rows,
+                "tile": self.n_tiles}[axis]
+
     def offsets(self) -> Dict[str, int]:
-        N, S, R = self.n_tokens, self.n_segs, self.n_rows
+        o = getattr(self, "_offsets", None)
+        if o is not None:
+            return o
         o, cur = {}, 0
-        for name, size in (("token_ids", N), ("positions", N), ("seg_of_token", N),
-                           ("seg_start", S + 1), ("seg_pos0", S), ("slots", S), ("logit_rows", R),
-                           ("tile_seg", self.n_tiles), ("tile_q0", self.n_tiles)):
+        for name, axis in CORE_FIELDS:
             o[name] = cur
-            cur += size
+            cur += self._axis(axis)
         for g in range(self.n_groups):
             o[f"block_table{g}"] = cur
-            cur += S * self.max_pages
+            cur += self.n_segs * self.max_pages
+        for name, (axis, _) in _EXTRA_FIELDS.items():
+            o[name] = cur
+            cur += self._axis(axis)
         o["_end"] = cur
+        self._offsets = o
         return o
+
+    def sizes(self) -> Dict[str, int]:
+        s = {name: self._axis(axis) for name, axis in CORE_FIELDS}
+        s.update({name: self._axis(axis) for name, (axis, _) in _EXTRA_FIELDS.items()})
+        return s
 
 
 class StepContext:
@@ -78,85 +128,114 @@ class StepContext:
         self.max_seg_len = max_seg_len      # longest portion of the step
         self.max_kv_len = max_kv_len        # longest sequence after the step
         self.rows_are_all_tokens = rows_are_all_tokens   # logit_rows == 0..N-1
-        o = layout.offsets()
-        N, S, R = self.n_tokens, self.n_segs, self.n_rows
-        self.token_ids = buf[o["token_ids"]:o["token_ids"] + N]
-        self.positions = buf[o["positions"]:o["positions"] + N]
-        self.seg_of_token = buf[o["seg_of_token"]:o["seg_of_token"] + N]
-        self.seg_start = buf[o["seg_start"]:o["seg_start"] + S + 1]
-        self.seg_pos0 = buf[o["seg_pos0"]:o["seg_pos0"] + S]
-        self.slots = buf[o["slots"]:o["slots"] + S]
-        self.logit_rows = buf[o["logit_rows"]:o["logit_rows"] + R]
+        o, sizes = layout.offsets(), layout.sizes()
+        for name, _ in CORE_FIELDS:         # ctx.token_ids, ctx.positions, ... ctx.tile_q0
+            setattr(self, name, buf[o[name]:o[name] + sizes[name]])
         self.n_tiles = layout.n_tiles
-        self.tile_seg = buf[o["tile_seg"]:o["tile_seg"] + layout.n_tiles]
-        self.tile_q0 = buf[o["tile_q0"]:o["tile_q0"] + layout.n_tiles]
+        S = self.n_segs
         self.block_tables = [
             buf[o[f"block_table{g}"]:o[f"block_table{g}"] + S * layout.max_pages].view(S, layout.max_pages)
             for g in range(layout.n_groups)]
+        self.extra = {name: buf[o[name]:o[name] + sizes[name]] for name in _EXTRA_FIELDS}
 
     @property
     def decode_only(self) -> bool:
         return self.max_seg_len == 1
 
 
-def pack_step(entries: List[StepEntry], starts: List[int], slots: List[int],
-              tables: List[List[List[int]]], layout: StepLayout, out: np.ndarray) -> None:
-    """Fill the packed host buffer.  ``starts[i]`` is entry i's first position, ``tables[g][i]``
-    its block table in group g."""
-    o = layout.offsets()
-    N = layout.n_tokens
-    tok = out[o["token_ids"]:o["token_ids"] + N]
-    pos = out[o["positions"]:o["positions"] + N]
-    seg = out[o["seg_of_token"]:o["seg_of_token"] + N]
-    seg_start = out[o["seg_start"]:o["seg_start"] + layout.n_segs + 1]
-    rows = out[o["logit_rows"]:o["logit_rows"] + layout.n_rows]
-    tile_seg = out[o["tile_seg"]:o["tile_seg"] + layout.n_tiles]
-    tile_q0 = out[o["tile_q0"]:o["tile_q0"] + layout.n_tiles]
-    if layout.n_tokens == layout.n_segs:
-        # single tokens only (decoding): no per-entry loops
-        S = layout.n_segs
-        tok[:] = [e.tokens[0] for e in entries]
-        pos[:] = starts
-        seg[:] = np.arange(S, dtype=np.int32)
-        seg_start[:] = np.arange(S + 1, dtype=np.int32)
-        tile_seg[:] = seg
-        tile_q0[:] = 0
-        r = 0
-        for i, e in enumerate(entries):
-            for w in e.want:
-                rows[r] = i + w
-                r += 1
-        _pack_tail(entries, starts, slots, tables, layout, out, o)
-        return
-    cur, r, nt = 0, 0, 0
+# ---- packing -----------------------------------------------------------------------------------------
+_E_NOT_LIVE, _E_CONTEXT, _E_PAGES, _E_BAD_ARG = -1, -4, -5, -6
+_E_TWICE, _E_EMPTY_SEG, _E_TOKEN, _E_WANT = -20, -21, -22, -23
+
+
+def _native_offsets(layout: StepLayout):
+    arr = getattr(layout, "_native_off", None)
+    if arr is None:
+        o = layout.offsets()
+        vals = [o[name] for name, _ in CORE_FIELDS] + [o[f"block_table{g}"] for g in range(layout.n_groups)]
+        layout._native_off = arr = (ctypes.c_int * len(vals))(*vals)
+        layout._native_sizes = (ctypes.c_int * 4)(layout.n_tokens, layout.n_segs, layout.n_rows, layout.n_tiles)
+    return arr, layout._native_sizes
+
+
+def prepare_step(cache, entries: Sequence[StepEntry], layout: StepLayout, out: np.ndarray, vocab: int,
+                 scratch_slot: int, scratch_pages: Sequence[int], tokens_known: bool = True):
+    """Check the entries, reserve the pages of all their requests (or of none) and fill ``out`` (int32,
+    ``layout.offsets()["_end"]`` long) in one native call.  An entry whose ``req_id`` is ``None`` is a
+    stand-in on the scratch slot and scratch pages.  With ``tokens_known=False`` the token ids are left
+    zero, to be filled in later.  Returns ``(fresh slots, longest sequence after the step)``; a refusal is
+    a :class:`GessoError` and leaves every request as it was."""
+    n = len(entries)
+    G = layout.n_groups
+    handles = (ctypes.c_int64 * n)()
+    n_new = (ctypes.c_int * n)()
+    want_n = (ctypes.c_int * n)()
+    toks: List[int] = []
+    wants: List[int] = []
     for i, e in enumerate(entries):
-        n = len(e.tokens)
-        for q0 in range(0, n, QUERY_TILE):
-            tile_seg[nt] = i
-            tile_q0[nt] = q0
-            nt += 1
-        tok[cur:cur + n] = np.asarray(e.tokens, dtype=np.int32)
-        pos[cur:cur + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
-        seg[cur:cur + n] = i
-        seg_start[i] = cur
-        k = len(e.want)
-        if k:
-            rows[r:r + k] = np.asarray(e.want, dtype=np.int64) + cur
-            r += k
-        cur += n
-    seg_start[layout.n_segs] = cur
-    _pack_tail(entries, starts, slots, tables, layout, out, o)
+        if e.req_id is not None:
+            h = cache.handle(e.req_id)
+            if h is None:
+                raise invalid(f"step: request {e.req_id!r} is not live (admit it first)")
+            handles[i] = h
+        k = n_new[i] = len(e.tokens)
+        want_n[i] = len(e.want)
+        if k < 1:
+            raise invalid(f"step: request {e.req_id!r} brings no tokens")
+        # ranges are checked here, on the values as given: the 32-bit arrays below would wrap a wider integer
+        try:
+            if tokens_known:
+                t = e.tokens.tolist() if isinstance(e.tokens, np.ndarray) else e.tokens
+                lo, hi = (t[0], t[0]) if k == 1 else (min(t), max(t))
+                if not (0 <= lo and hi < vocab):
+                    bad = next(x for x in t if not (0 <= x < vocab))
+                    raise invalid(f"step: token id {bad} of request {e.req_id!r} is outside the vocabulary (0..{vocab - 1})")
+                toks.extend(t)
+            if want_n[i]:
+                w = e.want.tolist() if isinstance(e.want, np.ndarray) else e.want
+                if not (0 <= min(w) and max(w) < k):
+                    bad = next(x for x in w if not (0 <= x < k))
+                    raise invalid(f"step: wanted place {bad} of request {e.req_id!r} is outside its {k} tokens")
+                wants.extend(w)
+        except TypeError:
+            raise invalid(f"step: tokens and wanted places of request {e.req_id!r} must be flat lists of integers") from None
+    try:
+        tok_arr = (ctypes.c_int * max(len(toks), 1))(*toks) if tokens_known else None
+        want_arr = (ctypes.c_int * max(len(wants), 1))(*wants)
+    except TypeError:
+        raise invalid("step: tokens and wanted places must be integers") from None
+    off, sizes = _native_offsets(layout)
+    scratch = (ctypes.c_int * (1 + G))(scratch_slot, *scratch_pages)
+    fresh = (ctypes.c_int * n)()
+    info = (ctypes.c_int * 8)()
+    e = hostlib.library().gesso_step_prepare(
+        cache.native(), handles, n_new, n, tok_arr, want_n, want_arr, off, len(off), sizes, G, layout.max_pages,
+        QUERY_TILE, int(vocab), scratch, ctypes.c_void_p(out.ctypes.data), int(out.size), fresh, info)
+    if e != 0:
+        raise _refusal(e, info, entries, cache, vocab)
+    if _EXTRA_FIELDS:
+        o, sz = layout.offsets(), layout.sizes()
+        for name, (_, fill) in _EXTRA_FIELDS.items():
+            fill(list(entries), out[o[name]:o[name] + sz[name]])
+    return list(fresh[:info[0]]), info[1]
 
 
-def _pack_tail(entries, starts, slots, tables, layout, out, o) -> None:
-    out[o["seg_pos0"]:o["seg_pos0"] + layout.n_segs] = np.asarray(starts, dtype=np.int32)
-    out[o["slots"]:o["slots"] + layout.n_segs] = np.asarray(slots, dtype=np.int32)
-    for g in range(layout.n_groups):
-        bt = out[o[f"block_table{g}"]:o[f"block_table{g}"] + layout.n_segs * layout.max_pages]
-        bt = bt.reshape(layout.n_segs, layout.max_pages)
-        bt[:] = FREED
-        for i, t in enumerate(tables[g]):
-            if isinstance(t, np.ndarray):
-                bt[i, :] = t                      # the manager's fixed-width row
-            elif t:
-                bt[i, :len(t)] = np.asarray(t, dtype=np.int32)
+def _refusal(e: int, info, entries, cache, vocab) -> GessoError:
+    i = info[4] if 0 <= info[4] < len(entries) else 0
+    rid = entries[i].req_id
+    if e == _E_TWICE:
+        return invalid(f"step: request {rid!r} appears twice in one step")
+    if e == _E_EMPTY_SEG:
+        return invalid(f"step: request {rid!r} brings no tokens")
+    if e == _E_TOKEN:
+        return invalid(f"step: token id {info[5]} of request {rid!r} is outside the vocabulary (0..{vocab - 1})")
+    if e == _E_WANT:
+        return invalid(f"step: wanted place {info[5]} of request {rid!r} is outside its {len(entries[i].tokens)} tokens")
+    if e == _E_NOT_LIVE:
+        return invalid(f"step: request {rid!r} is not live (admit it first)")
+    if e == _E_CONTEXT:
+        return resource(f"request {rid!r}: {cache.length(rid)}+{len(entries[i].tokens)} positions exceed the context "
+                        f"length {cache.max_positions}")
+    if e == _E_PAGES:
+        return resource("step needs " + cache.last_short())
+    return GessoError(ErrorCode.INTERNAL, f"step packer: the step does not fit its layout ({e})")

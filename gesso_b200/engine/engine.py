@@ -25,7 +25,7 @@ from ..cache.manager import CacheManager
 from .. import ops
 from ..csrc.lib import launch_count
 from ..errors import ErrorCode, GessoError, invalid, resource
-from .batch import QUERY_TILE, StepContext, StepEntry, StepLayout, count_tiles, pack_step
+from .batch import QUERY_TILE, StepContext, StepEntry, StepLayout, count_tiles, prepare_step
 from .model import Model, PagedView, StateView
 
 
@@ -40,6 +40,9 @@ class StagedStep:
     host: torch.Tensor
     max_kv: int
     all_rows: bool
+
+
+_ZERO_TOKEN = (0,)      # a stand-in's single token, and the place it wants
 
 
 class DeviceCache:
@@ -60,14 +63,19 @@ class DeviceCache:
         self.scratch_pages = [max(pages, 1) for pages in num_pages]
         self.scratch_slot = max(num_slots, 1)
         # One buffer for all fixed-size state, a slot's entries side by side (each padded to 128 bytes),
-        # so that a fresh slot is zeroed by one fill; entry i is the view [slots, *shape] into it.
-        sizes = [int(np.prod(need.shape)) for need, _ in plan.state_entries]
-        offsets = np.concatenate([[0], np.cumsum([-(-n // 32) * 32 for n in sizes])]).astype(int)
-        self._state_flat = torch.zeros((max(num_slots, 1) + 1, max(int(offsets[-1]), 1)), dtype=torch.float32,
+        # so that a fresh slot is zeroed by one fill; entry i is the view [slots, *shape] into it, in the
+        # dtype its need names.
+        dtypes = [getattr(torch, need.dtype, None) for need, _ in plan.state_entries]
+        for (need, _), t in zip(plan.state_entries, dtypes):
+            if not isinstance(t, torch.dtype):
+                raise invalid(f"state need: {need.dtype!r} is not a torch dtype")
+        nbytes = [int(np.prod(need.shape)) * t.itemsize for (need, _), t in zip(plan.state_entries, dtypes)]
+        offsets = np.concatenate([[0], np.cumsum([-(-n // 128) * 128 for n in nbytes])]).astype(int)
+        self._state_flat = torch.zeros((max(num_slots, 1) + 1, max(int(offsets[-1]), 128)), dtype=torch.uint8,
                                        device=dev)       # the last slot is the scratch slot of padded steps
         self.state: List[torch.Tensor] = [
-            self._state_flat[:, off:off + n].view((self._state_flat.shape[0],) + tuple(need.shape))
-            for (need, _), off, n in zip(plan.state_entries, offsets, sizes)]
+            self._state_flat[:, off:off + n].view(t).view((self._state_flat.shape[0],) + tuple(need.shape))
+            for (need, _), t, off, n in zip(plan.state_entries, dtypes, offsets, nbytes)]
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv + [self._state_flat])
@@ -139,41 +147,6 @@ class Engine:
         return self.cache.length(req_id)
 
     # ---- the step ----------------------------------------------------------------------------
-    def _validate(self, entries: Sequence[StepEntry]) -> List[StepEntry]:
-        """Check the entries; returns them with tokens and wanted places as integer arrays (one
-        conversion serves the checks and the packing of long portions)."""
-        if not entries:
-            raise invalid("step: no entries")
-        seen = set()
-        V = self.model.vocab_size
-        out = []
-        for e in entries:
-            if e.req_id in seen:
-                raise invalid(f"step: request {e.req_id!r} appears twice in one step")
-            seen.add(e.req_id)
-            if not self.cache.is_live(e.req_id):
-                raise invalid(f"step: request {e.req_id!r} is not live (admit it first)")
-            if self._broken and e.req_id in self._broken:
-                raise self._broken_error(e.req_id)
-            n = len(e.tokens)
-            if n < 1:
-                raise invalid(f"step: request {e.req_id!r} brings no tokens")
-            try:
-                toks = np.asarray(e.tokens, dtype=np.int64)
-                want = np.asarray(e.want, dtype=np.int64)
-            except (TypeError, ValueError, OverflowError):
-                raise invalid(f"step: tokens and wanted places of request {e.req_id!r} must be integers") from None
-            if toks.ndim != 1 or want.ndim != 1:
-                raise invalid(f"step: tokens and wanted places of request {e.req_id!r} must be flat lists")
-            if toks.min() < 0 or toks.max() >= V:
-                t = int(toks[(toks < 0) | (toks >= V)][0])
-                raise invalid(f"step: token id {t} of request {e.req_id!r} is outside the vocabulary (0..{V - 1})")
-            if want.size and (want.min() < 0 or want.max() >= n):
-                w = int(want[(want < 0) | (want >= n)][0])
-                raise invalid(f"step: wanted place {w} of request {e.req_id!r} is outside its {n} tokens")
-            out.append(StepEntry(e.req_id, toks, want))
-        return out
-
     def _pinned_buffer(self, n: int):
         i = self._pinned_next
         self._pinned_next = (i + 1) % len(self._pinned)
@@ -183,61 +156,54 @@ class Engine:
             self._pinned[i] = torch.empty((max(n, 4096),), dtype=torch.int32, pin_memory=True)
         return i, self._pinned[i]
 
-    def _prepare_single_tokens(self, entries: Sequence[StepEntry]):
-        """:meth:`_prepare` for a step of single tokens (decoding): the checks here, then one call of the
-        native manager reserves every request's next position and packs the step's metadata."""
-        V = self.model.vocab_size
-        for e in entries:
-            tok = e.tokens[0]
-            if not (0 <= tok < V):
-                raise invalid(f"step: token id {tok} of request {e.req_id!r} is outside the vocabulary (0..{V - 1})")
-            for w in e.want:
-                if w != 0:
-                    raise invalid(f"step: wanted place {w} of request {e.req_id!r} is outside its 1 tokens")
-            if not self.cache.is_live(e.req_id):
-                raise invalid(f"step: request {e.req_id!r} is not live (admit it first)")
-            if self._broken and e.req_id in self._broken:
-                raise self._broken_error(e.req_id)
-        n = len(entries)
-        layout = StepLayout(n_tokens=n, n_segs=n, n_rows=sum(1 for e in entries if len(e.want)),
-                            n_groups=len(self.cache.groups), max_pages=self.cache.max_pages_per_request, n_tiles=n)
-        size = layout.offsets()["_end"]
-        slot_i, host = self._pinned_buffer(size)
-        fresh, max_kv, _, written = self.cache.stage_single_tokens(
-            [e.req_id for e in entries], [int(e.tokens[0]) for e in entries], [len(e.want) > 0 for e in entries],
-            host.numpy()[:size])
-        if written != size:
-            raise GessoError(ErrorCode.INTERNAL, f"step metadata: {written} ints packed, layout has {size}")
-        for slot in fresh:
-            self.device_cache.zero_slot(slot)
-        self._all_rows = layout.n_rows == n
-        return layout, slot_i, host[:size], 1, max_kv
-
-    def _prepare(self, entries: Sequence[StepEntry]):
-        """Validate, reserve pages, zero fresh slots and pack the step's metadata on the host."""
+    def _prepare(self, entries: Sequence[StepEntry], tokens_known: bool = True):
+        """Check the entries, reserve pages (for all the step's requests or for none), zero fresh slots and
+        pack the step's metadata into pinned host memory: one call of the native step packer.  A mixed
+        step whose padded shape has a graph (or is due one) is filled up with stand-ins first."""
         self._padded_rows = None
-        if entries and all(len(e.tokens) == 1 and len(e.want) <= 1 for e in entries):
-            return self._prepare_single_tokens(entries)
-        entries = self._validate(entries)
-        # all-or-nothing across the batch, in one native call: every request's pages, or none and an error
-        starts, slots, fresh, max_kv, tables = self.cache.reserve_step([e.req_id for e in entries],
-                                                                       [len(e.tokens) for e in entries])
-        for slot in fresh:
-            self.device_cache.zero_slot(slot)
-        n_groups = len(self.cache.groups)
-        max_seg = max(len(e.tokens) for e in entries)
-        padded = self._padded_shape(entries)
+        if not entries:
+            raise invalid("step: no entries")
+        if self._broken:
+            for e in entries:
+                if e.req_id in self._broken:
+                    raise self._broken_error(e.req_id)
+        S = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        T, R = sum(lens), sum(len(e.want) for e in entries)
+        max_seg = max(lens) if lens else 0
+        n_groups, max_pages = len(self.cache.groups), self.cache.max_pages_per_request
+        padded = self._padded_shape(entries, S, T) if T > S else None
         if padded is not None:
-            return self._pack_padded(list(entries), starts, slots, tables, padded, max_kv)
-        layout = StepLayout(n_tokens=sum(len(e.tokens) for e in entries), n_segs=len(entries),
-                            n_rows=sum(len(e.want) for e in entries), n_groups=n_groups,
-                            max_pages=self.cache.max_pages_per_request,
-                            n_tiles=count_tiles(len(e.tokens) for e in entries))
+            T_b, S_b = padded
+            k = S_b - S                                   # stand-ins: k - 1 single tokens and one portion
+            portion = T_b - T - (k - 1)                   # >= 1
+            pad = [StepEntry(None, _ZERO_TOKEN, _ZERO_TOKEN) for _ in range(k - 1)]
+            # the portion wants what is left of the S_b rows (the same place over and over)
+            pad.append(StepEntry(None, [0] * portion, [0] * (S_b - R - (k - 1))))
+            packed = list(entries) + pad
+            layout = StepLayout(n_tokens=T_b, n_segs=S_b, n_rows=S_b, n_groups=n_groups, max_pages=max_pages,
+                                n_tiles=T_b // QUERY_TILE + S_b)
+            max_seg = max(max_seg, portion)
+        else:
+            packed = entries
+            layout = StepLayout(n_tokens=T, n_segs=S, n_rows=R, n_groups=n_groups, max_pages=max_pages,
+                                n_tiles=S if max_seg == 1 else count_tiles(lens))
         size = layout.offsets()["_end"]
         slot_i, host = self._pinned_buffer(size)
-        pack_step(list(entries), starts, slots, tables, layout, host.numpy()[:size])
-        self._all_rows = all(len(e.want) == len(e.tokens) and bool((e.want == np.arange(len(e.tokens))).all())
-                             for e in entries)
+        dc = self.device_cache
+        fresh, max_kv = prepare_step(self.cache, packed, layout, host.numpy()[:size], self.model.vocab_size,
+                                     dc.scratch_slot, dc.scratch_pages, tokens_known)
+        for slot in fresh:
+            dc.zero_slot(slot)
+        if padded is not None:
+            self._all_rows = False
+            self._padded_rows = R
+            return layout, slot_i, host[:size], layout.n_tokens, max_kv
+        if max_seg == 1:
+            self._all_rows = R == S
+        else:
+            self._all_rows = R == T and all(len(e.want) == len(e.tokens) and list(e.want) == list(range(len(e.tokens)))
+                                            for e in entries)
         return layout, slot_i, host[:size], max_seg, max_kv
 
     # ---- mixed steps in a few padded shapes, so that they replay graphs -------------------------------
@@ -248,12 +214,17 @@ class Engine:
     # ordinary entries to every kernel (what they compute is never read), so no kernel knows of padding.
     # Segments go up to a multiple of 8 (at least one stand-in), tokens to a multiple of 64, the wanted
     # rows to the number of segments, the attention tiles to the most that shape can have.
-    def _padded_shape(self, entries):
-        S, T = len(entries), sum(len(e.tokens) for e in entries)
-        if (not self.use_graphs or S < 2 or T > 8192 or T == S or any(len(e.want) > 1 for e in entries)):
+    def _padded_shape(self, entries, S: int, T: int):
+        if (not self.use_graphs or S < 2 or T > 8192 or any(len(e.want) > 1 for e in entries)):
             return None
         S_b = -(-(S + 1) // 8) * 8
         T_b = -(-(T + S_b - S) // 64) * 64
+        # The stand-in portion sits at positions 0 .. portion - 1 of a block table whose every entry is the
+        # scratch page, and reads the rotary table at those positions: it has to fit both (an engine with
+        # a context shorter than the padding runs its mixed steps unpadded).
+        portion = T_b - T - (S_b - S - 1)
+        if portion > min(self.cache.max_pages_per_request * self.page_size, self.max_positions):
+            return None
         key = (T_b, S_b, S_b, False)
         if key not in self._graphs:
             seen = self._portion_shapes.get(key, 0)
@@ -261,39 +232,6 @@ class Engine:
             if seen < 1 or sum(1 for k in self._graphs if k[0] > k[1] > 1) >= 48:
                 return None          # first time (or too many shapes already): as it is, launched one by one
         return T_b, S_b
-
-    def _pack_padded(self, entries, starts, slots, tables, shape, max_kv):
-        T_b, S_b = shape
-        S, T = len(entries), sum(len(e.tokens) for e in entries)
-        R = sum(len(e.want) for e in entries)
-        k = S_b - S                                   # stand-ins: k - 1 single tokens and one portion
-        portion = T_b - T - (k - 1)                   # >= 1
-        dc = self.device_cache
-        pad = [StepEntry(None, np.zeros((1,), dtype=np.int32), np.zeros((1,), dtype=np.int64)) for _ in range(k - 1)]
-        # the portion wants what is left of the S_b rows (the same place over and over)
-        pad.append(StepEntry(None, np.zeros((portion,), dtype=np.int32),
-                             np.zeros((S_b - R - (k - 1),), dtype=np.int64)))
-        n_groups = len(self.cache.groups)
-        max_pages = self.cache.max_pages_per_request
-        rows = [np.full((max_pages,), dc.scratch_pages[g], dtype=np.int32) for g in range(n_groups)]
-        all_entries = entries + pad
-        starts = list(starts) + [0] * k
-        slots = list(slots) + [dc.scratch_slot] * k
-        tables = [list(tables[g]) + [rows[g]] * k for g in range(n_groups)]
-        layout = StepLayout(n_tokens=T_b, n_segs=S_b, n_rows=S_b, n_groups=n_groups, max_pages=max_pages,
-                            n_tiles=T_b // QUERY_TILE + S_b)
-        size = layout.offsets()["_end"]
-        slot_i, host = self._pinned_buffer(size)
-        out = host.numpy()[:size]
-        pack_step(all_entries, starts, slots, tables, layout, out)
-        # the tiles that this step does not have repeat the stand-in portion's first one
-        o = layout.offsets()
-        used = count_tiles(len(e.tokens) for e in all_entries)
-        out[o["tile_seg"] + used:o["tile_seg"] + layout.n_tiles] = S_b - 1
-        out[o["tile_q0"] + used:o["tile_q0"] + layout.n_tiles] = 0
-        self._all_rows = False
-        self._padded_rows = R
-        return layout, slot_i, host[:size], T_b, max_kv
 
     def _upload(self, buf: torch.Tensor, slot_i: int, host: torch.Tensor) -> None:
         buf.copy_(host, non_blocking=True)
@@ -310,19 +248,21 @@ class Engine:
         return StepContext(layout, buf, self.status, max_seg, max_kv, self._all_rows)
 
     def views(self, ctx: StepContext):
+        """Per schedule entry what its mixer declared: ``None``, one view, or a tuple of views."""
         plan, dc = self.model.cache_plan, self.device_cache
         out = []
-        for e, p in enumerate(plan.entries):
-            if p.kind == "paged":
-                kv = dc.kv[p.group][p.index]
-                # K pages are [page, kv head, slot, feature]; V pages hold the same bytes as
-                # [page, kv head, feature, slot]
-                v = kv[1].view(kv.shape[1], kv.shape[2], kv.shape[4], kv.shape[3])
-                out.append(PagedView(kv[0], v, ctx.block_tables[p.group], writes=(p.owner == e)))
-            elif p.kind == "state":
-                out.append(StateView(dc.state[p.index], ctx.slots, writes=(p.owner == e)))
-            else:
-                out.append(None)
+        for e, plans in enumerate(plan.entries):
+            views = []
+            for p in plans:
+                if p.kind == "paged":
+                    kv = dc.kv[p.group][p.index]
+                    # K pages are [page, kv head, slot, feature]; V pages hold the same bytes as
+                    # [page, kv head, feature, slot]
+                    v = kv[1].view(kv.shape[1], kv.shape[2], kv.shape[4], kv.shape[3])
+                    views.append(PagedView(kv[0], v, ctx.block_tables[p.group], writes=(p.owner == e)))
+                else:
+                    views.append(StateView(dc.state[p.index], ctx.slots, writes=(p.owner == e)))
+            out.append(None if not views else views[0] if plan.single[e] else tuple(views))
         return out
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -380,8 +320,8 @@ class Engine:
         staged step that is never run costs nothing but its page reservations, which the requests keep."""
         if not self.use_graphs or not req_ids or len(req_ids) > self.max_graph_batch:
             return None
-        entries = [StepEntry(rid, [0], [0]) for rid in req_ids]
-        layout, slot_i, host, _, max_kv = self._prepare_single_tokens(entries)
+        entries = [StepEntry(rid, _ZERO_TOKEN, _ZERO_TOKEN) for rid in req_ids]
+        layout, slot_i, host, _, max_kv = self._prepare(entries, tokens_known=False)
         return StagedStep(tuple(req_ids), layout, slot_i, host, max_kv, self._all_rows)
 
     def step_staged(self, staged: StagedStep, tokens: Optional[Sequence[int]] = None,

@@ -53,14 +53,14 @@ class PagedView:
 
 @dataclass
 class StateView:
-    state: torch.Tensor          # [slots, *shape] float32
+    state: torch.Tensor          # [slots, *shape], the need's dtype
     slots: torch.Tensor          # [segments] int32
     writes: bool = True
 
 
 @dataclass
 class CacheSlotPlan:
-    kind: str                    # "paged" | "state" | "none"
+    kind: str                    # "paged" | "state"
     owner: int                   # schedule entry that owns the cache
     group: int = -1              # paged group index
     index: int = -1              # index inside the group / among the state tensors
@@ -68,44 +68,64 @@ class CacheSlotPlan:
 
 
 class CachePlan:
-    """Which cache every schedule entry uses, and the groups those caches form."""
+    """Which caches every schedule entry uses, and the groups those caches form.
+
+    A mixer declares no need, one, or a list of page and state needs (``Mixer.cache_need``);
+    ``entries[e]`` lists the plans of schedule entry e in the order of its needs, and ``single[e]`` says
+    that the mixer declared one bare need (its ``forward`` then gets the view itself, not a tuple)."""
 
     def __init__(self, spec: ModelSpec, blocks):
-        self.entries: List[CacheSlotPlan] = []
-        self.paged_groups: List[Tuple[PagedNeed, List[int]]] = []     # need, owning entries
-        self.state_entries: List[Tuple[StateNeed, int]] = []          # need, owning entry
+        self.entries: List[List[CacheSlotPlan]] = []
+        self.single: List[bool] = []
+        self.paged_groups: List[Tuple[PagedNeed, List[Tuple[int, int]]]] = []     # need, owning (entry, need index)
+        self.state_entries: List[Tuple[StateNeed, int]] = []                      # need, owning entry
         group_of: Dict[PagedNeed, int] = {}
         for e, entry in enumerate(spec.schedule):
             if not (0 <= entry.layer < len(blocks)):
                 raise invalid(f"schedule entry {e}: layer {entry.layer} does not exist")
-            need = blocks[entry.layer].cache_need()
-            if need is None:
-                self.entries.append(CacheSlotPlan("none", e))
-                continue
-            if entry.cache_of is not None:
+            declared = blocks[entry.layer].cache_need()
+            needs = [] if declared is None else (list(declared) if isinstance(declared, (list, tuple)) else [declared])
+            self.single.append(declared is not None and not isinstance(declared, (list, tuple)))
+            for need in needs:
+                if not isinstance(need, (PagedNeed, StateNeed)):
+                    raise invalid(f"schedule entry {e}: unknown cache need {need!r}")
+            if entry.cache_of is not None and needs:
                 o = entry.cache_of
-                if not (0 <= o < e) or spec.schedule[o].cache_of is not None:
+                if not (0 <= o < e) or spec.schedule[o].cache_of is not None or not self.entries[o]:
                     raise invalid(f"schedule entry {e}: cache_of must name an earlier entry that owns a cache")
-                op = self.entries[o]
-                same = (isinstance(need, PagedNeed) and op.kind == "paged"
-                        and (need.n_kv_heads, need.head_dim) == (op.need.n_kv_heads, op.need.head_dim)) or \
-                       (isinstance(need, StateNeed) and op.kind == "state" and need.shape == op.need.shape)
-                if not same:
+                theirs = self.entries[o]
+                if len(theirs) != len(needs):
                     raise invalid(f"schedule entry {e}: the cache of entry {o} has another geometry")
-                self.entries.append(CacheSlotPlan(op.kind, o, op.group, op.index, need))
+                plans = []
+                for need, op in zip(needs, theirs):
+                    same = (isinstance(need, PagedNeed) and op.kind == "paged"
+                            and (need.n_kv_heads, need.head_dim) == (op.need.n_kv_heads, op.need.head_dim)) or \
+                           (isinstance(need, StateNeed) and op.kind == "state"
+                            and (need.shape, need.dtype) == (op.need.shape, op.need.dtype))
+                    if not same:
+                        raise invalid(f"schedule entry {e}: the cache of entry {o} has another geometry")
+                    if isinstance(need, PagedNeed) and op.need.window is not None and \
+                            (need.window is None or need.window > op.need.window):
+                        # the owner's window decides when pages are given back: a reader that looks further
+                        # back would find them gone (and silently attend to fewer keys)
+                        raise invalid(f"schedule entry {e}: reads the cache of entry {o} with a window of "
+                                      f"{need.window or 'all'} keys, but that cache keeps only {op.need.window}")
+                    plans.append(CacheSlotPlan(op.kind, o, op.group, op.index, need))
+                self.entries.append(plans)
                 continue
-            if isinstance(need, PagedNeed):
-                if need not in group_of:
-                    group_of[need] = len(self.paged_groups)
-                    self.paged_groups.append((need, []))
-                g = group_of[need]
-                self.paged_groups[g][1].append(e)
-                self.entries.append(CacheSlotPlan("paged", e, g, len(self.paged_groups[g][1]) - 1, need))
-            elif isinstance(need, StateNeed):
-                self.state_entries.append((need, e))
-                self.entries.append(CacheSlotPlan("state", e, -1, len(self.state_entries) - 1, need))
-            else:
-                raise invalid(f"schedule entry {e}: unknown cache need {need!r}")
+            plans = []
+            for k, need in enumerate(needs):
+                if isinstance(need, PagedNeed):
+                    if need not in group_of:
+                        group_of[need] = len(self.paged_groups)
+                        self.paged_groups.append((need, []))
+                    g = group_of[need]
+                    self.paged_groups[g][1].append((e, k))
+                    plans.append(CacheSlotPlan("paged", e, g, len(self.paged_groups[g][1]) - 1, need))
+                else:
+                    self.state_entries.append((need, e))
+                    plans.append(CacheSlotPlan("state", e, -1, len(self.state_entries) - 1, need))
+            self.entries.append(plans)
 
     def group_specs(self) -> List[PagedGroupSpec]:
         return [PagedGroupSpec(f"kv{n.n_kv_heads}x{n.head_dim}" + (f"w{n.window}" if n.window else ""), n.window)
@@ -152,9 +172,9 @@ class Model:
         if ctx.rows_are_all_tokens and pending[0] is None:
             # every token's logits are wanted, in order: no gather, and the norm can ride in the
             # prologue of the head's matrix product
-            try:
+            if getattr(self.final_norm, "supports_lazy", False):
                 x = self.final_norm.add_norm(h, None, None, lazy=True)
-            except TypeError:
+            else:
                 x = self.final_norm.add_norm(h, None, None)
         else:
             x = self.final_norm.add_norm(h, pending[0], pending[1], rows=ctx.logit_rows)

@@ -13,7 +13,8 @@ Interfaces
                  returns the normed rows in the run dtype.
 ``Position``     ``bind(rt)``, ``tables(max_positions) -> (cos, sin)`` or
                  whatever its consumer mixer expects.
-``Mixer``        ``param_decls()``, ``cache_need()``, ``bind(tensors, rt)``,
+``Mixer``        ``param_decls()``, ``cache_need()`` (none, one need, or a list of
+                 page and state needs), ``bind(tensors, rt)``,
                  ``forward(x, ctx, cache) -> (delta, delta_bias)``.
 ``FeedForward``  ``param_decls()``, ``bind(tensors, rt)``,
                  ``forward(x, ctx) -> (delta, delta_bias)``.
@@ -60,9 +61,11 @@ class PagedNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A per-request state of fixed ``shape`` (float32), zero at the start of a request."""
+    """A per-request state of fixed ``shape``, zero at the start of a request.  ``dtype`` is the name of a
+    torch dtype (``float32``, ``bfloat16``, ``int32``, ...)."""
 
     shape: Tuple[int, ...]
+    dtype: str = "float32"
 
 
 class Part:
@@ -84,7 +87,9 @@ class Part:
 
 class Mixer(Part):
     def cache_need(self):
-        """``PagedNeed``, ``StateNeed`` or ``None``."""
+        """What this mixer keeps per request between steps: ``None``, one ``PagedNeed`` or ``StateNeed``
+        (``forward`` then gets that one view as ``cache``), or a list of them, pages and states in any
+        mix (``forward`` gets a tuple of views in the same order)."""
         return None
 
     def forward(self, x, ctx, cache):
@@ -97,6 +102,10 @@ class FeedForward(Part):
 
 
 class Norm(Part):
+    # True if ``add_norm`` takes ``lazy=True``: with nothing to add it may then return a norm that has not
+    # run yet (``ops.LazyNorm``) for a consumer that can apply it in the prologue of its matrix product.
+    supports_lazy = False
+
     def add_norm(self, h, delta, delta_bias, rows=None):
         raise NotImplementedError
 

@@ -69,11 +69,8 @@ class PreNormBlock:
 
     @staticmethod
     def _norm(norm, consumer, h, pending):
-        if getattr(consumer, "accepts_lazy_norm", False):
-            try:
-                return norm.add_norm(h, pending[0], pending[1], lazy=True)
-            except TypeError:          # a norm part without the lazy option
-                pass
+        if getattr(consumer, "accepts_lazy_norm", False) and getattr(norm, "supports_lazy", False):
+            return norm.add_norm(h, pending[0], pending[1], lazy=True)
         return norm.add_norm(h, pending[0], pending[1])
 
 

@@ -20,6 +20,8 @@ from .registry import register_norm
 
 
 class RMSNorm(Norm):
+    supports_lazy = True
+
     def __init__(self, spec):
         super().__init__(spec)
         self.size = int(spec["size"])

@@ -191,6 +191,43 @@ def test_mixed_steps_in_padded_shapes_replay_graphs(dtype, tol, models, plain_mo
     assert eng.stats()["pages_in_use"] == [0]
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL32), ("bfloat16", TOL16)])
+def test_mixed_steps_of_an_engine_with_a_short_context_stay_unpadded(dtype, tol, models, plain_models):
+    """The stand-in portion of a padded step sits at positions 0 .. up to 63 of a block table and of the
+    rotary table.  An engine whose context is shorter than that (32 positions, two pages a request) has
+    neither: its mixed steps must run as they are, and the repeated shapes below must not reach beyond a
+    block-table row or the table of angles (a page id read from there once sent K and V of the stand-in
+    into a live request's page)."""
+    from gesso_b200.engine import Engine, StepEntry
+    model = models("c", dtype)
+    plain = plain_models["c"]
+    seqs = prompts_for("c", [32, 30, 31], seed=77)
+    ref = [plain.logits(seq).numpy() for seq in seqs]
+    eng = Engine(model, max_positions=32, page_size=16, num_pages=6, max_requests=3)
+    for i in range(3):
+        eng.admit(i)
+    fed = [0, 0, 0]
+    for turn in range(40):
+        live = [i for i in range(3) if fed[i] < len(seqs[i])]
+        if not live:
+            break
+        entries, places = [], []
+        for i in live:          # the same two shapes over and over: 5 + 1 + 1 tokens, then 1 + 5 + 1, ...
+            n = min(5 if i == live[turn % len(live)] else 1, len(seqs[i]) - fed[i])
+            entries.append(StepEntry(i, seqs[i][fed[i]:fed[i] + n], [n - 1]))
+            places.append((i, fed[i] + n - 1))
+            fed[i] += n
+        logits = eng.step(entries).cpu().numpy().astype(np.float64)
+        for row, (i, pos) in enumerate(places):
+            err = float(np.abs(logits[row] - ref[i][pos]).max())
+            assert err <= tol * max(1.0, float(np.abs(ref[i][pos]).max())), (turn, i, pos, err)
+    eng.check_status()
+    assert fed == [32, 30, 31] and eng.stats()["padded_steps"] == 0
+    for i in range(3):
+        eng.release(i)
+    eng.cache.check_invariants()
+
+
 def test_sampled_ids_follow_the_plain_sampler(models, plain_models):
     import gesso_b200
     from plain_lfm2 import PlainSampler
@@ -234,8 +271,8 @@ def test_a_status_word_set_during_a_step_fails_that_steps_requests_only(models):
     back) and the others go on (src/Runtime/Runtime.jl:151-153, 175-178).  The word is set from the host
     here, between two steps: no kernel is made to fail."""
     import gesso_b200
-    model = models("c", "bfloat16")
-    prompts = prompts_for("c", [9, 30, 4, 12], seed=5)
+    model = models("a", "float32")         # float32: a request's ids do not depend on who else is in the batch
+    prompts = prompts_for("a", [9, 30, 4, 12], seed=5)
     alone = [gesso_b200.Session(model, context_length=128, max_batch=1).generate(p, 8) for p in prompts]
     for word in (0, 1):
         s = gesso_b200.Session(model, context_length=128, max_batch=2)

@@ -226,8 +226,8 @@ def test_schedule_names_a_layer_twice_and_shares_a_cache(dtype):
     spec = tiny_spec([attn_spec(), conv_spec(), attn_spec(window=6)], schedule=sched)
     model, w = build_model(spec, dtype, seed=3)
     plan = model.cache_plan
-    assert [p.kind for p in plan.entries] == ["paged", "state", "paged", "paged", "state"]
-    assert plan.entries[3].owner == 0 and plan.entries[2].owner == 2 and len(plan.state_entries) == 2
+    assert [[p.kind for p in ps] for ps in plan.entries] == [["paged"], ["state"], ["paged"], ["paged"], ["state"]]
+    assert plan.entries[3][0].owner == 0 and plan.entries[2][0].owner == 2 and len(plan.state_entries) == 2
     ids = torch.randint(0, 64, (37,), generator=torch.Generator().manual_seed(1)).tolist()
     want = plain_forward(spec, w, ids, sched)
     tol = 1e-4 if dtype == torch.float32 else 32 * 2.0 ** -9
@@ -351,6 +351,126 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     finally:
         unregister_architecture("ToyDecayLM")
         unregister("mixer", "toy_decay")
+
+
+def test_a_reader_may_not_look_further_back_than_the_cache_it_reads_keeps():
+    """The owner's window decides when pages are given back: a reader with a wider window (or none) over a
+    windowed cache would silently attend to fewer keys, so the plan refuses it; a narrower reader is fine."""
+    from gesso_b200.config import ScheduleEntry
+    from gesso_b200.errors import GessoError
+    sched = (ScheduleEntry(0), ScheduleEntry(1, cache_of=0))
+    for owner, reader, ok in ((6, None, False), (6, 9, False), (6, 6, True), (6, 3, True), (None, 5, True), (None, None, True)):
+        spec = tiny_spec([attn_spec(window=owner), attn_spec(window=reader)], schedule=sched)
+        if ok:
+            build_model(spec, torch.float32)
+        else:
+            with pytest.raises(GessoError, match="keeps only 6"):
+                build_model(spec, torch.float32)
+
+
+# ---- a toy mixer that needs pages AND two states, defined here ----------------------------------------------
+def register_toy_hybrid():
+    from gesso_b200 import ops
+    from gesso_b200.parts import Mixer, PagedNeed, ParamDecl, StateNeed, register_mixer
+
+    class HybridMixer(Mixer):
+        """Causal attention over pages (one head, no position encoding, no q/k norm) whose output is gated by
+        a running mean of the inputs kept in a float32 state, beside an int32 state that counts the tokens
+        seen: three caches declared as a list, handed to ``forward`` as a tuple in the same order."""
+
+        graph_safe = False
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.hidden = int(spec["hidden_size"])
+
+        def param_decls(self):
+            return {"qkv.weight": ParamDecl((3 * self.hidden, self.hidden), fan_in=self.hidden)}
+
+        def cache_need(self):
+            return [PagedNeed(1, self.hidden), StateNeed((self.hidden,)), StateNeed((1,), dtype="int32")]
+
+        def bind(self, tensors, rt):
+            self.w, self.rt = tensors["qkv.weight"], rt
+
+        def forward(self, x, ctx, cache):
+            pages, mean, count = cache
+            assert count.state.dtype == torch.int32 and mean.state.dtype == torch.float32
+            H = self.hidden
+            qkv = ops.linear(x, self.w, out_dtype=x.dtype)
+            q = ops.qk_norm_rope_store(qkv, None, None, 0.0, None, None, ctx.positions, ctx.seg_of_token,
+                                       pages.block_table, pages.k_pages, pages.v_pages, 1, 1, H, True, ctx.status)
+            o = self.rt.attention(q, pages, ctx, None, 1.0 / H ** 0.5).float()
+            starts, slots = ctx.seg_start.tolist(), mean.slots.tolist()
+            for s in range(ctx.n_segs):
+                m, n = mean.state[slots[s]].clone(), int(count.state[slots[s]].item())
+                for t in range(starts[s], starts[s + 1]):
+                    n += 1
+                    m = m + (x[t].float() - m) / n
+                    o[t] = o[t] * torch.tanh(m)
+                mean.state[slots[s]] = m
+                count.state[slots[s]] = n
+            return o.to(x.dtype), None
+
+    register_mixer("toy_hybrid", HybridMixer, replace=True)
+
+
+def test_toy_mixer_with_pages_and_states_registers_builds_and_steps():
+    from gesso_b200.config import PartSpec
+    from gesso_b200.engine import Engine, StepEntry
+    from gesso_b200.parts import unregister
+    register_toy_hybrid()
+    try:
+        H = 32
+        spec = tiny_spec([PartSpec("toy_hybrid", {"hidden_size": H}), conv_spec(hidden_size=H)], H=H)
+        model, w = build_model(spec, torch.float32, seed=6)
+        plan = model.cache_plan
+        assert [[p.kind for p in ps] for ps in plan.entries] == [["paged", "state", "state"], ["state"]]
+        assert plan.single == [False, True] and len(plan.paged_groups) == 1 and len(plan.state_entries) == 3
+
+        def plain(ids):
+            h = P.embedding(w["embedding.weight"], ids)
+            for b in spec.blocks:
+                p = b.prefix
+                xn = P.rmsnorm(h, w[p + "mixer_norm.weight"], 1e-5)
+                if b.mixer.kind == "toy_hybrid":
+                    q, k, v = (xn @ w[p + "mixer.qkv.weight"].T).split(H, dim=1)
+                    o = P.causal_attention(q[:, None], k[:, None], v[:, None])[:, 0]
+                    m, rows = torch.zeros(H, dtype=torch.float64), []
+                    for t in range(len(ids)):
+                        m = m + (xn[t] - m) / (t + 1)
+                        rows.append(o[t] * torch.tanh(m))
+                    mix = torch.stack(rows)
+                else:
+                    mix = P.short_conv_mixer(xn, w[p + "mixer.in_proj.weight"], w[p + "mixer.conv.weight"],
+                                             w[p + "mixer.out_proj.weight"])
+                h = h + mix
+                h = h + P.swiglu_ffn(P.rmsnorm(h, w[p + "ff_norm.weight"], 1e-5), w[p + "feed_forward.gate_proj.weight"],
+                                     w[p + "feed_forward.up_proj.weight"], w[p + "feed_forward.down_proj.weight"])
+            return P.rmsnorm(h, w["final_norm.weight"], 1e-5) @ w["embedding.weight"].T
+
+        g = torch.Generator().manual_seed(3)
+        a, b = torch.randint(0, 64, (23,), generator=g).tolist(), torch.randint(0, 64, (6,), generator=g).tolist()
+        eng = Engine(model, max_positions=64, page_size=4, num_pages=10, max_requests=2)
+        eng.admit("a")
+        eng.admit("b")
+        got_a = [eng.step([StepEntry("a", a[:9], list(range(9)))])]
+        out = eng.step([StepEntry("b", b, list(range(6))), StepEntry("a", a[9:12], [0, 1, 2])])     # mixed batch
+        got_b = out[:6]
+        got_a.append(out[6:])
+        for t in range(12, 23):
+            got_a.append(eng.step([StepEntry("a", [a[t]], [0])]))
+        eng.check_status()
+        assert rel_err(torch.cat(got_a), plain(a)) < 1e-5 and rel_err(got_b, plain(b)) < 1e-5
+        eng.release("b")
+        eng.admit("c")                                     # b's slot and pages again: states start from zero
+        assert rel_err(eng.step([StepEntry("c", b, list(range(6)))]), plain(b)) < 1e-5
+        eng.release("a")
+        eng.release("c")
+        eng.cache.check_invariants()
+        assert eng.cache.pages_in_use() == [0]
+    finally:
+        unregister("mixer", "toy_hybrid")
 
 
 # ---- a toy feed-forward with routing and a toy position encoding, defined here ---------------------------
