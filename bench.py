@@ -21,7 +21,23 @@ One JSON line is printed:
   flops / time / the bf16 peak;
 * ``roofline``: bytes a decode step has to read (every weight once + the cache of the live requests)
   / its time, against the measured copy bandwidth;
-* ``points``: decode tokens per second at batch 1 and 64.
+* ``points``: decode tokens per second at batch 1 and 64 (context 4,096) and at batch 8 with contexts of
+  512 and 2,048; ``rooflines``: the same fraction as ``roofline`` for every decode point;
+* ``blocks``: the timed steps cut into 8 blocks by events on the stream (no host wait between them): the
+  median and the extremes of their per-step times, beside the one bracket around all K steps that ``value``
+  comes from (the reference's rule: warm up, report samples, benchmark/runbenchmarks.jl:5-10);
+* ``cpu_baseline``: the plain float64 implementation of the tests (``tests/plain_lfm2.py``: whole
+  sequences, no cache, CPU) generating greedily at the two tiny configurations, in tokens per second.
+
+Other workloads, each printing one JSON line of its own:
+
+    python bench.py --workload serve350m     # LFM2-350M sizes: 64 live requests, prompts of 128-2,048 tokens
+                                             # in portions of 512 beside the decoding requests
+    python bench.py --workload serve700m     # LFM2-700M sizes: 32 requests, prompts of 64-4,096 tokens,
+                                             # 256 new tokens each, temperature 0.8
+
+both through ``Session.run_batch`` (scheduler, cache manager, sampler), with the host and device time of
+a step.
 
 Peaks come from ``MEASURED_PEAKS.json`` beside this file when the driver wrote it, else the
 fallback of an earlier measurement on this pool (6.65 TB/s, 1.59 PFLOP/s).
@@ -72,14 +88,17 @@ class ClockSampler(threading.Thread):
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
+    def __init__(self, uuid=None):
         super().__init__(daemon=True)
         self.samples, self.stop_flag = [], threading.Event()
+        # the device this process computes on, by UUID: index 0 of nvidia-smi is another GPU when the
+        # process sees one of several through CUDA_VISIBLE_DEVICES
+        self.gpu = str(uuid) if uuid else "0"
 
     def run(self):
         while not self.stop_flag.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                out = subprocess.run(["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
                                      capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
                 if out:
                     self.samples.append([x.strip() for x in out[0].split(",")])
@@ -103,7 +122,17 @@ class ClockSampler(threading.Thread):
                     reasons.add(n)
         mhz.sort()
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+                "samples": len(mhz), "gpu": self.gpu}
+
+
+def device_uuid():
+    """``GPU-...`` of cuda:0 as nvidia-smi names it."""
+    import torch
+    try:
+        u = str(torch.cuda.get_device_properties(0).uuid)
+        return u if u.startswith("GPU-") else "GPU-" + u
+    except Exception:
+        return None
 
 
 def model_flops_per_token(cfg_obj, n_layers_attn, n_layers_conv):
@@ -150,13 +179,22 @@ def time_decode(gb, model, batch, context, steps, warmup, page_size):
         one(k)
     torch.cuda.synchronize()
     launches0 = eng.launches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for k in range(warmup, warmup + steps):
-        one(k)
-    e1.record()
+    # one bracket around all K steps, and events on the stream that cut them into blocks (no host wait)
+    n_blocks = min(8, steps)
+    cuts = [round(i * steps / n_blocks) for i in range(n_blocks + 1)]
+    marks = [torch.cuda.Event(enable_timing=True) for _ in cuts]
+    marks[0].record()
+    nxt = 1
+    for k in range(steps):
+        one(warmup + k)
+        if k + 1 == cuts[nxt]:
+            marks[nxt].record()
+            nxt += 1
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    ms = marks[0].elapsed_time(marks[-1])
+    per_block = sorted(marks[i].elapsed_time(marks[i + 1]) / (cuts[i + 1] - cuts[i]) for i in range(n_blocks))
+    time_decode.blocks = {"n": n_blocks, "ms_per_step_median": round(per_block[n_blocks // 2], 4),
+                          "ms_per_step_min": round(per_block[0], 4), "ms_per_step_max": round(per_block[-1], 4)}
     launches = eng.launches - launches0 + steps          # + the argmax launch of every step
     eng.check_status()
     kv_len_mid = start_len + warmup + steps // 2
@@ -187,7 +225,7 @@ def time_e2e(gb, model, batch, context, steps, warmup, page_size):
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     h2d = (s.engine.h2d_bytes - h2d0) / steps
-    d2h = 2 * 4 * batch                                     # ids + flags read back, int32 each
+    d2h = 2 * 4 * batch + 2 * 4                             # ids + flags read back (int32 each) and the two status words
     return emitted / dt, h2d, d2h
 
 
@@ -215,6 +253,129 @@ def time_prefill(gb, model, tokens, page_size, reps=5):
     return best
 
 
+def cpu_baseline():
+    """The timed CPU baseline: the plain implementation of the tests (float64, whole sequences, no cache, one
+    function per part, ``tests/plain_lfm2.py``) generating greedily at the two tiny configurations with
+    the prompts the configurations name.  It is a restatement of the reference's formulas, not the
+    reference (a Julia project that cannot run here)."""
+    import tempfile
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import configs
+    from plain_lfm2 import PlainModel
+    from gesso_b200.weights import write_random_model
+    out = {"what": "tests/plain_lfm2.py (float64, no cache) on the CPU, greedy, tokens/s"}
+    g = torch.Generator().manual_seed(0)
+    for name, lengths, n_new in (("a", [7, 13, 1], 8), ("b", [1, 9, 17, 28, 40], 8)):
+        cfg, seed, _ = configs.TINY[name]
+        with tempfile.TemporaryDirectory() as d:
+            write_random_model(d, cfg, seed)
+            plain = PlainModel(d)
+            prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+            t0 = time.perf_counter()
+            for p in prompts:
+                plain.greedy(p, n_new)
+            out[f"tiny_{name}"] = round(len(prompts) * n_new / (time.perf_counter() - t0), 1)
+    return out
+
+
+SERVE = {
+    # BASELINE configuration 4: LFM2-350M layer sizes, a mixed batch of 64 decodes beside 512-token portions,
+    # random prompts of 128 to 2,048 tokens
+    "serve350m": dict(hidden=1024, heads=16, block_ff=6656, requests=96, max_batch=64, prompt=(128, 2048), new=64,
+                      chunk=512, temperature=0.0, top_p=1.0, context=2304),
+    # BASELINE configuration 5: LFM2-700M layer sizes, 32 concurrent requests, prompts of 64 to 4,096 tokens,
+    # 256 new tokens each, temperature 0.8
+    "serve700m": dict(hidden=1536, heads=24, block_ff=10240, requests=32, max_batch=32, prompt=(64, 4096), new=256,
+                      chunk=512, temperature=0.8, top_p=0.95, context=4352),
+}
+
+
+def serve_workload(name: str) -> int:
+    """One of the serving-like runs through ``Session.run_batch``; the second run of the workload is timed
+    (the first captures the graphs a serving process would have long had)."""
+    import torch
+    import gesso_b200 as gb
+    w = SERVE[name]
+    cfg = dict(LFM2_1_2B, hidden_size=w["hidden"], num_attention_heads=w["heads"], block_ff_dim=w["block_ff"])
+    model = gb.random_model(cfg, seed=0, dtype="bfloat16", max_positions=w["context"])
+    pages = w["max_batch"] * ((w["context"] + 15) // 16)
+
+    def run(seed):
+        g = torch.Generator().manual_seed(seed)
+        lens = torch.randint(w["prompt"][0], w["prompt"][1] + 1, (w["requests"],), generator=g).tolist()
+        prompts = [torch.randint(0, model.vocab_size, (n,), generator=g).tolist() for n in lens]
+        s = run.session
+        reqs = [gb.BatchRequest(p, max_new_tokens=w["new"], temperature=w["temperature"], top_p=w["top_p"], seed=i)
+                for i, p in enumerate(prompts)]
+        steps0, tokens0 = s.engine.steps_run, s.engine.tokens_run
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        t0 = time.perf_counter()
+        res = s.run_batch(reqs)
+        e1.record()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        assert all(r.status == "complete" for r in res), [(r.status, r.error) for r in res if r.status != "complete"][:2]
+        new = sum(len(r.ids) for r in res) - sum(lens)
+        return {"seconds": dt, "steps": s.engine.steps_run - steps0, "tokens": s.engine.tokens_run - tokens0,
+                "new_tokens": new, "device_ms": e0.elapsed_time(e1), "preemptions": s.stats()["preemptions"]}
+
+    run.session = gb.Session(model, context_length=w["context"], page_size=16, num_pages=pages, max_batch=w["max_batch"],
+                             max_tokens_per_step=4096, prefill_chunk=w["chunk"])
+    sampler = ClockSampler(device_uuid())
+    sampler.start()
+    run(1)
+    r = run(2)
+    clocks = sampler.summary()
+    # host time of a step: the wall time of the run minus the time the device was the one being waited for
+    # cannot be read from outside; what can is the wall time per step beside the device-busy time per step
+    busy_ms = device_busy_ms(run, 3)
+    print(json.dumps({
+        "workload": name, "metric": "tokens/s through Session.run_batch (prompt and new tokens; new tokens alone)",
+        "value": round(r["tokens"] / r["seconds"], 1), "new_tokens_per_s": round(r["new_tokens"] / r["seconds"], 1),
+        "unit": "tokens/s", "seconds": round(r["seconds"], 4), "steps": r["steps"],
+        "wall_ms_per_step": round(1000 * r["seconds"] / r["steps"], 4),
+        "device_busy_ms_per_step": round(busy_ms["busy_ms"] / busy_ms["steps"], 4),
+        "host_ms_per_step": round(busy_ms["host_s"] * 1000 / busy_ms["steps"], 4),
+        "preemptions": r["preemptions"], "dtype": "bf16", "data": "synthetic (uniform-random token ids, random weights seed 0)",
+        "config": dict({k: v for k, v in w.items() if not isinstance(v, tuple)}, prompt_min=w["prompt"][0],
+                       prompt_max=w["prompt"][1], layers=cfg["num_hidden_layers"], vocab=cfg["vocab_size"]),
+        "clocks": clocks}))
+    return 0
+
+
+def device_busy_ms(run, seed):
+    """One more run of the workload under the CUPTI activity trace: the summed duration of its kernels (the
+    device's busy time), and the host's own time per step, measured around ``Scheduler.step`` with the
+    device made to wait at every step's end so that the host time holds no waiting for the device."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from gesso_b200.engine import scheduler as sched_mod
+    host = {"s": 0.0, "steps": 0}
+    real_step = sched_mod.Scheduler.step
+
+    def timed_step(self):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = real_step(self)
+        host["s"] += time.perf_counter() - t0          # launches are asynchronous: this is host work
+        host["steps"] += 1
+        return out
+
+    sched_mod.Scheduler.step = timed_step
+    try:
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            r = run(seed)
+            torch.cuda.synchronize()
+    finally:
+        sched_mod.Scheduler.step = real_step
+    busy = sum(e.time_range.end - e.time_range.start for e in prof.events()
+               if e.device_type == torch.autograd.DeviceType.CUDA) / 1000.0
+    return {"busy_ms": busy, "steps": max(host["steps"], 1), "host_s": host["s"]}
+
+
 def reference_arm():
     """The reference is a Julia 1.12 project (Project.toml, no setup.py / pyproject.toml): pip cannot
     install it, no Julia toolchain exists here, and its CUDA extension has no short-convolution
@@ -237,12 +398,16 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--workload", default="decode", choices=["decode"] + sorted(SERVE),
+                    help="decode: the headline (default); serve350m / serve700m: serving-like runs through run_batch")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload != "decode":
+        return serve_workload(args.workload)
     warmup = max(args.warmup, 3)
 
     import torch
@@ -260,7 +425,7 @@ def main() -> int:
     model = gb.random_model(cfg, seed=0, dtype="bfloat16", max_positions=args.context)
     pk = peaks()
 
-    sampler = ClockSampler()
+    sampler = ClockSampler(device_uuid())
     sampler.start()
     ms_step, launches, kv_mid = time_decode(gb, model, args.batch, args.context, args.steps, warmup, args.page_size)
     clocks = sampler.summary()
@@ -269,12 +434,16 @@ def main() -> int:
     # bytes a decode step has to read: every weight it uses once + the cache of the live requests
     layer_flops, head_flops = model_flops_per_token(c, n_attn, n_conv)
     weight_bytes = (layer_flops // 2 + head_flops // 2) * 2                 # bf16
-    kv_bytes = args.batch * kv_mid * n_attn * 2 * c.num_key_value_heads * c.head_dim * 2
-    state_bytes = args.batch * n_conv * (c.conv_L_cache - 1) * c.hidden_size * 4
-    step_bytes = weight_bytes + kv_bytes + state_bytes
-    achieved = step_bytes / (ms_step * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+
+    def roofline_of(batch, kv_len, ms):
+        kv_bytes = batch * kv_len * n_attn * 2 * c.num_key_value_heads * c.head_dim * 2
+        state_bytes = batch * n_conv * (c.conv_L_cache - 1) * c.hidden_size * 4
+        achieved = (weight_bytes + kv_bytes + state_bytes) / (ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]}
+
+    roofline = roofline_of(args.batch, kv_mid, ms_step)
+    blocks = dict(time_decode.blocks)
 
     e2e_value, h2d, d2h = time_e2e(gb, model, args.batch, args.context, args.steps, warmup, args.page_size)
     e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
@@ -291,7 +460,7 @@ def main() -> int:
                    "attention_layers": n_attn, "global_batch": args.batch, "seq_len": args.context,
                    "page_size": args.page_size, "prefill_tokens": args.prefill_tokens,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (all weights read every step)"},
-        "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks,
+        "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks, "blocks": blocks,
     }
     if not args.no_points:
         ms_pf = time_prefill(gb, model, args.prefill_tokens, args.page_size)
@@ -300,11 +469,17 @@ def main() -> int:
         pf_flops = T * layer_flops + head_flops + attn_flops
         out["prefill"] = {"value": round(T * 1000.0 / ms_pf, 1), "tokens": T, "ms": round(ms_pf, 3),
                           "frac": round(pf_flops / (ms_pf * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
-        pts = {}
-        for b in (1, 64):
-            ms_b, _, _ = time_decode(gb, model, b, args.context, min(args.steps, 64), warmup, args.page_size)
-            pts[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+        pts, roofs = {}, {f"decode_b{args.batch}": roofline}
+        for b, ctx in ((1, args.context), (64, args.context), (args.batch, 512), (args.batch, 2048)):
+            if ctx > args.context or (b, ctx) == (args.batch, args.context):
+                continue
+            ms_b, _, kv_b = time_decode(gb, model, b, ctx, min(args.steps, 64), warmup, args.page_size)
+            name = f"decode_b{b}" if ctx == args.context else f"decode_b{b}_ctx{ctx}"
+            pts[name] = round(b * 1000.0 / ms_b, 1)
+            roofs[name] = roofline_of(b, kv_b, ms_b)
         out["points"] = pts
+        out["rooflines"] = {k: v["frac"] for k, v in roofs.items()}
+        out["cpu_baseline"] = cpu_baseline()
     print(json.dumps(out))
     return 0
 

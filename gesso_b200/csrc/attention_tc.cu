@@ -86,7 +86,9 @@ __device__ __forceinline__ void load_block(KVFrag<HD>& f, const bf16* __restrict
 // One 16-key block against one m16 tile of queries: scores, running softmax, outputs.
 // qf[c] / qg[c]: Q rows g and g+8, features 32c+8t..+8.  pos_a / pos_b: last visible key of rows g
 // and g+8; lo_a / lo_b: first visible key.  key0: first key of the block.
-template <int HD>
+// UPPER = false: rows 8..15 of the tile carry no query (a decoding step with at most 8 query heads per kv
+// head): their scores are not looked at, their probabilities are zero and their outputs are never read.
+template <int HD, bool UPPER = true>
 __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&qf)[HD / 32],
                                              const uint4 (&qg)[HD / 32], float (&o)[HD / 8][4], float (&m)[2],
                                              float (&l)[2], int key0, int t, int pos_a, int pos_b, int lo_a,
@@ -106,33 +108,41 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         sa[i] *= scale_log2;
-        sb[i] *= scale_log2;
+        if (UPPER) sb[i] *= scale_log2;
         if (need_mask) {
             const int key = kbase + i;
             if (key > pos_a || key < lo_a) sa[i] = -INFINITY;
-            if (key > pos_b || key < lo_b) sb[i] = -INFINITY;
+            if (UPPER && (key > pos_b || key < lo_b)) sb[i] = -INFINITY;
         }
     }
     const float ma = quad_max(fmaxf(fmaxf(sa[0], sa[1]), fmaxf(sa[2], sa[3])));
-    const float mb = quad_max(fmaxf(fmaxf(sb[0], sb[1]), fmaxf(sb[2], sb[3])));
-    const float na = fmaxf(m[0], ma), nb = fmaxf(m[1], mb);
-    const float ua = na == -INFINITY ? 0.f : na, ub = nb == -INFINITY ? 0.f : nb;   // all masked so far
-    const float alpha_a = exp2f(m[0] - ua), alpha_b = exp2f(m[1] - ub);
+    const float na = fmaxf(m[0], ma);
+    const float ua = na == -INFINITY ? 0.f : na;                                      // all masked so far
+    const float alpha_a = exp2f(m[0] - ua);
     m[0] = na;
-    m[1] = nb;
-    float pa[4], pb[4];
-    float la = 0.f, lb = 0.f;
+    float pa[4], pb[4] = {0.f, 0.f, 0.f, 0.f};
+    float la = 0.f, lb = 0.f, alpha_b = 1.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         pa[i] = exp2f(sa[i] - ua);
-        pb[i] = exp2f(sb[i] - ub);
         la += pa[i];
-        lb += pb[i];
     }
     l[0] = l[0] * alpha_a + la;
-    l[1] = l[1] * alpha_b + lb;
-    const unsigned a0 = pack_bf16(pa[0], pa[1]), a1 = pack_bf16(pb[0], pb[1]);
-    const unsigned a2 = pack_bf16(pa[2], pa[3]), a3 = pack_bf16(pb[2], pb[3]);
+    if (UPPER) {
+        const float mb = quad_max(fmaxf(fmaxf(sb[0], sb[1]), fmaxf(sb[2], sb[3])));
+        const float nb = fmaxf(m[1], mb);
+        const float ub = nb == -INFINITY ? 0.f : nb;
+        alpha_b = exp2f(m[1] - ub);
+        m[1] = nb;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            pb[i] = exp2f(sb[i] - ub);
+            lb += pb[i];
+        }
+        l[1] = l[1] * alpha_b + lb;
+    }
+    const unsigned a0 = pack_bf16(pa[0], pa[1]), a1 = UPPER ? pack_bf16(pb[0], pb[1]) : 0u;
+    const unsigned a2 = pack_bf16(pa[2], pa[3]), a3 = UPPER ? pack_bf16(pb[2], pb[3]) : 0u;
     // the running maximum seldom moves after the first blocks: rescale only when some row's did
     const bool rescale = __any_sync(0xffffffffu, alpha_a != 1.f || alpha_b != 1.f);
 #pragma unroll
@@ -140,8 +150,10 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
         if (rescale) {
             o[j][0] *= alpha_a;
             o[j][1] *= alpha_a;
-            o[j][2] *= alpha_b;
-            o[j][3] *= alpha_b;
+            if (UPPER) {
+                o[j][2] *= alpha_b;
+                o[j][3] *= alpha_b;
+            }
         }
         mma_bf16(o[j], a0, a1, a2, a3, f.v[j].x, f.v[j].y);
     }
@@ -161,7 +173,8 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
 // and everything but the block that holds the step's own token is requested before the wait for
 // the preceding kernels (which write that token's K and V and the queries), so the first keys are
 // on their way while those still run.
-#define DA_STAGES 6
+#define DA_STAGES_DEEP 6          // few blocks (small batches): a deep ring per warp, two blocks per SM
+#define DA_STAGES_WIDE 3          // many blocks: four blocks per SM hide each other's latencies instead
 
 __device__ __forceinline__ void cp_async_zfill16(void* smem_dst, const void* src, bool valid) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -172,11 +185,11 @@ __device__ __forceinline__ void cp_async_zfill8(void* smem_dst, const void* src,
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(valid ? 8 : 0));
 }
 
-template <int HD>
+template <int HD, int DA_STAGES, bool UPPER>
 __global__ void __launch_bounds__(128)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
-                        int page_size, const int* __restrict__ positions,
+                        int page_size, int page_shift, const int* __restrict__ positions,
                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int n_splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets) {
     // ring: [stage][piece][128 threads]: HD/16 pieces of 16 bytes for K, then HD/8 pieces of 8 bytes for V;
@@ -202,36 +215,45 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     const int mine_n = b0 + w < b1 ? (b1 - b0 - w + 3) / 4 : 0;      // blocks b0 + w + 4 i of this warp
 
     // page ids of this warp's blocks, 32 at a time: lane i holds the page of block i of the batch
+    // (page_shift >= 0: the page size is that power of two, and no division is needed)
     int pages = 0;
     auto fetch_pages = [&](int first_i) {
         const int i = first_i + lane;
-        pages = i < mine_n ? bt[((b0 + w + 4 * i) * 16) / page_size] : -1;
+        const int key = (b0 + w + 4 * i) * 16;
+        pages = i < mine_n ? bt[page_shift >= 0 ? key >> page_shift : key / page_size] : -1;
     };
     fetch_pages(0);
 
     unsigned char* ring = smem_raw;
     const int key_a = 4 * (g >> 1) + (g & 1);
-    int issued = 0;
+    // what does not change from block to block is added up once: this thread's place inside a page of its kv
+    // head, for K ([slot][feature]) and for V ([feature][slot]); a page is page_elems elements of either
+    const size_t page_elems = (size_t)nkv * page_size * HD;
+    const bf16* k_mine = k_pages + ((size_t)kvh * page_size + key_a) * HD + 8 * t;
+    const bf16* v_mine = v_pages + ((size_t)kvh * HD + g) * page_size + 4 * t;
+    unsigned char* ring_mine_k = ring + (size_t)threadIdx.x * 16;
+    unsigned char* ring_mine_v = ring + (size_t)KP * 16 * 128 + (size_t)threadIdx.x * 8;
+    int issued = 0, issue_stage = 0;
     auto issue = [&]() {                     // request block `issued` of this warp into its ring stage
         if (issued < mine_n) {
-            const int b = b0 + w + 4 * issued;
+            const int key0 = (b0 + w + 4 * issued) * 16;
             const int page = __shfl_sync(0xffffffffu, pages, issued & 31);
             const bool valid = page >= 0;    // a page given back behind a window: masked, zero-filled
-            const size_t pk = (size_t)(valid ? page : 0) * nkv + kvh;
-            const int sub = (b * 16) % page_size;
-            unsigned char* st = ring + (size_t)(issued % DA_STAGES) * STAGE_BYTES;
-            const bf16* ka = k_pages + (pk * page_size + sub + key_a) * HD + 8 * t;
+            const int sub = page_shift >= 0 ? key0 & (page_size - 1) : key0 % page_size;
+            const size_t at = (size_t)(valid ? page : 0) * page_elems;
+            const int stage_off = issue_stage * STAGE_BYTES;
+            const bf16* ka = k_mine + at + sub * HD;
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) {
-                cp_async_zfill16(st + ((size_t)(2 * c) * 128 + threadIdx.x) * 16, ka + 32 * c, valid);
-                cp_async_zfill16(st + ((size_t)(2 * c + 1) * 128 + threadIdx.x) * 16, ka + 2 * HD + 32 * c, valid);
+                cp_async_zfill16(ring_mine_k + stage_off + (2 * c) * 128 * 16, ka + 32 * c, valid);
+                cp_async_zfill16(ring_mine_k + stage_off + (2 * c + 1) * 128 * 16, ka + 2 * HD + 32 * c, valid);
             }
-            const bf16* vt = v_pages + (pk * HD + g) * page_size + sub + 4 * t;
-            unsigned char* sv = st + (size_t)KP * 16 * 128;
+            const bf16* vt = v_mine + at + sub;
 #pragma unroll
             for (int j = 0; j < VP; ++j)
-                cp_async_zfill8(sv + ((size_t)j * 128 + threadIdx.x) * 8, vt + (size_t)(8 * j) * page_size, valid);
+                cp_async_zfill8(ring_mine_v + stage_off + j * 128 * 8, vt + (size_t)(8 * j) * page_size, valid);
             ++issued;
+            if (++issue_stage == DA_STAGES) issue_stage = 0;
             if ((issued & 31) == 0) fetch_pages(issued);
         }
         asm volatile("cp.async.commit_group;\n" ::);      // an empty group keeps the count in step
@@ -256,7 +278,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
             qf[c] = g < G ? *reinterpret_cast<const uint4*>(qa + 32 * c) : make_uint4(0, 0, 0, 0);
-            qg[c] = g + 8 < G ? *reinterpret_cast<const uint4*>(qa + 8 * HD + 32 * c) : make_uint4(0, 0, 0, 0);
+            qg[c] = (UPPER && g + 8 < G) ? *reinterpret_cast<const uint4*>(qa + 8 * HD + 32 * c) : make_uint4(0, 0, 0, 0);
         }
     }
 
@@ -264,23 +286,24 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
+    int read_stage = 0;
 #pragma unroll 1
     for (int i = 0; i < mine_n; ++i) {
         const int b = b0 + w + 4 * i;
         asm volatile("cp.async.wait_group %0;\n" ::"n"(DA_STAGES - 1));
-        const unsigned char* st = ring + (size_t)(i % DA_STAGES) * STAGE_BYTES;
+        const int stage_off = read_stage * STAGE_BYTES;
+        if (++read_stage == DA_STAGES) read_stage = 0;
         KVFrag<HD> cur;
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
-            cur.k[0][c] = *reinterpret_cast<const uint4*>(st + ((size_t)(2 * c) * 128 + threadIdx.x) * 16);
-            cur.k[1][c] = *reinterpret_cast<const uint4*>(st + ((size_t)(2 * c + 1) * 128 + threadIdx.x) * 16);
+            cur.k[0][c] = *reinterpret_cast<const uint4*>(ring_mine_k + stage_off + (2 * c) * 128 * 16);
+            cur.k[1][c] = *reinterpret_cast<const uint4*>(ring_mine_k + stage_off + (2 * c + 1) * 128 * 16);
         }
-        const unsigned char* sv = st + (size_t)KP * 16 * 128;
 #pragma unroll
-        for (int j = 0; j < VP; ++j) cur.v[j] = *reinterpret_cast<const uint2*>(sv + ((size_t)j * 128 + threadIdx.x) * 8);
+        for (int j = 0; j < VP; ++j) cur.v[j] = *reinterpret_cast<const uint2*>(ring_mine_v + stage_off + j * 128 * 8);
         issue();                                          // refill the stage just read
         const bool need_mask = (b * 16 + 15 > pos) || (b * 16 < lo);
-        attend_block<HD>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask);
+        attend_block<HD, UPPER>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask);
     }
     asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();                                      // the ring is free: it becomes the merge buffer
@@ -460,27 +483,43 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
     if (G > 16 || n_splits < 1 || n_splits > 65535 || n_segs > 65535 || nkv > 65535) return GESSO_ERR_BAD_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return GESSO_ERR_BAD_SIZE;
     dim3 grid(n_splits, nkv, n_segs);
+    int page_shift = -1;
+    if ((page_size & (page_size - 1)) == 0)
+        for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
+    // Few blocks: two per SM with a deep ring each (a block must cover the memory latency by itself).  Many
+    // blocks (large batches): four per SM with a shallow ring each; the same bytes are in flight, and twice
+    // the warps keep the issue slots busy where one warp's chain of dependent instructions would not.
+    const long long blocks = (long long)n_splits * nkv * n_segs;
+    const bool wide = blocks >= 3LL * gesso_sm_count();
+    const int stages = wide ? DA_STAGES_WIDE : DA_STAGES_DEEP;
     const size_t merge = (size_t)4 * 16 * (hd + 2) * sizeof(float);
-    const size_t ring = (size_t)DA_STAGES * (hd / 16 * 16 + hd / 8 * 8) * 128;
+    const size_t ring = (size_t)stages * (hd / 16 * 16 + hd / 8 * 8) * 128;
     const size_t smem = ring > merge ? ring : merge;
     const float scale_log2 = scale * LOG2E;
-#define GO(HD)                                                                                              \
+#define GO3(HD, ST, UP)                                                                                     \
     do {                                                                                                    \
-        static bool configured = false;   /* once per head size, outside any stream capture */              \
+        static bool configured = false;   /* once per instantiation, outside any stream capture */          \
         if (!configured) {                                                                                  \
-            cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                                 (int)smem);                                                                \
+            cudaFuncSetAttribute(decode_attention_kernel<HD, ST, UP>,                                       \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
             configured = true;                                                                              \
         }                                                                                                   \
-        launch_pdl(decode_attention_kernel<HD>, grid, dim3(128), smem, stream,                              \
+        launch_pdl(decode_attention_kernel<HD, ST, UP>, grid, dim3(128), smem, stream,                      \
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,  \
-            positions, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml, tickets);        \
+            page_shift, positions, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml,      \
+            tickets);                                                                                       \
+    } while (0)
+#define GO(HD)                                                                                              \
+    do {                                                                                                    \
+        if (wide) { if (G > 8) GO3(HD, DA_STAGES_WIDE, true); else GO3(HD, DA_STAGES_WIDE, false); }        \
+        else { if (G > 8) GO3(HD, DA_STAGES_DEEP, true); else GO3(HD, DA_STAGES_DEEP, false); }             \
     } while (0)
     if (hd == 32) GO(32);
     else if (hd == 64) GO(64);
     else if (hd == 96) GO(96);
     else GO(128);
 #undef GO
+#undef GO3
     return launch_status();
 }
 

@@ -30,6 +30,8 @@ LIB_NAME = "libgesso_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler",
               "-fvisibility=hidden", "--expt-relaxed-constexpr"]
+# more flags for every file (macro definitions for tuning, say), part of the fingerprint
+NVCC_FLAGS += os.environ.get("GESSO_NVCC_FLAGS", "").split()
 
 
 _SLOW_FIRST = ("attention_generic", "gemm_skinny_")

@@ -69,7 +69,13 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 }
 
 #define SK_WARPS 8
-#define SK_STAGES_FOR(ROWS) (160 / (ROWS))   // chunks in flight per thread: 10 of 32 bytes or 20 of 16 bytes
+#ifndef SK_RING_UNITS
+#define SK_RING_UNITS 160                    // ring size in units of 512 bytes per block (160: 80 KB)
+#endif
+#ifndef SK_MIN_BLOCKS
+#define SK_MIN_BLOCKS 1                      // blocks per SM the register allocation leaves room for
+#endif
+#define SK_STAGES_FOR(ROWS) (SK_RING_UNITS / (ROWS))   // chunks in flight per thread: 10 of 32 bytes or 20 of 16 bytes
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -87,7 +93,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // (8 when there are too few 16-row tiles to fill the device; rows 8..15 of the MMA are then zero).
 // XC: chunks per warp and tile whose token-side fragments are kept in registers across tiles (0: reload).
 template <int NT, int EPI, bool NORM, int ROWS, int XC>
-__global__ void __launch_bounds__(SK_WARPS * 32)
+__global__ void __launch_bounds__(SK_WARPS * 32, SK_MIN_BLOCKS)
 skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, const float* __restrict__ norm_w,
                    float eps, const bf16* __restrict__ W, void* __restrict__ out, const float* __restrict__ bias,
                    int M, int N, int K, int ldk, int S, float* __restrict__ ws, int* __restrict__ tickets,
@@ -397,7 +403,10 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
 }
 
 #define SK_RING_BYTES(ROWS) (SK_STAGES_FOR(ROWS) * ((ROWS) / 8) * SK_WARPS * 32 * 16)
-#define SK_MAX_BLOCKS (2 * gesso_sm_count())
+#ifndef SK_BLOCKS_PER_SM
+#define SK_BLOCKS_PER_SM 2                               // persistent blocks per SM (two fit by shared memory and registers)
+#endif
+#define SK_MAX_BLOCKS (SK_BLOCKS_PER_SM * gesso_sm_count())
 
 #define SK_TICKETS 4096                                  // tiles a split product may have (ints at the head of the workspace)
 

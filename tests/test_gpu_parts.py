@@ -443,7 +443,8 @@ def test_toy_mixer_with_pages_and_states_registers_builds_and_steps():
                     mix = torch.stack(rows)
                 else:
                     mix = P.short_conv_mixer(xn, w[p + "mixer.in_proj.weight"], w[p + "mixer.conv.weight"],
-                                             w[p + "mixer.out_proj.weight"])
+                                             w[p + "mixer.out_proj.weight"], w.get(p + "mixer.in_proj.bias"),
+                                             w.get(p + "mixer.conv.bias"), w.get(p + "mixer.out_proj.bias"))
                 h = h + mix
                 h = h + P.swiglu_ffn(P.rmsnorm(h, w[p + "ff_norm.weight"], 1e-5), w[p + "feed_forward.gate_proj.weight"],
                                      w[p + "feed_forward.up_proj.weight"], w[p + "feed_forward.down_proj.weight"])

@@ -175,4 +175,6 @@ def poison_free_memory(eng) -> None:
     assert eng.cache.live_requests() == []
     for kv in eng.device_cache.kv:
         kv.fill_(float("nan"))
-    eng.device_cache._state_flat.fill_(float("nan"))
+    for st in eng.device_cache.state:
+        if st.is_floating_point():
+            st.fill_(float("nan"))
