@@ -15,7 +15,8 @@
 //     are assigned to the two 8-key score tiles so that a thread's four probabilities are keys
 //     4t..4t+3, which is one 8-byte read of a V^T row.
 // Softmax statistics and the output accumulate in float32 with a running maximum (base-2
-// exponentials with the 1/sqrt(d) scale folded in).  Reference design inputs: the split-K decode
+// exponentials with the 1/sqrt(d) scale folded in; the maximum is rounded up to a whole number, see
+// attend_block).  Reference design inputs: the split-K decode
 // kernels of ext/cuda_attention.jl:421-550 (block = kv head x key chunk, all query heads of the
 // group from one read, LSE combine); formulas as src/Inference/Inference.jl:1201-1207, 1398,
 // 1414-1457.
@@ -115,7 +116,12 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
             if (UPPER && (key > pos_b || key < lo_b)) sb[i] = -INFINITY;
         }
     }
-    const float ma = quad_max(fmaxf(fmaxf(sa[0], sa[1]), fmaxf(sa[2], sa[3])));
+    // The running maximum is kept as a whole number (scores are in the base-2 domain): rescaling by
+    // 2^(old - new) is then exact, and a probability rounded to bfloat16 against one whole number is the
+    // probability rounded against another times an exact power of two.  So what a row's keys add up to does
+    // not depend on the order of the blocks, on the warps and splits that share them, or on how the
+    // maximum grew on the way: only on the row's final maximum.
+    const float ma = ceilf(quad_max(fmaxf(fmaxf(sa[0], sa[1]), fmaxf(sa[2], sa[3]))));
     const float na = fmaxf(m[0], ma);
     const float ua = na == -INFINITY ? 0.f : na;                                      // all masked so far
     const float alpha_a = exp2f(m[0] - ua);
@@ -129,7 +135,7 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
     }
     l[0] = l[0] * alpha_a + la;
     if (UPPER) {
-        const float mb = quad_max(fmaxf(fmaxf(sb[0], sb[1]), fmaxf(sb[2], sb[3])));
+        const float mb = ceilf(quad_max(fmaxf(fmaxf(sb[0], sb[1]), fmaxf(sb[2], sb[3]))));
         const float nb = fmaxf(m[1], mb);
         const float ub = nb == -INFINITY ? 0.f : nb;
         alpha_b = exp2f(m[1] - ub);

@@ -212,7 +212,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             s.xmax[j & 1][half][r] = mx;
             mbar_arrive(&s.pair[q4]);
             if (!wait_all(&s.pair[q4], j & 1, 18)) { ok = false; break; }
-            const float m_blk = fmaxf(mx, s.xmax[j & 1][half ^ 1][r]) * scale_log2;
+            // rounded up to a whole number: every rescaling is then by an exact power of two, and the
+            // rounding of a probability to bfloat16 does not depend on which reference it was taken against
+            // (nor, therefore, on how a row's keys were cut into blocks and steps)
+            const float m_blk = ceilf(fmaxf(mx, s.xmax[j & 1][half ^ 1][r]) * scale_log2);
             // O += P V of the block before has finished: P may be rewritten, O may be rescaled
             if (j > 0) {
                 if (!wait_all(&s.o_full, (j - 1) & 1, 17)) { ok = false; break; }

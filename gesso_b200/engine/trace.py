@@ -32,14 +32,14 @@ from .engine import Engine
 PAGE_ROUND = 64   # a request's token count is rounded up to this (or to the page size, if larger)
 
 
-def make_engine(model, max_tokens: int, page_size: int = 16, max_requests: int = 4) -> Engine:
+def make_engine(model, max_tokens: int, page_size: int = 16, max_requests: int = 4, use_graphs: bool = True) -> Engine:
     """An engine whose page pool holds exactly ``max_tokens`` positions."""
     unit = max(PAGE_ROUND, page_size)
     if max_tokens < 1:
         raise invalid("--max-tokens must be >= 1")
     max_tokens = unit * ((max_tokens + unit - 1) // unit)
     return Engine(model, max_positions=min(max_tokens, model.rt.max_positions), page_size=page_size,
-                  num_pages=max_tokens // page_size, max_requests=max_requests)
+                  num_pages=max_tokens // page_size, max_requests=max_requests, use_graphs=use_graphs)
 
 
 def replay(engine: Engine, lines: IO[str], out_dir: str, done: Optional[IO[str]] = None) -> int:

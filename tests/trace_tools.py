@@ -122,10 +122,10 @@ def trace_mixed(reqs, seed: int, max_live: int = 4, decode_tail: int = 12,
 
 # ---- running and comparing --------------------------------------------------------------------------
 def run_in_process(model, tb: TraceBuilder, max_tokens: int, out_dir: str, page_size: int = 16, prepare=None,
-                   max_requests: int = 4):
+                   max_requests: int = 4, use_graphs: bool = True):
     """Replay ``tb`` on a fresh engine; ``prepare(engine)`` may touch the engine before the first step."""
     from gesso_b200.engine import trace
-    eng = trace.make_engine(model, max_tokens, page_size=page_size, max_requests=max_requests)
+    eng = trace.make_engine(model, max_tokens, page_size=page_size, max_requests=max_requests, use_graphs=use_graphs)
     if prepare is not None:
         prepare(eng)
     sink = io.StringIO()
