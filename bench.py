@@ -16,9 +16,9 @@ One JSON line is printed:
   before); inputs of a step are larger than L2 (all weights are read once per step);
 * ``e2e``: the same through the Python entry point (``Session.open_batch`` + ``step()``): host token
   ids in, sampled ids out, every step's metadata copied from pinned host memory and its ids read back;
-* ``prefill``: one request of 2,048 tokens, logits at its last position, best of five after two warm-up
-  runs (the engine replays a captured graph for a portion of a length it has seen before); ``frac`` =
-  flops / time / the bf16 peak;
+* ``prefill``: a prefill step of one request of 2,048 tokens, logits at its last position: the device time
+  per step of five such steps in a row (the engine replays a captured graph for a portion of a length it
+  has seen before); ``frac`` = flops / time / the bf16 peak;
 * ``roofline``: bytes a decode step has to read (every weight once + the cache of the live requests)
   / its time, against the measured copy bandwidth;
 * ``points``: decode tokens per second at batch 1 and 64 (context 4,096) and at batch 8 with contexts of
@@ -230,25 +230,36 @@ def time_e2e(gb, model, batch, context, steps, warmup, page_size):
 
 
 def time_prefill(gb, model, tokens, page_size, reps=5):
+    """Device time of one prefill step of ``tokens`` tokens (logits at the last position): ``reps`` requests are
+    prefilled back to back behind a first, untimed one, with events on the stream around the timed ones.  The
+    host prepares and launches a step while the device still runs the one before, as in a serving loop, so the
+    time between the events is the device's; a single step timed from an idle device would also count the
+    host's preparation and the launch of its graph (0.3 ms here), which steps in a row hide."""
     import torch
     from gesso_b200.engine.batch import StepEntry
     from gesso_b200.engine.engine import Engine
+    n = reps + 1
     eng = Engine(model, max_positions=max(tokens, 64), page_size=page_size,
-                 num_pages=(tokens + page_size - 1) // page_size + 1, max_requests=1)
+                 num_pages=n * ((tokens + page_size - 1) // page_size) + 1, max_requests=n)
     g = torch.Generator().manual_seed(3)
     p = torch.randint(0, model.vocab_size, (tokens,), generator=g).tolist()
     best = None
-    for r in range(reps + 2):
-        eng.admit("p")
+    for r in range(3):                       # the first rounds capture the step's graph
+        for i in range(n):
+            eng.admit(i)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        eng.step([StepEntry(0, p, [tokens - 1])])
         e0.record()
-        eng.step([StepEntry("p", p, [tokens - 1])])
+        for i in range(1, n):
+            eng.step([StepEntry(i, p, [tokens - 1])])
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        eng.release("p")
-        if r >= 2:
+        ms = e0.elapsed_time(e1) / reps
+        eng.check_status()
+        for i in range(n):
+            eng.release(i)
+        if r >= 1:
             best = ms if best is None else min(best, ms)
     return best
 

@@ -396,9 +396,14 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          int page_size, const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
                          const int* __restrict__ tile_seg, const int* __restrict__ tile_q0,
                          bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2) {
-    // long tiles first: the queries at the end of a prompt have the most keys to read
-    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
+    // Long tiles first: the queries at the end of a prompt have the most keys to read.  Blocks are handed
+    // out in the order of blockIdx.x: the (kv head, head pair) blocks of one tile are neighbours there and
+    // the tiles go from the longest to the shortest, a greedy schedule by decreasing work.
     const int G = nh / nkv;
+    const unsigned per_tile = (unsigned)nkv * (unsigned)(G / HPW);
+    const int tile = (int)(gridDim.x / per_tile) - 1 - (int)(blockIdx.x / per_tile);
+    const int kvh = (int)((blockIdx.x % per_tile) / (unsigned)(G / HPW));
+    const int hpair = (int)(blockIdx.x % (unsigned)(G / HPW));
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int seg = tile_seg[tile];
     const int t0 = seg_start[seg], n = seg_start[seg + 1] - t0;
@@ -415,7 +420,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     const int first_block = (window > 0 ? max(0, pos_first - window + 1) : 0) / 16;
     const int last_block = pos_last / 16;
     const int* bt = block_table + (size_t)seg * max_pages;
-    const int head0 = kvh * G + blockIdx.z * HPW;
+    const int head0 = kvh * G + hpair * HPW;
 
     uint4 qf[HPW][HD / 32], qg[HPW][HD / 32];
     float o[HPW][HD / 8][4], m[HPW][2], l[HPW][2];
@@ -536,10 +541,10 @@ GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const 
     if (n_tiles <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
-    if (nkv > 65535) return GESSO_ERR_BAD_SIZE;
+    if ((long long)n_tiles * nh > 2147483647LL) return GESSO_ERR_BAD_SIZE;
     const float scale_log2 = scale * LOG2E;
 #define GO(HD, HPW)                                                                                          \
-    prefill_attention_kernel<HD, HPW><<<dim3(n_tiles, nkv, G / HPW), 128, 0, stream>>>(                      \
+    prefill_attention_kernel<HD, HPW><<<dim3((unsigned)(n_tiles * nkv * (G / HPW))), 128, 0, stream>>>(      \
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,       \
         seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, window, scale_log2)
     if (hd <= 64 && G % 2 == 0) {

@@ -55,11 +55,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     extern __shared__ unsigned char fa_raw[];
     FaSmem& s = *reinterpret_cast<FaSmem*>(((size_t)fa_raw + 1023) & ~(size_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
+    // block waits, also one with nothing to do, so that the chain of dependences stays whole)
+    pdl_launch_dependents();
+    pdl_wait();
     const int TOK = 128 / G;                      // tokens per block
     const int sub = 64 / TOK;                     // blocks per 64-token tile of the step's tile list
-    // long tiles first: the queries at the end of a prompt have the most keys to read
-    const int bx = gridDim.x - 1 - blockIdx.x;
-    const int tile = bx / sub, kvh = blockIdx.y;
+    // Long tiles first: the queries at the end of a prompt have the most keys to read (up to 17 key blocks
+    // at 2,048 tokens where the first tiles have one).  Blocks are handed out in the order of blockIdx.x, so
+    // the kv heads of one tile are neighbours there and the tiles go from the longest to the shortest:
+    // a greedy schedule by decreasing work, which ends nearly level on every SM.
+    const int kvh = (int)(blockIdx.x % (unsigned)nkv);
+    const int bx = (int)(gridDim.x / (unsigned)nkv) - 1 - (int)(blockIdx.x / (unsigned)nkv);
+    const int tile = bx / sub;
     const int seg = tile_seg[tile];
     const int t0 = seg_start[seg], n = seg_start[seg + 1] - t0;
     const int q0 = tile_q0[tile] + (bx % sub) * TOK;
@@ -352,8 +360,9 @@ GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages
             return (int)cudaGetLastError();
         configured = true;
     }
-    const dim3 grid(n_tiles * (64 / TOK), nkv);
-    prefill_attention_tcgen05_kernel<<<grid, FA_THREADS, smem, stream>>>(
+    if ((long long)n_tiles * (64 / TOK) * nkv > 2147483647LL) return GESSO_ERR_BAD_SIZE;
+    const dim3 grid((unsigned)(n_tiles * (64 / TOK) * nkv));
+    launch_pdl(prefill_attention_tcgen05_kernel, grid, dim3(FA_THREADS), smem, stream,
         mq, mk, mv, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, G,
         window, scale * FA_LOG2E, num_pages, status);
     return launch_status();

@@ -46,6 +46,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
                                    float eps, TO* __restrict__ out, const int* __restrict__ rows, int H) {
     extern __shared__ float srow[];
     __shared__ float red[33];
+    // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
+    // block waits, also one with nothing to do, so that the chain of dependences stays whole)
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * H;
@@ -94,6 +98,10 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, cons
                        const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
                        int H) {
     __shared__ float red[33];
+    // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
+    // block waits, also one with nothing to do, so that the chain of dependences stays whole)
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * H;
@@ -142,6 +150,10 @@ add_rmsnorm_warp_kernel(float* __restrict__ h, const TD* __restrict__ delta, con
                         const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
                         int n_rows) {
     constexpr int H = VPL * 128;
+    // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
+    // block waits, also one with nothing to do, so that the chain of dependences stays whole)
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * NORM_WARP_ROWS + (threadIdx.x >> 5);
     if (r >= n_rows) return;
@@ -197,7 +209,7 @@ static bool launch_norm_warp(float* h, const void* delta, const float* delta_bia
                              const int* rows, int n_rows, int H, cudaStream_t stream) {
     const int grid = (n_rows + NORM_WARP_ROWS - 1) / NORM_WARP_ROWS;
 #define WLAUNCH(VPL)                                                                                         \
-    add_rmsnorm_warp_kernel<TD, TO, VPL><<<grid, NORM_WARP_ROWS * 32, 0, stream>>>(h, (const TD*)delta, delta_bias, w, \
+    launch_pdl(add_rmsnorm_warp_kernel<TD, TO, VPL>, dim3(grid), dim3(NORM_WARP_ROWS * 32), 0, stream, h, (const TD*)delta, delta_bias, w, \
                                                                                    eps, (TO*)out, rows, n_rows)
     switch (H) {
         case 512: WLAUNCH(4); return true;
@@ -229,7 +241,7 @@ GESSO_API int gesso_add_rmsnorm(float* h, const void* delta, int delta_dtype, co
     }
     if (H % 4 == 0 && H <= 4 * NORM_VEC_THREADS * NORM_VEC_MAX) {
 #define VLAUNCH(TD, TO)                                                                             \
-    add_rmsnorm_vec_kernel<TD, TO><<<n_rows, NORM_VEC_THREADS, 0, stream>>>(h, (const TD*)delta, delta_bias, w, eps, \
+    launch_pdl(add_rmsnorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(NORM_VEC_THREADS), 0, stream, h, (const TD*)delta, delta_bias, w, eps, \
                                                                              (TO*)out, rows, H)
         if (delta_dtype == GESSO_F32 && out_dtype == GESSO_F32) VLAUNCH(float, float);
         else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_BF16) VLAUNCH(bf16, bf16);
@@ -247,7 +259,7 @@ GESSO_API int gesso_add_rmsnorm(float* h, const void* delta, int delta_dtype, co
         if (smem > 48 * 1024)                                                                       \
             cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                  (int)smem);                                                        \
-        add_rmsnorm_kernel<TD, TO><<<n_rows, threads, smem, stream>>>(                              \
+        launch_pdl(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, stream,           \
             h, (const TD*)delta, delta_bias, w, eps, (TO*)out, rows, H);                            \
     } while (0)
     if (delta_dtype == GESSO_F32 && out_dtype == GESSO_F32) LAUNCH(float, float);

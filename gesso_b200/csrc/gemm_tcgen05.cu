@@ -78,6 +78,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = s.tmem_base;
+    // Launched programmatically: the set-up above ran while the kernel before still worked; nothing below
+    // reads or writes global memory before that kernel is complete.
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0) {
         // ---- producer ----
@@ -180,7 +184,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, co
     }
     const int tiles = ((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
     const dim3 grid(tiles < TC_SMS ? tiles : TC_SMS);
-    gemm_tcgen05_kernel<BN, STAGES, EPI><<<grid, TC_THREADS, smem, stream>>>(ma, mw, out, bias, M, N, K, status);
+    launch_pdl(gemm_tcgen05_kernel<BN, STAGES, EPI>, grid, dim3(TC_THREADS), smem, stream, ma, mw, out, bias, M, N, K,
+               status);
     return launch_status();
 }
 

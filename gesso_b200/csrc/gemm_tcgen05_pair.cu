@@ -68,6 +68,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     cluster_sync_all();            // both blocks' barriers are initialised before anybody signals across
     tc_fence_after();
     const unsigned tmem = s.tmem_base;
+    // Launched programmatically: what stands above (barriers, tensor memory) ran while the kernel before
+    // still worked; nothing below reads or writes global memory before that kernel is complete.
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0) {
         // ---- producer (both blocks) ----
@@ -172,7 +176,8 @@ static int tp_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, co
     const int tiles = ((N + TP_BN - 1) / TP_BN) * ((M + 2 * TP_BM - 1) / (2 * TP_BM));
     const int max_pairs = gesso_sm_count() / 2;            // one pair of blocks per two SMs
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    gemm_tcgen05_pair_kernel<EPI><<<dim3(2 * pairs), TP_THREADS, smem, stream>>>(ma, mw, out, bias, M, N, K, status);
+    launch_pdl(gemm_tcgen05_pair_kernel<EPI>, dim3(2 * pairs), dim3(TP_THREADS), smem, stream, ma, mw, out, bias, M, N, K,
+               status);
     return launch_status();
 }
 

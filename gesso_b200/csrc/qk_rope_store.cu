@@ -105,6 +105,10 @@ qk_norm_rope_store_tile_kernel(
     bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int nh, int nkv, int* __restrict__ status) {
     constexpr int LPH = HD / 8, HALF = HD / 2;
     __shared__ __align__(16) bf16 vt[64][HD + 8];
+    // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
+    // block waits, also one with nothing to do, so that the chain of dependences stays whole)
+    pdl_launch_dependents();
+    pdl_wait();
     const int tile = blockIdx.x, hs = blockIdx.y;            // hs < nh: a q head; else k head hs - nh (and its v head)
     const int seg = tile_seg[tile], q0 = tile_q0[tile];
     const int t0 = seg_start[seg], n = seg_start[seg + 1] - t0;
@@ -236,7 +240,7 @@ GESSO_API int gesso_qk_norm_rope_store_tiles(const void* qkv, const float* q_w, 
     if (!gesso_qk_rope_store_tiles_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const dim3 grid(n_tiles, nh + nkv);
 #define GO(HD)                                                                                                  \
-    qk_norm_rope_store_tile_kernel<HD><<<grid, 256, 0, stream>>>(                                               \
+    launch_pdl(qk_norm_rope_store_tile_kernel<HD>, grid, dim3(256), 0, stream,                                  \
         (const bf16*)qkv, q_w, k_w, eps, cos_t, sin_t, seg_start, seg_pos0, tile_seg, tile_q0, block_table,     \
         max_pages, page_size, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, nh, nkv, status)
     if (hd == 32) GO(32);

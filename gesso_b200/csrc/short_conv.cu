@@ -164,6 +164,10 @@ __global__ void conv_mix_run_kernel(const T* __restrict__ bcx, const float* __re
                                     const int* __restrict__ seg_of_token, const int* __restrict__ seg_start,
                                     const int* __restrict__ seg_pos0, const int* __restrict__ slots,
                                     T* __restrict__ out, int n_tokens, int H, int packed) {
+    // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
+    // block waits, also one with nothing to do, so that the chain of dependences stays whole)
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int V = ConvVec<T>::N;
     const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     const int tbeg = blockIdx.x * TB, tend = min(n_tokens, tbeg + TB);
@@ -233,6 +237,10 @@ __global__ void conv_state_update_kernel(const T* __restrict__ bcx, const float*
                                          float* __restrict__ state, long long slot_stride,
                                          const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
                                          const int* __restrict__ slots, int n_segs, int H, int L, int packed) {
+    // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
+    // block waits, also one with nothing to do, so that the chain of dependences stays whole)
+    pdl_launch_dependents();
+    pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int s = blockIdx.x;
     if (c >= H || s >= n_segs) return;
@@ -337,16 +345,16 @@ GESSO_API int gesso_short_conv(const void* bcx, int dtype, const float* in_bias,
             constexpr int TB = 8;
             dim3 rgrid((n_tokens + TB - 1) / TB, (H / vec + vthreads - 1) / vthreads);
 #define RUN(T, LL)                                                                                              \
-    conv_mix_run_kernel<T, TB, LL><<<rgrid, vthreads, 0, stream>>>(                                             \
-        (const T*)bcx, in_bias, taps, conv_bias, state, slot_stride, seg_of_token, seg_start, seg_pos0, slots,   \
-        (T*)out, n_tokens, H, packed)
+    launch_pdl(conv_mix_run_kernel<T, TB, LL>, rgrid, dim3(vthreads), 0, stream,                                \
+        (const T*)bcx, in_bias, taps, conv_bias, (const float*)state, slot_stride, seg_of_token, seg_start,     \
+        seg_pos0, slots, (T*)out, n_tokens, H, packed)
             if (dtype == GESSO_F32) {
                 if (L == 2) RUN(float, 2); else if (L == 3) RUN(float, 3); else RUN(float, 4);
-                conv_state_update_kernel<float><<<sgrid, threads, 0, stream>>>(
+                launch_pdl(conv_state_update_kernel<float>, sgrid, dim3(threads), 0, stream,
                     (const float*)bcx, in_bias, state, slot_stride, seg_start, seg_pos0, slots, n_segs, H, L, packed);
             } else {
                 if (L == 2) RUN(bf16, 2); else if (L == 3) RUN(bf16, 3); else RUN(bf16, 4);
-                conv_state_update_kernel<bf16><<<sgrid, threads, 0, stream>>>(
+                launch_pdl(conv_state_update_kernel<bf16>, sgrid, dim3(threads), 0, stream,
                     (const bf16*)bcx, in_bias, state, slot_stride, seg_start, seg_pos0, slots, n_segs, H, L, packed);
             }
 #undef RUN
