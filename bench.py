@@ -337,12 +337,12 @@ def serve_workload(name: str) -> int:
                              max_tokens_per_step=4096, prefill_chunk=w["chunk"])
     sampler = ClockSampler(device_uuid())
     sampler.start()
-    run(1)
-    r = run(2)
+    run(1)                      # the shapes of this workload's steps get their graphs
+    r = run(1)                  # the same requests again, timed
     clocks = sampler.summary()
     # host time of a step: the wall time of the run minus the time the device was the one being waited for
     # cannot be read from outside; what can is the wall time per step beside the device-busy time per step
-    busy_ms = device_busy_ms(run, 3)
+    busy_ms = device_busy_ms(run, 1)
     print(json.dumps({
         "workload": name, "metric": "tokens/s through Session.run_batch (prompt and new tokens; new tokens alone)",
         "value": round(r["tokens"] / r["seconds"], 1), "new_tokens_per_s": round(r["new_tokens"] / r["seconds"], 1),
@@ -358,12 +358,19 @@ def serve_workload(name: str) -> int:
 
 
 def device_busy_ms(run, seed):
-    """One more run of the workload under the CUPTI activity trace: the summed duration of its kernels (the
-    device's busy time), and the host's own time per step, measured around ``Scheduler.step`` with the
-    device made to wait at every step's end so that the host time holds no waiting for the device."""
+    """Two more runs of the workload.  One under the CUPTI activity trace: the summed duration of its kernels
+    is the device's busy time.  One with ``Scheduler.step`` timed on the host, the device idle when each step
+    begins (a synchronize before it, outside the timed part), so that the time of a step is the host's own
+    work (planning, packing, launching, digesting the step before) and holds no waiting for a busy device
+    beyond the read of the ids it is about to digest."""
     import torch
     from torch.profiler import ProfilerActivity, profile
     from gesso_b200.engine import scheduler as sched_mod
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run(seed)
+        torch.cuda.synchronize()
+    busy = sum(e.time_range.end - e.time_range.start for e in prof.events()
+               if e.device_type == torch.autograd.DeviceType.CUDA) / 1000.0
     host = {"s": 0.0, "steps": 0}
     real_step = sched_mod.Scheduler.step
 
@@ -371,19 +378,15 @@ def device_busy_ms(run, seed):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         out = real_step(self)
-        host["s"] += time.perf_counter() - t0          # launches are asynchronous: this is host work
+        host["s"] += time.perf_counter() - t0
         host["steps"] += 1
         return out
 
     sched_mod.Scheduler.step = timed_step
     try:
-        with profile(activities=[ProfilerActivity.CUDA]) as prof:
-            r = run(seed)
-            torch.cuda.synchronize()
+        run(seed)
     finally:
         sched_mod.Scheduler.step = real_step
-    busy = sum(e.time_range.end - e.time_range.start for e in prof.events()
-               if e.device_type == torch.autograd.DeviceType.CUDA) / 1000.0
     return {"busy_ms": busy, "steps": max(host["steps"], 1), "host_s": host["s"]}
 
 

@@ -207,18 +207,31 @@ class Engine:
         return layout, slot_i, host[:size], max_seg, max_kv
 
     # ---- mixed steps in a few padded shapes, so that they replay graphs -------------------------------
-    # A mixed step's kernels are launched one by one from the host unless its shape has a graph, and the
-    # shapes of mixed steps hardly ever repeat.  So a mixed step whose padded shape has come before is
-    # filled up to that shape with stand-in requests: single tokens and one portion of token id 0 at
-    # position 0, all on a scratch state slot and a scratch cache page that no request owns.  They are
-    # ordinary entries to every kernel (what they compute is never read), so no kernel knows of padding.
-    # Segments go up to a multiple of 8 (at least one stand-in), tokens to a multiple of 64, the wanted
-    # rows to the number of segments, the attention tiles to the most that shape can have.
+    # A mixed step's kernels are launched one by one from the host unless its shape has a graph (some 140
+    # launches, 2 ms of host time where the device needs 1.5), and the shapes of mixed steps hardly ever
+    # repeat.  So a mixed step is filled up to one of a few shapes with stand-in requests: single tokens and
+    # one portion of token id 0 at position 0, all on a scratch state slot and a scratch cache page that no
+    # request owns.  They are ordinary entries to every kernel (what they compute is never read), so no kernel
+    # knows of padding.  Segments go up to a multiple of 8 (at least one stand-in); tokens to the next of a
+    # ladder of sizes whose steps grow with the size (64 up to 512 tokens, then an eighth of the size, so at
+    # most an eighth of a step is padding); the wanted rows to the number of segments; the attention tiles
+    # to the most that shape can have.  A shape's graph is captured the first time the shape comes.
+    MAX_PADDED_SHAPES = 128
+
+    @staticmethod
+    def _padded_tokens(n: int) -> int:
+        if n <= 512:
+            return -(-n // 64) * 64
+        step = 64
+        while step * 16 < n:          # the step is between a sixteenth and an eighth of the size
+            step *= 2
+        return -(-n // step) * step
+
     def _padded_shape(self, entries, S: int, T: int):
         if (not self.use_graphs or S < 2 or T > 8192 or any(len(e.want) > 1 for e in entries)):
             return None
         S_b = -(-(S + 1) // 8) * 8
-        T_b = -(-(T + S_b - S) // 64) * 64
+        T_b = self._padded_tokens(T + S_b - S)
         # The stand-in portion sits at positions 0 .. portion - 1 of a block table whose every entry is the
         # scratch page, and reads the rotary table at those positions: it has to fit both (an engine with
         # a context shorter than the padding runs its mixed steps unpadded).
@@ -226,11 +239,8 @@ class Engine:
         if portion > min(self.cache.max_pages_per_request * self.page_size, self.max_positions):
             return None
         key = (T_b, S_b, S_b, False)
-        if key not in self._graphs:
-            seen = self._portion_shapes.get(key, 0)
-            self._portion_shapes[key] = seen + 1
-            if seen < 1 or sum(1 for k in self._graphs if k[0] > k[1] > 1) >= 48:
-                return None          # first time (or too many shapes already): as it is, launched one by one
+        if key not in self._graphs and sum(1 for k in self._graphs if k[0] > k[1] > 1) >= self.MAX_PADDED_SHAPES:
+            return None              # too many shapes already: as it is, launched one by one
         return T_b, S_b
 
     def _upload(self, buf: torch.Tensor, slot_i: int, host: torch.Tensor) -> None:
