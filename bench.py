@@ -37,7 +37,11 @@ Other workloads, each printing one JSON line of its own:
                                              # 256 new tokens each, temperature 0.8
 
 both through ``Session.run_batch`` (scheduler, cache manager, sampler), with the host and device time of
-a step.
+a step;
+
+    python bench.py --workload timeline --batch 8      # the kernels of one decoding step, by name
+
+a table (not JSON) of where a step's time goes, from the CUPTI activity trace.
 
 Peaks come from ``MEASURED_PEAKS.json`` beside this file when the driver wrote it, else the
 fallback of an earlier measurement on this pool (6.65 TB/s, 1.59 PFLOP/s).
@@ -390,6 +394,61 @@ def device_busy_ms(run, seed):
     return {"busy_ms": busy, "steps": max(host["steps"], 1), "host_s": host["s"]}
 
 
+def kernel_timeline(batch: int, context: int, page_size: int, layers=None) -> int:
+    """Where the time of one decoding step goes: the kernels of one graph-replayed step at ``batch`` and
+    ``context`` from the CUPTI activity trace (through ``torch.profiler``), summed by kernel name.  Kernels of a
+    step overlap (each is launched while its predecessor drains), so beside a kernel's own duration the table
+    gives the time from its start to its successor's start, which adds up to the step."""
+    import collections
+    import torch
+    import gesso_b200 as gb
+    from gesso_b200 import ops
+    from gesso_b200.engine.batch import StepEntry
+    from torch.profiler import ProfilerActivity, profile
+    cfg = dict(LFM2_1_2B)
+    if layers is not None and layers < cfg["num_hidden_layers"]:
+        cfg["num_hidden_layers"] = layers
+        cfg["full_attn_idxs"] = [i for i in cfg["full_attn_idxs"] if i < layers]
+    model = gb.random_model(cfg, seed=0, dtype="bfloat16", max_positions=context)
+    s, prompts, _ = decode_setup(gb, model, batch, context, 16, 8, page_size)
+    eng = s.engine
+    ids = [f"q{i}" for i in range(batch)]
+    for rid, p in zip(ids, prompts):
+        eng.admit(rid)
+        for c in range(0, len(p), 2048):
+            eng.step([StepEntry(rid, p[c:c + 2048], [])])
+
+    def one(k):
+        ops.argmax_rows(eng.step([StepEntry(rid, [(7 * k + i) % 1000], [0]) for i, rid in enumerate(ids)]))
+
+    for k in range(8):
+        one(k)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for k in range(8, 12):
+            one(k)
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+          and "Memcpy" not in e.name and "Memset" not in e.name]
+    ev.sort(key=lambda e: e.time_range.start)
+    first = [i for i, e in enumerate(ev) if "embed_gather" in e.name]
+    step = ev[first[-2]:first[-1]]                      # the last whole step
+    t0 = step[0].time_range.start
+    agg = collections.OrderedDict()
+    for i, e in enumerate(step):
+        nxt = step[i + 1].time_range.start if i + 1 < len(step) else e.time_range.end
+        a = agg.setdefault(e.name.split("(")[0][:72], [0.0, 0, 0.0])
+        a[0] += e.time_range.end - e.time_range.start
+        a[1] += 1
+        a[2] += nxt - e.time_range.start
+    print(f"one decoding step, batch {batch}, context {context}, {cfg['num_hidden_layers']} layers: "
+          f"{step[-1].time_range.end - t0:.1f} us, {len(step)} kernels")
+    print(f"{'start to next start, us':>24} {'launches':>8} {'each':>7} {'own duration each':>18}  kernel")
+    for name, (dur, n, s2s) in sorted(agg.items(), key=lambda kv: -kv[1][2]):
+        print(f"{s2s:24.1f} {n:8d} {s2s / n:7.2f} {dur / n:18.2f}  {name}")
+    return 0
+
+
 def reference_arm():
     """The reference is a Julia 1.12 project (Project.toml, no setup.py / pyproject.toml): pip cannot
     install it, no Julia toolchain exists here, and its CUDA extension has no short-convolution
@@ -412,14 +471,17 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode"] + sorted(SERVE),
-                    help="decode: the headline (default); serve350m / serve700m: serving-like runs through run_batch")
+    ap.add_argument("--workload", default="decode", choices=["decode", "timeline"] + sorted(SERVE),
+                    help="decode: the headline (default); serve350m / serve700m: serving-like runs through run_batch; "
+                         "timeline: the kernels of one decoding step at --batch and --context")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload == "timeline":
+        return kernel_timeline(args.batch, args.context, args.page_size, args.layers)
     if args.workload != "decode":
         return serve_workload(args.workload)
     warmup = max(args.warmup, 3)
