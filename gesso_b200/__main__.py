@@ -5,11 +5,14 @@ The reference's launcher takes ``--gguf PATH --n-ctx N --check`` and refuses unk
 ``max_tokens``, ``stop`` (docs/serving.md:95-106).  The same names are used here where this engine
 has the same thing; the model comes from a folder (``--model``) instead of a GGUF file.
 
-    generate     --model DIR --prompt-ids 1,2,3 [--max-new-tokens N] [--temperature T] [--top-p P]
+    generate     --model DIR | --random-weights SEED --config FILE
+                 --prompt-ids 1,2,3 [--max-new-tokens N] [--temperature T] [--top-p P]
                  [--seed S] [--stop-ids ..] [--eos-ids ..] [--dtype bfloat16|float32] [--n-ctx N]
                  [--page-size 16] [--num-pages N] [--max-batch B] [--prefill-chunk C]
     init-random  --config FILE --seed S --out DIR      write a model folder with random weights
     describe     --model DIR                           print the typed configuration and the layers
+    replay       --model DIR --dtype D --out DIR --max-tokens N   steps from standard input (bin/trace_run)
+    bench        [options of bench.py]                 the throughput measurements (bench.py at the root of the tree)
     check                                              build the kernels and run a tiny generation
 """
 from __future__ import annotations
@@ -28,7 +31,10 @@ def _parser() -> argparse.ArgumentParser:
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="command", required=True)
     g = sub.add_parser("generate", help="generate tokens for one or more prompts")
-    g.add_argument("--model", required=True)
+    g.add_argument("--model", help="folder with config.json and model.safetensors")
+    g.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                   help="instead of --model: random weights drawn from this seed for the configuration of --config")
+    g.add_argument("--config", help="config.json for --random-weights")
     g.add_argument("--prompt-ids", action="append", default=[], help="token ids, comma or space separated; repeatable")
     g.add_argument("--prompt-file", help="one prompt of token ids per line")
     g.add_argument("--max-new-tokens", type=int, default=8)
@@ -51,8 +57,36 @@ def _parser() -> argparse.ArgumentParser:
     r.add_argument("--std", type=float, default=0.02)
     d = sub.add_parser("describe", help="print the typed configuration")
     d.add_argument("--model", required=True)
+    t = sub.add_parser("replay", help="feed given token ids step by step and write logits (steps on standard input)")
+    t.add_argument("--model", required=True)
+    t.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    t.add_argument("--out", required=True)
+    t.add_argument("--max-tokens", type=int, required=True)
+    t.add_argument("--page-size", type=int, default=16)
+    sub.add_parser("bench", help="run bench.py with the options that follow", add_help=False)
     sub.add_parser("check", help="build the kernels and run a tiny generation on cuda:0")
     return ap
+
+
+def _replay(args) -> int:
+    """The same as ``bin/trace_run``: the engine's own step function fed from standard input."""
+    import gesso_b200
+    from .engine import trace
+    unit = max(trace.PAGE_ROUND, args.page_size)
+    max_tokens = unit * ((args.max_tokens + unit - 1) // unit)
+    model = gesso_b200.load(args.model, dtype=args.dtype, max_positions=max_tokens)
+    trace.replay(trace.make_engine(model, max_tokens, page_size=args.page_size), sys.stdin, args.out)
+    return 0
+
+
+def _bench(argv) -> int:
+    import os
+    import subprocess
+    script = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+    if not os.path.isfile(script):
+        print(f"bench: {script} not found (bench.py lives at the root of the source tree)", file=sys.stderr)
+        return 2
+    return subprocess.call([sys.executable, script] + list(argv))
 
 
 def _check() -> int:
@@ -95,7 +129,12 @@ def _check() -> int:
 
 
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "bench":
+        return _bench(argv[1:])            # bench.py parses (and refuses) its own options
     args = _parser().parse_args(argv)      # an unknown flag prints the usage and exits with 2
+    if args.command == "replay":
+        return _replay(args)
     if args.command == "init-random":
         from .config.registry import parse_strict_json
         from .weights.random_init import write_random_model
@@ -122,7 +161,19 @@ def main(argv=None) -> int:
     if not prompts:
         print("generate: no prompt given (--prompt-ids or --prompt-file)", file=sys.stderr)
         return 2
-    model = gesso_b200.load(args.model, dtype=args.dtype, max_positions=args.n_ctx)
+    if (args.model is None) == (args.random_weights is None):
+        print("generate: give either --model DIR or --random-weights SEED --config FILE", file=sys.stderr)
+        return 2
+    if args.model is not None:
+        model = gesso_b200.load(args.model, dtype=args.dtype, max_positions=args.n_ctx)
+    else:
+        if not args.config:
+            print("generate: --random-weights needs --config FILE", file=sys.stderr)
+            return 2
+        from .config.registry import parse_strict_json
+        with open(args.config) as f:
+            cfg = parse_strict_json(f.read(), args.config)
+        model = gesso_b200.random_model(cfg, seed=args.random_weights, dtype=args.dtype, max_positions=args.n_ctx)
     s = Session(model, context_length=args.n_ctx, page_size=args.page_size, num_pages=args.num_pages,
                 max_batch=args.max_batch, prefill_chunk=args.prefill_chunk)
     eos = None if args.eos_ids is None else _ids(args.eos_ids)

@@ -30,7 +30,7 @@ _SIGNATURES = {
     "gesso_short_conv": [P, I, P, P, P, P, LL, P, P, P, P, P, I, I, I, I, I, I, P],
     "gesso_skinny_conv_takes": [I, I, I, I],
     "gesso_skinny_gemm_conv": [P, P, P, F, P, P, I, I, I, P, P, P, P, LL, P, P, I, P],
-    "gesso_qk_norm_rope_store": [P, I, P, P, F, P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, P, P],
+    "gesso_qk_norm_rope_store": [P, I, P, P, F, P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, P, P],
     "gesso_paged_attention_generic": [P, P, P, I, P, I, I, P, P, P, I, I, I, I, I, F, P],
     "gesso_swiglu": [P, P, I, I, I, I, P],
     "gesso_skinny_gemm_takes": [I, I, I],

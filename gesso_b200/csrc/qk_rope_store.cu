@@ -19,6 +19,11 @@
 // are zero.  The token that ends a request's portion in a step writes those zeros along with its own
 // values (the same 32-byte sectors); no other token of the step touches them.
 //
+// The position part may rotate only the first `rot_dim` features of a head (the rest are normed and
+// passed on as they are) and may pair neighbours (2i, 2i+1) instead of the halves (i, i + rot_dim/2);
+// the tables are [max_positions, rot_dim/2] then.  The kernel that works by 64-token tiles takes the
+// full half-split layout only; everything else goes through the one below.
+//
 // One warp per (token, head).  Everything is float32 inside; stores round to the run type.
 #include "common.cuh"
 
@@ -28,7 +33,7 @@ __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ positions,
     const int* __restrict__ seg_of_token, const int* __restrict__ block_table, int max_pages, int page_size,
     T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int nh, int nkv,
-    int hd, int write_kv, int* __restrict__ status) {
+    int hd, int write_kv, int rot_dim, int interleaved, int* __restrict__ status) {
     // let the successor in first (it only prefetches what no running kernel writes until its own wait)
     pdl_launch_dependents();
     pdl_wait();
@@ -78,14 +83,21 @@ __global__ void qk_norm_rope_store_kernel(
     ss = warp_sum(ss);
     const float denom = w ? sqrtf(ss / (float)hd + eps) : 1.f;
     const bool rotate = cos_t != nullptr;   // no table: the mixer has no position encoding
-    const float* cs = rotate ? cos_t + (size_t)pos * half : nullptr;
-    const float* sn = rotate ? sin_t + (size_t)pos * half : nullptr;
-    for (int i = lane; i < half; i += 32) {
-        float a = to_f32(src[i]), b = to_f32(src[i + half]);
-        if (w) { a = (a / denom) * w[i]; b = (b / denom) * w[i + half]; }
-        const float c = rotate ? cs[i] : 1.f, s = rotate ? sn[i] : 0.f;
-        dst[i] = from_f32<T>(a * c - b * s);
-        dst[i + half] = from_f32<T>(a * s + b * c);
+    const int rot_half = rotate ? rot_dim >> 1 : 0;
+    const float* cs = rotate ? cos_t + (size_t)pos * rot_half : nullptr;
+    const float* sn = rotate ? sin_t + (size_t)pos * rot_half : nullptr;
+    for (int i = lane; i < rot_half; i += 32) {            // the rotated pairs
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + rot_half;
+        float a = to_f32(src[ia]), b = to_f32(src[ib]);
+        if (w) { a = (a / denom) * w[ia]; b = (b / denom) * w[ib]; }
+        const float c = cs[i], s = sn[i];
+        dst[ia] = from_f32<T>(a * c - b * s);
+        dst[ib] = from_f32<T>(a * s + b * c);
+    }
+    for (int i = 2 * rot_half + lane; i < hd; i += 32) {   // features the position part leaves alone
+        float a = to_f32(src[i]);
+        if (w) a = (a / denom) * w[i];
+        dst[i] = from_f32<T>(a);
     }
 }
 
@@ -254,9 +266,11 @@ GESSO_API int gesso_qk_norm_rope_store(const void* qkv, int dtype, const float* 
                                        const float* cos_t, const float* sin_t, const int* positions,
                                        const int* seg_of_token, const int* block_table, int max_pages,
                                        int page_size, void* q_out, void* k_pages, void* v_pages, int n_tokens,
-                                       int nh, int nkv, int hd, int write_kv, int* status, cudaStream_t stream) {
+                                       int nh, int nkv, int hd, int write_kv, int rot_dim, int interleaved,
+                                       int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || (hd & 1) || nh <= 0 || nkv <= 0 || page_size <= 0) return GESSO_ERR_BAD_SIZE;
+    if (cos_t != nullptr && (rot_dim < 2 || (rot_dim & 1) || rot_dim > hd)) return GESSO_ERR_BAD_SIZE;
     const int warps = 4;
     const long long total = (long long)n_tokens * (write_kv ? nh + 2 * nkv : nh);
     const long long blocks = (total + warps - 1) / warps;
@@ -264,11 +278,13 @@ GESSO_API int gesso_qk_norm_rope_store(const void* qkv, int dtype, const float* 
     if (dtype == GESSO_F32)
         launch_pdl(qk_norm_rope_store_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
             (const float*)qkv, q_w, k_w, eps, cos_t, sin_t, positions, seg_of_token, block_table, max_pages,
-            page_size, (float*)q_out, (float*)k_pages, (float*)v_pages, n_tokens, nh, nkv, hd, write_kv, status);
+            page_size, (float*)q_out, (float*)k_pages, (float*)v_pages, n_tokens, nh, nkv, hd, write_kv, rot_dim,
+            interleaved, status);
     else if (dtype == GESSO_BF16)
         launch_pdl(qk_norm_rope_store_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
             (const bf16*)qkv, q_w, k_w, eps, cos_t, sin_t, positions, seg_of_token, block_table, max_pages,
-            page_size, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, n_tokens, nh, nkv, hd, write_kv, status);
+            page_size, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, n_tokens, nh, nkv, hd, write_kv, rot_dim,
+            interleaved, status);
     else
         return GESSO_ERR_BAD_DTYPE;
     return launch_status();

@@ -195,10 +195,13 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
                        eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                        positions: torch.Tensor, seg_of_token: torch.Tensor, block_table: torch.Tensor,
                        k_pages: torch.Tensor, v_pages: torch.Tensor, nh: int, nkv: int, hd: int,
-                       write_kv: bool, status: torch.Tensor, tiles=None) -> torch.Tensor:
+                       write_kv: bool, status: torch.Tensor, tiles=None, rot_dim: Optional[int] = None,
+                       interleaved: bool = False) -> torch.Tensor:
     """Norm + rotate q and k, write k and v into their pages; returns q as [N, nh, hd].  ``tiles`` =
     (seg_start, seg_pos0, tile_seg, tile_q0) of a step with prompt portions lets bfloat16 runs take the
-    kernel that works by 64-token tiles (wide loads, v written along the slots of its transposed page)."""
+    kernel that works by 64-token tiles (wide loads, v written along the slots of its transposed page).
+    ``rot_dim`` (default: the head size) is how many leading features of a head the tables rotate, the
+    rest pass through normed; ``interleaved`` pairs neighbours (2i, 2i+1) instead of the two halves."""
     _cuda_contig(qkv, "qkv")
     N = qkv.shape[0]
     heads = nh + 2 * nkv if write_kv else nh
@@ -215,9 +218,15 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
     if cos is not None:
         _cuda_contig(cos, "cos", torch.float32)
         _cuda_contig(sin, "sin", torch.float32)
-        _need(cos.shape[1] == hd // 2, "rotary table width must be half the head size")
+        rot_dim = hd if rot_dim is None else int(rot_dim)
+        _need(2 <= rot_dim <= hd and rot_dim % 2 == 0, "rotary size must be even and at most the head size")
+        _need(cos.shape[1] == rot_dim // 2 and sin.shape[1] == rot_dim // 2,
+              "rotary table width must be half the rotary size")
+    else:
+        rot_dim = 0
     q_out = torch.empty((N, nh, hd), dtype=qkv.dtype, device=qkv.device)
-    if (tiles is not None and write_kv and qkv.dtype == torch.bfloat16 and tiles[2].numel() > 0
+    full_half_split = cos is None or (rot_dim == hd and not interleaved)
+    if (tiles is not None and write_kv and qkv.dtype == torch.bfloat16 and tiles[2].numel() > 0 and full_half_split
             and _lib.library().gesso_qk_rope_store_tiles_takes(hd, page_size, nh, nkv)):
         seg_start, seg_pos0, tile_seg, tile_q0 = tiles
         _lib.check(_lib.library().gesso_qk_norm_rope_store_tiles(
@@ -228,7 +237,8 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
     _lib.check(_lib.library().gesso_qk_norm_rope_store(
         _p(qkv), _dt(qkv), _p(q_w), _p(k_w), float(eps), _p(cos), _p(sin), _p(positions),
         _p(seg_of_token), _p(block_table), block_table.shape[1], page_size, _p(q_out), _p(k_pages),
-        _p(v_pages), N, nh, nkv, hd, 1 if write_kv else 0, _p(status), _stream()), "qk_norm_rope_store")
+        _p(v_pages), N, nh, nkv, hd, 1 if write_kv else 0, int(rot_dim), 1 if interleaved else 0, _p(status),
+        _stream()), "qk_norm_rope_store")
     return q_out
 
 

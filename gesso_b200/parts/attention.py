@@ -84,11 +84,14 @@ class GQAttention(Mixer):
         writes = cache.writes
         qkv = ops.linear(x, self.w_qkv if writes else self.w_q, out_dtype=x.dtype)
         cos, sin = self.position.tables()
+        # a position part without layout() rotates the whole head by halves
+        rot_dim, interleaved = self.position.layout() if hasattr(self.position, "layout") else (self.hd, False)
         q = ops.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, self.eps if self.eps is not None else 0.0,
                                    cos, sin, ctx.positions, ctx.seg_of_token, cache.block_table,
                                    cache.k_pages, cache.v_pages, self.nh, self.nkv, self.hd, writes, ctx.status,
                                    tiles=None if ctx.decode_only else (ctx.seg_start, ctx.seg_pos0, ctx.tile_seg,
-                                                                       ctx.tile_q0))
+                                                                       ctx.tile_q0),
+                                   rot_dim=rot_dim or None, interleaved=interleaved)
         o = self.rt.attention(q, cache, ctx, self.window, self.scale)
         if residual is not None:
             return ops.linear_residual(o, self.w_o, residual, None), None

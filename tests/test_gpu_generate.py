@@ -531,3 +531,26 @@ def test_command_line(model_dirs, plain_models, tmp_path):
     assert r.returncode == 0 and sorted(os.listdir(out)) == ["config.json", "model.safetensors"]
     d = subprocess.run([sys.executable, "-m", "gesso_b200", "describe", "--model", str(out)], capture_output=True, text=True, env=env)
     assert d.returncode == 0 and "short_conv" in d.stdout
+    # generate straight from a configuration and a seed, no folder in between
+    g = subprocess.run([sys.executable, "-m", "gesso_b200", "generate", "--random-weights", "3", "--config", str(cfg),
+                        "--prompt-ids", "5,6,7", "--max-new-tokens", "3", "--n-ctx", "64"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert g.returncode == 0, g.stderr[-1500:]
+    line = json.loads([l for l in g.stdout.splitlines() if l.startswith("{")][0])
+    assert line["status"] == "complete" and line["ids"][:3] == [5, 6, 7] and len(line["ids"]) == 6
+    both = subprocess.run([sys.executable, "-m", "gesso_b200", "generate", "--model", str(out), "--random-weights", "3",
+                           "--prompt-ids", "5"], capture_output=True, text=True, env=env, timeout=120)
+    assert both.returncode == 2
+    # replay as a sub-command: the same program as bin/trace_run
+    steps = '{"step": 0, "entries": [{"id": "a", "tokens": [5, 6, 7], "want": [2]}], "end": ["a"]}\n'
+    rp = subprocess.run([sys.executable, "-m", "gesso_b200", "replay", "--model", model_dirs["a"], "--dtype", "float32",
+                         "--out", str(tmp_path / "rp"), "--max-tokens", "64"], input=steps, capture_output=True, text=True,
+                        env=env, timeout=600)
+    assert rp.returncode == 0 and "done 0" in rp.stdout, rp.stderr[-1500:]
+    row = np.fromfile(tmp_path / "rp" / "0.f32", dtype="<f4")
+    ref = plain_models["a"].logits([5, 6, 7])[2].numpy()
+    assert row.shape == ref.shape and float(np.abs(row - ref).max()) <= TOL32 * max(1.0, float(np.abs(ref).max()))
+    # bench as a sub-command hands its options to bench.py, which refuses more than one GPU with exit code 2
+    bn = subprocess.run([sys.executable, "-m", "gesso_b200", "bench", "--gpus", "2"], capture_output=True, text=True, env=env,
+                        timeout=120)
+    assert bn.returncode == 2 and "one GPU" in bn.stdout

@@ -95,8 +95,13 @@ def test_rope_part_tables_and_refusal():
     assert abs(float(cos[pos, i]) - math.cos(pos * 1e6 ** (-2 * i / 24))) < 1e-7
     assert abs(float(sin[pos, 5]) - math.sin(pos * 1e6 ** (-10 / 24))) < 1e-7
     part.check_head_dim(24)
+    part.check_head_dim(32)                       # the leading 24 of 32 features rotate, the rest pass through
+    assert part.layout() == (24, False)
     with pytest.raises(GessoError):
-        part.check_head_dim(32)                   # partial rotary is refused
+        part.check_head_dim(16)                   # more rotated features than the head has
+    with pytest.raises(GessoError):
+        build_position(PartSpec("rope", {"theta": 1e6, "rotary_dim": 7}))
+    assert build_position(PartSpec("rope", {"theta": 1e4, "rotary_dim": 8, "interleaved": True})).layout() == (8, True)
     # one table per (theta, size) is shared
     other = build_position(PartSpec("rope", {"theta": 1e6, "rotary_dim": 24}))
     other.bind({}, rt)
@@ -130,6 +135,59 @@ def test_attention_part_alone(dtype, window):
     assert rel_err(torch.cat(outs), want) < (1e-5 if dtype == torch.float32 else 4 * BF16_EPS)
     if window:   # pages behind the window went back to the pool
         assert eng.cache.pages_in_use()[0] < (T + 3) // 4
+
+
+def plain_rope_general(x, positions, theta, rot, interleaved):
+    """Rotary on the leading ``rot`` features of [T, heads, d] (angles pos * theta^(-2i/rot)), pairs (i, i + rot/2)
+    or, interleaved, (2i, 2i+1); the other features untouched.  For rot == d and halves it is P.rope."""
+    T, nheads, d = x.shape
+    i = torch.arange(rot // 2, dtype=torch.float64)
+    ang = torch.as_tensor(positions, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * i / rot)
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    ia = torch.arange(0, rot, 2) if interleaved else torch.arange(rot // 2)
+    ib = ia + 1 if interleaved else ia + rot // 2
+    a, b = x[..., ia], x[..., ib]
+    out[..., ia] = a * c - b * s
+    out[..., ib] = a * s + b * c
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rot,interleaved", [(8, True), (4, False), (6, True), (2, False)])
+def test_attention_part_with_partial_and_interleaved_rotary(dtype, rot, interleaved):
+    """The position part's other layouts, chosen by its parameters alone: a rotation of the leading features only,
+    and pairs of neighbours instead of halves; prompt portions and single tokens, against plain attention."""
+    from gesso_b200.config import PartSpec
+    from gesso_b200.engine import Engine, StepEntry
+    assert torch.equal(plain_rope_general(torch.ones(3, 2, 8, dtype=torch.float64), [0, 5, 9], 777.0, 8, False),
+                       P.rope(torch.ones(3, 2, 8, dtype=torch.float64), [0, 5, 9], 777.0))
+    params = dict(ATTN, position=PartSpec("rope", {"theta": 777.0, "rotary_dim": rot, "interleaved": interleaved}))
+    spec = tiny_spec(PartSpec("gqa_attention", params))
+    model, w = build_model(spec, dtype)
+    eng = Engine(model, max_positions=64, page_size=16, num_pages=8, max_requests=2)
+    part = model.blocks[0].mixer
+    T, nh, nkv, hd = 40, 6, 2, 8
+    x = torch.randn(T, 48, generator=torch.Generator().manual_seed(8)).to(dtype)
+    eng.admit("r")
+    outs = []
+    for a, b in ((0, 21), (21, 38), (38, 39), (39, 40)):
+        ctx, views = make_ctx(eng, [StepEntry("r", [0] * (b - a), [])])
+        outs.append(part.forward(x[a:b].to(DEV).contiguous(), ctx, views[0])[0])
+        eng.cache.commit("r", b - a)
+    p = "layers.0.mixer."
+    xn = folded_input(x, w, "layers.0.mixer_norm.weight", dtype)
+    q = P.rmsnorm((xn @ w[p + "q_proj.weight"].T).reshape(T, nh, hd), w[p + "q_norm.weight"], 1e-5)
+    k = P.rmsnorm((xn @ w[p + "k_proj.weight"].T).reshape(T, nkv, hd), w[p + "k_norm.weight"], 1e-5)
+    v = (xn @ w[p + "v_proj.weight"].T).reshape(T, nkv, hd)
+    pos = list(range(T))
+    o = P.causal_attention(plain_rope_general(q, pos, 777.0, rot, interleaved),
+                           plain_rope_general(k, pos, 777.0, rot, interleaved), v)
+    want = o.reshape(T, nh * hd) @ w[p + "o_proj.weight"].T
+    assert rel_err(torch.cat(outs), want) < (1e-5 if dtype == torch.float32 else 4 * BF16_EPS)
+    # the layouts are not the same thing: the default one gives another result
+    wrong = P.causal_attention(P.rope(q, pos, 777.0), P.rope(k, pos, 777.0), v).reshape(T, nh * hd) @ w[p + "o_proj.weight"].T
+    assert rel_err(wrong, want) > 1e-2
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
