@@ -71,6 +71,9 @@ class ModelSpec:
     final_norm: PartSpec
     tie_embedding: bool
     embedding_scale: float = 1.0
+    # logits = softcap * tanh(logit_scale * logits / softcap); no cap when None (LFM2 has neither)
+    logit_scale: float = 1.0
+    logit_softcap: Optional[float] = None
     # internal tensor name -> names it may carry in a checkpoint (first is canonical)
     tensor_names: Mapping[str, Tuple[str, ...]] = field(default_factory=dict)
     # checkpoint tensor names (regular expressions) that are ignored when present

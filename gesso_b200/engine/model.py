@@ -8,7 +8,7 @@ Forward of one step (src/Inference/Inference.jl:2358-2521 is the reference's per
 
     h = embedding[token_ids]                      (float32 residual stream)
     for entry in schedule:  pending = block(h, pending, ctx, cache_view(entry))
-    logits = lm_head( final_norm(h + pending)[wanted rows] )
+    logits = lm_head( final_norm(h + pending)[wanted rows] )      (then the spec's logit scale / soft cap, if any)
 """
 from __future__ import annotations
 
@@ -178,4 +178,7 @@ class Model:
                 x = self.final_norm.add_norm(h, None, None)
         else:
             x = self.final_norm.add_norm(h, pending[0], pending[1], rows=ctx.logit_rows)
-        return ops.linear(x, self.lm_head, out_dtype=torch.float32)
+        logits = ops.linear(x, self.lm_head, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0 or self.spec.logit_softcap is not None:
+            ops.logit_transform(logits, self.spec.logit_scale, self.spec.logit_softcap)
+        return logits

@@ -470,6 +470,18 @@ def linear_swiglu(x, w_gate_up: torch.Tensor, packed: bool) -> torch.Tensor:
     return swiglu(linear(x, w_gate_up, out_dtype=x.dtype), packed)
 
 
+_lib.declare("gesso_logit_transform", [_lib.P, _lib.LL, _lib.F, _lib.F])
+
+
+def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[float] = None) -> torch.Tensor:
+    """``softcap * tanh(scale * logits / softcap)`` (``scale * logits`` without a cap), in place on float32 logits."""
+    _cuda_contig(logits, "logits", torch.float32)
+    _need(softcap is None or softcap > 0, "the soft cap must be positive")
+    _lib.check(_lib.library().gesso_logit_transform(_p(logits), logits.numel(), float(scale), float(softcap or 0.0),
+                                                   _stream()), "logit_transform")
+    return logits
+
+
 # ---- sampling ----------------------------------------------------------------------------------
 def argmax_rows(logits: torch.Tensor):
     _cuda_contig(logits, "logits", torch.float32)

@@ -701,3 +701,35 @@ def test_toy_routed_feed_forward_and_toy_position_register_build_and_step(dtype,
     finally:
         unregister("feed_forward", "toy_top1_experts")
         unregister("position", "toy_linear_rotary")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_logit_scale_and_soft_cap_of_a_model_spec(dtype):
+    """An architecture that scales its logits and caps them softly says so in its model spec; the step function
+    applies both after the head (LFM2 does neither).  Whole prompt and single tokens, against the formula."""
+    import dataclasses
+    from gesso_b200 import ops
+    from gesso_b200.engine import Engine, Model, StepEntry
+    from gesso_b200.weights import random_tensors
+    base = tiny_spec([conv_spec(), attn_spec()])
+    spec = dataclasses.replace(base, logit_scale=3.5, logit_softcap=2.0)
+    tensors = random_tensors(base, 9, style="fan_in")
+    ids = torch.randint(0, 64, (21,), generator=torch.Generator().manual_seed(4)).tolist()
+    plain_eng = Engine(Model(base, tensors, dtype, DEV, 64), max_positions=64, max_requests=1)
+    plain_eng.admit("r")
+    raw = plain_eng.step([StepEntry("r", ids, list(range(21)))]).double().cpu()
+    want = 2.0 * torch.tanh(3.5 * raw / 2.0)
+    eng = Engine(Model(spec, tensors, dtype, DEV, 64), max_positions=64, max_requests=1)
+    eng.admit("r")
+    got = [eng.step([StepEntry("r", ids[:17], list(range(17)))]).clone()]
+    for t in range(17, 21):
+        got.append(eng.step([StepEntry("r", [ids[t]], [0])]).clone())
+    got = torch.cat(got).double().cpu()
+    assert float(got.abs().max()) <= 2.0 and float(raw.abs().max()) > 0.5
+    # single tokens take other kernels than the whole prompt in bfloat16, so the raw logits differ by roundings there
+    assert float((got[:17] - want[:17]).abs().max()) < 1e-5
+    assert float((got - want).abs().max()) < (1e-4 if dtype == torch.float32 else 0.05)
+    # the kernel alone, without a cap
+    x = torch.randn(5, 33, device=DEV)
+    y = ops.logit_transform(x.clone(), 0.25, None)
+    assert torch.allclose(y, 0.25 * x, rtol=1e-6, atol=0)
