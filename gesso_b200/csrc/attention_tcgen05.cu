@@ -209,11 +209,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     if (key > pos || key < lo) v[i] = 0xff800000u;      // -inf
                 }
             }
+            // four independent chains of three-input maxima: 32 instructions for 64 scores
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 64; i += 4) {
+            for (int i = 0; i < 64; i += 8) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(v[i + u]));
+                for (int u = 0; u < 4; ++u)
+                    mx4[u] = max3(mx4[u], __uint_as_float(v[i + 2 * u]), __uint_as_float(v[i + 2 * u + 1]));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the other half of the row
@@ -247,17 +249,25 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             l *= alpha;
             if (raise) m_ref = m_blk;
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            float l4[4] = {0.f, 0.f, 0.f, 0.f};
+            // score * scale - maximum and the running sums as packed pairs (one instruction for two values);
+            // the exponentials one by one (the special-function unit has no packed form in float32)
+            const unsigned long long scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_use, -m_use);
+            unsigned long long l2[4] = {0ull, 0ull, 0ull, 0ull};      // four chains of pairs of partial sums
             unsigned pk[32];
 #pragma unroll
             for (int i = 0; i < 64; i += 2) {
-                const float e0 = ex2_approx(fmaf(__uint_as_float(v[i]), scale_log2, -m_use));
-                const float e1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), scale_log2, -m_use));
-                l4[(i >> 1) & 3] += e0 + e1;
+                float x0, x1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), scale2, neg_m2), x0, x1);
+                const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+                l2[(i >> 1) & 3] = add_f32x2(l2[(i >> 1) & 3], pack_f32x2(e0, e1));
                 __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
                 pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
             }
-            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            {
+                float a0, a1;
+                unpack_f32x2(add_f32x2(add_f32x2(l2[0], l2[1]), add_f32x2(l2[2], l2[3])), a0, a1);
+                l += a0 + a1;
+            }
             tmem_st32(tm_p + lane_base + half * 32, pk);
             tmem_st_wait();
             tc_fence_before();
