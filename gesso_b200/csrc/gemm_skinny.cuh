@@ -24,9 +24,12 @@
 //                    with C, stores y[M, H] and shifts bx into the state: no kernel of its own.
 // A long inner size with a narrow output (the feed-forward's down projection) is split along K over
 // S blocks per tile, so that a block's share of K is short enough for its token-side fragments to
-// stay in registers and there are enough blocks to fill the device.  The S partial tiles go to a
-// workspace; the block that arrives last (a ticket per tile) adds them in the order 0..S-1 and
-// runs the epilogue, so the result is the same whichever block that is.
+// stay in registers and there are enough blocks to fill the device.  The S blocks of a tile are a
+// thread-block cluster (S = 2, 4, 8): each leaves its partial tile in its own shared memory, the
+// cluster meets at its barrier, and every block adds the S parts of its share of the tile's elements
+// through distributed shared memory, in the order 0..S-1, and runs the epilogue on them: one barrier
+// per tile, no trip through global memory.  Where no cluster can be had (S = 16) the partial tiles go
+// to a workspace and the block that arrives last (a ticket per tile) adds them in the same order.
 // Formulas: src/Operators/cpu.jl:293-311 (norm), 482-488 (SwiGLU), 629-630 (x W^T).
 #pragma once
 #include <math.h>
@@ -69,6 +72,23 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 }
 
 #define SK_WARPS 8
+
+// the address of this block's shared-memory object `addr` in block `rank` of the cluster, and a read from there
+__device__ __forceinline__ unsigned sk_cluster_map(unsigned addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float sk_ld_cluster(unsigned addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+// all threads of all blocks of the cluster; what a block wrote to its shared memory before is visible after
+__device__ __forceinline__ void sk_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
 #ifndef SK_RING_UNITS
 #define SK_RING_UNITS 160                    // ring size in units of 512 bytes per block (160: 80 KB)
 #endif
@@ -92,7 +112,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // costs (norm statistics, pipeline fill) are paid once per block.  ROWS = 16 or 8 rows of W per tile
 // (8 when there are too few 16-row tiles to fill the device; rows 8..15 of the MMA are then zero).
 // XC: chunks per warp and tile whose token-side fragments are kept in registers across tiles (0: reload).
-template <int NT, int EPI, bool NORM, int ROWS, int XC>
+template <int NT, int EPI, bool NORM, int ROWS, int XC, bool CL = false>
 __global__ void __launch_bounds__(SK_WARPS * 32, SK_MIN_BLOCKS)
 skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, const float* __restrict__ norm_w,
                    float eps, const bf16* __restrict__ W, void* __restrict__ out, const float* __restrict__ bias,
@@ -106,6 +126,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     __shared__ float rinv[NT * 8];
     __shared__ float ssw[SK_WARPS][NT * 8];
     __shared__ int s_last;
+    __shared__ float cl_part[CL ? 2 : 1][CL ? ROWS * NT * 8 : 1];    // this block's partial tile, for its cluster
     const int ks = S > 1 ? (int)(blockIdx.x % (unsigned)S) : 0;      // which share of K
     const int bid = S > 1 ? (int)(blockIdx.x / (unsigned)S) : (int)blockIdx.x;
     const int gdim = S > 1 ? (int)(gridDim.x / (unsigned)S) : (int)gridDim.x;
@@ -305,7 +326,31 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
             __syncthreads();
         }
         const int n0 = tile * ROWS;
-        if (EPI != EPI_SWIGLU && EPI != EPI_CONV && !NORM && S > 1) {
+        if (CL) {
+            // the S blocks of this tile are one cluster (rank ks): partial tiles through distributed shared memory
+            constexpr int TILE = ROWS * NT * 8;
+            for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
+                const int r = idx % ROWS, m = idx / ROWS;
+                float v = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < SK_WARPS; ++ww) v += part[buf][ww][r][m];
+                cl_part[buf][idx] = v;
+            }
+            // One barrier per tile is enough: cl_part is double buffered, and a block writes a buffer again only
+            // after the barrier of the tile in between, which every block reaches after its reads of this one.
+            sk_cluster_sync();
+            const unsigned mine = (unsigned)__cvta_generic_to_shared(&cl_part[buf][0]);
+            for (int idx = ks + S * (int)threadIdx.x; idx < TILE; idx += S * (int)blockDim.x) {
+                const int r = idx % ROWS, m = idx / ROWS;
+                if (m >= M) continue;
+                float v = 0.f;
+                for (int sp = 0; sp < S; ++sp) v += sk_ld_cluster(sk_cluster_map(mine + 4u * (unsigned)idx, (unsigned)sp));
+                const size_t o = (size_t)m * N + n0 + r;
+                if (EPI == EPI_BF16) reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v);
+                else if (EPI == EPI_F32) reinterpret_cast<float*>(out)[o] = v;
+                else reinterpret_cast<float*>(out)[o] += v + (bias ? bias[n0 + r] : 0.f);
+            }
+        } else if (EPI != EPI_SWIGLU && EPI != EPI_CONV && !NORM && S > 1) {
             // this block's partial tile -> workspace; the last of the S blocks adds them up
             constexpr int TILE = ROWS * NT * 8;
             float* wsp = ws + (size_t)tile * S * TILE;
@@ -400,6 +445,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
         buf ^= 1;
     }
     cp_async_wait<0>();
+    if (CL) sk_cluster_sync();     // nobody leaves while a block of its cluster may still read its partial tile
 }
 
 #define SK_RING_BYTES(ROWS) (SK_STAGES_FOR(ROWS) * ((ROWS) / 8) * SK_WARPS * 32 * 16)
@@ -428,6 +474,38 @@ static int launch_one(const void* x, const float* h_in, const float* norm_w, flo
     return launch_status();
 }
 
+// The same for a product split along K whose S blocks per tile form a cluster (S = 2, 4, 8): no workspace.
+template <int NT, int EPI, int ROWS, int XC>
+static int launch_cluster(const void* x, const void* W, void* out, const float* bias, int M, int N, int K, int S,
+                          cudaStream_t stream) {
+    auto kernel = skinny_gemm_kernel<NT, EPI, false, ROWS, XC, true>;
+    static bool configured = false;   // once per instantiation, outside any stream capture
+    if (!configured) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_RING_BYTES(ROWS));
+        configured = true;
+    }
+    const int n_tiles = N / ROWS;
+    const int per_share = n_tiles < SK_MAX_BLOCKS / S ? n_tiles : SK_MAX_BLOCKS / S;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(per_share * S);
+    cfg.blockDim = dim3(SK_WARPS * 32);
+    cfg.dynamicSmemBytes = SK_RING_BYTES(ROWS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = gesso_pdl_enabled ? 2 : 1;
+    const ConvEpi none = {};
+    cudaLaunchKernelEx(&cfg, kernel, (const bf16*)x, (const float*)nullptr, (const float*)nullptr, 0.f, (const bf16*)W, out,
+                       bias, M, N, K / S, K, S, (float*)nullptr, (int*)nullptr, none);
+    return launch_status();
+}
+
 template <int NT, int EPI, bool NORM>
 static int launch_shape(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
                         const float* bias, int M, int N, int K, void* ws, long long ws_bytes, const ConvEpi& cv,
@@ -435,12 +513,17 @@ static int launch_shape(const void* x, const float* h_in, const float* norm_w, f
     // token-side fragments stay in registers when a warp has at most 8 chunks per tile (K <= 2048)
     auto cacheable = [](int k) { return k / 32 <= 8 * SK_WARPS && k % (32 * SK_WARPS) == 0 && NT * (k / (32 * SK_WARPS)) <= 16; };
     int S = 1;
-    if (!cacheable(K) && !NORM && EPI != EPI_SWIGLU && EPI != EPI_CONV && ws != nullptr && N / 8 <= SK_TICKETS) {
-        // split K over S blocks per tile, the smallest S whose share is cacheable and fits the workspace
+    if (!cacheable(K) && !NORM && EPI != EPI_SWIGLU && EPI != EPI_CONV) {
+        // split K over S blocks per tile, the smallest S whose share is cacheable: a cluster up to 8 blocks
+        // (no workspace); 16 blocks through the workspace if it is there and large enough
         for (int s = 2; s <= 16; s *= 2) {
             // sized for 16 token rows whatever M is: the choice of S must not depend on the batch
             const long long need = (long long)SK_TICKETS * 4 + (long long)N * s * 16 * 4;
-            if (K % s == 0 && cacheable(K / s) && need <= ws_bytes) { S = s; break; }
+            const bool room = s <= 8 || (ws != nullptr && N / 8 <= SK_TICKETS && need <= ws_bytes);
+            if (K % s == 0 && cacheable(K / s)) {
+                if (room) S = s;
+                break;
+            }
         }
     }
     const int Ks = K / S;
@@ -448,6 +531,22 @@ static int launch_shape(const void* x, const float* h_in, const float* norm_w, f
     const bool small_rows = EPI != EPI_SWIGLU && (N / 16) * S < SK_MAX_BLOCKS && N % 8 == 0;
     const int xc = cache_x ? Ks / (32 * SK_WARPS) : 0;
 #define GO(ROWS, XC) return launch_one<NT, EPI, NORM, ROWS, XC>(x, h_in, norm_w, eps, W, out, bias, M, N, K, S, ws, cv, stream)
+    if constexpr (!NORM && EPI != EPI_SWIGLU && EPI != EPI_CONV) {
+        if (S > 1 && S <= 8) {       // a split product whose share is cacheable: xc is 2, 4 or 8
+#define GC(ROWS, XC) return launch_cluster<NT, EPI, ROWS, XC>(x, W, out, bias, M, N, K, S, stream)
+            if (small_rows) {
+                if (xc == 8) GC(8, 8);
+                if (xc == 4) GC(8, 4);
+                if (xc == 2) GC(8, 2);
+            } else {
+                if (xc == 8) GC(16, 8);
+                if (xc == 4) GC(16, 4);
+                if (xc == 2) GC(16, 2);
+            }
+#undef GC
+            S = 1;                   // no cached shape for it: unsplit (never the case for the sizes that split)
+        }
+    }
     if constexpr (EPI == EPI_CONV) {
         if (xc == 8) GO(24, 8);
         if (xc == 4) GO(24, 4);
