@@ -95,6 +95,9 @@ __device__ __forceinline__ void sk_cluster_sync() {
 #ifndef SK_MIN_BLOCKS
 #define SK_MIN_BLOCKS 1                      // blocks per SM the register allocation leaves room for
 #endif
+#ifndef SK_BLOCKS_PER_SM
+#define SK_BLOCKS_PER_SM 2                               // persistent blocks per SM (two fit by shared memory and registers)
+#endif
 #define SK_STAGES_FOR(ROWS) (SK_RING_UNITS / (ROWS))   // chunks in flight per thread: 10 of 32 bytes or 20 of 16 bytes
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
@@ -112,8 +115,10 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // costs (norm statistics, pipeline fill) are paid once per block.  ROWS = 16 or 8 rows of W per tile
 // (8 when there are too few 16-row tiles to fill the device; rows 8..15 of the MMA are then zero).
 // XC: chunks per warp and tile whose token-side fragments are kept in registers across tiles (0: reload).
+// Two blocks have to fit an SM (the grid is sized for that): with two token tiles the register allocation
+// would otherwise go a few registers past half of the file and leave every second block waiting.
 template <int NT, int EPI, bool NORM, int ROWS, int XC, bool CL = false>
-__global__ void __launch_bounds__(SK_WARPS * 32, SK_MIN_BLOCKS)
+__global__ void __launch_bounds__(SK_WARPS * 32, NT >= 2 ? SK_BLOCKS_PER_SM : SK_MIN_BLOCKS)
 skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, const float* __restrict__ norm_w,
                    float eps, const bf16* __restrict__ W, void* __restrict__ out, const float* __restrict__ bias,
                    int M, int N, int K, int ldk, int S, float* __restrict__ ws, int* __restrict__ tickets,
@@ -231,7 +236,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
         return xb;
     };
     // Token-side fragments live in a small register queue: slot ii serves the items i = ii, ii + XD,
-    // ... of every tile.  With XC > 0 a tile has exactly XC items per warp and the queue is filled
+    // ... of every tile.  With XC > 0 a tile has at most XC items per warp and the queue is filled
     // once; otherwise a slot is refilled right after it is used, XD items ahead, so that the L2
     // latency of the activations never sits between the arrival of W and the MMA.
     constexpr int XD = XC > 0 ? XC : 4;
@@ -449,9 +454,6 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
 }
 
 #define SK_RING_BYTES(ROWS) (SK_STAGES_FOR(ROWS) * ((ROWS) / 8) * SK_WARPS * 32 * 16)
-#ifndef SK_BLOCKS_PER_SM
-#define SK_BLOCKS_PER_SM 2                               // persistent blocks per SM (two fit by shared memory and registers)
-#endif
 #define SK_MAX_BLOCKS (SK_BLOCKS_PER_SM * gesso_sm_count())
 
 #define SK_TICKETS 4096                                  // tiles a split product may have (ints at the head of the workspace)
@@ -510,8 +512,10 @@ template <int NT, int EPI, bool NORM>
 static int launch_shape(const void* x, const float* h_in, const float* norm_w, float eps, const void* W, void* out,
                         const float* bias, int M, int N, int K, void* ws, long long ws_bytes, const ConvEpi& cv,
                         cudaStream_t stream) {
-    // token-side fragments stay in registers when a warp has at most 8 chunks per tile (K <= 2048)
-    auto cacheable = [](int k) { return k / 32 <= 8 * SK_WARPS && k % (32 * SK_WARPS) == 0 && NT * (k / (32 * SK_WARPS)) <= 16; };
+    // token-side fragments stay in registers when a warp has at most 8 chunks per tile (K <= 2048); the queue
+    // has 2, 4 or 8 places, of which a tile uses the first ceil(chunks / warps)
+    auto per_warp = [](int k) { return (k / 32 + SK_WARPS - 1) / SK_WARPS; };
+    auto cacheable = [&](int k) { return k % 32 == 0 && per_warp(k) <= 8 && NT * per_warp(k) <= 16; };
     int S = 1;
     if (!cacheable(K) && !NORM && EPI != EPI_SWIGLU && EPI != EPI_CONV) {
         // split K over S blocks per tile, the smallest S whose share is cacheable: a cluster up to 8 blocks
@@ -520,7 +524,7 @@ static int launch_shape(const void* x, const float* h_in, const float* norm_w, f
             // sized for 16 token rows whatever M is: the choice of S must not depend on the batch
             const long long need = (long long)SK_TICKETS * 4 + (long long)N * s * 16 * 4;
             const bool room = s <= 8 || (ws != nullptr && N / 8 <= SK_TICKETS && need <= ws_bytes);
-            if (K % s == 0 && cacheable(K / s)) {
+            if (K % (32 * s) == 0 && cacheable(K / s)) {
                 if (room) S = s;
                 break;
             }
@@ -529,7 +533,7 @@ static int launch_shape(const void* x, const float* h_in, const float* norm_w, f
     const int Ks = K / S;
     const bool cache_x = cacheable(Ks);
     const bool small_rows = EPI != EPI_SWIGLU && (N / 16) * S < SK_MAX_BLOCKS && N % 8 == 0;
-    const int xc = cache_x ? Ks / (32 * SK_WARPS) : 0;
+    const int xc = !cache_x ? 0 : per_warp(Ks) <= 2 ? 2 : per_warp(Ks) <= 4 ? 4 : 8;
 #define GO(ROWS, XC) return launch_one<NT, EPI, NORM, ROWS, XC>(x, h_in, norm_w, eps, W, out, bias, M, N, K, S, ws, cv, stream)
     if constexpr (!NORM && EPI != EPI_SWIGLU && EPI != EPI_CONV) {
         if (S > 1 && S <= 8) {       // a split product whose share is cacheable: xc is 2, 4 or 8

@@ -750,7 +750,7 @@ def test_sampler_low_temperature_is_argmax_and_nucleus_keeps_the_top_set():
 # ---- skinny matrix product (steps of few tokens) -------------------------------------------------------
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(16, 32), (48, 96), (2048, 2048), (160, 8192), (503 * 16, 64), (32, 352),
-                                 (64, 4096), (2048, 8192), (48, 6144)])
+                                 (64, 4096), (2048, 8192), (48, 6144), (48, 6912), (32, 1728), (64, 1120)])
 def test_skinny_gemm_epilogues(M, N, K):
     from gesso_b200 import ops
     g = torch.Generator().manual_seed(M * 1000 + N + K)
@@ -784,12 +784,13 @@ def test_skinny_gemm_epilogues(M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 7, 8, 13, 16])
-@pytest.mark.parametrize("H,F", [(2048, 8192), (1536, 6144), (2048, 4096), (256, 10240), (2560, 5120)])
+@pytest.mark.parametrize("H,F", [(2048, 8192), (1536, 6144), (2048, 4096), (256, 10240), (2560, 5120), (1536, 6912)])
 def test_skinny_feed_forward_of_few_tokens(M, H, F):
     """The feed-forward of a decoding step at widths where a block walks several tiles (folded norm +
     gate/up product + SwiGLU, then the down product with its inner size split over blocks and the
-    residual add) against the formulas.  Inner sizes of 6 and 10 chunks per warp (1536, 2560) take the
-    path whose token-side fragments are reloaded tile after tile."""
+    residual add) against the formulas.  An inner size of 6 chunks per warp (1536) uses six places of a
+    queue of eight, 6912 splits into four shares of 54 chunks (seven per warp, the last one ragged), and
+    10 chunks per warp (2560) take the path whose token-side fragments are reloaded tile after tile."""
     from gesso_b200 import ops
     g = torch.Generator().manual_seed(M + H + F)
     gate = (torch.randn(F, H, generator=g) / math.sqrt(H)).to(torch.bfloat16).to(DEV)
