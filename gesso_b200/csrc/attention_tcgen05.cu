@@ -1,7 +1,8 @@
 // Flash prefill attention on the 5th-generation tensor cores (bfloat16, head size 64, paged cache).
 //
-// A block owns 128 query rows: 128/G consecutive tokens of one request times the G query heads of
-// one kv group, so a single copy of K and V serves every head of the group (the GQA map
+// A block owns up to 128 query rows: floor(128/G) consecutive tokens of one request times the G query
+// heads of one kv group (G = 2 .. 16; where G does not divide 128 the last 128 - G floor(128/G) rows
+// are zero and idle), so a single copy of K and V serves every head of the group (the GQA map
 // h -> h / (nh/nkv) of src/Inference/Inference.jl:1398).  It walks the keys in blocks of 128:
 //
 //   TMA warp      Q once (3-D tensor map [token][head][feature], 128-byte swizzle); per key block 8
@@ -60,7 +61,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     pdl_launch_dependents();
     pdl_wait();
     const int TOK = 128 / G;                      // tokens per block
-    const int sub = 64 / TOK;                     // blocks per 64-token tile of the step's tile list
+    const int sub = (64 + TOK - 1) / TOK;         // blocks per 64-token tile of the step's tile list
     // Long tiles first: the queries at the end of a prompt have the most keys to read (up to 17 key blocks
     // at 2,048 tokens where the first tiles have one).  Blocks are handed out in the order of blockIdx.x, so
     // the kv heads of one tile are neighbours there and the tiles go from the longest to the shortest:
@@ -70,10 +71,11 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int tile = bx / sub;
     const int seg = tile_seg[tile];
     const int t0 = seg_start[seg], n = seg_start[seg + 1] - t0;
-    const int q0 = tile_q0[tile] + (bx % sub) * TOK;
+    const int q_in_tile = (bx % sub) * TOK;
+    const int q0 = tile_q0[tile] + q_in_tile;
     if (q0 >= n) return;                          // nothing of this block lies inside the portion
     const int p0 = seg_pos0[seg];
-    const int rows_tok = min(TOK, n - q0);        // valid tokens of this block
+    const int rows_tok = min(min(TOK, 64 - q_in_tile), n - q0);       // valid tokens of this block
     const int pos_first = p0 + q0, pos_last = p0 + q0 + rows_tok - 1;
     const int first_key = window > 0 ? max(0, pos_first - window + 1) : 0;
     const int kb0 = first_key / FA_BK, kb1 = pos_last / FA_BK;         // key blocks kb0..kb1
@@ -94,6 +96,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         tmem_alloc(&s.tmem_base, 256);
         tmem_relinquish();
     }
+    if (TOK * G < 128) {
+        // the rows behind the last whole token are not written by the load of Q: zero them for the tensor cores
+        // (rows are independent, so what they hold could not reach another row, but NaN patterns would wander
+        // through these rows' softmax for nothing)
+        for (int i = TOK * G * FA_HD + (int)threadIdx.x; i < 128 * FA_HD; i += FA_THREADS) s.q[i] = __float2bfloat16(0.f);
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -106,7 +115,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         // the block table, one block ahead) and issue its two TMA loads themselves, so the eight
         // lookups and sixteen loads of a block go out side by side instead of one after the other.
         if (lane == 0) {
-            mbar_expect_tx(&s.q_full, 128 * FA_HD * sizeof(bf16));
+            mbar_expect_tx(&s.q_full, TOK * G * FA_HD * sizeof(bf16));
             tma_load_3d(s.q, &map_q, 0, kvh * G, t0 + q0, &s.q_full);
         }
         // A page beyond the sequence or given back behind a window is wholly masked.  Its probabilities
@@ -316,7 +325,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 GESSO_API int gesso_attention_tcgen05_takes(int hd, int page_size, int nh, int nkv) {
     if (hd != FA_HD || page_size < 16 || page_size % 16 != 0 || nkv <= 0 || nh % nkv != 0) return 0;
     const int G = nh / nkv;
-    return G == 2 || G == 4 || G == 8 || G == 16;
+    return G >= 2 && G <= 16;
 }
 
 // q: bf16 [n_tokens, nh, 64]; k_pages bf16 [pages, nkv, page_size, 64]; v_pages bf16 [pages, nkv, 64, page_size];
@@ -370,8 +379,9 @@ GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages
             return (int)cudaGetLastError();
         configured = true;
     }
-    if ((long long)n_tiles * (64 / TOK) * nkv > 2147483647LL) return GESSO_ERR_BAD_SIZE;
-    const dim3 grid((unsigned)(n_tiles * (64 / TOK) * nkv));
+    const int sub = (64 + TOK - 1) / TOK;
+    if ((long long)n_tiles * sub * nkv > 2147483647LL) return GESSO_ERR_BAD_SIZE;
+    const dim3 grid((unsigned)(n_tiles * sub * nkv));
     launch_pdl(prefill_attention_tcgen05_kernel, grid, dim3(FA_THREADS), smem, stream,
         mq, mk, mv, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, G,
         window, scale * FA_LOG2E, num_pages, status);

@@ -740,7 +740,7 @@ _lib.declare("gesso_prefill_attention_tcgen05", [_lib.P, _lib.P, _lib.P, _lib.I,
 
 
 def attention_tcgen05_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
-    """Head size 64, pages in multiples of 16 slots, 2 / 4 / 8 / 16 query heads per kv head."""
+    """Head size 64, pages in multiples of 16 slots, 2 to 16 query heads per kv head."""
     return bool(_lib.library().gesso_attention_tcgen05_takes(hd, page_size, nh, nkv))
 
 

@@ -101,7 +101,8 @@ def test_tcgen05_few_rows_clusters(cluster):
 
 # ---- flash prefill attention on tcgen05 --------------------------------------------------------------
 @pytest.mark.parametrize("window", [None, 50, 200])
-@pytest.mark.parametrize("nh,nkv,page", [(8, 2, 16), (32, 8, 16), (4, 2, 32), (8, 1, 16), (16, 1, 32)])
+@pytest.mark.parametrize("nh,nkv,page", [(8, 2, 16), (32, 8, 16), (4, 2, 32), (8, 1, 16), (16, 1, 32),
+                                         (24, 8, 16), (6, 2, 32), (10, 2, 16), (12, 2, 16), (7, 1, 16), (12, 1, 48)])
 def test_tcgen05_prefill_attention(window, nh, nkv, page):
     import test_gpu_kernels as K
     from gesso_b200 import ops
