@@ -234,6 +234,9 @@ struct ByteHist {
 struct CrossShared {
     ByteHist mine[2];          // this block's slice (two copies: peers may still read the pass before)
     ByteHist all;              // the whole row: the blocks' histograms added in rank order
+    ByteHist top[2];           // the whole row's histograms of the two top bytes, as the first walk over the row
+    unsigned long long top_prefix[2];     // built them, and the prefix each was built under: a later walk that
+    int top_valid[2];                     // comes by with the same prefix takes them as they are
     double red[33];
     double exchange[2];        // a value each block shows its peers (two copies, as above)
     unsigned long long prefix;
@@ -251,11 +254,14 @@ struct CrossShared {
 // far; `above` is the mass of all weights whose pattern is larger than any with this prefix.  Each
 // warp keeps a histogram of its own over its part of the block's slice: in a step of 32 elements
 // the lanes with the same byte value form a group (match.any), the group's first lane adds the
-// group's weights up in lane order and adds the sum to the warp's histogram (all 32 lanes with one
-// value, the usual case in the top bytes, take a butterfly instead).  The warps' histograms are
-// added in warp order, the blocks' in rank order (read from the peers' shared memory), so the sums
-// do not depend on timing.  As soon as the chosen value holds a single element, that element is
-// the answer and the remaining bytes are skipped.
+// group's weights up in lane order and adds the sum to the warp's histogram (steps with at most six
+// values, the usual case in the top bytes, take one butterfly per value instead, the other lanes
+// adding zero).  The warps' histograms are added in warp order, the blocks' in rank order (read from
+// the peers' shared memory), and the walk down the 256 values is a warp's scan in lane order, so the
+// sums do not depend on timing.  As soon as the chosen value holds a single element, that element is
+// the answer and the remaining bytes are skipped.  The histograms of the two top bytes are kept with
+// the prefix they were built under: the draw's walk follows the nucleus cut's path there nearly
+// always and then scans the row for neither.
 struct CrossResult { int id; double mass; };
 
 __device__ CrossResult descending_cross(const Weights& W, int V, int lo, int hi_id, double target, bool strict,
@@ -266,10 +272,20 @@ __device__ CrossResult descending_cross(const Weights& W, int V, int lo, int hi_
     if (threadIdx.x == 0) { sh.prefix = 0ull; sh.above = 0.0; sh.done = 0; }
     __syncthreads();
     for (int byte = 7; byte >= 0; --byte) {
-        for (int b = lane; b < 256; b += 32) { wh.mass[b] = 0.0; wh.count[b] = 0; wh.last[b] = -1; }
-        __syncwarp();
         const unsigned long long prefix = sh.prefix;
         const int shift = byte * 8;
+        // a histogram depends on the prefix, not on the target: where the second walk over a row follows the first
+        // one's path through the two top bytes (nearly all of the mass lies there) it takes the first one's histograms
+        const int lvl = 7 - byte;
+        const bool keep = lvl < 2;
+        if (keep && sh.top_valid[lvl] && sh.top_prefix[lvl] == prefix) {
+            const ByteHist& top = sh.top[lvl];
+            for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+                sh.all.mass[b] = top.mass[b]; sh.all.count[b] = top.count[b]; sh.all.last[b] = top.last[b];
+            }
+        } else {
+        for (int b = lane; b < 256; b += 32) { wh.mass[b] = 0.0; wh.count[b] = 0; wh.last[b] = -1; }
+        __syncwarp();
         for (int base = lo + warp * 32; base < hi_id; base += SAMPLE_THREADS) {
             const int i = base + lane;
             const bool valid = i < hi_id;
@@ -286,14 +302,30 @@ __device__ CrossResult descending_cross(const Weights& W, int V, int lo, int hi_
                 if (lane == 0) { wh.mass[b0] += sum; wh.count[b0] += 32; wh.last[b0] = base + 31; }
             } else {
                 const unsigned grp = __match_any_sync(0xffffffffu, b);
-                unsigned m = match ? grp : 0u;
+                const bool leader = match && lane == __ffs(grp) - 1;
+                unsigned leaders = __ballot_sync(0xffffffffu, leader);
                 double sum = 0.0;
-                while (__any_sync(0xffffffffu, m != 0u)) {
-                    const int src = m ? __ffs(m) - 1 : lane;
-                    const double v = __shfl_sync(0xffffffffu, w, src);
-                    if (m) { sum += v; m &= m - 1; }
+                if (__popc(leaders) <= 6) {
+                    // few values, large groups (the top bytes): one butterfly per value, the others adding zero
+                    while (leaders) {
+                        const int src = __ffs(leaders) - 1;
+                        leaders &= leaders - 1;
+                        const int bv = __shfl_sync(0xffffffffu, b, src);
+                        double t = (match && b == bv) ? w : 0.0;
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+                        if (lane == src) sum = t;
+                    }
+                } else {
+                    // many values, small groups: every lane walks the members of its group in lane order
+                    unsigned m = match ? grp : 0u;
+                    while (__any_sync(0xffffffffu, m != 0u)) {
+                        const int src = m ? __ffs(m) - 1 : lane;
+                        const double v = __shfl_sync(0xffffffffu, w, src);
+                        if (m) { sum += v; m &= m - 1; }
+                    }
                 }
-                if (match && lane == __ffs(grp) - 1) {
+                if (leader) {
                     wh.mass[b] += sum;
                     wh.count[b] += __popc(grp);
                     wh.last[b] = base + (31 - __clz(grp));     // bases ascend: the last write is the highest id
@@ -323,30 +355,69 @@ __device__ CrossResult descending_cross(const Weights& W, int V, int lo, int hi_
                 last = max(last, peer_i32(&mine.last[b], r));
             }
             sh.all.mass[b] = mass; sh.all.count[b] = count; sh.all.last[b] = last;
+            if (keep && !sh.top_valid[lvl]) { sh.top[lvl].mass[b] = mass; sh.top[lvl].count[b] = count; sh.top[lvl].last[b] = last; }
         }
         ++round;
+        }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            double run = sh.above;
-            int pick = -1, last_occupied = 0;
-            double run_before_last = run;
-            for (int b = 255; b >= 0; --b) {
-                if (sh.all.count[b] <= 0) continue;
-                const double next = run + sh.all.mass[b];
+        if (warp == 0) {
+            // The walk down the 256 values, by one warp: lane l owns the values 255 - 8 l .. 248 - 8 l, adds its
+            // occupied ones up, the lanes' sums are scanned in lane order (a fixed order: the same sums every
+            // time), and every lane then walks its eight values from the mass above them; the first lane with a
+            // crossing holds the answer.
+            double m[8];
+            int c[8];
+            double local = 0.0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int b = 255 - 8 * lane - k;
+                c[k] = sh.all.count[b];
+                m[k] = c[k] > 0 ? sh.all.mass[b] : 0.0;
+                local += m[k];
+            }
+            double incl = local;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            double run = __shfl_up_sync(0xffffffffu, incl, 1);
+            run = sh.above + (lane == 0 ? 0.0 : run);
+            int pick = -1, low = -1;                 // low: this lane's smallest occupied value
+            double run_pick = 0.0, run_low = 0.0;    // the mass above them
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (c[k] <= 0) continue;
+                const double next = run + m[k];
                 const bool crossed = strict ? (next > target) : (next >= target);
-                if (crossed) { pick = b; break; }
-                last_occupied = b;
-                run_before_last = run;
+                if (crossed && pick < 0) { pick = 255 - 8 * lane - k; run_pick = run; }
+                low = 255 - 8 * lane - k;
+                run_low = run;
                 run = next;
             }
-            // if nothing crossed (rounding), the walk ends in the smallest occupied bucket
-            if (pick < 0) { pick = last_occupied; run = run_before_last; }
-            sh.above = run;
-            sh.prefix = prefix | ((unsigned long long)pick << shift);
-            if (sh.all.count[pick] == 1) {        // one element left: it is the answer
-                sh.id = sh.all.last[pick];
-                sh.mass = run + sh.all.mass[pick];
-                sh.done = 1;
+            const unsigned crossed_in = __ballot_sync(0xffffffffu, pick >= 0);
+            const unsigned occupied_in = __ballot_sync(0xffffffffu, low >= 0);
+            int src;
+            if (crossed_in) {
+                src = __ffs(crossed_in) - 1;
+            } else {
+                // nothing crossed (rounding): the walk ends in the smallest occupied value
+                src = occupied_in ? 31 - __clz(occupied_in) : 0;
+                pick = low;
+                run_pick = run_low;
+            }
+            pick = __shfl_sync(0xffffffffu, pick, src);
+            run_pick = __shfl_sync(0xffffffffu, run_pick, src);
+            if (pick < 0) { pick = 0; run_pick = sh.above; }         // an empty histogram: nothing matched
+            if (lane == 0) {
+                if (keep && !sh.top_valid[lvl]) { sh.top_valid[lvl] = 1; sh.top_prefix[lvl] = prefix; }
+                sh.above = run_pick;
+                sh.prefix = prefix | ((unsigned long long)pick << shift);
+                if (sh.all.count[pick] == 1) {        // one element left: it is the answer
+                    sh.id = sh.all.last[pick];
+                    sh.mass = run_pick + sh.all.mass[pick];
+                    sh.done = 1;
+                }
             }
         }
         __syncthreads();
@@ -448,12 +519,14 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const double* __rest
     // this block's slice of the ids, in whole steps of 32
     const int per = ((V + C - 1) / C + 31) / 32 * 32;
     const int lo = min(V, (int)rank * per), hi_id = min(V, lo + per);
-    if (threadIdx.x == 0) s_bad = 0;
+    if (threadIdx.x == 0) { s_bad = 0; sh.top_valid[0] = sh.top_valid[1] = 0; }
     __syncthreads();
-    // the maximum and the check for non-finite values: every block over the whole row
+    // the maximum and the check for non-finite values: every block over its slice, the cluster puts them together
+    // (a slice with a non-finite value shows its peers a NaN)
     float hi = -INFINITY;
     int bad = 0;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+#pragma unroll 8
+    for (int i = lo + threadIdx.x; i < hi_id; i += blockDim.x) {
         const float v = row[i];
         if (!isfinite(v)) bad = 1;
         hi = fmaxf(hi, v);
@@ -468,8 +541,17 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const double* __rest
         if (threadIdx.x == 0) s_max[32] = v;
     }
     __syncthreads();
-    hi = s_max[32];
-    if (s_bad) {                                 // the same in every block: nobody waits at a barrier below
+    {
+        double maxima[SAMPLE_CLUSTER];
+        cluster_gather(s_bad ? (double)NAN : (double)s_max[32], maxima, sh, round);
+        bad = 0;
+        hi = -INFINITY;
+        for (int r = 0; r < C; ++r) {
+            if (maxima[r] != maxima[r]) bad = 1;
+            else hi = fmaxf(hi, (float)maxima[r]);
+        }
+    }
+    if (bad) {                                   // the same in every block: nobody waits at a barrier below
         if (threadIdx.x == 0 && rank == 0) { nonfinite[rowi] = 1; ids[rowi] = 0; }
         return;
     }
@@ -511,14 +593,32 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const double* __rest
         for (int i = i0; i < i1; ++i) mine += W(i);
         s_part[threadIdx.x] = mine;
         __syncthreads();
-        if (threadIdx.x == 0) {
-            int owner = -1;
-            for (int t = 0; t < (int)blockDim.x; ++t) {
-                if (r < run + s_part[t]) { owner = t; break; }
-                run += s_part[t];
+        if (threadIdx.x < 32) {
+            // the thread whose chunk holds the draw: lane l adds up the chunks of threads 32 l .. 32 l + 31, the
+            // lanes' sums are scanned in lane order, and each lane then walks its 32 chunks from the mass before them
+            const int lane = threadIdx.x, per_lane = (int)blockDim.x / 32;
+            double local = 0.0;
+            for (int t = 0; t < per_lane; ++t) local += s_part[lane * per_lane + t];
+            double incl = local;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
             }
-            sh.id = owner;
-            sh.above = run;
+            double before = __shfl_up_sync(0xffffffffu, incl, 1);
+            before = run + (lane == 0 ? 0.0 : before);
+            int owner = -1;
+            double at = 0.0;
+            for (int t = 0; t < per_lane; ++t) {
+                const double next = before + s_part[lane * per_lane + t];
+                if (r < next) { owner = lane * per_lane + t; at = before; break; }
+                before = next;
+            }
+            const unsigned found = __ballot_sync(0xffffffffu, owner >= 0);
+            const int src = found ? __ffs(found) - 1 : 0;
+            owner = __shfl_sync(0xffffffffu, owner, src);
+            at = __shfl_sync(0xffffffffu, at, src);
+            if (lane == 0) { sh.id = found ? owner : -1; sh.above = at; }
         }
         __syncthreads();
         const int owner = sh.id;
