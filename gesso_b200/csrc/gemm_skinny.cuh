@@ -66,6 +66,13 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
+// a load that stays where it is written (the compiler may not move it down to its use)
+__device__ __forceinline__ float ld_f32_now(const float* p) {
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];\n" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ unsigned pack2(float a, float b) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<unsigned*>(&v);
@@ -257,6 +264,15 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
     int c_stage = 0, buf = 0;
     for (int tk = 0; tk < my_tiles; ++tk) {
         const int tile = bid + tk * gdim;
+        // residual epilogue: the element of the stream this thread will add to is asked for now, so that its trip
+        // from the cache runs beside the tile's products instead of behind them (one element per thread: a tile
+        // has at most 256)
+        float h_old = 0.f;
+        if (EPI == EPI_RESID && (CL || S == 1)) {
+            const int idx = CL ? ks + S * (int)threadIdx.x : (int)threadIdx.x;
+            const int r = idx % ROWS, m = idx / ROWS;
+            if (idx < ROWS * NT * 8 && m < M) h_old = ld_f32_now(reinterpret_cast<const float*>(out) + (size_t)m * N + tile * ROWS + r);
+        }
 #pragma unroll 1
         for (int i0 = 0; i0 < CH; i0 += XD) {
 #pragma unroll
@@ -353,7 +369,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                 const size_t o = (size_t)m * N + n0 + r;
                 if (EPI == EPI_BF16) reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v);
                 else if (EPI == EPI_F32) reinterpret_cast<float*>(out)[o] = v;
-                else reinterpret_cast<float*>(out)[o] += v + (bias ? bias[n0 + r] : 0.f);
+                else reinterpret_cast<float*>(out)[o] = h_old + (v + (bias ? bias[n0 + r] : 0.f));
             }
         } else if (EPI != EPI_SWIGLU && EPI != EPI_CONV && !NORM && S > 1) {
             // this block's partial tile -> workspace; the last of the S blocks adds them up
@@ -444,7 +460,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const float* __restrict__ h_in, c
                 const size_t o = (size_t)m * N + n0 + r;
                 if (EPI == EPI_BF16) reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v);
                 else if (EPI == EPI_F32) reinterpret_cast<float*>(out)[o] = v;
-                else reinterpret_cast<float*>(out)[o] += v + (bias ? bias[n0 + r] : 0.f);
+                else reinterpret_cast<float*>(out)[o] = h_old + (v + (bias ? bias[n0 + r] : 0.f));
             }
         }
         buf ^= 1;
