@@ -166,11 +166,19 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
 }
 
 // ================================ decode: split-KV ==============================================
-// grid (splits, nkv, segments), 128 threads; a step of single tokens (token i is segment i).  The
+// grid (nkv, segments, splits), 128 threads; a step of single tokens (token i is segment i).  The
 // m16 rows are the query heads of the kv group (up to 16).  Every warp walks its share of the
 // split's 16-key blocks; the warps are merged in shared memory; with more than one split the
 // partial (m, l, O) goes to the workspace and the last split to arrive merges them (a ticket per
 // (segment, kv head), reset for the next launch).
+//
+// How many of the grid's splits a request uses is decided per step from two numbers the host packs
+// beside the positions (the longest sequence and the sum of all): few requests are cut so that one
+// wave of blocks fills the device, as many pieces each as that takes; and where the lengths are
+// uneven (the longest more than 1.5 times the average) no piece is longer than the average request,
+// so that a long request among short ones does not run alone at the end.  Pieces are never shorter
+// than DA_MIN_PER key blocks.  The splits a request does not use leave at once; they are the last
+// in launch order.  Without the two numbers every request uses every split.
 //
 // The kernel is bound by the stream of K and V, so that stream is kept deep and started early:
 // every thread copies the fragments it will need (64 bytes of K rows, 64 bytes of V^T rows per block
@@ -181,6 +189,7 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
 // on their way while those still run.
 #define DA_STAGES_DEEP 6          // few blocks (small batches): a deep ring per warp, two blocks per SM
 #define DA_STAGES_WIDE 3          // many blocks: four blocks per SM hide each other's latencies instead
+#define DA_MIN_PER 16             // key blocks (256 keys): finer pieces cost more in set-up and merge than they win
 
 __device__ __forceinline__ void cp_async_zfill16(void* smem_dst, const void* src, bool valid) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -197,7 +206,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
                         int page_size, int page_shift, const int* __restrict__ positions,
                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int n_splits,
-                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets) {
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
+                        const int* __restrict__ kv_span, int slots) {
     // ring: [stage][piece][128 threads]: HD/16 pieces of 16 bytes for K, then HD/8 pieces of 8 bytes for V;
     // afterwards the same memory serves the merge of the warps ([4 warps][16 rows][HD + 2] floats)
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -205,7 +215,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     __shared__ int s_last;
     constexpr int KP = HD / 16, VP = HD / 8;
     constexpr int STAGE_BYTES = (KP * 16 + VP * 8) * 128;
-    const int split = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
+    const int kvh = blockIdx.x, seg = blockIdx.y, split = blockIdx.z;
     const int G = nh / nkv;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int tok = seg;                     // a step of single tokens
@@ -215,7 +225,31 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 
     const int first_block = lo / 16, last_block = pos / 16;
     const int n_blocks = last_block - first_block + 1;
-    const int per = (n_blocks + n_splits - 1) / n_splits;
+    int used = n_splits;                     // pieces this request is cut into
+    if (n_splits > 1 && kv_span != nullptr) {
+        const int n_segs = (int)gridDim.y;
+        int longest = kv_span[0];
+        long long total = kv_span[1];
+        if (window > 0) {
+            longest = min(longest, window);
+            total = min(total, (long long)n_segs * window);
+        }
+        const int long_b = (longest + 15) / 16;
+        const int avg_b = max(1, (int)(total / (16LL * n_segs)));
+        const int base = n_segs * nkv;
+        int chunk = 0x7fffffff;
+        if (5 * base <= 4 * slots) {         // the requests' own blocks leave room in one wave: fill it
+            const long long work = (total / 16 + n_segs) * nkv;
+            chunk = max(DA_MIN_PER, (int)((work + slots - base - 1) / (slots - base)));
+        }
+        if (2 * long_b > 3 * avg_b) chunk = min(chunk, max(DA_MIN_PER, avg_b));
+        used = chunk == 0x7fffffff ? 1 : min(n_splits, max(1, (n_blocks + chunk - 1) / chunk));
+    }
+    if (split >= used) {                     // a piece this request does not need
+        pdl_launch_dependents();
+        return;
+    }
+    const int per = (n_blocks + used - 1) / used;
     const int b0 = first_block + split * per;
     const int b1 = min(last_block + 1, b0 + per);
     const int mine_n = b0 + w < b1 ? (b1 - b0 - w + 3) / 4 : 0;      // blocks b0 + w + 4 i of this warp
@@ -347,7 +381,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             acc += row[d] * f;
         }
         const int head = kvh * G + r;
-        if (n_splits == 1) {
+        if (used == 1) {
             out[((size_t)tok * nh + head) * HD + d] = __float2bfloat16_rn(acc / L);
         } else {
             const size_t pi = ((size_t)seg * nh + head) * n_splits + split;
@@ -355,12 +389,12 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
         }
     }
-    if (n_splits == 1) return;
+    if (used == 1) return;
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
         const int ticket = atomicAdd(&tickets[seg * nkv + kvh], 1);
-        s_last = ticket == n_splits - 1;
+        s_last = ticket == used - 1;
         if (s_last) tickets[seg * nkv + kvh] = 0;     // ready for the next launch
     }
     __syncthreads();
@@ -372,10 +406,10 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         const size_t p0 = ((size_t)seg * nh + head) * n_splits;
         float M = -INFINITY;
 #pragma unroll 8
-        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(part_ml + (p0 + s) * 2));
+        for (int s = 0; s < used; ++s) M = fmaxf(M, __ldcg(part_ml + (p0 + s) * 2));
         float L = 0.f, acc = 0.f;
 #pragma unroll 8
-        for (int s = 0; s < n_splits; ++s) {
+        for (int s = 0; s < used; ++s) {
             const float ms = __ldcg(part_ml + (p0 + s) * 2);
             const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
             L += __ldcg(part_ml + (p0 + s) * 2 + 1) * f;
@@ -487,21 +521,25 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
                                      const int* block_table, int max_pages, int page_size, const int* positions,
                                      void* out, int n_segs, int nh, int nkv, int hd,
                                      int window, float scale, int n_splits, float* part_o, float* part_ml,
-                                     int* tickets, cudaStream_t stream) {
+                                     int* tickets, const int* kv_span, cudaStream_t stream) {
     if (n_segs <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
     if (G > 16 || n_splits < 1 || n_splits > 65535 || n_segs > 65535 || nkv > 65535) return GESSO_ERR_BAD_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return GESSO_ERR_BAD_SIZE;
-    dim3 grid(n_splits, nkv, n_segs);
+    dim3 grid(nkv, n_segs, n_splits);
     int page_shift = -1;
     if ((page_size & (page_size - 1)) == 0)
         for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
     // Few blocks: two per SM with a deep ring each (a block must cover the memory latency by itself).  Many
     // blocks (large batches): four per SM with a shallow ring each; the same bytes are in flight, and twice
     // the warps keep the issue slots busy where one warp's chain of dependent instructions would not.
-    const long long blocks = (long long)n_splits * nkv * n_segs;
+    // (counted by the pieces that a step of even lengths uses: at most what two blocks per SM hold at once)
+    const long long base = (long long)nkv * n_segs;
+    const long long even = kv_span ? (2LL * gesso_sm_count() / base < 1 ? 1 : 2LL * gesso_sm_count() / base) : n_splits;
+    const long long blocks = base * (even < n_splits ? even : n_splits);
     const bool wide = blocks >= 3LL * gesso_sm_count();
+    const int slots = (wide ? 4 : 2) * gesso_sm_count();
     const int stages = wide ? DA_STAGES_WIDE : DA_STAGES_DEEP;
     const size_t merge = (size_t)4 * 16 * (hd + 2) * sizeof(float);
     const size_t ring = (size_t)stages * (hd / 16 * 16 + hd / 8 * 8) * 128;
@@ -518,7 +556,7 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
         launch_pdl(decode_attention_kernel<HD, ST, UP>, grid, dim3(128), smem, stream,                      \
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,  \
             page_shift, positions, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml,      \
-            tickets);                                                                                       \
+            tickets, kv_span, slots);                                                                       \
     } while (0)
 #define GO(HD)                                                                                              \
     do {                                                                                                    \

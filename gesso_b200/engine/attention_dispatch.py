@@ -18,7 +18,7 @@ def paged_attention(rt, q, cache, ctx, window, scale):
     nkv, page_size = cache.k_pages.shape[1], cache.k_pages.shape[2]
     if q.dtype == torch.bfloat16 and ops.fast_attention_takes(hd, page_size, nh, nkv):
         if ctx.decode_only:
-            splits = ops.decode_splits(ctx.n_segs, nkv, ctx.max_kv_len)
+            splits = ops.decode_splits(ctx.n_segs, nkv, ctx.max_kv_len, uneven=True)
             ws = None
             if splits > 1:
                 key = ("decode_attention_workspace", ctx.n_segs, nh, nkv, hd, splits)
@@ -30,7 +30,7 @@ def paged_attention(rt, q, cache, ctx, window, scale):
                           torch.zeros((ctx.n_segs * nkv,), dtype=torch.int32, device=dev))
                     rt.shared[key] = ws
             return ops.decode_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
-                                        window, scale, splits, ws)
+                                        window, scale, splits, ws, ctx.kv_span)
         if ops.attention_tcgen05_takes(hd, page_size, nh, nkv):
             # head 64 with 2..16 query heads per kv head: S and P in tensor memory, pages by TMA
             return ops.prefill_attention_tcgen05(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,

@@ -45,6 +45,7 @@ CORE_FIELDS: Tuple[Tuple[str, str], ...] = (
     ("logit_rows", "row"),         # tokens whose logits are wanted
     ("tile_seg", "tile"),          # the step's query tiles: segment ...
     ("tile_q0", "tile"),           # ... and first token inside the segment
+    ("kv_span", "two"),            # the longest sequence after the step and the sum of all (how decode attention cuts keys)
 )
 
 # fields added from outside: name -> (axis, fill(entries, view)); they follow the block tables
@@ -90,7 +91,7 @@ class StepLayout:
 
     def _axis(self, axis: str) -> int:
         return {"token": self.n_tokens, "seg": self.n_segs, "seg+1": self.n_segs + 1, "row": self.n_rows,
-                "tile": self.n_tiles}[axis]
+                "tile": self.n_tiles, "two": 2}[axis]
 
     def offsets(self) -> Dict[str, int]:
         o = getattr(self, "_offsets", None)

@@ -522,7 +522,7 @@ _lib.declare("gesso_qk_norm_rope_store_tiles", [_lib.P, _lib.P, _lib.P, _lib.F, 
 _lib.declare("gesso_attention_tc_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P,
                                         _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P, _lib.P,
-                                        _lib.P, _lib.P])
+                                        _lib.P, _lib.P, _lib.P])
 _lib.declare("gesso_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
                                          _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.P])
 
@@ -548,11 +548,18 @@ def fast_attention_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
 DECODE_BLOCKS_PER_SM = int(os.environ.get("GESSO_DECODE_BLOCKS_PER_SM", "2"))
 
 
-def decode_splits(n_segs: int, nkv: int, max_kv_len: int) -> int:
-    """How many ways the keys of a request are split so that about DECODE_BLOCKS_PER_SM blocks per SM
-    are busy."""
+DECODE_UNEVEN_SPLITS = int(os.environ.get("GESSO_DECODE_UNEVEN_SPLITS", "4"))
+
+
+def decode_splits(n_segs: int, nkv: int, max_kv_len: int, uneven: bool = False) -> int:
+    """The most pieces the keys of a request are cut into: so many that about DECODE_BLOCKS_PER_SM blocks
+    per SM are busy; with ``uneven`` (the kernel is told the step's lengths and cuts a request that is long
+    among short ones even where the batch alone fills the device) at least DECODE_UNEVEN_SPLITS for more
+    than one request."""
     blocks = (max_kv_len + 15) // 16
     want = (DECODE_BLOCKS_PER_SM * sm_count()) // (n_segs * nkv)      # rounded down: all blocks resident at once
+    if uneven and n_segs > 1:
+        want = max(want, DECODE_UNEVEN_SPLITS)
     # at least 16 blocks (256 keys) per split: finer splits cost more in their set-up and in the merge of
     # the parts than they win (one request at 4,096 keys: 1,393 tokens/s with 16 splits, 1,226 with 37)
     return max(1, min(want, (blocks + 15) // 16))
@@ -561,13 +568,18 @@ def decode_splits(n_segs: int, nkv: int, max_kv_len: int) -> int:
 def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                      block_table: torch.Tensor, positions: torch.Tensor,
                      window: Optional[int], scale: float, n_splits: int,
-                     workspace=None) -> torch.Tensor:
+                     workspace=None, kv_span: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Split-KV attention for a step of single tokens (token i is request i).  ``workspace`` = (part_o, part_ml, tickets) of
-    sizes [segs*nh*splits*hd], [segs*nh*splits*2] float32 and [segs*nkv] int32 (zeroed once)."""
+    sizes [segs*nh*splits*hd], [segs*nh*splits*2] float32 and [segs*nkv] int32 (zeroed once).  ``kv_span``: int32 [2]
+    on the device, the longest sequence of the step and the sum of all: a request then uses as many of the
+    ``n_splits`` pieces as the step's lengths call for (without it, all of them)."""
     _cuda_contig(q, "q", torch.bfloat16)
     S, nh, hd = q.shape
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
     _need(k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16, "cache pages must be bfloat16")
+    if kv_span is not None:
+        _cuda_contig(kv_span, "kv_span", torch.int32)
+        _need(kv_span.numel() == 2, "kv_span holds two numbers")
     out = torch.empty((S, nh * hd), dtype=q.dtype, device=q.device)
     if n_splits > 1:
         if workspace is None:
@@ -582,7 +594,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     _lib.check(_lib.library().gesso_decode_attention(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(positions),
         _p(out), S, nh, nkv, hd, int(window or 0), float(scale), int(n_splits), _p(part_o),
-        _p(part_ml), _p(tickets), _stream()), "decode_attention")
+        _p(part_ml), _p(tickets), _p(kv_span), _stream()), "decode_attention")
     return out
 
 

@@ -624,6 +624,34 @@ def test_decode_attention_at_the_benchmark_context(splits):
         assert rel_err(out, want) < 2 * BF16_EPS
 
 
+@pytest.mark.parametrize("window", [None, 700])
+@pytest.mark.parametrize("kv_lens", [[4096, 300, 64, 1, 2047], [1500] * 3, [4000] + [40] * 44, [900, 880, 910, 870] * 10,
+                                     [3000, 2900, 100, 90, 80, 3100, 17, 16, 15] * 4])
+@pytest.mark.parametrize("splits", [1, 4, 8])
+def test_decode_attention_cut_by_the_steps_lengths(splits, kv_lens, window):
+    """The kernel is told the longest sequence of the step and the sum of all and decides per request how
+    many of the grid's pieces it uses: one long request among short ones, even lengths that fill the device
+    by themselves, few requests that do not, and a window that bounds what a request reads."""
+    from gesso_b200 import ops
+    nh, nkv, hd, page = 24, 8, 64, 16
+    new_lens = [1] * len(kv_lens)
+    q, ks, vs, kp, vp, bt, positions, seg, starts = make_attention_case(nh, nkv, hd, page, torch.bfloat16, kv_lens,
+                                                                         new_lens, 77 + splits)
+    want = attention_reference_new_rows(q, ks, vs, new_lens, window)
+    S = len(kv_lens)
+    ws = (torch.empty(S * nh * splits * hd, device=DEV), torch.empty(S * nh * splits * 2, device=DEV),
+          torch.zeros(S * nkv, dtype=torch.int32, device=DEV))
+    span = i32([max(kv_lens), sum(kv_lens)])
+    for _ in range(2):      # twice with one workspace: the tickets must count the pieces in use, and be reset
+        out = ops.decode_attention(q.to(DEV), kp, vp, bt, i32(positions.tolist()), window, 1.0 / math.sqrt(hd), splits, ws,
+                                   kv_span=span)
+        assert torch.isfinite(out).all()
+        assert rel_err(out, want) < 2 * BF16_EPS
+    # the cut changes which partial sums are merged, not what is summed
+    whole = ops.decode_attention(q.to(DEV), kp, vp, bt, i32(positions.tolist()), window, 1.0 / math.sqrt(hd), splits, ws)
+    assert rel_err(out, whole.double().cpu()) < BF16_EPS
+
+
 @pytest.mark.parametrize("window", [None, 50])
 @pytest.mark.parametrize("nh,nkv,hd,page", [c for c in CASES if c[2] in (32, 64, 96, 128)])
 def test_prefill_attention_flash(window, nh, nkv, hd, page):
