@@ -171,8 +171,25 @@ def prepare_step(cache, entries: Sequence[StepEntry], layout: StepLayout, out: n
     handles = (ctypes.c_int64 * n)()
     n_new = (ctypes.c_int * n)()
     want_n = (ctypes.c_int * n)()
-    toks: List[int] = []
+    # token ids go into one int32 array: arrays are copied as they are, runs of lists are converted together
+    total = 0
+    for e in entries:
+        total += len(e.tokens)
+    tok_np = np.empty(max(total, 1), dtype=np.int32) if tokens_known else None
+    run: List[int] = []                 # ids of consecutive list entries not yet copied, and where they go
+    run_at = 0
     wants: List[int] = []
+
+    def flush(upto: int) -> None:
+        nonlocal run
+        if run:
+            a = np.asarray(run)
+            if a.dtype.kind not in "iu":
+                raise invalid("step: tokens and wanted places must be integers")
+            tok_np[run_at:upto] = a
+            run = []
+
+    cur = 0
     for i, e in enumerate(entries):
         if e.req_id is not None:
             h = cache.handle(e.req_id)
@@ -186,12 +203,23 @@ def prepare_step(cache, entries: Sequence[StepEntry], layout: StepLayout, out: n
         # ranges are checked here, on the values as given: the 32-bit arrays below would wrap a wider integer
         try:
             if tokens_known:
-                t = e.tokens.tolist() if isinstance(e.tokens, np.ndarray) else e.tokens
-                lo, hi = (t[0], t[0]) if k == 1 else (min(t), max(t))
+                t = e.tokens
+                if isinstance(t, np.ndarray):
+                    if t.ndim != 1 or t.dtype.kind not in "iu":
+                        raise TypeError
+                    lo, hi = int(t.min()), int(t.max())
+                else:
+                    lo, hi = (t[0], t[0]) if k == 1 else (min(t), max(t))
                 if not (0 <= lo and hi < vocab):
-                    bad = next(x for x in t if not (0 <= x < vocab))
+                    bad = next(int(x) for x in t if not (0 <= x < vocab))
                     raise invalid(f"step: token id {bad} of request {e.req_id!r} is outside the vocabulary (0..{vocab - 1})")
-                toks.extend(t)
+                if isinstance(t, np.ndarray):
+                    flush(cur)
+                    tok_np[cur:cur + k] = t
+                else:
+                    if not run:
+                        run_at = cur
+                    run.extend(t)
             if want_n[i]:
                 w = e.want.tolist() if isinstance(e.want, np.ndarray) else e.want
                 if not (0 <= min(w) and max(w) < k):
@@ -200,10 +228,13 @@ def prepare_step(cache, entries: Sequence[StepEntry], layout: StepLayout, out: n
                 wants.extend(w)
         except TypeError:
             raise invalid(f"step: tokens and wanted places of request {e.req_id!r} must be flat lists of integers") from None
+        cur += k
     try:
-        tok_arr = (ctypes.c_int * max(len(toks), 1))(*toks) if tokens_known else None
+        if tokens_known:
+            flush(cur)
+        tok_arr = tok_np.ctypes.data_as(ctypes.POINTER(ctypes.c_int)) if tokens_known else None
         want_arr = (ctypes.c_int * max(len(wants), 1))(*wants)
-    except TypeError:
+    except (TypeError, ValueError, OverflowError):
         raise invalid("step: tokens and wanted places must be integers") from None
     off, sizes = _native_offsets(layout)
     scratch = (ctypes.c_int * (1 + G))(scratch_slot, *scratch_pages)

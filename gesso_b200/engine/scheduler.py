@@ -40,6 +40,8 @@ import itertools
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 from ..errors import ErrorCode, GessoError, invalid, resource
 from ..sampling.sampler import SamplingParams, SplitMix64
 from .batch import StepEntry
@@ -71,6 +73,10 @@ class Request:
 
     def __post_init__(self):
         self.prompt = [int(t) for t in self.prompt]
+        try:    # portions of the prompt are handed to the engine as views of this array (no list per step)
+            self._prompt_arr = np.asarray(self.prompt, dtype=np.int64) if self.prompt else None
+        except OverflowError:
+            self._prompt_arr = None         # an id no machine integer holds: the step's check names it
         if self.max_new_tokens < 0:
             raise invalid("request: max_new_tokens must be >= 0")
         self.rng = SplitMix64(self.sampling.seed)
@@ -89,7 +95,7 @@ class Request:
         if start >= p:
             return self.generated[start - p:start - p + n]
         if start + n <= p:
-            return self.prompt[start:start + n]
+            return self.prompt[start:start + n] if self._prompt_arr is None or n < 8 else self._prompt_arr[start:start + n]
         return self.prompt[start:] + self.generated[:start + n - p]
 
     @property
@@ -172,12 +178,19 @@ class Scheduler:
     def _left(self, r: Request) -> int:
         return len(r.prompt) + len(r.generated) - r.fed
 
-    def _pages_short(self, wants: Dict[object, Tuple[Request, int]], spare: int = 0) -> bool:
-        need = [spare] * len(self.cache.groups)
+    def _need(self, wants: Dict[object, Tuple[Request, int]]) -> List[int]:
+        """Pages per group that the planned tokens still have to be handed."""
+        need = [0] * len(self.cache.groups)
         for r, n in wants.values():
             for g, k in enumerate(self.cache.pages_needed(r.req_id, n)):
                 need[g] += k
-        return any(k > f for k, f in zip(need, self.cache.free_pages()))
+        return need
+
+    def _short(self, need: List[int], extra: Optional[List[int]] = None, spare: int = 0) -> bool:
+        free = self.cache.free_pages()
+        if extra is None:
+            return any(k + spare > f for k, f in zip(need, free))
+        return any(k + e + spare > f for k, e, f in zip(need, extra, free))
 
     def plan(self) -> StepPlan:
         plan = StepPlan(entries=[])
@@ -207,25 +220,28 @@ class Scheduler:
         # 1. every decoding request gets its one token; preempt from the newest while they do not fit
         for r in decoders:
             wants[r.req_id] = (r, 1)
-        while self._pages_short(wants) and len(self.running) > 1:
+        need = self._need(wants)                 # kept in step with `wants` from here on
+        while self._short(need) and len(self.running) > 1:
             victim = self.running[-1]
             self._preempt(victim)
             plan.preempted.append(victim)
             wants.pop(victim.req_id, None)
+            need = self._need(wants)
             if victim in prefillers:
                 prefillers.remove(victim)
-        if self._pages_short(wants):
+        if self._short(need):
             # a single request is left and its next token has no page: it has outgrown the pool
             for r, _ in list(wants.values()):
                 self._finish(r, FAILED, resource(f"request {r.req_id!r} does not fit the cache pool"))
             wants.clear()
+            need = self._need(wants)
         budget -= len(wants)
         # 2. prompt portions of running requests, oldest first, shrunk to what the pool can hold
         for r in prefillers:
             if budget <= 0:
                 break
             n = min(self._left(r), self.prefill_chunk, budget)
-            n = self._fit(r, n, wants)
+            n = self._fit(r, n, need)
             if n > 0:
                 wants[r.req_id] = (r, n)
                 budget -= n
@@ -236,7 +252,7 @@ class Scheduler:
             self.engine.admit(r.req_id)
             n = min(self._left(r), self.prefill_chunk, budget)
             # a newcomer leaves one spare page per running request, so that their next tokens fit
-            n = self._fit(r, n, wants, spare=len(self.running))
+            n = self._fit(r, n, need, spare=len(self.running))
             if n <= 0:
                 self.engine.release(r.req_id)      # no room for even one token now: stays queued
                 break
@@ -253,7 +269,7 @@ class Scheduler:
                 victim = self.running[-1]
                 self._preempt(victim)
                 plan.preempted.append(victim)
-            n = self._fit(r, min(self._left(r), self.prefill_chunk, self.max_tokens_per_step), wants)
+            n = self._fit(r, min(self._left(r), self.prefill_chunk, self.max_tokens_per_step), [0] * len(self.cache.groups))
             if n <= 0:
                 self._finish(r, FAILED, resource(f"request {r.req_id!r} does not fit the cache pool"))
             else:
@@ -263,13 +279,15 @@ class Scheduler:
                 plan.entries.append((r, r.fed, wants[r.req_id][1]))
         return plan
 
-    def _fit(self, r: Request, n: int, wants: Dict[object, Tuple[Request, int]], spare: int = 0) -> int:
-        """Largest portion <= n of request r that the free pages hold beside what is planned."""
+    def _fit(self, r: Request, n: int, need: List[int], spare: int = 0) -> int:
+        """Largest portion <= n of request r that the free pages hold beside what is planned (``need``: the
+        pages the plan takes so far; the portion's own pages are added to it when it fits)."""
         n = min(n, self.cache.max_positions - self.cache.length(r.req_id))
         while n > 0:
-            trial = dict(wants)
-            trial[r.req_id] = (r, n)
-            if not self._pages_short(trial, spare):
+            own = self.cache.pages_needed(r.req_id, n)
+            if not self._short(need, own, spare):
+                for g, k in enumerate(own):
+                    need[g] += k
                 return n
             # shrink to the last page border below n (or give up)
             filled = self.cache.length(r.req_id) + n
