@@ -5,17 +5,21 @@
 // are zero and idle), so a single copy of K and V serves every head of the group (the GQA map
 // h -> h / (nh/nkv) of src/Inference/Inference.jl:1398).  It walks the keys in blocks of 128:
 //
-//   TMA warp      Q once (3-D tensor map [token][head][feature], 128-byte swizzle); per key block 8
-//                 K pages ([slot][feature] rows of 128 bytes, 128-byte swizzle) and 8 V pages
-//                 ([feature][slot] rows of 32 bytes, 32-byte swizzle) into a two-stage ring;
+//   TMA warps     one brings Q once (3-D tensor map [token][head][feature], 128-byte swizzle) and per key block
+//                 the 8 K pages ([slot][feature] rows of 128 bytes, 128-byte swizzle), another the 8 V pages
+//                 ([feature][slot] rows of 32 bytes, 32-byte swizzle), each into a two-stage ring with barriers
+//                 of its own: a K stage is free again when its block's scores are computed, a V stage after
+//                 O += P V, so the keys of block j + 2 are under way during the softmax of block j;
 //   MMA thread    S[128 x 128] = Q K^T   (tcgen05.mma, M 128, N 128, K 4 x 16) into tensor memory, issued
 //                 for block j+1 as soon as the softmax warps hold S of block j in registers;
 //                 O[128 x 64] += P V     (A operand P read from tensor memory, B = one V page per K = 16
-//                 step), accumulated in tensor memory over all blocks;
-//   8 softmax warps  two threads per query row, 64 of the 128 scores each (one tcgen05.ld, no second
-//                 pass): mask, maximum (the two halves meet through shared memory), base-2 exponentials
-//                 with log2(e)/sqrt(d) folded into one multiply-add, sum, P as packed bfloat16 back to
-//                 tensor memory (tcgen05.st).
+//                 step), accumulated in tensor memory over all blocks; the thread watches the barriers of
+//                 both and issues whichever product is ready;
+//   4 softmax warps  one thread per query row, all 128 scores of a block in registers (four tcgen05.ld, no
+//                 second pass, no exchange between threads): mask, maximum, base-2 exponentials with
+//                 log2(e)/sqrt(d) folded into one multiply-add, sum, P as packed bfloat16 back to tensor memory
+//                 (tcgen05.st).  These warps hold 208 registers a thread: the four other warps of the block
+//                 (two of them idle) give theirs up (setmaxnreg), so that two blocks still fit an SM.
 // The running maximum is only raised when a block exceeds it by more than 8 (a factor 256, far inside
 // the range of bfloat16 and float32): then the row of O in tensor memory and the running sum are scaled
 // down, which after the first blocks is rare; the result O / l is the same function either way.
@@ -32,7 +36,9 @@
 #define FA_HD 64
 #define FA_BK 128
 #define FA_STAGES 2
-#define FA_THREADS 320                 // warp 0: TMA, warp 1: MMA, warps 2..9: softmax
+#define FA_THREADS 256                 // warps 0..3: softmax (one thread per query row), warp 4: TMA, warp 5: MMA, 6 and 7 idle
+#define FA_REGS_SOFTMAX 208             // registers per softmax thread: the other warp group gives most of its own away
+#define FA_REGS_OTHER 40
 #define FA_LOG2E 1.4426950408889634f
 #define FA_RAISE 8.f                   // the reference maximum follows the true one at this distance
 
@@ -40,9 +46,8 @@ struct __align__(1024) FaSmem {
     bf16 q[128 * FA_HD];                       // 16 KB
     bf16 k[FA_STAGES][FA_BK * FA_HD];          // 16 KB per stage: 8 pages x [16][64]
     bf16 v[FA_STAGES][FA_BK * FA_HD];          // 16 KB per stage: 8 pages x [64][16]
-    unsigned long long q_full, full[FA_STAGES], empty[FA_STAGES], s_full, s_free, p_ready, o_full, pair[4];
-    float xmax[2][2][128];                     // [block parity][half][row]: the halves' maxima
-    float xsum[2][128];                        // [half][row]: the halves' sums, at the end
+    unsigned long long q_full, k_full[FA_STAGES], k_empty[FA_STAGES], v_full[FA_STAGES], v_empty[FA_STAGES], s_full, s_free,
+        p_ready, o_full;
     unsigned tmem_base;
 };
 
@@ -84,15 +89,17 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
     if (threadIdx.x == 0) {
         mbar_init(&s.q_full, 1);
-        for (int i = 0; i < FA_STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
+        for (int i = 0; i < FA_STAGES; ++i) {
+            mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1);
+            mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1);
+        }
         mbar_init(&s.s_full, 1);
-        mbar_init(&s.s_free, 256);
-        mbar_init(&s.p_ready, 256);
+        mbar_init(&s.s_free, 128);
+        mbar_init(&s.p_ready, 128);
         mbar_init(&s.o_full, 1);
-        for (int i = 0; i < 4; ++i) mbar_init(&s.pair[i], 64);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) {       // S: columns 0..127, P: 128..191 (bfloat16 pairs), O: 192..255
+    if (warp == 5) {       // S: columns 0..127, P: 128..191 (bfloat16 pairs), O: 192..255
         tmem_alloc(&s.tmem_base, 256);
         tmem_relinquish();
     }
@@ -109,12 +116,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const unsigned tmem = s.tmem_base;
     const unsigned tm_s = tmem, tm_p = tmem + 128, tm_o = tmem + 192;
 
-    if (warp == 0) {
-        // ---- TMA producer ----
+    if (warp >= 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(FA_REGS_OTHER));
+    }
+    if (warp == 4 || warp == 6) {
+        // ---- TMA producers: warp 4 brings Q and the K pages, warp 6 the V pages ----
+        // The two rings have barriers of their own: a K stage is free again when the scores of its block are
+        // computed, long before the block's V stage (free after O += P V), so the keys of block j + 2 are on
+        // their way while block j is still in its softmax.
         // Lanes 0..7 each own one 16-key page of a block: they look their page up (one coalesced read of
-        // the block table, one block ahead) and issue its two TMA loads themselves, so the eight
-        // lookups and sixteen loads of a block go out side by side instead of one after the other.
-        if (lane == 0) {
+        // the block table, one block ahead) and issue its TMA load themselves, so the eight lookups and
+        // loads of a block go out side by side instead of one after the other.
+        const bool keys = warp == 4;
+        if (keys && lane == 0) {
             mbar_expect_tx(&s.q_full, TOK * G * FA_HD * sizeof(bf16));
             tma_load_3d(s.q, &map_q, 0, kvh * G, t0 + q0, &s.q_full);
         }
@@ -125,71 +139,84 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const int key0 = (kb0 + j) * FA_BK + lane * 16;
             return (lane < FA_BK / 16 && j < n_blocks && key0 <= pos_last) ? bt[key0 / page_size] : -1;
         };
+        unsigned long long* full = keys ? s.k_full : s.v_full;
+        unsigned long long* empty = keys ? s.k_empty : s.v_empty;
         int page = lookup(0);
         bool ok = true;
         for (int j = 0; j < n_blocks && ok; ++j) {
             const int st = j % FA_STAGES;
             const int next_page = lookup(j + 1);
             if (lane == 0) {
-                if (!mbar_wait_idle(&s.empty[st], ((j / FA_STAGES) & 1) ^ 1)) { atomicExch(status, 12); ok = false; }
-                else mbar_expect_tx(&s.full[st], 2 * FA_BK * FA_HD * sizeof(bf16));
+                if (!mbar_wait_idle(&empty[st], ((j / FA_STAGES) & 1) ^ 1)) { atomicExch(status, keys ? 12 : 11); ok = false; }
+                else mbar_expect_tx(&full[st], FA_BK * FA_HD * sizeof(bf16));
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (ok && lane < FA_BK / 16) {
                 const int sl = ((kb0 + j) * FA_BK + lane * 16) % page_size;
                 const int pg = page < 0 ? num_pages : page;          // num_pages: the first row past the end
-                tma_load_2d(s.k[st] + lane * 16 * FA_HD, &map_k, 0, (pg * nkv + kvh) * page_size + sl, &s.full[st]);
-                tma_load_2d(s.v[st] + lane * 16 * FA_HD, &map_v, sl, (pg * nkv + kvh) * FA_HD, &s.full[st]);
+                if (keys) tma_load_2d(s.k[st] + lane * 16 * FA_HD, &map_k, 0, (pg * nkv + kvh) * page_size + sl, &full[st]);
+                else tma_load_2d(s.v[st] + lane * 16 * FA_HD, &map_v, sl, (pg * nkv + kvh) * FA_HD, &full[st]);
             }
             page = next_page;
         }
-    } else if (warp == 1) {
+    } else if (warp == 5) {
         // ---- tensor-core issue ----
+        // One thread issues both kinds of product and takes whichever is ready: the scores of the next block
+        // (its keys have landed, the softmax warps hold the scores before it in registers) or O += P V of the
+        // oldest block whose probabilities are written and whose values have landed.  Neither waits for the other.
         if (elect_one()) {
             constexpr unsigned idesc_s = make_idesc(128, FA_BK);
             constexpr unsigned idesc_o = make_idesc(128, FA_HD);
             bool ok = mbar_wait_idle(&s.q_full, 0);
             if (!ok) atomicExch(status, 13);
             const unsigned long long dq = make_desc(smem_u32(s.q));
-            auto issue_s = [&](int j) {          // S = Q K_j^T, K_j in stage j % 2
-                const unsigned long long dk = make_desc(smem_u32(s.k[j % FA_STAGES]));
+            unsigned long long dk[FA_STAGES], dv[FA_STAGES];
 #pragma unroll
-                for (int k = 0; k < FA_HD / 16; ++k) umma_f16(tm_s, dq + 2 * k, dk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
-                umma_commit(&s.s_full);
-            };
-            if (ok) {
-                if (!mbar_wait_idle(&s.full[0], 0)) { atomicExch(status, 14); ok = false; }
-                else { tc_fence_after(); issue_s(0); }
+            for (int i = 0; i < FA_STAGES; ++i) {
+                dk[i] = make_desc(smem_u32(s.k[i]));
+                dv[i] = make_desc_sw32(smem_u32(s.v[i]));
             }
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                const int st = j % FA_STAGES;
-                if (j + 1 < n_blocks) {
-                    // the scores of the next block, as soon as its keys are here and S is free again
-                    if (!mbar_wait_idle(&s.full[(j + 1) % FA_STAGES], ((j + 1) / FA_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
-                    if (!mbar_wait_idle(&s.s_free, j & 1)) { atomicExch(status, 19); ok = false; break; }
+            int s_next = 0, pv_next = 0;             // the next block whose scores / whose P V is to be issued
+            unsigned idle = 0;
+            while (pv_next < n_blocks && ok) {
+                bool progressed = false;
+                if (s_next < n_blocks && mbar_test(&s.k_full[s_next % FA_STAGES], (s_next / FA_STAGES) & 1) &&
+                    (s_next == 0 || mbar_test(&s.s_free, (s_next - 1) & 1))) {
                     tc_fence_after();
-                    issue_s(j + 1);
-                }
-                if (!mbar_wait_idle(&s.p_ready, j & 1)) { atomicExch(status, 15); ok = false; break; }
-                tc_fence_after();
+                    const unsigned long long d = dk[s_next % FA_STAGES];
 #pragma unroll
-                for (int kk = 0; kk < FA_BK / 16; ++kk)
-                    umma_f16_ts(tm_o, tm_p + 8 * kk, make_desc_sw32(smem_u32(s.v[st] + kk * 16 * FA_HD)), idesc_o,
-                                (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&s.o_full);
-                umma_commit(&s.empty[st]);
+                    for (int k = 0; k < FA_HD / 16; ++k) umma_f16(tm_s, dq + 2 * k, d + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+                    umma_commit(&s.s_full);
+                    umma_commit(&s.k_empty[s_next % FA_STAGES]);      // the keys are free when the scores are done
+                    ++s_next;
+                    progressed = true;
+                }
+                if (pv_next < s_next && mbar_test(&s.p_ready, pv_next & 1) &&
+                    mbar_test(&s.v_full[pv_next % FA_STAGES], (pv_next / FA_STAGES) & 1)) {
+                    tc_fence_after();
+                    const unsigned long long d = dv[pv_next % FA_STAGES];
+#pragma unroll
+                    for (int kk = 0; kk < FA_BK / 16; ++kk)          // one V page (16 keys x 64 features, 2 KB) per step
+                        umma_f16_ts(tm_o, tm_p + 8 * kk, d + kk * (16 * FA_HD * (int)sizeof(bf16) / 16), idesc_o,
+                                    (pv_next > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(&s.o_full);
+                    umma_commit(&s.v_empty[pv_next % FA_STAGES]);
+                    ++pv_next;
+                    progressed = true;
+                }
+                if (progressed) idle = 0;
+                else if (++idle > WAIT_LIMIT) { atomicExch(status, 14); ok = false; }
             }
         }
-    } else {
-        // ---- softmax: two threads per query row, 64 scores each ----
-        const int q4 = warp & 3;                          // the quarter of tensor-memory lanes this warp may touch
-        const int half = (warp - 2) >> 2;                 // which 64 of the block's 128 keys
-        const int r = q4 * 32 + lane;                     // row = token * G + head
+    } else if (warp < 4) {
+        // ---- softmax: one thread per query row (warps 0..3: the four quarters of the tensor-memory lanes) ----
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(FA_REGS_SOFTMAX));
+        const int r = warp * 32 + lane;                   // row = token * G + head
         const int tok = r / G, hg = r % G;
         const bool valid = tok < rows_tok;
         const int pos = p0 + q0 + min(tok, rows_tok - 1);
         const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-        const unsigned lane_base = (unsigned)(q4 * 32) << 16;
+        const unsigned lane_base = (unsigned)(warp * 32) << 16;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         // a wait that ran out ends the whole warp: the tensor-memory loads and stores below are warp-wide
@@ -200,122 +227,119 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             return false;
         };
         for (int j = 0; j < n_blocks && ok; ++j) {
-            const int key0 = (kb0 + j) * FA_BK + half * 64;
+            const int key0 = (kb0 + j) * FA_BK;
             if (!wait_all(&s.s_full, j & 1, 16)) { ok = false; break; }
             tc_fence_after();
-            unsigned v[64];
-            tmem_ld32(tm_s + lane_base + half * 64, reinterpret_cast<unsigned(&)[32]>(v[0]));
-            tmem_ld32(tm_s + lane_base + half * 64 + 32, reinterpret_cast<unsigned(&)[32]>(v[32]));
+            unsigned v[FA_BK];
+#pragma unroll
+            for (int c = 0; c < FA_BK; c += 32) tmem_ld32(tm_s + lane_base + c, reinterpret_cast<unsigned(&)[32]>(v[c]));
             tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(&s.s_free);                       // S may be overwritten by the next block's scores
             // masking is a pass of its own behind a warp-wide branch: most blocks lie wholly inside the
             // visible range, and their inner loops then carry no compare at all
-            if (__any_sync(0xffffffffu, key0 + 63 > pos || key0 < lo)) {
+            if (__any_sync(0xffffffffu, key0 + FA_BK - 1 > pos || key0 < lo)) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
+                for (int i = 0; i < FA_BK; ++i) {
                     const int key = key0 + i;
                     if (key > pos || key < lo) v[i] = 0xff800000u;      // -inf
                 }
             }
-            // four independent chains of three-input maxima: 32 instructions for 64 scores
+            // four independent chains of three-input maxima: 64 instructions for 128 scores
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 64; i += 8) {
+            for (int i = 0; i < FA_BK; i += 8) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
                     mx4[u] = max3(mx4[u], __uint_as_float(v[i + 2 * u]), __uint_as_float(v[i + 2 * u + 1]));
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // the other half of the row
-            s.xmax[j & 1][half][r] = mx;
-            mbar_arrive(&s.pair[q4]);
-            if (!wait_all(&s.pair[q4], j & 1, 18)) { ok = false; break; }
             // rounded up to a whole number: every rescaling is then by an exact power of two, and the
             // rounding of a probability to bfloat16 does not depend on which reference it was taken against
             // (nor, therefore, on how a row's keys were cut into blocks and steps)
-            const float m_blk = ceilf(fmaxf(mx, s.xmax[j & 1][half ^ 1][r]) * scale_log2);
+            const float m_blk = ceilf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2);
             // O += P V of the block before has finished: P may be rewritten, O may be rescaled
             if (j > 0) {
                 if (!wait_all(&s.o_full, (j - 1) & 1, 17)) { ok = false; break; }
                 tc_fence_after();
             }
-            // raise the reference maximum?  (both threads of a row decide alike; the warp acts as one,
-            // rows that stay are scaled by 1)
+            // raise the reference maximum?  (the warp acts as one, rows that stay are scaled by 1)
             const bool raise = m_blk > m_ref + FA_RAISE;
             const float alpha = (raise && m_ref != -INFINITY) ? ex2_approx(m_ref - m_blk) : 1.f;
             if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
-                for (int c = 0; c < 32; c += 16) {        // seldom taken: keep its registers few
+                for (int c = 0; c < FA_HD; c += 16) {     // seldom taken: keep its registers few
                     unsigned o[16];
-                    tmem_ld16(tm_o + lane_base + half * 32 + c, o);
+                    tmem_ld16(tm_o + lane_base + c, o);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st16(tm_o + lane_base + half * 32 + c, o);
+                    tmem_st16(tm_o + lane_base + c, o);
                 }
             }
             l *= alpha;
             if (raise) m_ref = m_blk;
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             // score * scale - maximum and the running sums as packed pairs (one instruction for two values);
-            // the exponentials one by one (the special-function unit has no packed form in float32)
+            // the exponentials one by one (the special-function unit has no packed form in float32); the
+            // probabilities go back to tensor memory 32 at a time as packed bfloat16
             const unsigned long long scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_use, -m_use);
             unsigned long long l2[4] = {0ull, 0ull, 0ull, 0ull};      // four chains of pairs of partial sums
-            unsigned pk[32];
 #pragma unroll
-            for (int i = 0; i < 64; i += 2) {
-                float x0, x1;
-                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), scale2, neg_m2), x0, x1);
-                const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
-                l2[(i >> 1) & 3] = add_f32x2(l2[(i >> 1) & 3], pack_f32x2(e0, e1));
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-                pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
+            for (int c = 0; c < FA_BK; c += 32) {
+                unsigned pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0, x1;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[c + i]), __uint_as_float(v[c + i + 1])), scale2, neg_m2),
+                                 x0, x1);
+                    const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+                    l2[(i >> 1) & 3] = add_f32x2(l2[(i >> 1) & 3], pack_f32x2(e0, e1));
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                    pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
+                }
+                tmem_st16(tm_p + lane_base + c / 2, pk);
             }
             {
                 float a0, a1;
                 unpack_f32x2(add_f32x2(add_f32x2(l2[0], l2[1]), add_f32x2(l2[2], l2[3])), a0, a1);
                 l += a0 + a1;
             }
-            tmem_st32(tm_p + lane_base + half * 32, pk);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&s.p_ready);
         }
         if (ok) {
-            // the last O += P V, the other half's sum, and out = O / l
+            // the last O += P V, and out = O / l
             if (!wait_all(&s.o_full, (n_blocks - 1) & 1, 17)) ok = false;
         }
         if (ok) {
             tc_fence_after();
-            s.xsum[half][r] = l;
-            mbar_arrive(&s.pair[q4]);
-            if (!wait_all(&s.pair[q4], n_blocks & 1, 18)) ok = false;
-        }
-        if (ok) {
-            const float inv = 1.f / (l + s.xsum[half ^ 1][r]);
-            unsigned o[32];
-            tmem_ld32(tm_o + lane_base + half * 32, o);
-            tmem_ld_wait();
-            if (valid) {
-                bf16* dst = out + ((size_t)(t0 + q0 + tok) * nh + (size_t)kvh * G + hg) * FA_HD + half * 32;
+            const float inv = 1.f / l;
+            bf16* dst = out + ((size_t)(t0 + q0 + tok) * nh + (size_t)kvh * G + hg) * FA_HD;
 #pragma unroll
-                for (int d = 0; d < 32; d += 8) {
-                    unsigned w4[4];
+            for (int c = 0; c < FA_HD; c += 32) {
+                unsigned o[32];
+                tmem_ld32(tm_o + lane_base + c, o);
+                tmem_ld_wait();
+                if (valid) {
 #pragma unroll
-                    for (int i = 0; i < 8; i += 2) {
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[d + i]) * inv,
-                                                                  __uint_as_float(o[d + i + 1]) * inv);
-                        w4[i / 2] = *reinterpret_cast<unsigned*>(&b2);
+                    for (int d = 0; d < 32; d += 8) {
+                        unsigned w4[4];
+#pragma unroll
+                        for (int i = 0; i < 8; i += 2) {
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[d + i]) * inv,
+                                                                      __uint_as_float(o[d + i + 1]) * inv);
+                            w4[i / 2] = *reinterpret_cast<unsigned*>(&b2);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c + d) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                     }
-                    *reinterpret_cast<uint4*>(dst + d) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 5) {
         tc_fence_after();
         tmem_dealloc(tmem, 256);
     }

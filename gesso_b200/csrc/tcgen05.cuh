@@ -30,6 +30,18 @@ __device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
+// One look at a barrier's phase without waiting (a thread that watches several barriers at once).
+__device__ __forceinline__ bool mbar_test(void* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: false after WAIT_LIMIT polls (the caller records the failure and leaves).
 __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
     for (unsigned i = 0; i < WAIT_LIMIT; ++i)
