@@ -362,7 +362,7 @@ def serve_workload(name: str) -> int:
 
 
 def device_busy_ms(run, seed):
-    """Two more runs of the workload.  One under the CUPTI activity trace: the summed duration of its kernels
+    """Two more runs of the workload.  One under the CUPTI activity trace: the time covered by its kernels
     is the device's busy time.  One with ``Scheduler.step`` timed on the host, the device idle when each step
     begins (a synchronize before it, outside the timed part), so that the time of a step is the host's own
     work (planning, packing, launching, digesting the step before) and holds no waiting for a busy device
@@ -373,8 +373,19 @@ def device_busy_ms(run, seed):
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         run(seed)
         torch.cuda.synchronize()
-    busy = sum(e.time_range.end - e.time_range.start for e in prof.events()
-               if e.device_type == torch.autograd.DeviceType.CUDA) / 1000.0
+    # the union of the kernels' intervals: kernels launched programmatically start while their predecessor
+    # still runs, so the sum of their durations would count that time twice
+    spans = sorted((e.time_range.start, e.time_range.end) for e in prof.events()
+                   if e.device_type == torch.autograd.DeviceType.CUDA)
+    busy, cur_end = 0.0, None
+    for a, b in spans:
+        if cur_end is None or a > cur_end:
+            busy += b - a
+            cur_end = b
+        elif b > cur_end:
+            busy += b - cur_end
+            cur_end = b
+    busy /= 1000.0
     host = {"s": 0.0, "steps": 0}
     real_step = sched_mod.Scheduler.step
 
