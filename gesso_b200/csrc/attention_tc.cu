@@ -173,7 +173,7 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
 // (segment, kv head), reset for the next launch).
 //
 // How many of the grid's splits a request uses is decided per step from two numbers the host packs
-// beside the positions (the longest sequence and the sum of all): few requests are cut so that one
+// beside the positions (the longest sequence and the average one): few requests are cut so that one
 // wave of blocks fills the device, as many pieces each as that takes; and where the lengths are
 // uneven (the longest more than 1.5 times the average) no piece is longer than the average request,
 // so that a long request among short ones does not run alone at the end.  Pieces are never shorter
@@ -228,18 +228,17 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     int used = n_splits;                     // pieces this request is cut into
     if (n_splits > 1 && kv_span != nullptr) {
         const int n_segs = (int)gridDim.y;
-        int longest = kv_span[0];
-        long long total = kv_span[1];
+        int longest = kv_span[0], average = kv_span[1];
         if (window > 0) {
             longest = min(longest, window);
-            total = min(total, (long long)n_segs * window);
+            average = min(average, window);
         }
         const int long_b = (longest + 15) / 16;
-        const int avg_b = max(1, (int)(total / (16LL * n_segs)));
+        const int avg_b = max(1, average / 16);
         const int base = n_segs * nkv;
         int chunk = 0x7fffffff;
         if (5 * base <= 4 * slots) {         // the requests' own blocks leave room in one wave: fill it
-            const long long work = (total / 16 + n_segs) * nkv;
+            const long long work = (long long)(avg_b + 1) * n_segs * nkv;
             chunk = max(DA_MIN_PER, (int)((work + slots - base - 1) / (slots - base)));
         }
         if (2 * long_b > 3 * avg_b) chunk = min(chunk, max(DA_MIN_PER, avg_b));

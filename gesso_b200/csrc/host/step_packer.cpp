@@ -37,7 +37,7 @@ enum Field {
     F_LOGIT_ROWS,      // [rows]     tokens whose logits are wanted
     F_TILE_SEG,        // [tiles]    the step's query tiles: segment ...
     F_TILE_Q0,         // [tiles]    ... and first token inside the segment
-    F_KV_SPAN,         // [2]        the longest sequence after the step, and the sum of all of them (in positions)
+    F_KV_SPAN,         // [2]        the longest sequence after the step and the average one, over the real requests
     F_BLOCK_TABLE0,    // [segs][max_pages] per paged group g: field F_BLOCK_TABLE0 + g
 };
 
@@ -163,13 +163,15 @@ HOST_API int gesso_step_prepare(void* cm, const int64_t* rids, const int* n_new,
         }
         if (!standin) ++real;
         if (standin && k > max_kv) max_kv = k;
-        if (p0 + k > kv_longest) kv_longest = p0 + k;
-        kv_sum += p0 + k;
+        if (!standin) {                      // stand-ins hold one key on a scratch page: they say nothing about the step
+            if (p0 + k > kv_longest) kv_longest = p0 + k;
+            kv_sum += p0 + k;
+        }
         cur += k;
     }
     seg_start[n] = cur;
     kv_span[0] = kv_longest;
-    kv_span[1] = kv_sum > 2147483647LL ? 2147483647 : (int)kv_sum;
+    kv_span[1] = n_real > 0 ? (int)((kv_sum + n_real - 1) / n_real) : 0;
     info[3] = tile;
     for (; tile < cap_tiles; ++tile) {        // the tiles a padded step does not have
         tile_seg[tile] = n - 1;

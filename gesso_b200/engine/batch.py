@@ -45,7 +45,7 @@ CORE_FIELDS: Tuple[Tuple[str, str], ...] = (
     ("logit_rows", "row"),         # tokens whose logits are wanted
     ("tile_seg", "tile"),          # the step's query tiles: segment ...
     ("tile_q0", "tile"),           # ... and first token inside the segment
-    ("kv_span", "two"),            # the longest sequence after the step and the sum of all (how decode attention cuts keys)
+    ("kv_span", "two"),            # the longest sequence after the step and the average one (how decode attention cuts keys)
 )
 
 # fields added from outside: name -> (axis, fill(entries, view)); they follow the block tables

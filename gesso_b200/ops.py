@@ -571,7 +571,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                      workspace=None, kv_span: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Split-KV attention for a step of single tokens (token i is request i).  ``workspace`` = (part_o, part_ml, tickets) of
     sizes [segs*nh*splits*hd], [segs*nh*splits*2] float32 and [segs*nkv] int32 (zeroed once).  ``kv_span``: int32 [2]
-    on the device, the longest sequence of the step and the sum of all: a request then uses as many of the
+    on the device, the longest sequence of the step and the average one: a request then uses as many of the
     ``n_splits`` pieces as the step's lengths call for (without it, all of them)."""
     _cuda_contig(q, "q", torch.bfloat16)
     S, nh, hd = q.shape

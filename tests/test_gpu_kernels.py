@@ -629,7 +629,7 @@ def test_decode_attention_at_the_benchmark_context(splits):
                                      [3000, 2900, 100, 90, 80, 3100, 17, 16, 15] * 4])
 @pytest.mark.parametrize("splits", [1, 4, 8])
 def test_decode_attention_cut_by_the_steps_lengths(splits, kv_lens, window):
-    """The kernel is told the longest sequence of the step and the sum of all and decides per request how
+    """The kernel is told the longest sequence of the step and the average one and decides per request how
     many of the grid's pieces it uses: one long request among short ones, even lengths that fill the device
     by themselves, few requests that do not, and a window that bounds what a request reads."""
     from gesso_b200 import ops
@@ -641,7 +641,7 @@ def test_decode_attention_cut_by_the_steps_lengths(splits, kv_lens, window):
     S = len(kv_lens)
     ws = (torch.empty(S * nh * splits * hd, device=DEV), torch.empty(S * nh * splits * 2, device=DEV),
           torch.zeros(S * nkv, dtype=torch.int32, device=DEV))
-    span = i32([max(kv_lens), sum(kv_lens)])
+    span = i32([max(kv_lens), -(-sum(kv_lens) // len(kv_lens))])
     for _ in range(2):      # twice with one workspace: the tickets must count the pieces in use, and be reset
         out = ops.decode_attention(q.to(DEV), kp, vp, bt, i32(positions.tolist()), window, 1.0 / math.sqrt(hd), splits, ws,
                                    kv_span=span)

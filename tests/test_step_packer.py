@@ -51,9 +51,9 @@ def plain_pack(entries, starts, slots, tables, layout, scratch_slot, scratch_pag
             out[at:at + layout.max_pages] = tables[g][i]
         cur += n
     out[o["seg_start"] + len(entries)] = cur
-    ends = [starts[i] + len(e.tokens) for i, e in enumerate(entries)]
-    out[o["kv_span"]] = max(ends)            # the longest sequence after the step, and the sum of all
-    out[o["kv_span"] + 1] = sum(ends)
+    ends = [starts[i] + len(e.tokens) for i, e in enumerate(entries) if e.req_id is not None]
+    out[o["kv_span"]] = max(ends, default=0)                 # the longest sequence after the step and the
+    out[o["kv_span"] + 1] = -(-sum(ends) // len(ends)) if ends else 0      # average one, over the real requests
     while tile < layout.n_tiles:
         out[o["tile_seg"] + tile] = len(entries) - 1
         out[o["tile_q0"] + tile] = 0
