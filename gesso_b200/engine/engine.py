@@ -86,6 +86,8 @@ class DeviceCache:
 
 
 class Engine:
+    accepts_device_tokens = True      # step(entries, device_tokens=...): token ids the host has not read yet
+
     def __init__(self, model: Model, *, max_positions: Optional[int] = None, page_size: int = 16,
                  num_pages: Optional[int] = None, max_requests: int = 8, use_graphs: bool = True):
         self.model = model
@@ -275,8 +277,13 @@ class Engine:
             out.append(None if not views else views[0] if plan.single[e] else tuple(views))
         return out
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens=None) -> Optional[torch.Tensor]:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` (``None`` if nothing is wanted).
+
+        ``device_tokens``: ``(ids, runs)`` for a step some of whose token ids the host has not seen yet:
+        ``ids`` is an int32 tensor on the device (what an earlier selection left there), ``runs`` a list of
+        ``(first id, first token of the step, count)``; those tokens (whatever the entries say) are copied
+        from ``ids`` on the device, in stream order, before the step's kernels run.
 
         A step of single tokens only (decoding) replays a CUDA graph captured for its batch size:
         the metadata goes into the graph's fixed buffer and the whole layer loop is one launch.
@@ -290,6 +297,12 @@ class Engine:
         """
         # a refusal here (bad entries, no pages: all requests' pages are reserved or none) leaves every
         # request as it was
+        if device_tokens is not None:
+            ids, runs = device_tokens
+            n_given = sum(len(e.tokens) for e in entries)
+            if (ids.dtype != torch.int32 or not ids.is_cuda
+                    or any(n < 1 or src < 0 or dst < 0 or src + n > ids.numel() or dst + n > n_given for src, dst, n in runs)):
+                raise invalid("step: device tokens must be int32 ids on the device and runs inside them and the step")
         layout, slot_i, host, max_seg, max_kv = self._prepare(entries)
         req_ids = [e.req_id for e in entries]
         self._unchecked.update(req_ids)
@@ -297,16 +310,17 @@ class Engine:
             with ops.tc_status_scope(self._tc_status):
                 if self._padded_rows is not None:
                     # a mixed step filled up to a shape that has a graph (or gets one now)
-                    logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg)
+                    logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg, device_tokens=device_tokens)
                     logits = logits[:self._padded_rows] if self._padded_rows else None
                     self.padded_steps_run += 1
                 elif self.use_graphs and max_seg == 1 and layout.n_segs <= self.max_graph_batch:
-                    logits = self._step_graph(layout, slot_i, host, max_kv)
+                    logits = self._step_graph(layout, slot_i, host, max_kv, device_tokens=device_tokens)
                 elif self.use_graphs and self._portion_graph_wanted(layout):
-                    logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg)
+                    logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg, device_tokens=device_tokens)
                 else:
                     buf = torch.empty((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
                     self._upload(buf, slot_i, host)
+                    self._fill_device_tokens(buf, layout, device_tokens)
                     ctx = StepContext(layout, buf, self.status, max_seg, max_kv, self._all_rows)
                     before = launch_count()
                     logits = self.model.forward(ctx, self.views(ctx))
@@ -357,7 +371,7 @@ class Engine:
         try:
             with ops.tc_status_scope(self._tc_status):
                 logits = self._step_graph(staged.layout, staged.slot_i, staged.host, staged.max_kv,
-                                          device_tokens=device_tokens, token_at=at)
+                                          device_tokens=None if device_tokens is None else (device_tokens, [(0, 0, n)]))
             self.cache.commit_single_tokens(staged.req_ids)
         except Exception as e:
             self._mark_broken(staged.req_ids, f"a step it took part in failed ({type(e).__name__}: {e})")
@@ -379,15 +393,25 @@ class Engine:
         self._portion_shapes[key] = seen + 1
         return seen >= 1 and sum(1 for k in self._graphs if k[0] > k[1] == 1) < 8
 
+    @staticmethod
+    def _fill_device_tokens(buf: torch.Tensor, layout: StepLayout, device_tokens) -> None:
+        """Token ids that are still on the device go into the step's metadata there (device to device, in
+        stream order, behind the upload of the rest)."""
+        if device_tokens is None:
+            return
+        ids, runs = device_tokens
+        at = layout.offsets()["token_ids"]
+        for src, dst, n in runs:
+            buf[at + dst:at + dst + n].copy_(ids[src:src + n])
+
     def _step_graph(self, layout: StepLayout, slot_i: int, host: torch.Tensor, max_kv: int,
-                    device_tokens: Optional[torch.Tensor] = None, token_at: int = 0, max_seg: int = 1):
+                    device_tokens=None, max_seg: int = 1):
         key = (layout.n_tokens, layout.n_segs, layout.n_rows, self._all_rows)
         g = self._graphs.get(key)
         if g is None:
             buf = torch.zeros((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
             self._upload(buf, slot_i, host)
-            if device_tokens is not None:
-                buf[token_at:token_at + device_tokens.numel()].copy_(device_tokens)
+            self._fill_device_tokens(buf, layout, device_tokens)
             ctx = StepContext(layout, buf, self.status, max_seg, self.max_positions, self._all_rows)
             views = self.views(ctx)
             # One eager run first: libraries initialise lazily, and capture records rather than runs,
@@ -418,8 +442,7 @@ class Engine:
             return logits
         graph, buf, out, n_launch = g
         self._upload(buf, slot_i, host)
-        if device_tokens is not None:
-            buf[token_at:token_at + device_tokens.numel()].copy_(device_tokens)     # device to device, in stream order
+        self._fill_device_tokens(buf, layout, device_tokens)
         graph.replay()
         self.launches += n_launch
         return out

@@ -66,6 +66,7 @@ class Request:
     error: Optional[Exception] = None
     generated: List[int] = field(default_factory=list)
     fed: int = 0                      # tokens of prompt+generated that are in the cache
+    pending: int = 0                  # tokens selected on the device for it that the host has not read yet
     preemptions: int = 0
     cancelled: bool = False
     rng: Optional[SplitMix64] = None
@@ -108,6 +109,12 @@ class Request:
 
 
 _FAILED_STEP = object()      # what Scheduler._run returns for a step that raised
+_UNREAD_TOKEN = (0,)         # stands in a step's entries for a token id that is still on the device
+_FIRST_PLACE = (0,)
+
+
+class _NeedSync(Exception):
+    """Planning around tokens that are still on the device met a decision that needs them read first."""
 
 
 @dataclass
@@ -142,6 +149,9 @@ class Scheduler:
         self._staged = None                       # the next decoding step, prepared while this one runs
         self._inflight = None                     # (requests, selection) of a step whose tokens are not read yet
         self.pipeline = pipeline
+        self._planning_ahead = False              # plan() runs around tokens the host has not read yet
+        self._ahead_requests: List[Request] = []
+        self.steps_ahead = 0                      # steps launched before the step before them was digested
 
     # ---- adding --------------------------------------------------------------------------------
     def add(self, req: Request) -> Request:
@@ -176,7 +186,13 @@ class Scheduler:
 
     # ---- planning (pure bookkeeping: no device work) ------------------------------------------------
     def _left(self, r: Request) -> int:
-        return len(r.prompt) + len(r.generated) - r.fed
+        return len(r.prompt) + len(r.generated) + r.pending - r.fed
+
+    def _ending(self, r: Request) -> bool:
+        """A token selected for it and not read yet is certainly its last (its count or the context is full):
+        it takes no part in a step planned before that token is read."""
+        return r.pending > 0 and (len(r.generated) + r.pending >= r.max_new_tokens
+                                  or len(r.prompt) + len(r.generated) + r.pending > self.cache.max_positions)
 
     def _need(self, wants: Dict[object, Tuple[Request, int]]) -> List[int]:
         """Pages per group that the planned tokens still have to be handed."""
@@ -204,7 +220,7 @@ class Scheduler:
         # steady decoding (nobody waits, everybody has exactly its last sampled token to run, and the
         # pools hold a page for everyone who crosses a page border): nothing to decide
         if not self.waiting and self.running and len(self.running) <= self.max_tokens_per_step \
-                and all(r.generated and self._left(r) == 1 for r in self.running):
+                and all((r.generated or r.pending) and self._left(r) == 1 and not self._ending(r) for r in self.running):
             ps = self.cache.page_size
             at_border = sum(1 for r in self.running if self.cache.length(r.req_id) % ps == 0)
             free = self.cache.free_pages()
@@ -215,13 +231,16 @@ class Scheduler:
 
         budget = self.max_tokens_per_step
         wants: Dict[object, Tuple[Request, int]] = {}
-        decoders = [r for r in self.running if self._left(r) == 1 and r.generated]
-        prefillers = [r for r in self.running if r not in decoders]
+        going = [r for r in self.running if not self._ending(r)]
+        decoders = [r for r in going if self._left(r) == 1 and (r.generated or r.pending)]
+        prefillers = [r for r in going if r not in decoders]
         # 1. every decoding request gets its one token; preempt from the newest while they do not fit
         for r in decoders:
             wants[r.req_id] = (r, 1)
         need = self._need(wants)                 # kept in step with `wants` from here on
         while self._short(need) and len(self.running) > 1:
+            if self._planning_ahead:
+                raise _NeedSync()                # a preemption: first read what the victim was given
             victim = self.running[-1]
             self._preempt(victim)
             plan.preempted.append(victim)
@@ -230,6 +249,8 @@ class Scheduler:
             if victim in prefillers:
                 prefillers.remove(victim)
         if self._short(need):
+            if self._planning_ahead:
+                raise _NeedSync()
             # a single request is left and its next token has no page: it has outgrown the pool
             for r, _ in list(wants.values()):
                 self._finish(r, FAILED, resource(f"request {r.req_id!r} does not fit the cache pool"))
@@ -263,6 +284,8 @@ class Scheduler:
             wants[r.req_id] = (r, n)
             budget -= n
         if not wants and self.running:
+            if self._planning_ahead:
+                raise _NeedSync()
             # nothing fits although requests are live: the oldest alone must be able to move
             r = self.running[0]
             while len(self.running) > 1:
@@ -351,7 +374,10 @@ class Scheduler:
 
     def _select_launch(self, logits, requests: List[Request]):
         ticket = self._status_launch()          # before the ids' copy: it has landed when they have
-        return self.select.launch(logits, requests), ticket
+        selection = self.select.launch(logits, requests)
+        for r in requests:
+            r.pending += 1                      # until _digest has read the token
+        return selection, ticket
 
     def _select_wait(self, pending) -> List[object]:
         selection, ticket = pending
@@ -363,6 +389,8 @@ class Scheduler:
         """Take the selected tokens in: append, call hooks, finish what has ended."""
         emitted: List[Tuple[Request, int]] = []
         for r, tok in zip(requests, tokens):
+            if r.pending > 0:
+                r.pending -= 1
             if r.state != RUNNING:
                 continue                    # failed with its step: what was selected for it is dropped
             if isinstance(tok, Exception):
@@ -417,7 +445,7 @@ class Scheduler:
         if not plan.entries:
             return []
         entries, samplers = [], []
-        for r, start, n in plan.entries:
+        for r, start, n in plan.entries:      # (nothing is pending here: the step before has been digested)
             last = start + n == r.length
             entries.append(StepEntry(r.req_id, r.tokens(start, n), [n - 1] if last else []))
             if last:
@@ -439,11 +467,62 @@ class Scheduler:
         if not samplers:
             return []
         launch = getattr(self.select, "launch", None)
-        if launch is not None and self.pipeline and self._staged is not None:
+        if launch is not None and self.pipeline and (self._staged is not None or self._can_go_ahead()):
             # the selection is launched, not awaited: the next call takes it from there
             self._inflight = (samplers, self._select_launch(logits, samplers))
             return self._advance()
         return self._digest(samplers, self._select_now(logits, samplers))
+
+    def _can_go_ahead(self) -> bool:
+        """Any step, not only a steady decoding one, can be launched before the step before it is digested if
+        the engine takes token ids that are still on the device."""
+        return self.pipeline and getattr(self.engine, "accepts_device_tokens", False)
+
+    def _launch_ahead(self, prev_requests: List[Request], prev_selection):
+        """Plan and launch the step after the one in flight around the tokens that one is still selecting:
+        the requests it selects for take part with a token id that is copied on the device; a request whose
+        unread token is certainly its last sits the step out.  What the plan cannot decide without reading
+        the tokens (a preemption, a request that has outgrown the pool) makes it give up: ``None``.
+        Returns ``(samplers, selection or None)`` of the launched step."""
+        self._planning_ahead = True
+        try:
+            plan = self.plan()
+        except _NeedSync:
+            return None
+        finally:
+            self._planning_ahead = False
+        if not plan.entries:
+            return None
+        place = {id(r): i for i, r in enumerate(prev_requests)}
+        unread, known = [], []
+        for r, start, n in plan.entries:
+            if start >= len(r.prompt) + len(r.generated):
+                unread.append((place[id(r)], r, start, n))       # its token is the one being selected
+            else:
+                known.append((r, start, n))
+        unread.sort(key=lambda x: x[0])                          # in the order of the selection's rows
+        entries, samplers, runs, requests = [], [], [], []
+        for k, (i, r, start, n) in enumerate(unread):
+            entries.append(StepEntry(r.req_id, _UNREAD_TOKEN, _FIRST_PLACE))
+            samplers.append(r)
+            requests.append((r, n))
+            if runs and runs[-1][0] + runs[-1][2] == i:
+                runs[-1] = (runs[-1][0], runs[-1][1], runs[-1][2] + 1)
+            else:
+                runs.append((i, k, 1))
+        for r, start, n in known:
+            last = start + n == len(r.prompt) + len(r.generated) + r.pending
+            entries.append(StepEntry(r.req_id, r.tokens(start, n), [n - 1] if last else []))
+            requests.append((r, n))
+            if last:
+                samplers.append(r)
+        self._ahead_requests = [r for r, _ in requests]          # whom a failure of this step concerns
+        logits = self.engine.step(entries, device_tokens=(prev_selection.ids, runs) if runs else None)
+        self.steps += 1
+        self.steps_ahead += 1
+        for r, n in requests:
+            r.fed += n
+        return samplers, (self._select_launch(logits, samplers) if samplers else None)
 
     def _advance(self) -> List[Tuple[Request, int]]:
         """One turn of the pipelined decoding: launch the step after the one in flight from the ids on the
@@ -462,6 +541,28 @@ class Scheduler:
                 ahead = self._select_launch(logits, requests)
             except Exception as e:
                 ahead_error = e                   # the step in flight is still good: digest it first
+        elif self._can_go_ahead():
+            # not a steady decoding step (somebody waits, prompts are being read, the batch changes): plan
+            # around the unread tokens and launch; whoever turns out to have ended has run one step too many
+            launched, failed_with = None, None
+            self._ahead_requests = []
+            try:
+                launched = self._launch_ahead(requests, pending[0])
+            except Exception as e:
+                failed_with = e                   # the step in flight is still good: digest it first
+            emitted = self._digest(requests, self._select_wait(pending))
+            if failed_with is not None:
+                self._fail(self._ahead_requests or list(self.running), failed_with)
+                self._inflight = None
+                return emitted
+            if launched is None or launched[1] is None:
+                self._inflight = None             # nothing launched, or a step that selects nothing
+                return emitted
+            samplers, selection = launched
+            self._inflight = (samplers, selection)
+            if all(r.state == RUNNING for r in samplers) and len(samplers) == len(self.running) and not self.waiting:
+                self._stage_next(samplers, pending_tokens=1)     # steady decoding from here on
+            return emitted
         emitted = self._digest(requests, self._select_wait(pending))
         if ahead_error is not None:
             self._fail(requests, ahead_error)

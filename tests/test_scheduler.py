@@ -384,6 +384,109 @@ def test_pipelined_decoding_with_cancel_and_hooks():
     assert eng.cache.pages_in_use() == [0] and not s.has_work
 
 
+# ---- any step one step ahead of the host (prompt portions, arrivals, a batch that changes) ------------------
+class AheadEngine(PipelinedEngine):
+    """Takes token ids that are 'still on the device' in any step: ``device_tokens = (ids, runs)``."""
+
+    accepts_device_tokens = True
+
+    def __init__(self, raise_at=(), **kw):
+        super().__init__(**kw)
+        self.raise_at, self.n, self.ahead_steps = set(raise_at), 0, 0
+
+    def step(self, entries, device_tokens=None):
+        k, self.n = self.n, self.n + 1
+        if k in self.raise_at:
+            raise GessoError(ErrorCode.LAUNCH, f"step {k}: a kernel refused its sizes")
+        if device_tokens is not None:
+            ids, runs = device_tokens
+            flat = [t for e in entries for t in e.tokens]
+            for src, dst, n in runs:
+                flat[dst:dst + n] = ids[src:src + n]
+            filled, cur = [], 0
+            for e in entries:
+                filled.append(type(e)(e.req_id, flat[cur:cur + len(e.tokens)], e.want))
+                cur += len(e.tokens)
+            entries = filled
+            self.ahead_steps += 1
+        return super().step(entries)
+
+
+def ahead(**kw):
+    eng = AheadEngine(**{k: kw.pop(k) for k in ("raise_at", "num_pages", "page_size", "slots", "ctx") if k in kw})
+    return eng, Scheduler(eng, HistorySelect(), vocab_size=100, **kw)
+
+
+def test_steps_with_prompt_portions_run_ahead_and_give_the_same_tokens():
+    prompts = [[1, 2, 3], [9] * 11, [4], [7, 8, 9, 10, 11, 12], [5] * 7, [6, 1]]
+    news = (5, 9, 1, 4, 2, 7)
+    eng, s = ahead(max_batch=3, max_tokens_per_step=8, prefill_chunk=4)
+    reqs = [s.add(Request(p, n)) for p, n in zip(prompts, news)]
+    s.run()
+    for p, r, n in zip(prompts, reqs, news):
+        assert r.status == COMPLETE and r.ids == solo(p, n), (p, r.ids)
+    assert s.steps_ahead > 5 and eng.ahead_steps > 5        # steps planned around tokens the host had not read
+    assert all(sum(len(e[1]) for e in st) <= 8 for st in eng.log)          # the token budget holds
+    assert eng.cache.pages_in_use() == [0] and eng.cache.slots_in_use() == 0 and not s.has_work
+    # a request whose unread token is certainly its last sits the next step out: no request was ever run
+    # on a token beyond its count
+    fed = {}
+    for st in eng.log:
+        for rid, toks, _ in st:
+            fed[rid] = fed.get(rid, 0) + len(toks)
+    for r in reqs:
+        assert fed[r.req_id] == len(r.prompt) + len(r.generated) - 1
+
+
+def test_running_ahead_drops_the_step_too_many_and_takes_arrivals():
+    full_a, full_b = solo([5, 6, 7], 14), solo([8, 1] * 5, 14)
+    eng, s = ahead(max_batch=3, prefill_chunk=3)
+    a = s.add(Request([5, 6, 7], 14, stop_ids=[full_a[3 + 6]]))       # its 7th new token stops it
+    b = s.add(Request([8, 1] * 5, 14))
+    seen = []
+    c = s.add(Request([2, 2, 2, 2, 2], 20, on_token=lambda t: (seen.append(t), len(seen) < 4)[1]))
+    late = None
+    for i in range(80):
+        if not s.has_work:
+            break
+        s.step()
+        if i == 6:
+            late = s.add(Request([3, 3, 3, 3], 5))
+    assert a.status == STOP and a.ids == full_a[:3 + 7]
+    assert b.status == COMPLETE and b.ids == full_b
+    assert c.status == STOP and c.ids == solo([2, 2, 2, 2, 2], 20)[:5 + 4]
+    assert late.status == COMPLETE and late.ids == solo([3, 3, 3, 3], 5)
+    assert s.steps_ahead > 0 and eng.cache.pages_in_use() == [0] and not s.has_work
+
+
+def test_running_ahead_yields_where_a_preemption_is_needed():
+    """Pages run out: a plan made around unread tokens gives up, the tokens are read, the newest request is
+    preempted as ever, and nobody's tokens change."""
+    prompts = [[1] * 6, [2] * 6, [3] * 6]
+    eng, s = ahead(num_pages=7, page_size=4, slots=3, ctx=40, max_batch=3, prefill_chunk=8)
+    reqs = [s.add(Request(p, 10)) for p in prompts]
+    s.run()
+    for p, r in zip(prompts, reqs):
+        assert r.status == COMPLETE and r.ids == solo(p, 10)
+    assert s.preemptions > 0 and eng.cache.pages_in_use() == [0]
+
+
+def test_a_step_launched_ahead_that_raises_fails_its_requests_only():
+    prompts = [[1, 2, 3], [4, 5], [6, 7, 8, 9], [10]]
+    eng, s = ahead(raise_at={2}, max_batch=2)
+    reqs = [s.add(Request(p, 4)) for p in prompts]
+    s.run()
+    failed = [r for r in reqs if r.status == FAILED]
+    done = [r for r in reqs if r.status == COMPLETE]
+    assert failed and done and len(failed) + len(done) == 4
+    for r in failed:
+        assert r.error.code == ErrorCode.LAUNCH
+        assert r.ids == solo(r.prompt, 4)[:len(r.ids)]          # what was read before the failure stands
+    for r in done:
+        assert r.ids == solo(r.prompt, 4)
+    assert eng.cache.pages_in_use() == [0] and eng.cache.slots_in_use() == 0
+
+
 # ---- a step that fails is terminal for its own requests only (src/Runtime/Runtime.jl:151-153, 175-178) ----
 class FailingEngine(FakeEngine):
     """Raises in the steps whose numbers are in ``raise_at``; reports a bad status word after the steps in
