@@ -271,6 +271,7 @@ class Session:
         if self.last_scheduler is not None:
             s["scheduler_steps"] = self.last_scheduler.steps
             s["preemptions"] = self.last_scheduler.preemptions
+            s["steps_ahead"] = self.last_scheduler.steps_ahead      # launched before the step before was digested
         return s
 
 

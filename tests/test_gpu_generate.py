@@ -76,6 +76,8 @@ def test_batch_equals_solo_and_is_deterministic(models, plain_models):
             for i, p in enumerate(prompts)]
     res = s.run_batch(reqs)
     assert [r.status for r in res] == ["complete"] * 5
+    # steps with prompt portions were planned and launched around tokens the host had not read yet
+    assert s.stats()["steps_ahead"] >= 5
     solo = gesso_b200.Session(model, context_length=128, max_batch=1)
     for i, (p, r) in enumerate(zip(prompts, res)):
         assert r.ids == solo.generate(p, 9, temperature=0.7 if i % 2 else 0.0, top_p=0.9, seed=1 + i)
