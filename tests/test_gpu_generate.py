@@ -297,6 +297,56 @@ def test_a_status_word_set_during_a_step_fails_that_steps_requests_only(models):
         assert s.generate(prompts[0], 8) == alone[0]    # and the session is free again
 
 
+@pytest.mark.parametrize("use_graphs", [True, False])
+def test_a_step_takes_token_ids_that_are_still_on_the_device(use_graphs, models):
+    """``Engine.step(entries, device_tokens=(ids, runs))``: the tokens named by the runs come from a device
+    tensor, whatever the entries hold in their place; the logits equal those of the same step fed from the
+    host, in a decoding step, in a mixed step, and when the shape's graph is replayed a second time."""
+    import gesso_b200
+    from gesso_b200.engine import Engine, StepEntry
+    model = models("b", "float32")
+    vocab = model.vocab_size
+
+    def run(from_device):
+        eng = Engine(model, max_positions=64, max_requests=4, use_graphs=use_graphs)
+        for rid in "abcd":
+            eng.admit(rid)
+        eng.step([StepEntry("a", [3, 4, 5], []), StepEntry("b", [6], []), StepEntry("c", [7, 8], [])])
+        outs = []
+        ids = torch.tensor([11 % vocab, 12 % vocab, 13 % vocab, 14 % vocab], dtype=torch.int32, device="cuda")
+        for turn in range(2):                  # the second turn replays what the first captured
+            real = [int(t) for t in ids.tolist()]
+            # a decoding step of a, b, c: ids 0, 2, 3 (two runs)
+            if from_device:
+                entries = [StepEntry(r, [0], [0]) for r in "abc"]
+                outs.append(eng.step(entries, device_tokens=(ids, [(0, 0, 1), (2, 1, 2)])).clone())
+            else:
+                outs.append(eng.step([StepEntry("a", [real[0]], [0]), StepEntry("b", [real[2]], [0]),
+                                      StepEntry("c", [real[3]], [0])]).clone())
+            # a mixed step: b and a decode from ids 1 and 0, d brings a portion from the host
+            portion = [(5 + 3 * turn + i) % vocab for i in range(5)]
+            if from_device:
+                entries = [StepEntry("b", [0], [0]), StepEntry("a", [0], [0]), StepEntry("d", portion, [4])]
+                outs.append(eng.step(entries, device_tokens=(ids, [(1, 0, 1), (0, 1, 1)])).clone())
+            else:
+                outs.append(eng.step([StepEntry("b", [real[1]], [0]), StepEntry("a", [real[0]], [0]),
+                                      StepEntry("d", portion, [4])]).clone())
+            ids = (ids + 17) % vocab
+        eng.check_status()
+        return outs
+
+    for got, want in zip(run(True), run(False)):
+        assert torch.equal(got, want)
+    eng = Engine(model, max_positions=64, max_requests=2)
+    eng.admit("a")
+    ids = torch.zeros(2, dtype=torch.int32, device="cuda")
+    with pytest.raises(gesso_b200.GessoError, match="device tokens"):
+        eng.step([StepEntry("a", [1], [0])], device_tokens=(ids, [(1, 0, 2)]))          # a run past the ids
+    with pytest.raises(gesso_b200.GessoError, match="device tokens"):
+        eng.step([StepEntry("a", [1], [0])], device_tokens=(ids.long(), [(0, 0, 1)]))   # not int32
+    assert eng.length("a") == 0
+
+
 def test_a_request_of_a_failed_step_can_only_be_released(models):
     """Driving the engine directly: after a step that failed, or whose status was bad, its requests have
     keys, values and state of a half-run step in the cache; a further step with one of them is refused."""
