@@ -36,7 +36,8 @@ _SIGNATURES = {
     "gesso_skinny_gemm_takes": [I, I, I],
     "gesso_skinny_gemm": [P, P, P, F, P, P, P, I, I, I, I, P, LL, P],
     "gesso_gemm_f32": [P, I, P, I, P, P, I, I, I, P],
-    "gesso_argmax_rows": [P, I, I, P, P, P, P, P],
+    "gesso_argmax_rows": [P, I, I, P, P, P, P, P, P],
+    "gesso_copy_words": [I, P, P, P, P],
     "gesso_sample_rows": [P, I, I, P, P, P, P, P, P, P],
 }
 

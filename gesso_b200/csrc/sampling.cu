@@ -24,7 +24,8 @@
 
 // ---- greedy ----------------------------------------------------------------------------------
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ ids, int* __restrict__ nonfinite) {
+argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ ids, int* __restrict__ nonfinite,
+                   int* __restrict__ host_out) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ int s_bad;
@@ -62,6 +63,12 @@ argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ id
         if (lane == 0) {
             ids[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
             nonfinite[blockIdx.x] = s_bad;
+            // pinned host memory [2][rows]: the result goes there without a copy of its own (the host sees it once
+            // it has waited for an event behind this kernel)
+            if (host_out) {
+                host_out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+                host_out[gridDim.x + blockIdx.x] = s_bad;
+            }
         }
     }
 }
@@ -121,7 +128,7 @@ argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict
 }
 
 __global__ void argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx,
-                                    int* __restrict__ ids, int* __restrict__ nonfinite) {
+                                    int* __restrict__ ids, int* __restrict__ nonfinite, int* __restrict__ host_out) {
     const int row = blockIdx.x, lane = threadIdx.x;     // 32 threads, one per slice
     pdl_launch_dependents();
     pdl_wait();
@@ -134,22 +141,30 @@ __global__ void argmax_final_kernel(const float* __restrict__ pval, const int* _
         bad |= __shfl_xor_sync(0xffffffffu, bad, o);
         if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    if (lane == 0) { ids[row] = bi == 0x7fffffff ? 0 : bi; nonfinite[row] = bad; }
+    if (lane == 0) {
+        ids[row] = bi == 0x7fffffff ? 0 : bi;
+        nonfinite[row] = bad;
+        if (host_out) {          // pinned host memory [2][rows]: the result goes there without a copy of its own
+            host_out[row] = bi == 0x7fffffff ? 0 : bi;
+            host_out[gridDim.x + row] = bad;
+        }
+    }
 }
 
 // scratch: n_rows * ARGMAX_SPLIT floats and 2 * n_rows * ARGMAX_SPLIT ints (may be null for narrow rows)
+// host_out: null, or pinned host memory of 2 * n_rows ints that takes the ids and the flags as well
 GESSO_API int gesso_argmax_rows(const float* logits, int n_rows, int V, int* ids, int* nonfinite,
-                                float* scratch_val, int* scratch_idx, cudaStream_t stream) {
+                                float* scratch_val, int* scratch_idx, int* host_out, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0) return GESSO_ERR_BAD_SIZE;
     if (V < 8192 || !scratch_val || !scratch_idx || n_rows > 65535) {
-        argmax_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, ids, nonfinite);
+        argmax_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, ids, nonfinite, host_out);
         return launch_status();
     }
     launch_pdl(argmax_partial_kernel, dim3(ARGMAX_SPLIT, n_rows), dim3(256), 0, stream, logits, V, scratch_val,
                scratch_idx);
     launch_pdl(argmax_final_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)scratch_val,
-               (const int*)scratch_idx, ids, nonfinite);
+               (const int*)scratch_idx, ids, nonfinite, host_out);
     return launch_status();
 }
 

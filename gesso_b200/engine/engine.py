@@ -245,12 +245,38 @@ class Engine:
             return None              # too many shapes already: as it is, launched one by one
         return T_b, S_b
 
-    def _upload(self, buf: torch.Tensor, slot_i: int, host: torch.Tensor) -> None:
-        buf.copy_(host, non_blocking=True)
+    def _upload(self, buf: torch.Tensor, slot_i: int, host: torch.Tensor, layout: Optional[StepLayout] = None,
+                device_tokens=None) -> None:
+        """The step's metadata from pinned host memory into ``buf``, and the token ids that are still on the
+        device behind it.  Small buffers go by one kernel that reads the pinned memory itself (no change to
+        the copy engine and back between two steps); where the device-sourced tokens are the first tokens of
+        the step (as the scheduler puts them) the same launch copies them, and the host's place-holders for
+        them are left out of the upload."""
+        n = host.numel()
+        if ops.KERNEL_COPIES and n <= ops.KERNEL_COPY_MAX_WORDS:
+            skip, segs = 0, []
+            if device_tokens is not None:
+                ids, runs = device_tokens
+                at = layout.offsets()["token_ids"]
+                covered = sorted((dst, cnt) for _, dst, cnt in runs)
+                prefix = 0
+                for dst, cnt in covered:
+                    if dst != prefix:
+                        prefix = -1
+                        break
+                    prefix += cnt
+                if at == 0 and prefix > 0 and len(runs) <= 5:
+                    skip = prefix
+                    segs = [((buf, dst), (ids, src), cnt) for src, dst, cnt in runs]
+                    device_tokens = None
+            ops.copy_words([((buf, skip), (host, skip), n - skip)] + segs)
+        else:
+            buf.copy_(host, non_blocking=True)
         if self._pinned_events[slot_i] is None:
             self._pinned_events[slot_i] = torch.cuda.Event()
         self._pinned_events[slot_i].record()
-        self.h2d_bytes += host.numel() * 4
+        self.h2d_bytes += n * 4
+        self._fill_device_tokens(buf, layout, device_tokens)
 
     def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
         """Reserve pages, zero fresh slots and upload the step's metadata (one transfer)."""
@@ -319,8 +345,7 @@ class Engine:
                     logits = self._step_graph(layout, slot_i, host, max_kv, max_seg=max_seg, device_tokens=device_tokens)
                 else:
                     buf = torch.empty((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
-                    self._upload(buf, slot_i, host)
-                    self._fill_device_tokens(buf, layout, device_tokens)
+                    self._upload(buf, slot_i, host, layout, device_tokens)
                     ctx = StepContext(layout, buf, self.status, max_seg, max_kv, self._all_rows)
                     before = launch_count()
                     logits = self.model.forward(ctx, self.views(ctx))
@@ -410,8 +435,7 @@ class Engine:
         g = self._graphs.get(key)
         if g is None:
             buf = torch.zeros((host.numel(),), dtype=torch.int32, device=self.model.rt.device)
-            self._upload(buf, slot_i, host)
-            self._fill_device_tokens(buf, layout, device_tokens)
+            self._upload(buf, slot_i, host, layout, device_tokens)
             ctx = StepContext(layout, buf, self.status, max_seg, self.max_positions, self._all_rows)
             views = self.views(ctx)
             # One eager run first: libraries initialise lazily, and capture records rather than runs,
@@ -441,8 +465,7 @@ class Engine:
             self._graphs[key] = (graph, buf, out, n_launch)
             return logits
         graph, buf, out, n_launch = g
-        self._upload(buf, slot_i, host)
-        self._fill_device_tokens(buf, layout, device_tokens)
+        self._upload(buf, slot_i, host, layout, device_tokens)
         graph.replay()
         self.launches += n_launch
         return out
@@ -470,7 +493,10 @@ class Engine:
         without waiting.  Returns a ticket for :meth:`status_read_finish`."""
         self._status_turn = (self._status_turn + 1) % len(self._status_host)
         host = self._status_host[self._status_turn]
-        host.copy_(self.status_words, non_blocking=True)
+        if ops.KERNEL_COPIES:
+            ops.copy_words([((host, 0), (self.status_words, 0), host.numel())])
+        else:
+            host.copy_(self.status_words, non_blocking=True)
         covered, self._unchecked = self._unchecked, set()
         return host, covered
 

@@ -483,18 +483,47 @@ def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[
 
 
 # ---- sampling ----------------------------------------------------------------------------------
-def argmax_rows(logits: torch.Tensor):
+def argmax_rows(logits: torch.Tensor, host_out: Optional[torch.Tensor] = None):
+    """Greedy ids and non-finite flags of every row.  ``host_out``: pinned host int32 ``[2, R]`` that the
+    kernel writes the same two rows into (no copy of its own is needed then; valid once the stream has
+    passed the kernel)."""
     _cuda_contig(logits, "logits", torch.float32)
     R, V = logits.shape
+    if host_out is not None:
+        _need(host_out.dtype == torch.int32 and host_out.is_pinned() and host_out.is_contiguous()
+              and tuple(host_out.shape) == (2, R), "argmax host output must be pinned int32 [2, rows]")
     both = torch.empty((2, R), dtype=torch.int32, device=logits.device)   # one buffer: one copy to the host
     ids, bad = both[0], both[1]
     sv = si = None
     if V >= 8192:      # wide rows are scanned by 32 blocks each; their partial results need scratch
         sv = torch.empty((R * 32,), dtype=torch.float32, device=logits.device)
         si = torch.empty((R * 64,), dtype=torch.int32, device=logits.device)
-    _lib.check(_lib.library().gesso_argmax_rows(_p(logits), R, V, _p(ids), _p(bad), _p(sv), _p(si), _stream()),
+    _lib.check(_lib.library().gesso_argmax_rows(_p(logits), R, V, _p(ids), _p(bad), _p(sv), _p(si),
+                                                host_out.data_ptr() if host_out is not None else None, _stream()),
                "argmax_rows")
     return ids, bad
+
+
+KERNEL_COPIES = os.environ.get("GESSO_KERNEL_COPIES", "1") != "0"
+KERNEL_COPY_MAX_WORDS = 1 << 18      # above 1 MB the copy engine is the better mover
+
+
+def copy_words(segments) -> None:
+    """Copy 32-bit words between device memory and pinned host memory with one kernel launch on the current
+    stream: ``segments`` is a list of up to six ``(dst, src, n_words)``, ``dst`` / ``src`` being ``(tensor,
+    first word)`` pairs (int32 tensors, contiguous; a host tensor must be pinned).  The segments of one call
+    must not overlap.  Between decoding steps this replaces memcpy operations, each of which costs a change
+    between the compute and the copy engines."""
+    n = len(segments)
+    _need(1 <= n <= 6, "copy_words takes one to six segments")
+    dst, src, cnt = (ctypes.c_void_p * n)(), (ctypes.c_void_p * n)(), (ctypes.c_longlong * n)()
+    for k, ((dt, d0), (st, s0), words) in enumerate(segments):
+        for t, at in ((dt, d0), (st, s0)):
+            _need(t.dtype == torch.int32 and t.is_contiguous() and (t.is_cuda or t.is_pinned()),
+                  "copy_words takes contiguous int32 tensors on the device or in pinned host memory")
+            _need(0 <= at and at + words <= t.numel() and words >= 0, "copy_words: a segment leaves its tensor")
+        dst[k], src[k], cnt[k] = dt.data_ptr() + 4 * d0, st.data_ptr() + 4 * s0, words
+    _lib.check(_lib.library().gesso_copy_words(n, dst, src, cnt, _stream()), "copy_words")
 
 
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, u: torch.Tensor):

@@ -130,8 +130,12 @@ def select_launch(logits: torch.Tensor, params: Sequence[SamplingParams],
     R = logits.shape[0]
     if R == 0:
         return None
-    ids, bad = ops.argmax_rows(logits)
     sampled = [i for i, p in enumerate(params) if not p.greedy]
+    host = _pinned_rows(R)
+    # all greedy: the selection kernel writes ids and flags into the pinned buffer itself (no copy operation
+    # between this step and the next)
+    direct = not sampled and ops.KERNEL_COPIES
+    ids, bad = ops.argmax_rows(logits, host_out=host if direct else None)
     if not sampled and ids.data_ptr() + 4 * R == bad.data_ptr():
         # all greedy: ids and flags sit in one buffer, one copy brings both
         both = ids.new_empty(0).set_(ids.untyped_storage(), ids.storage_offset(), (2, R))
@@ -153,8 +157,8 @@ def select_launch(logits: torch.Tensor, params: Sequence[SamplingParams],
             ids = torch.where(pick, sids, ids)
             bad = torch.where(pick, sbad, bad)
         both = torch.stack([ids, bad])
-    host = _pinned_rows(R)
-    host.copy_(both, non_blocking=True)
+    if not direct:
+        host.copy_(both, non_blocking=True)
     event = torch.cuda.Event()
     event.record()
     return PendingSelection(both, host, event, R)

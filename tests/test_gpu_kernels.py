@@ -775,6 +775,42 @@ def test_sampler_low_temperature_is_argmax_and_nucleus_keeps_the_top_set():
     assert seen <= {5, 50} and 5 in seen
 
 
+# ---- copies between steps by a kernel -------------------------------------------------------------------
+def test_copy_words_between_device_and_pinned_memory():
+    """One launch, several segments, either way round, odd offsets and lengths (the 16-byte form and the
+    word-by-word form); and the greedy selection writing ids and flags into pinned memory itself."""
+    from gesso_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    host = torch.randint(0, 1 << 30, (5000,), generator=g, dtype=torch.int32).pin_memory()
+    dev = torch.zeros(6000, dtype=torch.int32, device=DEV)
+    ids = torch.arange(100, 164, dtype=torch.int32, device=DEV)
+    back = torch.zeros(300, dtype=torch.int32).pin_memory()
+    ops.copy_words([((dev, 8), (host, 8), 4000), ((dev, 0), (ids, 3), 5), ((dev, 5), (ids, 40), 3),
+                    ((dev, 4101), (host, 4001), 999)])
+    ops.copy_words([((back, 1), (dev, 0), 290)])
+    torch.cuda.synchronize()
+    want = torch.zeros(6000, dtype=torch.int32)
+    want[8:4008] = host[8:4008]
+    want[0:5] = torch.arange(103, 108)
+    want[5:8] = torch.arange(140, 143)
+    want[4101:5100] = host[4001:5000]
+    assert torch.equal(dev.cpu(), want)
+    assert torch.equal(back[1:291], want[:290]) and int(back[0]) == 0 and int(back[291]) == 0
+    with pytest.raises(Exception):
+        ops.copy_words([((dev, 5990), (host, 0), 20)])                       # leaves its tensor
+    with pytest.raises(Exception):
+        ops.copy_words([((dev, 0), (torch.zeros(4, dtype=torch.int32), 0), 4)])  # pageable host memory
+    for V in (503, 65536):
+        logits = torch.randn(7, V, generator=g).to(DEV)
+        logits[3, 11] = float("nan")
+        out = torch.full((2, 7), -1, dtype=torch.int32).pin_memory()
+        got_ids, got_bad = ops.argmax_rows(logits, host_out=out)
+        torch.cuda.synchronize()
+        assert torch.equal(out[0], got_ids.cpu()) and torch.equal(out[1], got_bad.cpu())
+        ref_ids, ref_bad = ops.argmax_rows(logits)
+        assert torch.equal(got_ids, ref_ids) and torch.equal(got_bad, ref_bad) and int(out[1, 3]) == 1
+
+
 # ---- skinny matrix product (steps of few tokens) -------------------------------------------------------
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(16, 32), (48, 96), (2048, 2048), (160, 8192), (503 * 16, 64), (32, 352),
